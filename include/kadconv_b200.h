@@ -1,0 +1,151 @@
+/*
+ * kadconv_b200 -- C ABI of the B200 (sm_100a) KAD-Conv inference kernels.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless the name says host;
+ *   - activations are NHWC ("channels last"): element (b, y, x, c) of a [B,H,W,C] tensor lives at
+ *     ((b*H + y)*W + x)*C + c; parameters are float32 unless stated otherwise;
+ *   - `dtype` is the storage type of the activations (KAD_F32 / KAD_F16 / KAD_BF16); all arithmetic
+ *     accumulates in float32;
+ *   - the caller owns every buffer (inputs, outputs, scratch); nothing is allocated, nothing
+ *     synchronises, every kernel is launched on `stream` (a cudaStream_t passed as void*) and the
+ *     calls can be captured in a CUDA graph;
+ *   - return value 0 on success, a negative KAD_ERR_* otherwise; kad_last_error_string() gives the
+ *     reason for the calling thread. No call throws or exits.
+ *
+ * Each declaration names the reference interface it stands in for (paths relative to the
+ * reference project). The reference's own native ABI is a pair of pybind11 torch extensions taking
+ * torch::Tensor (KAD-CNet/inference/acceleration/kadc_dcn16.cpp:247-330 and kadc_gemm_silu.cpp:22-33).
+ */
+#ifndef KADCONV_B200_H_
+#define KADCONV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { KAD_F32 = 0, KAD_F16 = 1, KAD_BF16 = 2 };
+enum { KAD_OK = 0, KAD_ERR_INVALID = -1, KAD_ERR_CUDA = -2, KAD_ERR_UNSUPPORTED = -3, KAD_ERR_DEVICE_WAIT = -4 };
+enum { KAD_ACT_NONE = 0, KAD_ACT_SILU = 1, KAD_ACT_RELU = 2 };
+
+/* Library version (major*10000 + minor*100 + patch). */
+int kad_version(void);
+/* Reason for the last non-zero return on this thread (empty string if none). */
+const char* kad_last_error_string(void);
+
+/* Layout conversion at the module boundary: the reference is NCHW-contiguous end to end
+ * (KAD-Conv/kadconv/fast.py:38-40 requires is_contiguous()). */
+int kad_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W, int dtype, void* stream);
+int kad_nhwc_to_nchw(const void* src, void* dst, int B, int C, int H, int W, int dtype, void* stream);
+
+/* Modulated deformable 3x3 convolution, stride 1, padding 1, with a fused per-channel epilogue.
+ *   y[b,p,o] = post[o] * act( scale[o] * sum_{k,i} Wt[k][i][o] * m[b,p,k] * bilinear(x[b,:,:,i], p + k + d[b,p,k]) + shift[o] )
+ * Replaces torchvision.ops.deform_conv2d as called by DSC.forward (KAD-Conv/kadconv/kad_conv.py:63-67,
+ * KAD-CNet/models/module/ops.py:68-72) together with the BatchNorm, ReLU and branch scale that follow it
+ * in KADConv (kad_conv.py:101-102,:110); native counterpart: dcn16x32_kernel
+ * (KAD-CNet/inference/acceleration/kadc_dcn16_kernel.cu:92-314).
+ *
+ *   x       [B,H,W,Cin]  dtype
+ *   offset  [B,H,W,18]   float32 if offset_f32 else dtype; channel 2k = dy, 2k+1 = dx of tap k = ky*3+kx.
+ *                        NULL means zero offsets (an ordinary 3x3 convolution).
+ *   mask    [B,H,W,9]    same type rule as offset (mask_f32); NULL means all ones.
+ *   weight  SIMT path:   float32 [9][Cin][Cout]  (tap-major, Cout contiguous), packed by kad_dsc_pack_weight_simt()
+ *           tensor path: see kad_dsc_tc_supported(); dtype, packed by kad_dsc_pack_weight_tc()
+ *   scale/shift/post     float32 [Cout] or NULL (1 / 0 / 1). Conv bias goes into shift.
+ *   act     KAD_ACT_*
+ *   y       [B,H,W,Cout] float32 if y_f32 else dtype
+ *   gap_partial  NULL, or float32 [B][gap_tiles][Cout]: per-tile sums of y over pixels, in a fixed order
+ *                (deterministic); gap_tiles = kad_dsc_gap_tiles(H, W, path).
+ */
+typedef struct KadDscArgs {
+    const void* x; const void* offset; const void* mask; const void* weight;
+    const float* scale; const float* shift; const float* post;
+    void* y; float* gap_partial;
+    int B, H, W, Cin, Cout;
+    int dtype, offset_f32, mask_f32, y_f32, act;
+    int path;            /* 0 = SIMT (any shape, any dtype); 1 = tcgen05 implicit GEMM (see kad_dsc_tc_supported) */
+    int* status;         /* device int[4], zeroed by the caller; the tensor path records a wait that gave up here */
+} KadDscArgs;
+int kad_dsc_forward(const KadDscArgs* args, void* stream);
+int kad_dsc_gap_tiles(int H, int W, int path);
+/* 1 if the tcgen05 path can run this shape: dtype f16/bf16, Cin % 32 == 0, Cout % 16 == 0, Cout <= 256. */
+int kad_dsc_tc_supported(int Cin, int Cout, int dtype);
+/* Packs W[Cout][Cin][3][3] (float32, the layout of DSC.weight) into the tensor path's K-major
+ * operand: dst is dtype [9*Cin/64 (rounded up)][Cout][64]; K index = (ci/32)*288 + tap*32 + ci%32. */
+int kad_dsc_pack_weight_tc(const float* w_oihw, void* dst, int Cin, int Cout, int dtype, void* stream);
+size_t kad_dsc_packed_weight_bytes(int Cin, int Cout, int dtype);
+/* Packs W[Cout][Cin][3][3] (float32) into the SIMT path's float32 [9][Cin][Cout]. The same routine packs
+ * DSC.conv_offset.weight ([18][Cin][3][3]) for the offset convolution, which runs as kad_dsc_forward
+ * with offset = mask = NULL (KAD-Conv/kadconv/kad_conv.py:55-56,:64). */
+int kad_dsc_pack_weight_simt(const float* w_oihw, float* dst, int Cin, int Cout, void* stream);
+
+/* Average pool (kernel = stride = pool, floor mode) fused with a 1x1 convolution, bias and activation:
+ *   y[b,q,o] = act( sum_i w[o][i] * mean_{p in pool x pool block q} x[b,p,i] + bias[o] )
+ * Replaces F.avg_pool2d + convs[i][0] in KADConv.forward (kad_conv.py:115,:101) and, with pool = 1 and
+ * KAD_ACT_SILU, Conv.forward_fuse for k = 1 (KAD-CNet/models/common.py:56-57); native counterpart:
+ * gemm_bias_silu_kernel (KAD-CNet/inference/acceleration/kadc_gemm_silu.cu:125-176).
+ *   x [B,H,W,Cin] dtype (channel stride x_cstride >= Cin elements per pixel, so a channel slice of a wider
+ *   tensor can be read in place), w float32 [Cout][Cin], bias float32 [Cout] or NULL,
+ *   y [B,H/pool,W/pool,Cout] dtype written with per-pixel stride y_cstride >= Cout (concat in place). */
+int kad_pool_project(const void* x, const float* w, const float* bias, void* y,
+                     int B, int H, int W, int Cin, int Cout, int pool, int act,
+                     int x_cstride, int y_cstride, int dtype, void* stream);
+
+/* LCSA, step 1: row sums [B,H,C] (over x) and column sums [B,W,C] (over y) of x[B,H,W,C], float32.
+ * Replaces pool_h / pool_w of LCSA.forward (kad_conv.py:27-28,:39). */
+int kad_lcsa_sums(const void* x, float* rowsum, float* colsum, int B, int H, int W, int C, int dtype, void* stream);
+/* LCSA, step 2: mask = sigmoid(1x1( dw11x1( relu(bn(dw1x11(rowmean + colmean))) ) )), [B,H,W,9].
+ * Replaces LCSA.excite + the sigmoid in DSC.forward (kad_conv.py:29-39,:65); counterpart of the Triton
+ * kernels k_reduce_hconv_bn_relu / k_vconv_pointwise9 (kadc_fused_sm75.py:830-888,:905-996).
+ *   w1 [C][11] (1x11 depthwise), b1 [C], bn_scale/bn_shift [C] (folded BatchNorm), w2 [C][11] (11x1),
+ *   b2 [C], w3 [9][C], b3 [9]; scratch float32 [B*W*C + W*C]; mask float32 if mask_f32 else dtype. */
+int kad_lcsa_mask(const float* rowsum, const float* colsum,
+                  const float* w1, const float* b1, const float* bn_scale, const float* bn_shift,
+                  const float* w2, const float* b2, const float* w3, const float* b3,
+                  float* scratch, void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
+
+/* SE excite from the DSC epilogue's per-tile sums: att[b,:] = sigmoid(W2 relu(W1 mean + b1) + b2).
+ * Replaces y.mean((2,3)) and fc[i] in KADConv.forward (kad_conv.py:105-109,:117); native counterpart:
+ * partial_gap_se_kernel (kadc_dcn16_kernel.cu:499-556).
+ *   gap_partial [B][tiles][C], w1 [Hd][C], b1 [Hd], w2 [C][Hd], b2 [C], att float32 [B][C]. */
+int kad_se_excite(const float* gap_partial, int tiles, float inv_count,
+                  const float* w1, const float* b1, const float* w2, const float* b2,
+                  float* att, int B, int C, int Hd, void* stream);
+
+/* Channel attention on a full tensor (squeeze + rescale), for SE blocks outside KAD-Conv:
+ * kad_se_squeeze writes float32 partial sums [B][tiles][C] (tiles = kad_se_squeeze_tiles(H,W));
+ * kad_se_rescale computes y = x * att[b,c]. */
+int kad_se_squeeze_tiles(int H, int W);
+int kad_se_squeeze(const void* x, float* gap_partial, int B, int H, int W, int C, int dtype, void* stream);
+int kad_se_rescale(const void* x, const float* att, void* y, int B, int H, int W, int C, int dtype, void* stream);
+
+/* Tail of KADConv.forward (kad_conv.py:117-121): out = cat_i( upsample_i( y_i * att_i ) ) + x with bilinear
+ * upsampling, align_corners = False. Counterpart of k_upsample_bilinear_att / k_cat_residual_att0
+ * (kadc_fused_sm75.py:1245-1331).
+ *   x, out [B,H,W,C] dtype; y_i [B,H_i,W_i,c_i] dtype, att_i float32 [B][c_i], i = 0..2, sum c_i = C. */
+typedef struct KadMergeArgs {
+    const void* x; void* out;
+    const void* y[3]; const float* att[3];
+    int c[3], h[3], w[3];
+    int B, H, W, C, dtype;
+} KadMergeArgs;
+int kad_merge_upsample_residual(const KadMergeArgs* args, void* stream);
+
+/* 1x1 convolution as a tcgen05 GEMM with bias and activation, TMA-fed operands:
+ *   y[m, n] = act( sum_k x[m, k] * w[n, k] + bias[n] ),  m over B*H*W pixels.
+ * Replaces Conv.forward_fuse for k = 1 (KAD-CNet/models/common.py:56-57 after fuse_conv_and_bn,
+ * utils/torch_utils.py:244-265); native counterpart gemm_bias_silu_kernel (kadc_gemm_silu.cu:125-176).
+ *   x [M][ldx] dtype (K valid channels, ldx >= K, ldx % 8 == 0), w dtype [N][Kp] with Kp = K rounded up to 8,
+ *   bias float32 [N] or NULL, y [M][ldy] dtype. Requires dtype f16/bf16, K % 8 == 0, N % 8 == 0. */
+int kad_gemm1x1_tc_supported(int K, int N, int dtype);
+int kad_gemm1x1_bias_act(const void* x, const void* w, const float* bias, void* y,
+                         long long M, int K, int N, int ldx, int ldy, int act, int dtype,
+                         int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KADCONV_B200_H_ */

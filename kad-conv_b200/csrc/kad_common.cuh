@@ -1,0 +1,61 @@
+// Shared helpers for the kadconv_b200 kernels: storage-type load/store, error reporting.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/kadconv_b200.h"
+
+namespace kad {
+
+// ---- error reporting (thread-local, never throws) ------------------------------------------------
+std::string& last_error();
+int fail(int code, const char* fmt, ...);
+
+#define KAD_CHECK_ARG(cond, ...) do { if (!(cond)) return kad::fail(KAD_ERR_INVALID, __VA_ARGS__); } while (0)
+#define KAD_CHECK_LAUNCH(what) do { cudaError_t e_ = cudaGetLastError(); \
+    if (e_ != cudaSuccess) return kad::fail(KAD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e_)); } while (0)
+
+// ---- storage types -----------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Reads element i of a buffer that is float32 when `f32` is set and T otherwise.
+template <typename T>
+__device__ __forceinline__ float load_mixed(const void* p, size_t i, int f32) {
+    return f32 ? reinterpret_cast<const float*>(p)[i] : to_f<T>(reinterpret_cast<const T*>(p)[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_mixed(void* p, size_t i, int f32, float v) {
+    if (f32) reinterpret_cast<float*>(p)[i] = v; else reinterpret_cast<T*>(p)[i] = from_f<T>(v);
+}
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == KAD_ACT_SILU) return v * sigmoidf_(v);
+    if (act == KAD_ACT_RELU) return fmaxf(v, 0.0f);
+    return v;
+}
+
+inline size_t dtype_size(int dtype) { return dtype == KAD_F32 ? 4 : 2; }
+
+// Dispatch a templated launcher on the storage type.
+#define KAD_DISPATCH_DTYPE(dtype, ...)                                                   \
+    switch (dtype) {                                                                     \
+        case KAD_F32:  { using T = float;          __VA_ARGS__; break; }                 \
+        case KAD_F16:  { using T = __half;         __VA_ARGS__; break; }                 \
+        case KAD_BF16: { using T = __nv_bfloat16;  __VA_ARGS__; break; }                 \
+        default: return kad::fail(KAD_ERR_INVALID, "unknown dtype %d", (int)(dtype));    \
+    }
+
+}  // namespace kad

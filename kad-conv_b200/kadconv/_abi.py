@@ -1,0 +1,88 @@
+"""ctypes binding of libkadconv_b200.so (the C ABI declared in include/kadconv_b200.h).
+
+The library is the only compute back end of this package: there is no CPU path and no other
+GPU back end. If it has not been built, importing this module raises with the build command.
+"""
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / '_lib' / 'libkadconv_b200.so'
+
+KAD_F32, KAD_F16, KAD_BF16 = 0, 1, 2
+ACT_NONE, ACT_SILU, ACT_RELU = 0, 1, 2
+PATH_SIMT, PATH_TC = 0, 1
+
+
+class KadDscArgs(Structure):
+    _fields_ = [('x', c_void_p), ('offset', c_void_p), ('mask', c_void_p), ('weight', c_void_p),
+                ('scale', c_void_p), ('shift', c_void_p), ('post', c_void_p),
+                ('y', c_void_p), ('gap_partial', c_void_p),
+                ('B', c_int), ('H', c_int), ('W', c_int), ('Cin', c_int), ('Cout', c_int),
+                ('dtype', c_int), ('offset_f32', c_int), ('mask_f32', c_int), ('y_f32', c_int), ('act', c_int),
+                ('path', c_int), ('status', c_void_p)]
+
+
+class KadMergeArgs(Structure):
+    _fields_ = [('x', c_void_p), ('out', c_void_p), ('y', c_void_p * 3), ('att', c_void_p * 3),
+                ('c', c_int * 3), ('h', c_int * 3), ('w', c_int * 3),
+                ('B', c_int), ('H', c_int), ('W', c_int), ('C', c_int), ('dtype', c_int)]
+
+
+# name -> (restype, argtypes); every symbol declared in include/kadconv_b200.h
+SIGNATURES = {
+    'kad_version': (c_int, []),
+    'kad_last_error_string': (c_char_p, []),
+    'kad_nchw_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_nhwc_to_nchw': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_dsc_forward': (c_int, [POINTER(KadDscArgs), c_void_p]),
+    'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int]),
+    'kad_dsc_tc_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_dsc_pack_weight_tc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    'kad_dsc_packed_weight_bytes': (c_size_t, [c_int, c_int, c_int]),
+    'kad_dsc_pack_weight_simt': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    'kad_pool_project': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_void_p]),
+    'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_lcsa_mask': (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_se_excite': (c_int, [c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p]),
+    'kad_se_squeeze_tiles': (c_int, [c_int, c_int]),
+    'kad_se_squeeze': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_se_rescale': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_merge_upsample_residual': (c_int, [POINTER(KadMergeArgs), c_void_p]),
+    'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_gemm1x1_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+def library_path():
+    return _LIB_PATH
+
+
+def load():
+    """Load the shared library once; raise if it is missing (no fallback exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f'{_LIB_PATH} is missing: build the CUDA library first with '
+            f'`python {_LIB_PATH.parents[2] / "build.py"}` (needs nvcc with sm_100a support). '
+            'kadconv has no CPU or PyTorch fallback for its accelerated path.')
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)     # AttributeError if the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code, what):
+    if code != 0:
+        msg = load().kad_last_error_string().decode(errors='replace')
+        raise RuntimeError(f'{what} failed ({code}): {msg}')

@@ -1,0 +1,144 @@
+"""enable_fast_inference / disable_fast_inference: the B200 pipeline behind the reference's switch.
+
+Same call as KAD-Conv/kadconv/fast.py:68-118 of the reference project: layers are found by class NAME
+('KADConv', 'KADC4', 'KADC4_m'), their ``forward`` is replaced per instance, ``disable_fast_inference``
+restores the plain forward. Differences, all on purpose:
+  * batch >= 1, H != W, float32 / float16 / bfloat16, NCHW-contiguous or channels_last inputs
+    (the reference's fast path takes float32 (1,C,H,H) contiguous only, fast.py:38-40);
+  * no silent fallback: an input the CUDA path cannot take (CPU tensor, training mode) raises.
+
+Per layer and call the pipeline is, in NHWC:
+  pool+project (x3) -> per branch: LCSA sums, LCSA mask, offset conv, DSC(+BN+ReLU+scale+SE partial sums),
+  SE excite -> merge (attention, bilinear upsample, concat, residual).
+Folded parameters are computed once per (layer, device) and cached on the module.
+"""
+import types
+
+import torch
+
+from . import ops
+
+_LAYER_TYPES = {'KADConv', 'KADC4', 'KADC4_m'}
+_FAST_ATTR = '_kad_b200'
+
+
+def _bn_fold(bn):
+    eps = bn.eps
+    m = bn.weight.detach().float() / torch.sqrt(bn.running_var.detach().float() + eps)
+    a = bn.bias.detach().float() - bn.running_mean.detach().float() * m
+    return m, a
+
+
+class _BranchParams:
+    """Float32, contiguous, device-resident parameters of one KAD-Conv branch."""
+
+    def __init__(self, conv_seq, fc, scale_seq, device):
+        proj, dsc, bn = conv_seq[0], conv_seq[1], conv_seq[2]
+        f = lambda t: t.detach().float().contiguous().to(device)
+        c = dsc.weight.shape[0]
+        self.c = c
+        self.w_proj = f(proj.weight.view(proj.weight.shape[0], -1))
+        self.b_proj = f(proj.bias)
+        ex = dsc.RCA_mask.excite
+        m1, a1 = _bn_fold(ex[1])
+        self.lcsa = dict(w1=f(ex[0].weight.view(c, 11)), b1=f(ex[0].bias), bn_m=f(m1), bn_a=f(a1),
+                         w2=f(ex[3].weight.view(c, 11)), b2=f(ex[3].bias),
+                         w3=f(ex[4].weight.view(9, c)), b3=f(ex[4].bias))
+        self.w_off = ops.pack_dsc_weight_simt(dsc.conv_offset.weight.to(device))
+        self.b_off = f(dsc.conv_offset.bias)
+        self.dsc_weight_raw = f(dsc.weight)
+        self.w_dsc_simt = ops.pack_dsc_weight_simt(self.dsc_weight_raw)
+        self.w_dsc_tc = {}
+        m, a = _bn_fold(bn)
+        self.ep_scale = f(m)
+        self.ep_shift = f(a + dsc.bias.detach().float() * m)     # conv bias passes through the BN affine
+        self.ep_post = f(scale_seq[0].weight.view(-1))
+        self.fc_w1, self.fc_b1 = f(fc[0].weight), f(fc[0].bias)
+        self.fc_w2, self.fc_b2 = f(fc[2].weight), f(fc[2].bias)
+
+    def dsc_weight(self, dtype):
+        """(path, packed weight) for activations of `dtype`."""
+        if dtype != torch.float32 and ops.dsc_tc_supported(self.c, self.c, dtype):
+            if dtype not in self.w_dsc_tc:
+                self.w_dsc_tc[dtype] = ops.pack_dsc_weight_tc(self.dsc_weight_raw, dtype)
+            return ops.PATH_TC, self.w_dsc_tc[dtype]
+        return ops.PATH_SIMT, self.w_dsc_simt
+
+
+def _prepare(layer, device):
+    st = getattr(layer, _FAST_ATTR, None)
+    if st is None or st['device'] != device:
+        st = {'device': device,
+              'branches': [_BranchParams(layer.convs[i], layer.fc[i], layer.weight[i], device) for i in range(layer.n)]}
+        object.__setattr__(layer, _FAST_ATTR, st)
+    return st
+
+
+def kadconv_forward_nhwc(layer, x):
+    """The accelerated KADConv forward on a contiguous NHWC tensor; returns NHWC."""
+    if layer.n != 3:
+        raise RuntimeError('the B200 pipeline implements the 3-branch KAD-Conv (n=3)')
+    B, H, W, C = x.shape
+    if H < 4 or W < 4:
+        raise RuntimeError(f'KAD-Conv needs H, W >= 4 for its 1/4-resolution branch, got {H}x{W}')
+    st = _prepare(layer, x.device)
+    ys, atts = [], []
+    for i, br in enumerate(st['branches']):
+        t = ops.pool_project(x, br.w_proj, br.b_proj, pool=2 ** i)
+        mask = ops.lcsa_mask(t, br.lcsa, mask_f32=True)
+        offset = ops.dsc_forward(t, br.w_off, shift=br.b_off, y_f32=True)
+        path, w = br.dsc_weight(t.dtype)
+        y, gap = ops.dsc_forward(t, w, offset, mask, scale=br.ep_scale, shift=br.ep_shift, post=br.ep_post,
+                                 act=ops.ACT_RELU, path=path, want_gap=True, cout=br.c)
+        atts.append(ops.se_excite(gap, t.shape[1] * t.shape[2], br.fc_w1, br.fc_b1, br.fc_w2, br.fc_b2))
+        ys.append(y)
+    return ops.merge_upsample_residual(x, ys, atts)
+
+
+def _fast_forward(layer, x):
+    if layer.training:
+        raise RuntimeError('kadconv fast inference is enabled: call model.eval() (or disable_fast_inference for training)')
+    if not x.is_cuda:
+        raise RuntimeError('kadconv fast inference has no CPU path: move the input to the GPU')
+    if x.dim() != 4:
+        raise ValueError('KADConv expects a [B,C,H,W] tensor')
+    channels_last = x.permute(0, 2, 3, 1).is_contiguous()
+    out = kadconv_forward_nhwc(layer, ops.to_nhwc(x))
+    if channels_last:
+        return out.permute(0, 3, 1, 2)      # same logical shape, channels_last memory like the input
+    return ops.to_nchw(out)
+
+
+def enable_fast_inference(model, build_dir=None, allow_untested_gpu=False):
+    """Switch every KAD-Conv layer in ``model`` to the B200 CUDA pipeline (in place); returns ``model``.
+
+    ``build_dir`` and ``allow_untested_gpu`` are accepted for call compatibility with the reference; the
+    library is prebuilt in-tree and targets sm_100a only.
+    """
+    from . import _abi
+    _abi.load()
+    if model.training:
+        raise ValueError('call model.eval() before enable_fast_inference()')
+    device = next(model.parameters()).device
+    if device.type != 'cuda':
+        raise ValueError('move the model to a CUDA device first')
+    if torch.cuda.get_device_capability(device)[0] != 10:
+        raise ValueError('the kadconv_b200 kernels are built for sm_100a (B200) only')
+    layers = [m for m in model.modules() if type(m).__name__ in _LAYER_TYPES]
+    if not layers:
+        raise ValueError('no KAD-Conv layer found in the model')
+    for layer in layers:
+        _prepare(layer, device)
+        layer.forward = types.MethodType(_fast_forward, layer)
+    return model
+
+
+def disable_fast_inference(model):
+    """Go back to the plain PyTorch forward."""
+    for m in model.modules():
+        if type(m).__name__ in _LAYER_TYPES:
+            if 'forward' in vars(m):
+                del m.forward
+            if _FAST_ATTR in vars(m):
+                object.__delattr__(m, _FAST_ATTR)
+    return model

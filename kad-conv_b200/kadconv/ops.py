@@ -1,0 +1,274 @@
+"""Operator-level wrappers: torch tensors in, C-ABI calls on the current CUDA stream, torch tensors out.
+
+Activations are NHWC here: a tensor of shape [B, H, W, C] that is contiguous. PyTorch only provides
+device memory, the stream and the caching allocator (so the calls stay CUDA-graph capturable).
+"""
+import ctypes
+
+import torch
+
+from . import _abi
+from ._abi import ACT_NONE, ACT_RELU, ACT_SILU, KAD_BF16, KAD_F16, KAD_F32, PATH_SIMT, PATH_TC
+
+_DT = {torch.float32: KAD_F32, torch.float16: KAD_F16, torch.bfloat16: KAD_BF16}
+
+
+def dtype_code(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f'kadconv supports float32, float16 and bfloat16 activations, got {t.dtype}') from None
+
+
+def _cuda(t, name):
+    if not t.is_cuda:
+        raise RuntimeError(f'kadconv: {name} must be a CUDA tensor (there is no CPU path)')
+    if not t.is_contiguous():
+        raise RuntimeError(f'kadconv: {name} must be contiguous')
+    return t
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f32(t, name):
+    if t is None:
+        return None
+    if t.dtype != torch.float32:
+        raise TypeError(f'kadconv: {name} must be float32')
+    return _cuda(t, name)
+
+
+def to_nhwc(x):
+    """[B,C,H,W] logical tensor -> contiguous [B,H,W,C]; free when x is already channels_last."""
+    if x.dim() != 4:
+        raise ValueError('expected a 4-D tensor')
+    v = x.permute(0, 2, 3, 1)
+    if v.is_contiguous():
+        return v
+    x = _cuda(x.contiguous(), 'x')
+    B, C, H, W = x.shape
+    out = torch.empty((B, H, W, C), dtype=x.dtype, device=x.device)
+    _abi.check(_abi.load().kad_nchw_to_nhwc(_ptr(x), _ptr(out), B, C, H, W, dtype_code(x), _stream()), 'kad_nchw_to_nhwc')
+    return out
+
+
+def to_nchw(y):
+    """Contiguous [B,H,W,C] -> contiguous [B,C,H,W]."""
+    y = _cuda(y, 'y')
+    B, H, W, C = y.shape
+    out = torch.empty((B, C, H, W), dtype=y.dtype, device=y.device)
+    _abi.check(_abi.load().kad_nhwc_to_nchw(_ptr(y), _ptr(out), B, C, H, W, dtype_code(y), _stream()), 'kad_nhwc_to_nchw')
+    return out
+
+
+def pack_dsc_weight_simt(w):
+    """[Cout,Cin,3,3] -> float32 [9,Cin,Cout] on the weight's device."""
+    w = _cuda(w.detach().float().contiguous(), 'weight')
+    Cout, Cin = w.shape[:2]
+    out = torch.empty((9, Cin, Cout), dtype=torch.float32, device=w.device)
+    _abi.check(_abi.load().kad_dsc_pack_weight_simt(_ptr(w), _ptr(out), Cin, Cout, _stream()), 'kad_dsc_pack_weight_simt')
+    return out
+
+
+def dsc_tc_supported(Cin, Cout, dtype):
+    return bool(_abi.load().kad_dsc_tc_supported(Cin, Cout, _DT[dtype]))
+
+
+def pack_dsc_weight_tc(w, dtype):
+    """[Cout,Cin,3,3] -> the tensor path's packed K-major operand in `dtype`."""
+    w = _cuda(w.detach().float().contiguous(), 'weight')
+    Cout, Cin = w.shape[:2]
+    lib = _abi.load()
+    nbytes = lib.kad_dsc_packed_weight_bytes(Cin, Cout, _DT[dtype])
+    if nbytes == 0:
+        raise RuntimeError(f'the tensor path does not support Cin={Cin} Cout={Cout} {dtype}')
+    out = torch.empty(nbytes // 2, dtype=dtype, device=w.device)
+    _abi.check(lib.kad_dsc_pack_weight_tc(_ptr(w), _ptr(out), Cin, Cout, _DT[dtype], _stream()), 'kad_dsc_pack_weight_tc')
+    return out
+
+
+_status = {}
+
+
+def status_word(device):
+    """Per-device int32[4] the tensor-core kernels report a timed-out wait in (checked by check_status)."""
+    key = (device.type, device.index)
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device):
+    """Synchronises and raises if a tensor-core kernel gave up on a wait since the last check."""
+    st = status_word(device).cpu()
+    if int(st[0]) != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f'kadconv tensor-core kernel aborted: role {int(st[0])}, detail {int(st[1])}, block {int(st[2])}')
+
+
+def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=None, act=ACT_NONE,
+                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None):
+    """Deformable 3x3 convolution with fused epilogue on NHWC tensors.
+
+    x [B,H,W,Cin]; offset [B,H,W,18] (float32 or x.dtype) or None; mask [B,H,W,9] or None;
+    weight: pack_dsc_weight_simt(...) for PATH_SIMT or pack_dsc_weight_tc(...) for PATH_TC.
+    Returns y [B,H,W,Cout] (and the per-tile channel sums [B,tiles,Cout] when want_gap).
+    """
+    lib = _abi.load()
+    x = _cuda(x, 'x')
+    B, H, W, Cin = x.shape
+    if path == PATH_SIMT:
+        if weight.dim() != 3 or weight.shape[0] != 9 or weight.shape[1] != Cin or weight.dtype != torch.float32:
+            raise ValueError('SIMT path expects weight packed as float32 [9,Cin,Cout]')
+        Cout = weight.shape[2]
+    else:
+        if cout is None:
+            raise ValueError('tensor path needs cout')
+        Cout = cout
+    a = _abi.KadDscArgs()
+    a.x = x.data_ptr(); a.weight = _cuda(weight, 'weight').data_ptr()
+    if offset is not None:
+        _cuda(offset, 'offset')
+        if tuple(offset.shape) != (B, H, W, 18):
+            raise ValueError(f'offset must be [B,H,W,18], got {tuple(offset.shape)}')
+        a.offset = offset.data_ptr(); a.offset_f32 = int(offset.dtype == torch.float32)
+        if not a.offset_f32 and offset.dtype != x.dtype:
+            raise TypeError('offset must be float32 or the activation dtype')
+    if mask is not None:
+        _cuda(mask, 'mask')
+        if tuple(mask.shape) != (B, H, W, 9):
+            raise ValueError(f'mask must be [B,H,W,9], got {tuple(mask.shape)}')
+        a.mask = mask.data_ptr(); a.mask_f32 = int(mask.dtype == torch.float32)
+        if not a.mask_f32 and mask.dtype != x.dtype:
+            raise TypeError('mask must be float32 or the activation dtype')
+    for name, t in (('scale', scale), ('shift', shift), ('post', post)):
+        if t is not None:
+            if _f32(t, name).numel() != Cout:
+                raise ValueError(f'{name} must have {Cout} elements')
+            setattr(a, name, t.data_ptr())
+    y = torch.empty((B, H, W, Cout), dtype=torch.float32 if y_f32 else x.dtype, device=x.device)
+    gap = None
+    if want_gap:
+        tiles = lib.kad_dsc_gap_tiles(H, W, path)
+        gap = torch.empty((B, tiles, Cout), dtype=torch.float32, device=x.device)
+        a.gap_partial = gap.data_ptr()
+    a.y = y.data_ptr()
+    a.B, a.H, a.W, a.Cin, a.Cout = B, H, W, Cin, Cout
+    a.dtype = dtype_code(x); a.y_f32 = int(y_f32); a.act = act; a.path = path
+    a.status = status_word(x.device).data_ptr()
+    _abi.check(lib.kad_dsc_forward(ctypes.byref(a), _stream()), 'kad_dsc_forward')
+    return (y, gap) if want_gap else y
+
+
+def pool_project(x, w, bias=None, pool=1, act=ACT_NONE, cin=None, out=None, out_coff=0):
+    """avg-pool (pool x pool, floor) + 1x1 conv + bias + activation. x [B,H,W,Cx] NHWC; only the first
+    `cin` channels (default all) are read. With `out` ([B,Ho,Wo,Cy]) the result is written into its channels
+    [out_coff, out_coff + Cout) in place; otherwise a new tensor is returned."""
+    x = _cuda(x, 'x'); w = _f32(w, 'w'); bias = _f32(bias, 'bias')
+    B, H, W, Cx = x.shape
+    Cin = Cx if cin is None else cin
+    Cout = w.shape[0]
+    if w.shape[1] != Cin:
+        raise ValueError(f'weight is {tuple(w.shape)} but Cin = {Cin}')
+    Ho, Wo = H // pool, W // pool
+    if out is None:
+        out = torch.empty((B, Ho, Wo, Cout), dtype=x.dtype, device=x.device)
+        dst, ycs = out, Cout
+    else:
+        _cuda(out, 'out')
+        ycs = out.shape[3]
+        dst = out.view(-1)[out_coff:]
+    _abi.check(_abi.load().kad_pool_project(_ptr(x), _ptr(w), _ptr(bias), ctypes.c_void_p(dst.data_ptr()), B, H, W, Cin, Cout, pool, act,
+                                            Cx, ycs, dtype_code(x), _stream()), 'kad_pool_project')
+    return out
+
+
+def lcsa_mask(x, prm, mask_f32=True):
+    """sigmoid(LCSA(x)) for NHWC x -> [B,H,W,9]. `prm`: dict of float32 tensors w1[C,11], b1, bn_m, bn_a,
+    w2[C,11], b2, w3[9,C], b3 (BatchNorm already folded into bn_m / bn_a)."""
+    lib = _abi.load()
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    dev = x.device
+    rows = torch.empty((B, H, C), dtype=torch.float32, device=dev)
+    cols = torch.empty((B, W, C), dtype=torch.float32, device=dev)
+    _abi.check(lib.kad_lcsa_sums(_ptr(x), _ptr(rows), _ptr(cols), B, H, W, C, dtype_code(x), _stream()), 'kad_lcsa_sums')
+    scratch = torch.empty(B * W * C + W * C, dtype=torch.float32, device=dev)
+    mask = torch.empty((B, H, W, 9), dtype=torch.float32 if mask_f32 else x.dtype, device=dev)
+    _abi.check(lib.kad_lcsa_mask(_ptr(rows), _ptr(cols), _ptr(prm['w1']), _ptr(prm['b1']), _ptr(prm['bn_m']), _ptr(prm['bn_a']),
+                                 _ptr(prm['w2']), _ptr(prm['b2']), _ptr(prm['w3']), _ptr(prm['b3']), _ptr(scratch), _ptr(mask),
+                                 B, H, W, C, int(mask_f32), dtype_code(x), _stream()), 'kad_lcsa_mask')
+    return mask
+
+
+def se_excite(gap, count, w1, b1, w2, b2):
+    """gap [B,tiles,C] per-tile sums over `count` pixels -> attention [B,C] float32."""
+    B, tiles, C = gap.shape
+    Hd = w1.shape[0]
+    att = torch.empty((B, C), dtype=torch.float32, device=gap.device)
+    _abi.check(_abi.load().kad_se_excite(_ptr(gap), tiles, ctypes.c_float(1.0 / count), _ptr(_f32(w1, 'w1')), _ptr(_f32(b1, 'b1')),
+                                         _ptr(_f32(w2, 'w2')), _ptr(_f32(b2, 'b2')), _ptr(att), B, C, Hd, _stream()), 'kad_se_excite')
+    return att
+
+
+def se_squeeze(x):
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    lib = _abi.load()
+    tiles = lib.kad_se_squeeze_tiles(H, W)
+    gap = torch.empty((B, tiles, C), dtype=torch.float32, device=x.device)
+    _abi.check(lib.kad_se_squeeze(_ptr(x), _ptr(gap), B, H, W, C, dtype_code(x), _stream()), 'kad_se_squeeze')
+    return gap
+
+
+def se_rescale(x, att):
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    y = torch.empty_like(x)
+    _abi.check(_abi.load().kad_se_rescale(_ptr(x), _ptr(_f32(att, 'att')), _ptr(y), B, H, W, C, dtype_code(x), _stream()), 'kad_se_rescale')
+    return y
+
+
+def merge_upsample_residual(x, ys, atts):
+    """out = cat_i(upsample(ys[i] * atts[i])) + x, all NHWC."""
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    out = torch.empty_like(x)
+    a = _abi.KadMergeArgs()
+    a.x = x.data_ptr(); a.out = out.data_ptr()
+    for i in range(3):
+        yi = _cuda(ys[i], f'y{i}')
+        a.y[i] = yi.data_ptr(); a.att[i] = _f32(atts[i], f'att{i}').data_ptr()
+        a.c[i], a.h[i], a.w[i] = yi.shape[3], yi.shape[1], yi.shape[2]
+    a.B, a.H, a.W, a.C, a.dtype = B, H, W, C, dtype_code(x)
+    _abi.check(_abi.load().kad_merge_upsample_residual(ctypes.byref(a), _stream()), 'kad_merge_upsample_residual')
+    return out
+
+
+def gemm1x1_supported(K, N, dtype):
+    return dtype in (torch.float16, torch.bfloat16) and bool(_abi.load().kad_gemm1x1_tc_supported(K, N, _DT[dtype]))
+
+
+def gemm1x1_bias_act(x, w, bias=None, act=ACT_SILU, k=None, out=None, out_coff=0):
+    """1x1 convolution on tensor cores. x [..., Cx] NHWC (first k channels used), w [N, Kp] in x.dtype
+    (Kp = k rounded up to 8), bias float32 [N]. Writes into out[..., out_coff:out_coff+N] when given."""
+    x = _cuda(x, 'x'); w = _cuda(w, 'w')
+    Cx = x.shape[-1]
+    K = Cx if k is None else k
+    N = w.shape[0]
+    M = x.numel() // Cx
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=x.dtype, device=x.device)
+        dst, ldy = out, N
+    else:
+        ldy = out.shape[-1]
+        dst = out.view(-1)[out_coff:]
+    _abi.check(_abi.load().kad_gemm1x1_bias_act(_ptr(x), _ptr(w), _ptr(_f32(bias, 'bias')), ctypes.c_void_p(dst.data_ptr()), M, K, N, Cx, ldy, act,
+                                                dtype_code(x), _ptr(status_word(x.device)), _stream()), 'kad_gemm1x1_bias_act')
+    return out

@@ -1,0 +1,102 @@
+"""The KADConv module on the B200 pipeline against the CPU oracle and the reference-made fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import kadconv_shapes, rel_err, round_to
+from oracle import kad_oracle as ko
+from oracle import seeding
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(dim, seed, dtype=torch.float32, scale_mode='uniform', se_min_hidden=32):
+    import kadconv
+    layer = kadconv.KADConv(dim, se_min_hidden=se_min_hidden).eval()
+    sd = seeding.seeded_state_dict(kadconv_shapes(dim, se_min_hidden), seed=seed, scale_mode=scale_mode)
+    if dtype != torch.float32:
+        sd = {k: round_to(v, dtype) for k, v in sd.items()}
+    layer.load_state_dict(sd)
+    return layer, sd
+
+
+@pytest.mark.parametrize('name', ['kadconv_c24', 'kadconv_c64'])
+def test_fixture_fp32(golden_dir, name):
+    import kadconv
+    g = np.load(golden_dir / f'{name}.npz')
+    dim, seed, shape = int(g['dim']), int(g['seed']), tuple(int(v) for v in g['shape'])
+    layer, _ = _layer(dim, seed)
+    x = seeding.seeded_input(shape, seed=seed)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda()).cpu()
+    assert y.shape == x.shape
+    assert (y - torch.from_numpy(g['y'])).abs().max().item() <= 1e-4
+
+
+def test_c0_config_fp32():
+    """configs[0]: KADConv(64), [2,64,80,80] fp32, max-abs 1e-4."""
+    import kadconv
+    layer, sd = _layer(64, 0)
+    x = seeding.seeded_input((2, 64, 80, 80), seed=0)
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda()).cpu()
+        y_cl = layer(x.cuda().contiguous(memory_format=torch.channels_last)).cpu()
+    assert (y - ref).abs().max().item() <= 1e-4
+    assert (y_cl - ref).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize('dim,shape', [(32, (1, 32, 25, 25)), (48, (2, 48, 12, 50)), (30, (1, 30, 9, 14)), (66, (1, 66, 6, 5))])
+def test_odd_sizes_fp32(dim, shape):
+    """Odd sizes (25 -> 12 -> 6 pyramid), H != W, widths that are no multiple of anything."""
+    import kadconv
+    layer, sd = _layer(dim, sum(shape))
+    x = seeding.seeded_input(shape, seed=sum(shape))
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda()).cpu()
+    assert (y - ref).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_16bit_relative(dtype):
+    import kadconv
+    layer, sd = _layer(48, 21, dtype=dtype)
+    x = round_to(seeding.seeded_input((2, 48, 20, 28), seed=21), dtype)
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda().to(dtype)).float().cpu()
+    assert rel_err(y, ref) <= 1e-2
+
+
+def test_wide_layer_uses_tensor_path_fp16():
+    """KADConv(96): all three branches are 32 channels wide -> the DSCs run on tcgen05."""
+    import kadconv
+    from kadconv import ops
+    dtype = torch.float16
+    layer, sd = _layer(96, 5, dtype=dtype, se_min_hidden=64)
+    x = round_to(seeding.seeded_input((2, 96, 24, 20), seed=5), dtype)
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda().to(dtype)).float().cpu()
+    ops.check_status(torch.device('cuda', 0))
+    assert rel_err(y, ref) <= 1e-2
+
+
+def test_fast_mode_refuses_cpu_and_training():
+    import kadconv
+    layer, _ = _layer(24, 1)
+    kadconv.enable_fast_inference(layer.cuda())
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(1, 24, 8, 8))
+    layer.train()
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(1, 24, 8, 8, device='cuda'))
+    layer.eval()
+    kadconv.disable_fast_inference(layer)
+    assert 'forward' not in vars(layer)

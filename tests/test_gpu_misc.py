@@ -1,0 +1,125 @@
+"""Smaller kernels against torch CPU references: layout, pooled projection, LCSA mask, SE, merge, 1x1 GEMM."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import nhwc, rel_err, round_to
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.from_numpy((scale * np.random.default_rng(seed).standard_normal(shape)).astype(np.float32))
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+def test_layout_round_trip(dtype):
+    from kadconv import ops
+    x = _rand((3, 37, 9, 21), 0).to(dtype).cuda()
+    n = ops.to_nhwc(x)
+    assert torch.equal(n, x.permute(0, 2, 3, 1).contiguous())
+    assert torch.equal(ops.to_nchw(n), x)
+
+
+@pytest.mark.parametrize('pool', [1, 2, 4])
+def test_pool_project(pool):
+    from kadconv import ops
+    x = _rand((2, 45, 13, 18), 1)
+    w = _rand((22, 45), 2, 0.2); b = _rand((22,), 3, 0.1)
+    ref = F.conv2d(F.avg_pool2d(x, pool) if pool > 1 else x, w.view(22, 45, 1, 1), b)
+    y = ops.pool_project(nhwc(x).cuda(), w.cuda(), b.cuda(), pool=pool).cpu().permute(0, 3, 1, 2)
+    assert (y - ref).abs().max().item() <= 1e-5
+    ys = ops.pool_project(nhwc(x).cuda(), w.cuda(), b.cuda(), pool=pool, act=ops.ACT_SILU).cpu().permute(0, 3, 1, 2)
+    assert (ys - F.silu(ref)).abs().max().item() <= 1e-5
+
+
+def test_pool_project_wide_and_sliced():
+    from kadconv import ops
+    x = _rand((1, 300, 5, 7), 4)
+    w = _rand((150, 200), 5, 0.1)
+    ref = F.conv2d(x[:, :200], w.view(150, 200, 1, 1))
+    out = torch.zeros((1, 5, 7, 160), device='cuda')
+    ops.pool_project(nhwc(x).cuda(), w.cuda(), None, cin=200, out=out, out_coff=8)
+    assert (out[..., 8:158].cpu().permute(0, 3, 1, 2) - ref).abs().max().item() <= 1e-4
+    assert out[..., :8].abs().max().item() == 0 and out[..., 158:].abs().max().item() == 0
+
+
+def test_lcsa_mask_matches_module():
+    import kadconv
+    from kadconv import ops
+    from kadconv.fast import _bn_fold
+    torch.manual_seed(0)
+    m = kadconv.LCSA(21, 9).eval()
+    bn = m.excite[1]
+    bn.running_mean.normal_(0, 0.2); bn.running_var.uniform_(0.5, 1.5); bn.weight.data.uniform_(0.5, 1.5); bn.bias.data.normal_(0, 0.1)
+    x = _rand((2, 21, 14, 9), 6)
+    with torch.no_grad():
+        ref = torch.sigmoid(m(x))
+    ex = m.excite
+    bm, ba = _bn_fold(bn)
+    f = lambda t: t.detach().float().contiguous().cuda()
+    prm = dict(w1=f(ex[0].weight.view(21, 11)), b1=f(ex[0].bias), bn_m=f(bm), bn_a=f(ba), w2=f(ex[3].weight.view(21, 11)),
+               b2=f(ex[3].bias), w3=f(ex[4].weight.view(9, 21)), b3=f(ex[4].bias))
+    y = ops.lcsa_mask(nhwc(x).cuda(), prm).cpu().permute(0, 3, 1, 2)
+    assert (y - ref).abs().max().item() <= 1e-5
+
+
+def test_se_squeeze_excite_rescale():
+    from kadconv import ops
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
+        x = round_to(_rand((2, 64, 21, 17), 7), dtype)
+        w1 = _rand((16, 64), 8, 0.2); b1 = _rand((16,), 9, 0.1); w2 = _rand((64, 16), 10, 0.2); b2 = _rand((64,), 11, 0.1)
+        a = torch.sigmoid(F.linear(F.relu(F.linear(x.mean((2, 3)), w1, b1)), w2, b2))
+        ref = x * a.view(2, 64, 1, 1)
+        xg = nhwc(x).cuda().to(dtype)
+        gap = ops.se_squeeze(xg)
+        att = ops.se_excite(gap, 21 * 17, w1.cuda(), b1.cuda(), w2.cuda(), b2.cuda())
+        y = ops.se_rescale(xg, att).float().cpu().permute(0, 3, 1, 2)
+        assert (att.cpu() - a).abs().max().item() <= 1e-5
+        assert rel_err(y, ref) <= tol
+
+
+def test_merge_upsample_residual():
+    from kadconv import ops
+    B, H, W = 2, 25, 18
+    cs = (22, 21, 21)
+    x = _rand((B, 64, H, W), 12)
+    ys = [_rand((B, c, H // (2 ** i), W // (2 ** i)), 13 + i) for i, c in enumerate(cs)]
+    atts = [torch.sigmoid(_rand((B, c), 20 + i)) for i, c in enumerate(cs)]
+    feats = []
+    for i in range(3):
+        t = ys[i] * atts[i].view(B, -1, 1, 1)
+        if i:
+            t = F.interpolate(t, size=(H, W), mode='bilinear', align_corners=False)
+        feats.append(t)
+    ref = torch.cat(feats, 1) + x
+    out = ops.merge_upsample_residual(nhwc(x).cuda(), [nhwc(t).cuda() for t in ys], [a.cuda() for a in atts])
+    assert (out.cpu().permute(0, 3, 1, 2) - ref).abs().max().item() <= 1e-5
+
+
+@pytest.mark.parametrize('M,K,N,dtype', [(1000, 128, 256, torch.bfloat16), (333, 72, 64, torch.float16), (5000, 360, 128, torch.float16),
+                                         (777, 512, 288, torch.float16), (129, 64, 32, torch.bfloat16), (4096, 96, 48, torch.float16)])
+def test_gemm1x1_bias_silu(M, K, N, dtype):
+    """Fused 1x1 GEMM + bias + SiLU on tcgen05 (detector shapes incl. K, N that are no multiple of 64)."""
+    from kadconv import ops
+    x = round_to(_rand((M, K), 30), dtype); w = round_to(_rand((N, K), 31, 1.0 / np.sqrt(K)), dtype); b = _rand((N,), 32, 0.1)
+    ref = F.silu(x @ w.t() + b)
+    y = ops.gemm1x1_bias_act(x.cuda().to(dtype).view(1, M, 1, K), w.cuda().to(dtype), b.cuda(), act=ops.ACT_SILU)
+    torch.cuda.synchronize()
+    ops.check_status(torch.device('cuda', 0))
+    assert rel_err(y.float().cpu().view(M, N), ref) <= 1e-2
+
+
+def test_gemm1x1_slices_in_place():
+    """Reads a channel slice of a wider tensor and writes into a channel slice of the output (concat-free)."""
+    from kadconv import ops
+    dtype = torch.float16
+    x = round_to(_rand((600, 160), 33), dtype); w = round_to(_rand((40, 64), 34, 0.125), dtype)
+    ref = x[:, :64] @ w.t()
+    out = torch.zeros((600, 96), dtype=dtype, device='cuda')
+    ops.gemm1x1_bias_act(x.cuda().to(dtype), w.cuda().to(dtype), None, act=ops.ACT_NONE, k=64, out=out, out_coff=16)
+    torch.cuda.synchronize()
+    ops.check_status(torch.device('cuda', 0))
+    assert rel_err(out[:, 16:56].float().cpu(), ref) <= 1e-2
+    assert out[:, :16].abs().max().item() == 0 and out[:, 56:].abs().max().item() == 0
