@@ -1,0 +1,206 @@
+"""B200 execution of KAD-CNet-S: NHWC, fp16/bf16, KAD-Conv layers and 1x1 convolutions on the
+kadconv_b200 CUDA kernels.
+
+The engine walks the same graph as kadcnet.model.DetectionModel (which mirrors the reference's
+DetectionModel._forward_once, KAD-CNet/models/yolo.py:538-559) but keeps every activation as a
+contiguous [B,H,W,C] tensor:
+  * every KAD-Conv layer (42 in KAD-CNet-S)  -> kadconv.fast.kadconv_forward_nhwc (CUDA pipeline)
+  * every Conv with k = 1 (+ folded BN + SiLU) -> tcgen05 GEMM + bias + SiLU, reading channel slices in
+    place (the ELAN / CSP `chunk` never copies)
+  * 3x3 convolutions, pools, nearest upsampling -> library kernels on channels_last views (outside the
+    KAD-Conv hot path; they are the next item to be replaced)
+  * head decode -> the reference's op sequence, so the fp16 rounding points are the same.
+There is no CPU path: the engine raises on a non-CUDA input.
+"""
+import torch
+import torch.nn.functional as F
+
+from kadconv import ops
+from kadconv.fast import kadconv_forward_nhwc
+
+from . import model as M
+
+
+def _nchw_view(t):
+    """[B,H,W,C] contiguous -> logical [B,C,H,W] view (channels_last strides), no copy."""
+    return t.permute(0, 3, 1, 2)
+
+
+def _nhwc(t):
+    """logical [B,C,H,W] tensor in channels_last memory -> [B,H,W,C] contiguous view (copy only if needed)."""
+    v = t.permute(0, 2, 3, 1)
+    return v if v.is_contiguous() else v.contiguous()
+
+
+class _Conv1x1:
+    def __init__(self, conv_mod, dtype, device):
+        conv = conv_mod.conv
+        assert conv.kernel_size == (1, 1) and conv.groups == 1 and conv.bias is not None, 'fuse() the model first'
+        self.n, self.k = conv.out_channels, conv.in_channels
+        self.act = ops.ACT_SILU if isinstance(conv_mod.act, torch.nn.SiLU) else ops.ACT_NONE
+        w = conv.weight.detach().float().view(self.n, self.k)
+        self.bias = conv.bias.detach().float().contiguous().to(device)
+        self.tc = ops.gemm1x1_supported(self.k, self.n, dtype)
+        self.w = (w.to(dtype) if self.tc else w).contiguous().to(device)
+
+    def __call__(self, x, in_coff=0, cx=None, out=None, out_coff=0):
+        """x [B,H,W,Cx]; reads channels [in_coff, in_coff+k)."""
+        if self.tc and (in_coff * x.element_size()) % 16 == 0:
+            src = x if in_coff == 0 else x.view(-1)[in_coff:]
+            return ops.gemm1x1_bias_act_raw(src, x.shape, self.w, self.bias, self.act, self.k, out, out_coff)
+        xs = x[..., in_coff:in_coff + self.k].contiguous() if (in_coff or x.shape[-1] != self.k) else x
+        return ops.pool_project(xs, self.w.float(), self.bias, pool=1, act=self.act, out=out, out_coff=out_coff)
+
+
+class _ConvKxK:
+    """3x3 (or grouped / strided) convolution + bias + SiLU through the library on a channels_last view."""
+
+    def __init__(self, conv_mod, dtype, device):
+        conv = conv_mod.conv if hasattr(conv_mod, 'conv') else conv_mod
+        self.w = conv.weight.detach().to(device, dtype).contiguous(memory_format=torch.channels_last)
+        self.b = conv.bias.detach().to(device, dtype)
+        self.stride, self.padding, self.groups = conv.stride, conv.padding, conv.groups
+        self.silu = hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)
+
+    def __call__(self, x):
+        y = F.conv2d(_nchw_view(x), self.w, self.b, self.stride, self.padding, 1, self.groups)
+        if self.silu:
+            y = F.silu(y, inplace=True)
+        return _nhwc(y)
+
+
+def _conv(conv_mod, dtype, device):
+    k = conv_mod.conv.kernel_size
+    if k == (1, 1) and conv_mod.conv.groups == 1:
+        return _Conv1x1(conv_mod, dtype, device)
+    return _ConvKxK(conv_mod, dtype, device)
+
+
+class FastDetector(torch.nn.Module):
+    """Callable with the model's signature: forward(x[B,3,H,W]) -> (y[B,4+nc,A], [raw P3,P4,P5] as NCHW views)."""
+
+    def __init__(self, model, dtype=torch.float16):
+        super().__init__()
+        if any(hasattr(m, 'bn') for m in model.modules() if isinstance(m, M.Conv)):
+            raise ValueError('call model.fuse() first: the engine runs the Conv+BN-folded model')
+        if model.training:
+            raise ValueError('call model.eval() first')
+        device = next(model.parameters()).device
+        if device.type != 'cuda':
+            raise ValueError('move the model to a CUDA device first (there is no CPU path)')
+        self.model, self.dtype, self.device = model, dtype, device
+        self.stride = model.stride
+        self.plan = [self._compile(m) for m in model.model]
+
+    # ---- per-module closures -------------------------------------------------------------------
+    def _compile(self, m):
+        dt, dev = self.dtype, self.device
+        if isinstance(m, M.Conv):
+            c = _conv(m, dt, dev)
+            return lambda x: c(x)
+        if isinstance(m, M.AConv):
+            c = _ConvKxK(m.cv1, dt, dev)
+            return lambda x: c(_nhwc(F.avg_pool2d(_nchw_view(x), 2, 1, 0, False, True)))
+        if isinstance(m, M.ELAN1):
+            cv1, cv2, cv3, cv4 = (_conv(t, dt, dev) for t in (m.cv1, m.cv2, m.cv3, m.cv4))
+            half = m.c
+
+            def elan(x):
+                t = cv1(x)
+                y2 = cv2(t[..., half:].contiguous())
+                y3 = cv3(y2)
+                return cv4(torch.cat((t, y2, y3), -1))
+            return elan
+        if isinstance(m, M.RepNCSPELAN4_KADC):
+            cv1, cv4 = _conv(m.cv1, dt, dev), _conv(m.cv4, dt, dev)
+            b2, c2 = self._csp(m.cv2[0]), _conv(m.cv2[1], dt, dev)
+            b3, c3 = self._csp(m.cv3[0]), _conv(m.cv3[1], dt, dev)
+            half = m.c
+
+            def gelan(x):
+                t = cv1(x)
+                y2 = c2(b2(t, half))
+                y3 = c3(b3(y2, 0))
+                return cv4(torch.cat((t, y2, y3), -1))
+            return gelan
+        if isinstance(m, M.SPPELAN):
+            cv1, cv5 = _conv(m.cv1, dt, dev), _conv(m.cv5, dt, dev)
+
+            def spp(x):
+                ys = [cv1(x)]
+                for _ in range(3):
+                    ys.append(_nhwc(F.max_pool2d(_nchw_view(ys[-1]), 5, 1, 2)))
+                return cv5(torch.cat(ys, -1))
+            return spp
+        if isinstance(m, torch.nn.Upsample):
+            def up(x):
+                B, H, W, C = x.shape
+                return x.view(B, H, 1, W, 1, C).expand(B, H, 2, W, 2, C).reshape(B, 2 * H, 2 * W, C)
+            return up
+        if isinstance(m, M.Concat):
+            return lambda xs: torch.cat(xs, -1)
+        if isinstance(m, M.DDetect):
+            return self._head(m)
+        raise TypeError(f'no B200 execution for {type(m).__name__}')
+
+    def _csp(self, m):
+        """RepNCSP_KADC: cv3(cat(KADConv x n (cv1(x)), cv2(x))); x is read as a channel slice in place."""
+        dt, dev = self.dtype, self.device
+        cv1, cv2, cv3 = _conv(m.cv1, dt, dev), _conv(m.cv2, dt, dev), _conv(m.cv3, dt, dev)
+        layers = list(m.m)
+
+        def csp(x, in_coff):
+            a = cv1(x, in_coff=in_coff)
+            for layer in layers:
+                a = kadconv_forward_nhwc(layer, a)
+            cat = torch.empty(a.shape[:-1] + (2 * a.shape[-1],), dtype=a.dtype, device=a.device)
+            cat[..., :a.shape[-1]].copy_(a)
+            cv2(x, in_coff=in_coff, out=cat, out_coff=a.shape[-1])
+            return cv3(cat)
+        return csp
+
+    def _head(self, m):
+        dt, dev = self.dtype, self.device
+        box = [[_ConvKxK(s[0], dt, dev), _ConvKxK(s[1], dt, dev), _ConvKxK(s[2], dt, dev)] for s in m.cv2]
+        cls = [[_ConvKxK(s[0], dt, dev), _ConvKxK(s[1], dt, dev), _ConvKxK(s[2], dt, dev)] for s in m.cv3]
+        proj = torch.arange(m.reg_max, dtype=torch.float32, device=dev).to(dt).view(1, 1, m.reg_max, 1)
+        cache = {}
+
+        def head(feats):
+            raw = []
+            for i, f in enumerate(feats):
+                b = box[i][2](box[i][1](box[i][0](f)))
+                c = cls[i][2](cls[i][1](cls[i][0](f)))
+                raw.append(torch.cat((b, c), -1))                         # [B,H,W,no]
+            B = raw[0].shape[0]
+            key = tuple(tuple(r.shape[1:3]) for r in raw)
+            if key not in cache:
+                fake = [torch.empty((1, 1, h, w), dtype=dt, device=dev) for h, w in key]
+                cache[key] = tuple(t.transpose(0, 1) for t in M.make_anchors(fake, m.stride, 0.5))
+            anchors, strides = cache[key]
+            # the reference's sequence (KAD-CNet/models/yolo.py:112-127), on [B,no,A] with A in (y,x) order
+            allr = torch.cat([r.reshape(B, -1, m.no) for r in raw], 1).transpose(1, 2)
+            bx, cl = allr.split((4 * m.reg_max, m.nc), 1)
+            A = bx.shape[2]
+            d = (bx.reshape(B, 4, m.reg_max, A).softmax(2) * proj).sum(2)
+            lt, rb = d.split(2, 1)
+            a = anchors.unsqueeze(0)
+            x1y1, x2y2 = a - lt, a + rb
+            dbox = torch.cat(((x1y1 + x2y2) / 2, x2y2 - x1y1), 1) * strides
+            return torch.cat((dbox, cl.sigmoid()), 1), [_nchw_view(r) for r in raw]
+        return head
+
+    # ---- forward -------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, x):
+        if not x.is_cuda:
+            raise RuntimeError('FastDetector has no CPU path: move the input to the GPU')
+        x = ops.to_nhwc(x.to(self.dtype))
+        ys = []
+        save = self.model.save
+        for m, fn in zip(self.model.model, self.plan):
+            if m.f != -1:
+                x = ys[m.f] if isinstance(m.f, int) else [x if j == -1 else ys[j] for j in m.f]
+            x = fn(x)
+            ys.append(x if m.i in save else None)
+        return x

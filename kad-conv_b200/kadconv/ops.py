@@ -272,3 +272,23 @@ def gemm1x1_bias_act(x, w, bias=None, act=ACT_SILU, k=None, out=None, out_coff=0
     _abi.check(_abi.load().kad_gemm1x1_bias_act(_ptr(x), _ptr(w), _ptr(_f32(bias, 'bias')), ctypes.c_void_p(dst.data_ptr()), M, K, N, Cx, ldy, act,
                                                 dtype_code(x), _ptr(status_word(x.device)), _stream()), 'kad_gemm1x1_bias_act')
     return out
+
+
+def gemm1x1_bias_act_raw(src, shape, w, bias, act, k, out=None, out_coff=0):
+    """Like gemm1x1_bias_act, for an input that is a channel slice of a wider NHWC tensor: `src` is a
+    flat view starting at the slice's first element, `shape` the [B,H,W,Cx] shape of the full tensor."""
+    Cx = shape[-1]
+    M = 1
+    for d in shape[:-1]:
+        M *= d
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(tuple(shape[:-1]) + (N,), dtype=w.dtype, device=w.device)
+        dst, ldy = out, N
+    else:
+        ldy = out.shape[-1]
+        dst = out.view(-1)[out_coff:]
+    _abi.check(_abi.load().kad_gemm1x1_bias_act(ctypes.c_void_p(src.data_ptr()), _ptr(w), _ptr(_f32(bias, 'bias')),
+                                                ctypes.c_void_p(dst.data_ptr()), M, k, N, Cx, ldy, act, _DT[w.dtype],
+                                                _ptr(status_word(w.device)), _stream()), 'kad_gemm1x1_bias_act')
+    return out
