@@ -389,52 +389,77 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 const int sa = (int)(ia % NA);
                 if (!mbar_wait(&bars->a_empty[sa], (uint32_t)(((ia / NA) & 1) ^ 1), abort_flag)) { report(p.status, 7, s); ok = false; break; }
                 const uint32_t a_stage = a_base + sa * A_STAGE_BYTES;
+                const int nu = (2 * s + 1 < p.units) ? 2 : 1;     // a trailing single unit is produced twice (harmless)
+                int tapj[2], ccj[2], swj[2];
+#pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const int u = 2 * s + j;
-                    if (u >= p.units) break;
-                    const int cc = u / 9, tap = u - cc * 9;
-                    const long long iwc = iw + cc;           // window counter of this chunk
-                    const int sw = (int)(iwc % NWIN);
-                    if (tap == 0) {                          // a new 32-channel chunk starts: its window must have landed
-                        if (!mbar_wait(&bars->win_full[sw], (uint32_t)((iwc / NWIN) & 1), abort_flag)) { report(p.status, 8, u); ok = false; break; }
+                    const int u = 2 * s + (j < nu ? j : 0);
+                    ccj[j] = u / 9; tapj[j] = u - ccj[j] * 9;
+                    const long long iwc = iw + ccj[j];           // window counter of this chunk
+                    swj[j] = (int)(iwc % NWIN);
+                    if (j < nu && tapj[j] == 0) {                // a new 32-channel chunk starts: its window must have landed
+                        if (!mbar_wait(&bars->win_full[swj[j]], (uint32_t)((iwc / NWIN) & 1), abort_flag)) { report(p.status, 8, u); ok = false; }
                     }
-                    const uint32_t win = win_base + sw * WIN_BYTES + sub * 16;
+                }
+                if (!ok) break;
+                // Four independent (unit, row) tasks per thread: all table reads first, then all sixteen corner
+                // loads, then the arithmetic, so that the loads overlap instead of forming one dependent chain.
+                uint4 ent[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass)
+                        ent[j][pass] = lds128(tab_base + (uint32_t)((pass * 64 + rloc) * 9 + tapj[j]) * 16);
+                uint4 v[2][2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t win = win_base + swj[j] * WIN_BYTES + sub * 16;
 #pragma unroll
                     for (int pass = 0; pass < 2; ++pass) {
-                        const int row = pass * 64 + rloc;
-                        const uint4 ent = lds128(tab_base + (uint32_t)(row * 9 + tap) * 16);
-                        __half2 wa = *reinterpret_cast<const __half2*>(&ent.x), wb = *reinterpret_cast<const __half2*>(&ent.y);
-                        __half w00 = __low2half(wa), w01 = __high2half(wa), w10 = __low2half(wb), w11 = __high2half(wb);
-                        const int addr = (int)ent.z;
-                        uint4 res;
+                        const int addr = (int)ent[j][pass].z;
                         if (addr >= 0) {
                             // the two rows of a quarter-warp read one even and one odd window pixel first:
                             // their 64-byte segments then fall in different bank halves (ww is even)
                             const bool swp = (((addr >> 6) & 1) != g);
                             const uint32_t first = win + addr + (swp ? 64 : 0), second = win + addr + (swp ? 0 : 64);
-                            const uint4 vA = lds128(first), vB = lds128(second);
-                            const uint4 vC = lds128(first + rowpitch), vD = lds128(second + rowpitch);
-                            res = interp8<T>(vA, vB, vC, vD, swp ? w01 : w00, swp ? w00 : w01, swp ? w11 : w10, swp ? w10 : w11);
+                            v[j][pass][0] = lds128(first); v[j][pass][1] = lds128(second);
+                            v[j][pass][2] = lds128(first + rowpitch); v[j][pass][3] = lds128(second + rowpitch);
                         } else {
-                            const int y0 = (int)ent.w >> 16, x0 = (int)(short)(ent.w & 0xffff);
-                            const T* xb = reinterpret_cast<const T*>(p.x) + (size_t)b * p.H * p.W * p.Cin + cc * UNIT + sub * 8;
+                            const uint32_t pos = ent[j][pass].w;
+                            const int y0 = (int)pos >> 16, x0 = (int)(short)(pos & 0xffff);
+                            const T* xb = reinterpret_cast<const T*>(p.x) + (size_t)b * p.H * p.W * p.Cin + ccj[j] * UNIT + sub * 8;
                             const uint4 z = make_uint4(0, 0, 0, 0);
                             const bool y0ok = y0 >= 0, y1ok = y0 + 1 < p.H, x0ok = x0 >= 0, x1ok = x0 + 1 < p.W;
-                            const uint4 vA = (y0ok && x0ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0) * p.Cin) : z;
-                            const uint4 vB = (y0ok && x1ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0 + 1) * p.Cin) : z;
-                            const uint4 vC = (y1ok && x0ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0) * p.Cin) : z;
-                            const uint4 vD = (y1ok && x1ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0 + 1) * p.Cin) : z;
-                            res = interp8<T>(vA, vB, vC, vD, w00, w01, w10, w11);
+                            v[j][pass][0] = (y0ok && x0ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0) * p.Cin) : z;
+                            v[j][pass][1] = (y0ok && x1ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0 + 1) * p.Cin) : z;
+                            v[j][pass][2] = (y1ok && x0ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0) * p.Cin) : z;
+                            v[j][pass][3] = (y1ok && x1ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0 + 1) * p.Cin) : z;
                         }
-                        sts128(a_stage + (uint32_t)row * 128 + (uint32_t)(((j * 4 + sub) ^ (row & 7)) << 4), res);
-                    }
-                    if (tap == 8) {                          // this chunk's window is no longer needed
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->win_empty[sw]);
                     }
                 }
-                if (!ok) break;
-                fence_proxy_async();                         // generic-proxy stores -> visible to the tensor core
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const int row = pass * 64 + rloc;
+                        const uint4 e = ent[j][pass];
+                        const __half2 wa = *reinterpret_cast<const __half2*>(&e.x), wb = *reinterpret_cast<const __half2*>(&e.y);
+                        const __half w00 = __low2half(wa), w01 = __high2half(wa), w10 = __low2half(wb), w11 = __high2half(wb);
+                        const int addr = (int)e.z;
+                        const bool swp = addr >= 0 && (((addr >> 6) & 1) != g);
+                        const uint4 res = interp8<T>(v[j][pass][0], v[j][pass][1], v[j][pass][2], v[j][pass][3],
+                                                     swp ? w01 : w00, swp ? w00 : w01, swp ? w11 : w10, swp ? w10 : w11);
+                        sts128(a_stage + (uint32_t)row * 128 + (uint32_t)(((j * 4 + sub) ^ (row & 7)) << 4), res);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    if (j < nu && tapj[j] == 8) {                // this chunk's window is no longer needed
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars->win_empty[swj[j]]);
+                    }
+                }
+                fence_proxy_async();                             // generic-proxy stores -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->a_full[sa]);
             }

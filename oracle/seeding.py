@@ -59,6 +59,8 @@ def seeded_state_dict(shapes, seed=0, offset_std=0.5, scale_mode='uniform', cls_
         elif leaf == 'weight':
             fan_in = int(np.prod(shape[1:])) if len(shape) > 1 else shape[0]
             bound = 1.0 / math.sqrt(max(fan_in, 1))
+            if '.cv3.' in key and key.endswith('.2.weight'):
+                bound *= 60.0   # detector class logits: spread the scores so that NMS is not a field of ties
             v = g.uniform(-bound, bound, shape)
         else:  # plain conv / linear bias
             v = g.normal(0.0, 0.1, shape)
