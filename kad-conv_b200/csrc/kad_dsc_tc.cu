@@ -12,9 +12,10 @@
 //   warp  6     TMA of the input window: for every 32-channel chunk the tile's footprint plus a halo is
 //               copied to shared memory ([wh][ww][32 ch], zero fill outside the image = zero padding),
 //               double buffered
-//   warps 7-14  producers: the data-dependent A operand. Per tile they first build a table of the
-//               128 x 9 samples (four corner weights x mask, window address); then for every unit they
-//               gather the four corners from the window (plain global loads for the rare sample that falls
+//   warps 7-22  producers: the data-dependent A operand. Per tile they first build a table of the
+//               128 x 9 samples (four corner weights x mask, window address; the offsets and masks were
+//               prefetched one tile ahead); then, in two groups that alternate stages, they gather the four
+//               corners of every sample from the window (plain global loads for the rare sample that falls
 //               outside it), interpolate, and store the 16-byte results in the swizzled K-major layout
 //               the tensor core reads.
 //
@@ -22,6 +23,7 @@
 // role leaves its loop, outstanding TMA copies are waited for (bounded), TMEM is freed and the
 // kernel returns with a code in the caller's status word.
 #include <mutex>
+#include <stdlib.h>
 
 #include "kad_common.cuh"
 #include "kad_sm100.cuh"
@@ -54,9 +56,9 @@ constexpr int WIN_PX_MAX = 704;         // pixels per window buffer
 constexpr int WIN_BYTES = WIN_PX_MAX * 64;
 constexpr int NWIN = 2;
 constexpr int TABLE_BYTES = BM * 9 * 16;
-constexpr int EPI_WARPS = 4, PROD_WARPS = 8;
+constexpr int EPI_WARPS = 4, PROD_WARPS = 16, PROD_GROUPS = 2, GROUP_WARPS = PROD_WARPS / PROD_GROUPS;
 constexpr int WARP_MMA = 4, WARP_TMA_B = 5, WARP_TMA_WIN = 6, WARP_PROD0 = 7;
-constexpr int NTHREADS_TC = (WARP_PROD0 + PROD_WARPS) * 32;   // 480
+constexpr int NTHREADS_TC = (WARP_PROD0 + PROD_WARPS) * 32;   // 736
 constexpr int ACC_COLS = 256;           // TMEM columns per accumulator buffer
 constexpr int SMEM_LIMIT = 227 * 1024;
 
@@ -70,6 +72,8 @@ struct TcParams {
     int units, stages, nchunks;                 // K structure
     int nb, b_stage_bytes;                      // B ring
     int offset_f32, mask_f32, y_f32, act, fmt;
+    int dbg;
+    long long* trace;
 };
 
 struct SmemLayout {
@@ -139,6 +143,9 @@ __device__ __forceinline__ uint4 interp8<__nv_bfloat16>(uint4 a, uint4 b, uint4 
     return r;
 }
 
+// Development trace: role r of CTA 0 appends clock64 stamps to trace[r*4096 ...].
+#define KAD_TR(role, cnt) do { if (p.trace && blockIdx.x == 0 && (cnt) < 4096) p.trace[(role) * 4096 + (cnt)++] = clock64(); } while (0)
+
 __device__ __forceinline__ void report(int* status, int code, int detail) {
     if (atomicCAS(status, 0, code) == 0) { status[1] = detail; status[2] = blockIdx.x; }
 }
@@ -150,7 +157,8 @@ __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t parity, int l
     return mbar_wait(bar, parity, abort_flag);
 }
 
-template <typename T>
+// AFFINE: the epilogue applies scale/shift/activation/post; otherwise it only converts and stores.
+template <typename T, bool AFFINE>
 __global__ void __launch_bounds__(NTHREADS_TC, 1)
 dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const TcParams p, const SmemLayout L) {
@@ -162,7 +170,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const int tiles_per_img = p.tiles_x * p.tiles_y;
 
     if (tid == 0) {
-        for (int i = 0; i < NA; ++i) { mbar_init(&bars->a_full[i], PROD_WARPS); mbar_init(&bars->a_empty[i], 1); }
+        for (int i = 0; i < NA; ++i) { mbar_init(&bars->a_full[i], GROUP_WARPS); mbar_init(&bars->a_empty[i], 1); }
         for (int i = 0; i < 4; ++i) { mbar_init(&bars->b_full[i], 1); mbar_init(&bars->b_empty[i], 1); }
         for (int i = 0; i < NWIN; ++i) { mbar_init(&bars->win_full[i], 1); mbar_init(&bars->win_empty[i], PROD_WARPS); }
         for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], EPI_WARPS * 32); }
@@ -189,10 +197,13 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         // =========================================================================== epilogue
         float* gsum = epi + 768;   // [4 warps][256] column sums for the SE squeeze
         int it = 0;
+        int etr = 0;
         for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
             const int buf = it & 1;
+            if (tid == 0) KAD_TR(2, etr);
             if (!mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag)) { report(p.status, 1, it); break; }
             tc_fence_after();
+            if (tid == 0) KAD_TR(2, etr);
             const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
             const int ty0 = (tr / p.tiles_x) * p.th, tx0 = (tr % p.tiles_x) * p.tw;
             const int r = warp * 32 + lane;
@@ -207,11 +218,21 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 if (nc == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
                 tmem_ld_wait();
                 float o[32];
+                if (AFFINE) {
+                    const float4* sc4 = reinterpret_cast<const float4*>(epi + c0);
+                    const float4* sh4 = reinterpret_cast<const float4*>(epi + 256 + c0);
+                    const float4* po4 = reinterpret_cast<const float4*>(epi + 512 + c0);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float a = __uint_as_float(v[j]);
-                    int c = c0 + j;
-                    o[j] = (j < nc) ? apply_act(fmaf(a, epi[c], epi[256 + c]), p.act) * epi[512 + c] : 0.f;
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        const float4 sc = sc4[q4], sh = sh4[q4], po = po4[q4];
+                        o[4 * q4 + 0] = apply_act(fmaf(__uint_as_float(v[4 * q4 + 0]), sc.x, sh.x), p.act) * po.x;
+                        o[4 * q4 + 1] = apply_act(fmaf(__uint_as_float(v[4 * q4 + 1]), sc.y, sh.y), p.act) * po.y;
+                        o[4 * q4 + 2] = apply_act(fmaf(__uint_as_float(v[4 * q4 + 2]), sc.z, sh.z), p.act) * po.z;
+                        o[4 * q4 + 3] = apply_act(fmaf(__uint_as_float(v[4 * q4 + 3]), sc.w, sh.w), p.act) * po.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(v[j]);
                 }
                 if (live) {
                     if (p.y_f32) {
@@ -236,7 +257,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 if (p.gap_partial) {
                     // column sums over the warp's 32 rows: butterfly that halves the columns per lane each step
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] = live ? (p.y_f32 ? o[j] : to_f<T>(from_f<T>(o[j]))) : 0.f;
+                    for (int j = 0; j < 32; ++j) o[j] = (live && j < nc) ? (p.y_f32 ? o[j] : to_f<T>(from_f<T>(o[j]))) : 0.f;
 #pragma unroll
                     for (int step = 16; step >= 1; step >>= 1) {
                         const bool upper = (lane & step) != 0;
@@ -247,13 +268,12 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                             o[j] = keep + __shfl_xor_sync(0xffffffffu, send, step);
                         }
                     }
-                    // lane l now holds the sum of column bitrev-free index: column = sum over steps of (lane&step)
-                    int col = lane;   // the selection above keeps column bit `step` equal to lane bit `step`
-                    if (col < nc) gsum[warp * 256 + c0 + col] = o[0];
+                    if (lane < nc) gsum[warp * 256 + c0 + lane] = o[0];   // lane l ends up with column l
                 }
             }
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[buf]);
+            if (tid == 0) KAD_TR(2, etr);
             if (p.gap_partial) {
                 if (!group_sync(&bars->gap_ready, it & 1, lane, abort_flag)) { report(p.status, 10, it); break; }
                 for (int c = tid; c < p.N; c += EPI_WARPS * 32)
@@ -267,21 +287,28 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         const uint32_t idesc = instr_desc_f16(p.fmt, p.N);
         const uint32_t a_base = smem_u32(smem + L.a), b_base = smem_u32(smem + L.b);
         int it = 0;
-        long long ia = 0, ib = 0;   // stage counters of the A and B rings
+        uint32_t ia = 0;            // stage counter, shared numbering of the A and B rings
         bool ok = true;
+        int trc = 0;
         for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { report(p.status, 2, it); break; }
             tc_fence_after();
+            if (lane == 0) KAD_TR(1, trc);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * ACC_COLS);
-            for (int s = 0; s < p.stages; ++s, ++ia, ++ib) {
-                const int sa = (int)(ia % NA), sb = (int)(ib % p.nb);
-                if (!mbar_wait(&bars->a_full[sa], (uint32_t)((ia / NA) & 1), abort_flag)) { report(p.status, 3, s); ok = false; break; }
-                if (!mbar_wait(&bars->b_full[sb], (uint32_t)((ib / p.nb) & 1), abort_flag)) { report(p.status, 4, s); ok = false; break; }
+            for (int s = 0; s < p.stages; ++s, ++ia) {
+                const uint32_t sa = ia % NA, sb = ia % (uint32_t)p.nb;
+                // lane 0 waits for the A stage, lane 1 for the B stage: the two waits overlap
+                bool okw = true;
+                if (lane == 0 && !(p.dbg & 32)) okw = mbar_wait(&bars->a_full[sa], (ia / NA) & 1, abort_flag);
+                else if (lane == 1 && !(p.dbg & 2)) okw = mbar_wait(&bars->b_full[sb], (ia / (uint32_t)p.nb) & 1, abort_flag);
+                if (!__all_sync(0xffffffffu, okw)) { report(p.status, 3, s); ok = false; break; }
                 tc_fence_after();
+                if (lane == 0) KAD_TR(1, trc);
                 if (lane == 0) {
                     const int nk = (2 * s + 1 < p.units) ? 4 : 2;   // a trailing single unit fills half a stage
                     const uint32_t aaddr = a_base + sa * A_STAGE_BYTES, baddr = b_base + sb * p.b_stage_bytes;
+                    if (!(p.dbg & 4))
                     for (int k = 0; k < nk; ++k)
                         umma_f16(tacc, smem_desc_sw128(aaddr + k * 32), smem_desc_sw128(baddr + k * 32), idesc, (s | k) ? 1u : 0u);
                     umma_commit(&bars->a_empty[sa]);
@@ -293,177 +320,240 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
     } else if (warp == WARP_TMA_B) {
         // =========================================================================== weights
-        if (lane == 0) {
+        if (lane == 0 && !(p.dbg & 2)) {
             tma_prefetch_desc(&map_w);
-            long long ib = 0;
+            uint32_t ib = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
                 for (int s = 0; s < p.stages; ++s, ++ib) {
-                    const int sb = (int)(ib % p.nb);
-                    if (!mbar_wait(&bars->b_empty[sb], (uint32_t)(((ib / p.nb) & 1) ^ 1), abort_flag)) { report(p.status, 5, s); ok = false; break; }
+                    const uint32_t sb = ib % (uint32_t)p.nb;
+                    if (!mbar_wait(&bars->b_empty[sb], ((ib / (uint32_t)p.nb) & 1) ^ 1, abort_flag)) { report(p.status, 5, s); ok = false; break; }
                     mbar_arrive_expect_tx(&bars->b_full[sb], (uint32_t)p.b_stage_bytes);
                     tma_load_2d(smem + L.b + sb * p.b_stage_bytes, &map_w, 0, s * p.N, &bars->b_full[sb]);
                 }
             }
             if (!ok || *abort_flag) {   // let copies in flight land before the CTA goes away
-                for (int i = 0; i < p.nb && i < ib; ++i) {
-                    long long j = ib - 1 - i;
-                    mbar_wait(&bars->b_full[j % p.nb], (uint32_t)((j / p.nb) & 1), abort_flag + 0);
+                for (uint32_t i = 0; i < (uint32_t)p.nb && i < ib; ++i) {
+                    uint32_t j = ib - 1 - i;
+                    mbar_wait(&bars->b_full[j % (uint32_t)p.nb], (j / (uint32_t)p.nb) & 1, abort_flag);
                 }
             }
         }
     } else if (warp == WARP_TMA_WIN) {
         // =========================================================================== input windows
-        if (lane == 0) {
+        if (lane == 0 && !(p.dbg & 8)) {
             tma_prefetch_desc(&map_x);
-            long long iw = 0;
+            uint32_t iw = 0;
             bool ok = true;
             const uint32_t win_bytes = (uint32_t)(p.wh * p.ww * 64);
             for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
                 const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
                 const int wy0 = (tr / p.tiles_x) * p.th - 1 - p.halo, wx0 = (tr % p.tiles_x) * p.tw - 1 - p.halo;
                 for (int cc = 0; cc < p.nchunks; ++cc, ++iw) {
-                    const int sw = (int)(iw % NWIN);
-                    if (!mbar_wait(&bars->win_empty[sw], (uint32_t)(((iw / NWIN) & 1) ^ 1), abort_flag)) { report(p.status, 6, cc); ok = false; break; }
+                    const uint32_t sw = iw % NWIN;
+                    if (!mbar_wait(&bars->win_empty[sw], ((iw / NWIN) & 1) ^ 1, abort_flag)) { report(p.status, 6, cc); ok = false; break; }
                     mbar_arrive_expect_tx(&bars->win_full[sw], win_bytes);
                     tma_load_4d(smem + L.win + sw * WIN_BYTES, &map_x, cc * UNIT, wx0, wy0, b, &bars->win_full[sw]);
                 }
             }
             if (!ok || *abort_flag) {
-                for (int i = 0; i < NWIN && i < iw; ++i) {
-                    long long j = iw - 1 - i;
-                    mbar_wait(&bars->win_full[j % NWIN], (uint32_t)((j / NWIN) & 1), abort_flag);
+                for (uint32_t i = 0; i < NWIN && i < iw; ++i) {
+                    uint32_t j = iw - 1 - i;
+                    mbar_wait(&bars->win_full[j % NWIN], (j / NWIN) & 1, abort_flag);
                 }
             }
         }
     } else {
         // =========================================================================== producers
-        const int pw = warp - WARP_PROD0;            // 0..7
-        const int ptid = tid - WARP_PROD0 * 32;      // 0..255
+        // 16 warps in two groups of 8; group g fills the stages s = g, g+2, ... so that the per-stage latency
+        // (barrier wait, gather, proxy fence) of one group overlaps the other group's stage.
+        const int pw = warp - WARP_PROD0;            // 0..15
+        const int grp = pw / GROUP_WARPS, pwg = pw % GROUP_WARPS;
+        const int ptid = tid - WARP_PROD0 * 32;      // 0..511
         const int sub = lane & 3, g = (lane >> 2) & 1, q = lane >> 3;
-        const int rloc = pw * 8 + g * 4 + q;         // row within a 64-row pass
+        const int rloc = pwg * 8 + g * 4 + q;        // row within a 64-row pass; (row >> 2) & 1 == g
         const uint32_t a_base = smem_u32(smem + L.a), win_base = smem_u32(smem + L.win), tab_base = smem_u32(smem + L.table);
         uint4* table = reinterpret_cast<uint4*>(smem + L.table);
-        const int rowpitch = p.ww * 64;
-        long long ia = 0, iw = 0;
+        const uint32_t rowpitch = (uint32_t)p.ww * 64;
+        // per-thread constants of its two rows (pass 0 / 1): table row base and swizzled store offsets per unit slot
+        uint32_t tab_row[2], st_off[2][2];
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            const int row = pass * 64 + rloc;
+            tab_row[pass] = tab_base + (uint32_t)(row * 9) * 16;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) st_off[pass][j] = (uint32_t)row * 128 + (uint32_t)(((j * 4 + sub) ^ (row & 7)) << 4);
+        }
+        constexpr int TAB_ITERS = (BM * 9 + PROD_WARPS * 32 - 1) / (PROD_WARPS * 32);   // 3
+        float pf[TAB_ITERS][3];                      // offsets (dy, dx) and mask of this thread's table entries
+
+        // loads the raw sample parameters of a tile into registers (issued one tile ahead)
+        auto prefetch = [&](int tile_) {
+            const int b_ = tile_ / tiles_per_img, tr_ = tile_ - b_ * tiles_per_img;
+            const int ty0_ = (tr_ / p.tiles_x) * p.th, tx0_ = (tr_ % p.tiles_x) * p.tw;
+#pragma unroll
+            for (int i = 0; i < TAB_ITERS; ++i) {
+                const int e = ptid + i * PROD_WARPS * 32;
+                pf[i][0] = 0.f; pf[i][1] = 0.f; pf[i][2] = 1.f;
+                if (e < BM * 9 && tile_ < p.ntiles) {
+                    const int r = e / 9, k = e - r * 9;
+                    const int ry = r / p.tw, rx = r - ry * p.tw;
+                    const int py = ty0_ + ry, px = tx0_ + rx;
+                    if (r < p.th * p.tw && py < p.H && px < p.W) {
+                        const size_t pix = ((size_t)b_ * p.H + py) * p.W + px;
+                        if (p.offset) { pf[i][0] = load_mixed<T>(p.offset, pix * 18 + 2 * k, p.offset_f32); pf[i][1] = load_mixed<T>(p.offset, pix * 18 + 2 * k + 1, p.offset_f32); }
+                        if (p.mask) pf[i][2] = load_mixed<T>(p.mask, pix * 9 + k, p.mask_f32);
+                    }
+                }
+            }
+        };
+
         bool ok = true;
         int it = 0;
+        int trc = 0; const bool trp = (pw == 0 && lane == 0);
+        prefetch(blockIdx.x);
         for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
             const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
             const int ty0 = (tr / p.tiles_x) * p.th, tx0 = (tr % p.tiles_x) * p.tw;
             const int wy0 = ty0 - 1 - p.halo, wx0 = tx0 - 1 - p.halo;
-            // ---- sample table of the tile: [row][tap] -> {w00|w01, w10|w11, window offset or -1, y0<<16|x0}
+            if (trp) KAD_TR(0, trc);
             // everybody is done reading the previous table
             if (!group_sync(&bars->tab_free, it & 1, lane, abort_flag)) { report(p.status, 12, it); break; }
-            for (int e = ptid; e < BM * 9; e += PROD_WARPS * 32) {
-                const int r = e / 9, k = e - r * 9;
-                const int ry = r / p.tw, rx = r - ry * p.tw;
-                const int py = ty0 + ry, px = tx0 + rx;
-                float w00 = 0.f, w01 = 0.f, w10 = 0.f, w11 = 0.f;
-                int addr = 0, pos = 0;
-                if (r < p.th * p.tw && py < p.H && px < p.W) {
-                    const size_t pix = ((size_t)b * p.H + py) * p.W + px;
-                    float dy = 0.f, dx = 0.f, m = 1.f;
-                    if (p.offset) { dy = load_mixed<T>(p.offset, pix * 18 + 2 * k, p.offset_f32); dx = load_mixed<T>(p.offset, pix * 18 + 2 * k + 1, p.offset_f32); }
-                    if (p.mask) m = load_mixed<T>(p.mask, pix * 9 + k, p.mask_f32);
-                    const float sy = (float)(py + k / 3 - 1) + dy, sx = (float)(px + k % 3 - 1) + dx;
-                    if (sy > -1.f && sy < (float)p.H && sx > -1.f && sx < (float)p.W) {
-                        const float fy = floorf(sy), fx = floorf(sx);
-                        const int y0 = (int)fy, x0 = (int)fx;
-                        const float ly = sy - fy, lx = sx - fx, hy = 1.f - ly, hx = 1.f - lx;
-                        w00 = hy * hx * m; w01 = hy * lx * m; w10 = ly * hx * m; w11 = ly * lx * m;
-                        const int wy = y0 - wy0, wx = x0 - wx0;
-                        if (wy >= 0 && wy + 1 < p.wh && wx >= 0 && wx + 1 < p.ww) addr = (wy * p.ww + wx) * 64;
-                        else { addr = -1; pos = (int)(((unsigned)y0 << 16) | ((unsigned)x0 & 0xffffu)); }
+            // ---- sample table [row][tap] -> {w_first|w_second, w_first_below|w_second_below, window offset|flags, y0<<16|x0}
+            // The 'first' corner is the one whose window pixel parity equals the row's group bit, so that the two rows
+            // a quarter-warp reads together touch different halves of the shared-memory banks (ww is even).
+            // flags: bit 0 = second corner lies 64 bytes before the first; bit 1 = sample outside the window (global path).
+#pragma unroll
+            for (int i = 0; i < TAB_ITERS; ++i) {
+                const int e = ptid + i * PROD_WARPS * 32;
+                if (e < BM * 9) {
+                    const int r = e / 9, k = e - r * 9;
+                    const int ry = r / p.tw, rx = r - ry * p.tw;
+                    const int py = ty0 + ry, px = tx0 + rx;
+                    float w00 = 0.f, w01 = 0.f, w10 = 0.f, w11 = 0.f;
+                    uint32_t word = 0, pos = 0;
+                    if (r < p.th * p.tw && py < p.H && px < p.W) {
+                        const float sy = (float)(py + k / 3 - 1) + pf[i][0], sx = (float)(px + k % 3 - 1) + pf[i][1];
+                        if (sy > -1.f && sy < (float)p.H && sx > -1.f && sx < (float)p.W) {
+                            const float m = pf[i][2];
+                            const float fy = floorf(sy), fx = floorf(sx);
+                            const int y0 = (int)fy, x0 = (int)fx;
+                            const float ly = sy - fy, lx = sx - fx, hy = 1.f - ly, hx = 1.f - lx;
+                            w00 = hy * hx * m; w01 = hy * lx * m; w10 = ly * hx * m; w11 = ly * lx * m;
+                            const int wy = y0 - wy0, wx = x0 - wx0;
+                            if (wy >= 0 && wy + 1 < p.wh && wx >= 0 && wx + 1 < p.ww) {
+                                const uint32_t addr = (uint32_t)(wy * p.ww + wx) * 64;
+                                if ((int)((addr >> 6) & 1) != ((r >> 2) & 1)) {      // start with the right-hand corner
+                                    word = (addr + 64) | 1u;
+                                    float t = w00; w00 = w01; w01 = t; t = w10; w10 = w11; w11 = t;
+                                } else {
+                                    word = addr;
+                                }
+                            } else {
+                                word = 2u; pos = ((uint32_t)y0 << 16) | ((uint32_t)x0 & 0xffffu);
+                            }
+                        }
                     }
+                    __half2 wa = __floats2half2_rn(w00, w01), wb = __floats2half2_rn(w10, w11);
+                    uint4 ent;
+                    ent.x = *reinterpret_cast<uint32_t*>(&wa); ent.y = *reinterpret_cast<uint32_t*>(&wb);
+                    ent.z = word; ent.w = pos;
+                    table[e] = ent;
                 }
-                __half2 wa = __floats2half2_rn(w00, w01), wb = __floats2half2_rn(w10, w11);
-                uint4 ent;
-                ent.x = *reinterpret_cast<uint32_t*>(&wa); ent.y = *reinterpret_cast<uint32_t*>(&wb);
-                ent.z = (uint32_t)addr; ent.w = (uint32_t)pos;
-                table[e] = ent;
             }
+            if (trp) KAD_TR(0, trc);
             if (!group_sync(&bars->tab_ready, it & 1, lane, abort_flag)) { report(p.status, 13, it); break; }
+            if (trp) KAD_TR(0, trc);
+            prefetch(tile + (int)gridDim.x);         // next tile's offsets and mask arrive while this tile is gathered
 
-            for (int s = 0; s < p.stages && ok; ++s, ++ia) {
-                const int sa = (int)(ia % NA);
-                if (!mbar_wait(&bars->a_empty[sa], (uint32_t)(((ia / NA) & 1) ^ 1), abort_flag)) { report(p.status, 7, s); ok = false; break; }
+            int have_cc = -1;                        // chunks whose window this thread has already waited for
+            const uint32_t ia0 = (uint32_t)it * (uint32_t)p.stages, iw0 = (uint32_t)it * (uint32_t)p.nchunks;
+            for (int s = grp; s < p.stages && ok; s += PROD_GROUPS) {
+                const uint32_t ia = ia0 + (uint32_t)s;
+                const uint32_t sa = ia % NA;
+                if (!mbar_wait(&bars->a_empty[sa], ((ia / NA) & 1) ^ 1, abort_flag)) { report(p.status, 7, s); ok = false; break; }
+                if (trp) KAD_TR(0, trc);
                 const uint32_t a_stage = a_base + sa * A_STAGE_BYTES;
                 const int nu = (2 * s + 1 < p.units) ? 2 : 1;     // a trailing single unit is produced twice (harmless)
-                int tapj[2], ccj[2], swj[2];
+                int tapj[2], ccj[2];
+                uint32_t winj[2];
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int u = 2 * s + (j < nu ? j : 0);
                     ccj[j] = u / 9; tapj[j] = u - ccj[j] * 9;
-                    const long long iwc = iw + ccj[j];           // window counter of this chunk
-                    swj[j] = (int)(iwc % NWIN);
-                    if (j < nu && tapj[j] == 0) {                // a new 32-channel chunk starts: its window must have landed
-                        if (!mbar_wait(&bars->win_full[swj[j]], (uint32_t)((iwc / NWIN) & 1), abort_flag)) { report(p.status, 8, u); ok = false; }
+                    const uint32_t iwc = iw0 + (uint32_t)ccj[j];     // window counter of this chunk
+                    const uint32_t sw = iwc % NWIN;
+                    if (ccj[j] > have_cc && !(p.dbg & 8)) {          // first use of this chunk: its window must have landed
+                        if (!mbar_wait(&bars->win_full[sw], (iwc / NWIN) & 1, abort_flag)) { report(p.status, 8, u); ok = false; }
+                        have_cc = ccj[j];
                     }
+                    winj[j] = win_base + sw * WIN_BYTES + sub * 16;
                 }
                 if (!ok) break;
-                // Four independent (unit, row) tasks per thread: all table reads first, then all sixteen corner
-                // loads, then the arithmetic, so that the loads overlap instead of forming one dependent chain.
-                uint4 ent[2][2];
+                if (!(p.dbg & 1)) {
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int pass = 0; pass < 2; ++pass) {
+                    // two independent tasks (the stage's two units of one row): table reads, then eight corner
+                    // loads, then the arithmetic
+                    uint4 ent[2], v[2][4];
 #pragma unroll
-                    for (int pass = 0; pass < 2; ++pass)
-                        ent[j][pass] = lds128(tab_base + (uint32_t)((pass * 64 + rloc) * 9 + tapj[j]) * 16);
-                uint4 v[2][2][4];
+                    for (int j = 0; j < 2; ++j) ent[j] = lds128(tab_row[pass] + (uint32_t)tapj[j] * 16);
+                    const bool slow = ((ent[0].z | ent[1].z) & 2u) != 0;
+                    if (!__any_sync(0xffffffffu, slow)) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t first = winj[j] + (ent[j].z & ~63u);
+                            const uint32_t second = first + 64u - ((ent[j].z & 1u) << 7);
+                            v[j][0] = lds128(first); v[j][1] = lds128(second);
+                            v[j][2] = lds128(first + rowpitch); v[j][3] = lds128(second + rowpitch);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            if (!(ent[j].z & 2u)) {
+                                const uint32_t first = winj[j] + (ent[j].z & ~63u);
+                                const uint32_t second = first + 64u - ((ent[j].z & 1u) << 7);
+                                v[j][0] = lds128(first); v[j][1] = lds128(second);
+                                v[j][2] = lds128(first + rowpitch); v[j][3] = lds128(second + rowpitch);
+                            } else {
+                                const uint32_t pos = ent[j].w;
+                                const int y0 = (int)pos >> 16, x0 = (int)(short)(pos & 0xffff);
+                                const T* xb = reinterpret_cast<const T*>(p.x) + (size_t)b * p.H * p.W * p.Cin + ccj[j] * UNIT + sub * 8;
+                                const uint4 z = make_uint4(0, 0, 0, 0);
+                                const bool y0ok = y0 >= 0, y1ok = y0 + 1 < p.H, x0ok = x0 >= 0, x1ok = x0 + 1 < p.W;
+                                v[j][0] = (y0ok && x0ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0) * p.Cin) : z;
+                                v[j][1] = (y0ok && x1ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0 + 1) * p.Cin) : z;
+                                v[j][2] = (y1ok && x0ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0) * p.Cin) : z;
+                                v[j][3] = (y1ok && x1ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0 + 1) * p.Cin) : z;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const __half2 wa = *reinterpret_cast<const __half2*>(&ent[j].x), wb = *reinterpret_cast<const __half2*>(&ent[j].y);
+                        const uint4 res = interp8<T>(v[j][0], v[j][1], v[j][2], v[j][3], __low2half(wa), __high2half(wa),
+                                                     __low2half(wb), __high2half(wb));
+                        sts128(a_stage + st_off[pass][j], res);
+                    }
+                }
+                }
+                // release a chunk's window after this group's last stage that reads it
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const uint32_t win = win_base + swj[j] * WIN_BYTES + sub * 16;
-#pragma unroll
-                    for (int pass = 0; pass < 2; ++pass) {
-                        const int addr = (int)ent[j][pass].z;
-                        if (addr >= 0) {
-                            // the two rows of a quarter-warp read one even and one odd window pixel first:
-                            // their 64-byte segments then fall in different bank halves (ww is even)
-                            const bool swp = (((addr >> 6) & 1) != g);
-                            const uint32_t first = win + addr + (swp ? 64 : 0), second = win + addr + (swp ? 0 : 64);
-                            v[j][pass][0] = lds128(first); v[j][pass][1] = lds128(second);
-                            v[j][pass][2] = lds128(first + rowpitch); v[j][pass][3] = lds128(second + rowpitch);
-                        } else {
-                            const uint32_t pos = ent[j][pass].w;
-                            const int y0 = (int)pos >> 16, x0 = (int)(short)(pos & 0xffff);
-                            const T* xb = reinterpret_cast<const T*>(p.x) + (size_t)b * p.H * p.W * p.Cin + ccj[j] * UNIT + sub * 8;
-                            const uint4 z = make_uint4(0, 0, 0, 0);
-                            const bool y0ok = y0 >= 0, y1ok = y0 + 1 < p.H, x0ok = x0 >= 0, x1ok = x0 + 1 < p.W;
-                            v[j][pass][0] = (y0ok && x0ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0) * p.Cin) : z;
-                            v[j][pass][1] = (y0ok && x1ok) ? ldg128(xb + ((ptrdiff_t)y0 * p.W + x0 + 1) * p.Cin) : z;
-                            v[j][pass][2] = (y1ok && x0ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0) * p.Cin) : z;
-                            v[j][pass][3] = (y1ok && x1ok) ? ldg128(xb + ((ptrdiff_t)(y0 + 1) * p.W + x0 + 1) * p.Cin) : z;
+                    if (j < nu && (j == nu - 1 || ccj[j + 1 < 2 ? j + 1 : j] != ccj[j]) && !(p.dbg & 8)) {
+                        const int Lc = (9 * ccj[j] + 8) >> 1;                 // last stage holding a unit of the chunk
+                        const int Lg = Lc - ((Lc - grp) & 1);                 // ... that belongs to this group
+                        if (s == Lg) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&bars->win_empty[(iw0 + (uint32_t)ccj[j]) % NWIN]);
                         }
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                    for (int pass = 0; pass < 2; ++pass) {
-                        const int row = pass * 64 + rloc;
-                        const uint4 e = ent[j][pass];
-                        const __half2 wa = *reinterpret_cast<const __half2*>(&e.x), wb = *reinterpret_cast<const __half2*>(&e.y);
-                        const __half w00 = __low2half(wa), w01 = __high2half(wa), w10 = __low2half(wb), w11 = __high2half(wb);
-                        const int addr = (int)e.z;
-                        const bool swp = addr >= 0 && (((addr >> 6) & 1) != g);
-                        const uint4 res = interp8<T>(v[j][pass][0], v[j][pass][1], v[j][pass][2], v[j][pass][3],
-                                                     swp ? w01 : w00, swp ? w00 : w01, swp ? w11 : w10, swp ? w10 : w11);
-                        sts128(a_stage + (uint32_t)row * 128 + (uint32_t)(((j * 4 + sub) ^ (row & 7)) << 4), res);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    if (j < nu && tapj[j] == 8) {                // this chunk's window is no longer needed
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->win_empty[swj[j]]);
-                    }
-                }
-                fence_proxy_async();                             // generic-proxy stores -> visible to the tensor core
+                if (!(p.dbg & 64)) fence_proxy_async();          // generic-proxy stores -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->a_full[sa]);
+                if (trp) KAD_TR(0, trc);
             }
-            iw += p.nchunks;
         }
     }
 
@@ -548,6 +638,8 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     p.b_stage_bytes = a.Cout * 128;
     p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
     p.fmt = a.dtype == KAD_BF16 ? 1 : 0;
+    { const char* e = getenv("KAD_DSC_TC_DEBUG"); p.dbg = e ? atoi(e) : 0; }
+    { const char* e = getenv("KAD_DSC_TC_TRACE"); p.trace = e ? (long long*)strtoull(e, nullptr, 16) : nullptr; }
 
     // shared-memory carve-up (offsets from a 1024-byte aligned base)
     SmemLayout L{};
@@ -596,18 +688,13 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int grid = p.ntiles < sms ? p.ntiles : sms;
-    cudaError_t e;
-    if (a.dtype == KAD_F16) {
-        auto kern = dsc_tc_kernel<__half>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_tc smem attribute (%zu bytes): %s", smem, cudaGetErrorString(e));
-        kern<<<grid, NTHREADS_TC, smem, st>>>(map_x, map_w, p, L);
-    } else {
-        auto kern = dsc_tc_kernel<__nv_bfloat16>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_tc smem attribute (%zu bytes): %s", smem, cudaGetErrorString(e));
-        kern<<<grid, NTHREADS_TC, smem, st>>>(map_x, map_w, p, L);
-    }
+    const bool affine = a.scale || a.shift || a.post || a.act != KAD_ACT_NONE;
+    void (*kern)(const CUtensorMap, const CUtensorMap, const TcParams, const SmemLayout);
+    if (a.dtype == KAD_F16) kern = affine ? dsc_tc_kernel<__half, true> : dsc_tc_kernel<__half, false>;
+    else kern = affine ? dsc_tc_kernel<__nv_bfloat16, true> : dsc_tc_kernel<__nv_bfloat16, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_tc smem attribute (%zu bytes): %s", smem, cudaGetErrorString(e));
+    kern<<<grid, NTHREADS_TC, smem, st>>>(map_x, map_w, p, L);
     KAD_CHECK_LAUNCH("dsc_tc_kernel");
     return KAD_OK;
 }
