@@ -241,6 +241,131 @@ def run_c1(args, rank, world, local):
     return res
 
 
+
+# ------------------------------------------------------------------------------------------- C4
+C4 = dict(images=64, H=800, W=800, mb=8, conf=0.001, iou=0.65, max_det=300)
+C4_GFLOP_PER_IMAGE = 38.9          # 2*MAC of the fused model at 800x800 (72 % 3x3 conv, 22 % 1x1 conv, 1.9 % DSC GEMM)
+C4_MIN_BYTES_PER_IMAGE = 0.35e9    # sum of conv inputs + outputs in fp16: the activation traffic floor
+
+
+def c4_images(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 256, (n, 3, C4['H'], C4['W']), dtype=torch.uint8, generator=g)
+
+
+def c4_cpu_sample(n_images=2):
+    """The plain PyTorch modules (what the reference's raw backend executes) + NMS, fp32, all host cores."""
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression
+    torch.set_num_threads(os.cpu_count() or 1)
+    model = kadcnet.load_model(None, 'raw', 'cpu', randomize=True, seed=0)
+    imgs = c4_images(n_images + 1)
+    with torch.no_grad():
+        non_max_suppression(model(imgs[:1].float() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])   # warm-up
+        t0 = time.perf_counter()
+        for i in range(1, n_images + 1):
+            non_max_suppression(model(imgs[i:i + 1].float() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])
+        dt = time.perf_counter() - t0
+    return n_images / dt, n_images, dt
+
+
+def run_c4(args, rank, world, local):
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression
+    from kadcnet.runtime import StaticGraph
+    from kadcnet.sharding import gather_detections, shard_range
+    from kadconv import _abi, ops
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    host_group = torch.distributed.new_group(backend='gloo') if world > 1 else None
+    fast = kadcnet.load_model(None, 'optimized', str(device), randomize=True, seed=0, dtype=torch.float16)
+    a, b = shard_range(C4['images'], rank, world)
+    n_local = b - a
+    host = c4_images(C4['images'])[a:b].pin_memory()
+    dev = host.to(device)
+    mb = min(C4['mb'], n_local)
+    stream = torch.cuda.current_stream()
+
+    def forward(u8):
+        return fast(u8.to(torch.float16).div_(255.0))[0]
+
+    k0 = _abi.KERNELS_LAUNCHED[0]
+    forward(dev[:mb])
+    kernels_per_mb = _abi.KERNELS_LAUNCHED[0] - k0
+    graphs = {}
+
+    def run_mb(u8):
+        n = u8.shape[0]
+        if n not in graphs:
+            graphs[n] = StaticGraph(forward, u8)
+        y = graphs[n](u8, clone=False)
+        return non_max_suppression(y, C4['conf'], C4['iou'], max_det=C4['max_det'])
+
+    def step(src, to_host):
+        dets = []
+        for i in range(0, n_local, mb):
+            u8 = src[i:i + mb]
+            if not u8.is_cuda:
+                u8 = u8.to(device, non_blocking=True)
+            d = run_mb(u8)
+            dets.extend([t.cpu() for t in d] if to_host else d)
+        return dets
+
+    for _ in range(max(args.warmup, 3)):
+        dets = step(dev, False)
+    torch.cuda.synchronize(); ops.check_status(device)
+    n_det = sum(t.shape[0] for t in dets)
+    sampler = ClockSampler(local); sampler.start()
+    barrier(world); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step(dev, False)
+    e1.record(stream)
+    torch.cuda.synchronize(); barrier(world)
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(e0.elapsed_time(e1), world, device)
+    # forward-only time of one mini-batch graph (for the roofline line)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for _ in range(5):
+        graphs[mb](dev[:mb], clone=False)
+    g1.record(stream); torch.cuda.synchronize()
+    fwd_ms = g0.elapsed_time(g1) / 5
+
+    n_e2e = max(2, min(args.steps, 5))
+    step(host, True)
+    torch.cuda.synchronize(); barrier(world)
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(n_e2e):
+        dets_host = step(host, True)
+    f1.record(stream)
+    torch.cuda.synchronize(); barrier(world)
+    e2e_ms = max_over_ranks(f0.elapsed_time(f1), world, device) / n_e2e
+    ops.check_status(device)
+    all_d = gather_detections(dets_host, rank, world, group=host_group)     # final host gather to rank 0
+    n_total = sum(t.shape[0] for t in all_d) if rank == 0 else None
+    pk = peaks()
+    ips_fwd = mb / (fwd_ms * 1e-3)
+    return {
+        'metric': 'KAD-CNet-S 800x800 images/s', 'value': C4['images'] * args.steps / (ms_total * 1e-3), 'unit': 'images/s',
+        'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_total / args.steps,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
+        'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 64 uint8 3x800x800 images per step '
+                               'sharded by batch over the ranks, backbone + neck + head + decode + NMS (conf 0.001, IoU 0.65, max_det 300)',
+                   'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
+                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape; NMS eager'},
+        'roofline': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+                     'frac': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9 / pk['hbm_gbs'], 'traffic': None, 'peak_source': pk['_source'],
+                     'kernel': 'whole forward graph (minimum activation traffic 0.35 GB/image, fp16)',
+                     'forward_ms_per_mini_batch': fwd_ms, 'tensor_frac': ips_fwd * C4_GFLOP_PER_IMAGE / 1e3 / pk['bf16_tflops_sustained']},
+        'e2e': {'value': C4['images'] / (e2e_ms * 1e-3), 'unit': 'images/s', 'h2d_bytes_per_step': host.numel(),
+                'd2h_bytes_per_step': int(sum(t.numel() * 4 for t in dets_host)), 'ms_per_step': e2e_ms},
+        'gpu_launches': args.steps * (n_local // mb) * kernels_per_mb, 'own_kernels_per_mini_batch': kernels_per_mb,
+        'clocks': clocks,
+    }
+
 # ------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -248,7 +373,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c1', choices=['c1'])
+    ap.add_argument('--workload', default='c1', choices=['c1', 'c4'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     args = ap.parse_args()
     rank, world, local = dist_setup(args.gpus)
@@ -274,10 +399,17 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline')
-    res = run_c1(args, rank, world, local)
+    res = run_c4(args, rank, world, local) if args.workload == 'c4' else run_c1(args, rank, world, local)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             model, cores = cpu_info()
+            if args.workload == 'c4':
+                ips, n, dt = c4_cpu_sample()
+                res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                                       'sample': f'{n} images 3x800x800 in {dt:.1f} s, fp32 plain PyTorch modules + torchvision deform_conv2d + NMS',
+                                       'cpu': model, 'os_cpu_count': cores}
+                print(json.dumps(res))
+                return
             ips, n, dt = c1_cpu_sample()
             res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                                    'sample': f'{n} of the 16 c1 feature maps in {dt:.1f} s, fp32, torchvision.ops.deform_conv2d (the call DSC.forward makes)',

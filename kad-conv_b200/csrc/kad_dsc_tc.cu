@@ -312,7 +312,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     for (int k = 0; k < nk; ++k)
                         umma_f16(tacc, smem_desc_sw128(aaddr + k * 32), smem_desc_sw128(baddr + k * 32), idesc, (s | k) ? 1u : 0u);
                     umma_commit(&bars->a_empty[sa]);
-                    umma_commit(&bars->b_empty[sb]);
+                    if (!(p.dbg & 128)) umma_commit(&bars->b_empty[sb]);
                     if (s == p.stages - 1) umma_commit(&bars->acc_full[buf]);
                 }
                 __syncwarp();

@@ -76,12 +76,14 @@ def _state_dict_from(checkpoint, key):
 
 
 def load_model(weights=None, backend='raw', device='cuda:0', config=None, fuse=True, checkpoint_key='auto',
-               dtype=torch.float16, seed=0, state_dict=None):
+               dtype=torch.float16, seed=0, state_dict=None, randomize=False):
     if backend not in {'raw', 'optimized', 'graph'}:
         raise ValueError(backend)
     numerical_protocol()
     torch.manual_seed(seed)
     model = DetectionModel(config)
+    if state_dict is None and weights is None and randomize:
+        randomize_for_benchmark(model, seed)
     if state_dict is not None:
         model.load_state_dict(state_dict)
     elif weights is not None:
@@ -101,3 +103,27 @@ def load_model(weights=None, backend='raw', device='cuda:0', config=None, fuse=T
     if backend == 'graph':
         fast.forward = graph_forward(fast.forward)
     return fast
+
+
+def randomize_for_benchmark(model, seed=0, offset_std=0.5, cls_bias=-3.0, cls_gain=60.0):
+    """Seeded synthetic weights for a model without a checkpoint. The stock initialisation is degenerate for
+    inference measurements: zero offset convolutions (no deformation), identity BatchNorm statistics, and class
+    biases so low that NMS receives no candidate. This redraws those tensors in place (call before fuse())."""
+    g = torch.Generator().manual_seed(seed)
+    head = model.model[-1]
+    with torch.no_grad():
+        for name, m in model.named_modules():
+            if isinstance(m, torch.nn.BatchNorm2d):
+                m.running_mean.copy_(torch.randn(m.running_mean.shape, generator=g) * 0.1)
+                m.running_var.copy_(torch.rand(m.running_var.shape, generator=g) + 0.5)
+                m.weight.copy_(torch.rand(m.weight.shape, generator=g) + 0.5)
+                m.bias.copy_(torch.randn(m.bias.shape, generator=g) * 0.1)
+            elif name.endswith('conv_offset'):
+                fan_in = m.weight[0].numel()
+                m.weight.copy_(torch.randn(m.weight.shape, generator=g) * (offset_std / fan_in ** 0.5))
+                m.bias.copy_(torch.randn(m.bias.shape, generator=g) * (0.1 * offset_std))
+        for seq in head.cv3:
+            last = seq[-1]
+            last.weight.mul_(cls_gain)
+            last.bias.copy_(torch.randn(last.bias.shape, generator=g) * 0.1 + cls_bias)
+    return model

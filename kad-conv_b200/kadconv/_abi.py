@@ -82,7 +82,13 @@ def load():
     return lib
 
 
+# Number of kernels launched through this binding so far (a plain counter the benchmark reads).
+KERNELS_LAUNCHED = [0]
+_KERNELS_PER_CALL = {'kad_lcsa_sums': 2, 'kad_lcsa_mask': 2}
+
+
 def check(code, what):
+    KERNELS_LAUNCHED[0] += _KERNELS_PER_CALL.get(what, 1)
     if code != 0:
         msg = load().kad_last_error_string().decode(errors='replace')
         raise RuntimeError(f'{what} failed ({code}): {msg}')

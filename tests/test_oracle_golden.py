@@ -77,3 +77,23 @@ def test_detector_matches_reference_fixture(golden_dir):
     gd = torch.from_numpy(g['det'])
     assert det.shape == gd.shape and gd.shape[0] > 10
     assert torch.equal(det, gd)     # same boxes, same order, bit for bit
+
+
+def test_c_restatement_matches_fixture(golden_dir):
+    """The plain-C deformable convolution (oracle/dsc_oracle.c) against the torchvision-made fixture."""
+    import ctypes
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    subprocess.run(['make', '-s', '-C', str(root / 'oracle')], check=True)
+    lib = ctypes.CDLL(str(root / 'oracle' / '_build' / 'libkad_oracle.so'))
+    g = np.load(golden_dir / 'dcn_op.npz')
+    a = {k: np.ascontiguousarray(g[k], dtype=np.float32) for k in g.files}
+    B, Cin, H, W = a['x'].shape
+    Cout = a['weight'].shape[0]
+    y = np.zeros((B, Cout, H, W), dtype=np.float32)
+    P = ctypes.POINTER(ctypes.c_float)
+    ptr = lambda t: t.ctypes.data_as(P)
+    lib.kad_oracle_deform_conv3x3(ptr(a['x']), ptr(a['offset']), ptr(a['mask']), ptr(a['weight']), ptr(a['bias']), ptr(y),
+                                  B, Cin, Cout, H, W)
+    assert np.abs(y - a['y']).max() <= 2e-5
