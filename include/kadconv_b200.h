@@ -107,6 +107,23 @@ int kad_lcsa_mask(const float* rowsum, const float* colsum,
                   const float* w2, const float* b2, const float* w3, const float* b3,
                   float* scratch, void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
 
+/* LCSA step 2 without a scratch argument and without any allocation. No counterpart in the reference project: it
+ * exists for hosts that cannot create device memory where they call this library (a server whose own pool took all
+ * of HBM at start-up, or a frame loop that must avoid the device-wide synchronisation of cudaMalloc / cudaFree).
+ * The scratch kad_lcsa_mask() asks for lives in a fixed array inside the library's device image instead
+ * (kad_lcsa_mask_noalloc_max_floats() float32 values, 4 MiB, held by every GPU that loads the library until the
+ * process exits). Same arguments and result as kad_lcsa_mask minus `scratch`.
+ *   - (B+1)*W*C must not exceed kad_lcsa_mask_noalloc_max_floats(); larger problems get KAD_ERR_UNSUPPORTED.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call during start-up, before any stream capture begins on that device.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different streams) race on it.
+ *     Nothing needs clearing between calls; each call overwrites the part it reads. */
+size_t kad_lcsa_mask_noalloc_max_floats(void);
+int kad_lcsa_mask_noalloc(const float* rowsum, const float* colsum,
+                          const float* w1, const float* b1, const float* bn_scale, const float* bn_shift,
+                          const float* w2, const float* b2, const float* w3, const float* b3,
+                          void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
+
 /* SE excite from the DSC epilogue's per-tile sums: att[b,:] = sigmoid(W2 relu(W1 mean + b1) + b2).
  * Replaces y.mean((2,3)) and fc[i] in KADConv.forward (kad_conv.py:105-109,:117); native counterpart:
  * partial_gap_se_kernel (kadc_dcn16_kernel.cu:499-556).

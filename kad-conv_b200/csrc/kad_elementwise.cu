@@ -1,5 +1,7 @@
 // Bandwidth-bound kernels of the KAD-Conv path: layout conversion, the LCSA mask branch, the SE
 // squeeze / excite / rescale, and the upsample + concat + residual tail. All NHWC, fp32 arithmetic.
+#include <mutex>
+
 #include "kad_common.cuh"
 
 namespace kad {
@@ -389,4 +391,53 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     });
     KAD_CHECK_LAUNCH("merge_kernel");
     return KAD_OK;
+}
+
+
+// ------------------------------------------------------------------------------ allocation-free LCSA mask
+// Some hosts of this library may not create device memory on their frame path: an inference server that handed
+// the whole HBM to its own pool at start-up has nothing left for cudaMalloc to return, and a latency-bound loop
+// cannot afford the device-wide synchronisation that cudaMalloc / cudaFree imply. kad_lcsa_mask() asks such a
+// caller for a scratch buffer it may not be able to produce; this variant keeps the scratch inside the library
+// image instead: a fixed array in device memory that every GPU loading the library holds until the process exits.
+namespace {
+constexpr size_t LCSA_STATIC_FLOATS = (size_t)1 << 20;                 // 4 MiB of float32 per device
+static __device__ __align__(256) float g_lcsa_scratch[LCSA_STATIC_FLOATS];
+constexpr int MAX_DEVICES = 64;
+float* g_lcsa_scratch_ptr[MAX_DEVICES] = {};                           // device address of the array, per device
+std::mutex g_lcsa_scratch_mutex;
+}  // namespace
+
+extern "C" size_t kad_lcsa_mask_noalloc_max_floats(void) { return LCSA_STATIC_FLOATS; }
+
+extern "C" int kad_lcsa_mask_noalloc(const float* rowsum, const float* colsum,
+                                     const float* w1, const float* b1, const float* bn_scale, const float* bn_shift,
+                                     const float* w2, const float* b2, const float* w3, const float* b3,
+                                     void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream) {
+    KAD_CHECK_ARG(B > 0 && H > 0 && W > 0 && C > 0, "kad_lcsa_mask_noalloc: bad shape");
+    const size_t need = ((size_t)B + 1) * (size_t)W * (size_t)C;
+    if (need > LCSA_STATIC_FLOATS)
+        return fail(KAD_ERR_UNSUPPORTED, "kad_lcsa_mask_noalloc: (B+1)*W*C = %zu floats exceeds the built-in scratch of %zu floats; "
+                    "use kad_lcsa_mask with a caller-provided scratch buffer", need, (size_t)LCSA_STATIC_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_lcsa_mask_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    KAD_CHECK_ARG(dev >= 0 && dev < MAX_DEVICES, "kad_lcsa_mask_noalloc: device index %d out of range", dev);
+    float* scratch = nullptr;
+    {
+        // First call on this device: resolve the array's DEVICE address. In host code the symbol itself is only a
+        // host-side handle, not something a kernel can dereference, so the address must come from the runtime,
+        // queried while this device is current.
+        std::lock_guard<std::mutex> lock(g_lcsa_scratch_mutex);
+        if (!g_lcsa_scratch_ptr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_lcsa_scratch);
+            if (e != cudaSuccess || !p)
+                return fail(KAD_ERR_CUDA, "kad_lcsa_mask_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_lcsa_scratch_ptr[dev] = static_cast<float*>(p);
+        }
+        scratch = g_lcsa_scratch_ptr[dev];
+    }
+    // Every element of scratch[0, need) is overwritten before it is read, so stale contents of an earlier call are harmless.
+    return kad_lcsa_mask(rowsum, colsum, w1, b1, bn_scale, bn_shift, w2, b2, w3, b3, scratch, mask, B, H, W, C, mask_f32, dtype, stream);
 }

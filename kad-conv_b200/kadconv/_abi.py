@@ -45,6 +45,8 @@ SIGNATURES = {
                                  c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask': (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_lcsa_mask_noalloc_max_floats': (c_size_t, []),
+    'kad_lcsa_mask_noalloc': (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_se_excite': (c_int, [c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_void_p]),
     'kad_se_squeeze_tiles': (c_int, [c_int, c_int]),
