@@ -204,17 +204,17 @@ def run_c1(args, rank, world, local):
                              mask=hm.to(device, non_blocking=True))
         out_host.copy_(y, non_blocking=True)
 
-    for i in range(2):
+    n_e2e = 0 if args.profile else max(2, min(args.steps, 10))
+    for i in range(2 if n_e2e else 0):
         e2e_step(i)
     torch.cuda.synchronize(); barrier(world)
-    n_e2e = max(2, min(args.steps, 10))
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record(stream)
     for i in range(n_e2e):
         e2e_step(i)
     f1.record(stream)
     torch.cuda.synchronize(); barrier(world)
-    e2e_ms = max_over_ranks(f0.elapsed_time(f1), world, device) / n_e2e
+    e2e_ms = max_over_ranks(f0.elapsed_time(f1), world, device) / max(n_e2e, 1)
     ops.check_status(device)
     h2d = sum(t.numel() * t.element_size() for t in sets[0]['host'])
     d2h = out_host.numel() * out_host.element_size()
@@ -233,8 +233,8 @@ def run_c1(args, rank, world, local):
                      'frac': achieved / pk['bf16_tflops'], 'traffic': NCU_TRAFFIC['c1'], 'peak_source': pk['_source'] + ' (burst)',
                      'kernel': 'dsc_tc_kernel', 'flops_per_launch': C1_FLOPS, 'algorithmic_bytes': C1_BYTES,
                      'hbm_frac_of_peak': C1_BYTES / (kern_ms * 1e-3) / 1e9 / pk['hbm_gbs']},
-        'e2e': {'value': world * C1['B'] / (e2e_ms * 1e-3), 'unit': 'images/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
-                'ms_per_step': e2e_ms},
+        'e2e': None if args.profile else {'value': world * C1['B'] / (e2e_ms * 1e-3), 'unit': 'images/s', 'h2d_bytes_per_step': h2d,
+                                           'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms},
         'gpu_launches': args.steps * 1,
         'clocks': clocks,
     }
@@ -271,7 +271,7 @@ def c4_cpu_sample(n_images=2):
 
 def run_c4(args, rank, world, local):
     import kadcnet
-    from kadcnet.postprocess import non_max_suppression
+    from kadcnet.postprocess import non_max_suppression_device as non_max_suppression
     from kadcnet.runtime import StaticGraph
     from kadcnet.sharding import gather_detections, shard_range
     from kadconv import _abi, ops
@@ -283,7 +283,9 @@ def run_c4(args, rank, world, local):
     n_local = b - a
     host = c4_images(C4['images'])[a:b].pin_memory()
     dev = host.to(device)
-    mb = min(C4['mb'], n_local)
+    mb = max(1, min(args.mini_batch, n_local))
+    while n_local % mb:
+        mb -= 1
     stream = torch.cuda.current_stream()
 
     def forward(u8):
@@ -292,6 +294,15 @@ def run_c4(args, rank, world, local):
     k0 = _abi.KERNELS_LAUNCHED[0]
     forward(dev[:mb])
     kernels_per_mb = _abi.KERNELS_LAUNCHED[0] - k0
+    if args.profile:
+        # short eager run for a profiler's launch list: one warm mini-batch, then one forward + NMS under an NVTX-free region
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record(); d = non_max_suppression(forward(dev[:mb]), C4['conf'], C4['iou'], max_det=C4['max_det']); t1.record()
+        torch.cuda.synchronize()
+        return {'metric': 'KAD-CNet-S 800x800 images/s', 'value': mb / (t0.elapsed_time(t1) * 1e-3), 'unit': 'images/s', 'n_gpus': world,
+                'config': {'workload': f'c4 profile run: one eager mini-batch of {mb} images'}, 'own_kernels_per_mini_batch': kernels_per_mb,
+                'e2e': None, 'gpu_launches': kernels_per_mb}
     graphs = {}
 
     def run_mb(u8):
@@ -355,7 +366,7 @@ def run_c4(args, rank, world, local):
         'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 64 uint8 3x800x800 images per step '
                                'sharded by batch over the ranks, backbone + neck + head + decode + NMS (conf 0.001, IoU 0.65, max_det 300)',
                    'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
-                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape; NMS eager'},
+                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)'},
         'roofline': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                      'frac': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9 / pk['hbm_gbs'], 'traffic': None, 'peak_source': pk['_source'],
                      'kernel': 'whole forward graph (minimum activation traffic 0.35 GB/image, fp16)',
@@ -366,6 +377,124 @@ def run_c4(args, rank, world, local):
         'clocks': clocks,
     }
 
+
+# ------------------------------------------------------------------------------------------- C2
+C2 = dict(B=16, C=128, H=200, W=200, Cout=256, se_hidden=16)
+
+
+class OpTimer:
+    """Wraps the kadconv.ops entry points with CUDA events so that a composite forward reports per-kernel-group times."""
+    NAMES = ['pool_project', 'lcsa_mask', 'dsc_forward', 'se_excite', 'merge_upsample_residual', 'se_squeeze', 'se_rescale',
+             'gemm1x1_bias_act', 'to_nhwc', 'to_nchw']
+
+    def __init__(self, ops):
+        self.ops, self.orig, self.events = ops, {}, []
+
+    def __enter__(self):
+        for n in self.NAMES:
+            f = getattr(self.ops, n)
+            self.orig[n] = f
+
+            def wrapped(*a, _f=f, _n=n, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); r = _f(*a, **k); e1.record()
+                self.events.append((_n, e0, e1))
+                return r
+            setattr(self.ops, n, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        for n, f in self.orig.items():
+            setattr(self.ops, n, f)
+
+    def totals(self):
+        torch.cuda.synchronize()
+        out = {}
+        for n, e0, e1 in self.events:
+            d = out.setdefault(n, [0, 0.0]); d[0] += 1; d[1] += e0.elapsed_time(e1)
+        return out
+
+
+def run_c2(args, rank, world, local):
+    import kadconv
+    import kadconv.fast as fast
+    from kadconv import _abi, ops
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    dt, s = torch.bfloat16, 2
+    B, C, H, W, Co, Hd = C2['B'], C2['C'], C2['H'], C2['W'], C2['Cout'], C2['se_hidden']
+    g = torch.Generator().manual_seed(0)
+    layer = kadconv.KADConv(C).eval()
+    with torch.no_grad():
+        for name, m in layer.named_modules():
+            if isinstance(m, torch.nn.BatchNorm2d):
+                m.running_mean.normal_(0, 0.1, generator=g); m.running_var.uniform_(0.5, 1.5, generator=g)
+                m.weight.uniform_(0.5, 1.5, generator=g); m.bias.normal_(0, 0.1, generator=g)
+            elif name.endswith('conv_offset'):
+                m.weight.normal_(0, 0.5 / m.weight[0].numel() ** 0.5, generator=g); m.bias.normal_(0, 0.05, generator=g)
+        for w in layer.weight:
+            w[0].weight.normal_(0, 1, generator=g)                 # branch scales ~ N(0,1)
+    layer = kadconv.enable_fast_inference(layer.to(device))
+    w11 = (torch.randn((Co, C), generator=g) / C ** 0.5).to(device); b11 = (0.1 * torch.randn(Co, generator=g)).to(device)
+    se = [t.to(device) for t in (torch.randn((Hd, Co), generator=g) / Co ** 0.5, 0.1 * torch.randn(Hd, generator=g),
+                                 torch.randn((Co, Hd), generator=g) / Hd ** 0.5, 0.1 * torch.randn(Co, generator=g))]
+    xs = [torch.randn((B, H, W, C), generator=g).to(device, dt) for _ in range(2)]     # NHWC, 164 MB each
+
+    def step(i):
+        y = fast.kadconv_forward_nhwc(layer, xs[i & 1])
+        z = ops.pool_project(y, w11, b11, pool=2, act=ops.ACT_SILU)                     # stride-2 pool + 1x1 GEMM + SiLU
+        att = ops.se_excite(ops.se_squeeze(z), (H // 2) * (W // 2), *se)
+        return ops.se_rescale(z, att)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize(); ops.check_status(device)
+    k0 = _abi.KERNELS_LAUNCHED[0]
+    sampler = ClockSampler(local); sampler.start()
+    barrier(world); torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize(); barrier(world)
+    clocks = sampler.stop()
+    launches = _abi.KERNELS_LAUNCHED[0] - k0
+    ms_total = max_over_ranks(e0.elapsed_time(e1), world, device)
+    with OpTimer(ops) as tm:
+        for i in range(4):
+            step(i)
+    tot = tm.totals()
+    pk = peaks()
+    px = B * H * W
+    widths = [C - (C // 3) * 2, C // 3, C // 3]
+    alg = {   # algorithmic bytes per step of each kernel group (formulas: DESIGN.md section 3)
+        'pool_project': sum(s * (px * C + (px >> (2 * i)) * c) for i, c in enumerate(widths)) + s * (px * C + (px // 4) * Co),
+        'lcsa_mask': sum((px >> (2 * i)) * (s * c + 4 * 9) for i, c in enumerate(widths)),
+        'dsc_forward': sum((px >> (2 * i)) * (s * (c + c) + 4 * 27) + (px >> (2 * i)) * (s * c + 4 * 18) for i, c in enumerate(widths)),
+        'merge_upsample_residual': 2 * s * px * C + sum(s * (px >> (2 * i)) * c for i, c in enumerate(widths)),
+        'se_squeeze': s * (px // 4) * Co, 'se_rescale': 2 * s * (px // 4) * Co, 'se_excite': 0,
+    }
+    stages = []
+    for n, (cnt, ms) in sorted(tot.items(), key=lambda kv: -kv[1][1]):
+        us = ms * 1e3 / 4
+        gbs = alg.get(n, 0) / (us * 1e-6) / 1e9 if us > 0 else 0.0
+        stages.append({'op': n, 'calls_per_step': cnt // 4, 'us_per_step': us, 'algorithmic_MB': alg.get(n, 0) / 1e6, 'GB_per_s': gbs,
+                       'frac_of_hbm_peak': gbs / pk['hbm_gbs']})
+    top = stages[0]
+    return {
+        'metric': 'KAD-Conv downsampling composition (bf16) feature maps/s', 'value': world * B * args.steps / (ms_total * 1e-3), 'unit': 'images/s',
+        'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_total / args.steps, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': 'c2: x[16,128,200,200] bf16 -> KADConv(128) (branch scales N(0,1)) -> avg-pool 2 + 1x1 GEMM 128->256 + SiLU -> SE (hidden 16) '
+                               '-> rescale; a composition of reference classes (no such module exists in the reference)',
+                   'l2': 'two 164 MB inputs alternated', 'layout': 'NHWC'},
+        'roofline': {'bound': 'hbm', 'achieved': top['GB_per_s'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s', 'frac': top['frac_of_hbm_peak'],
+                     'traffic': None, 'kernel': top['op'], 'peak_source': pk['_source']},
+        'stages': stages, 'e2e': None, 'gpu_launches': launches, 'clocks': clocks,
+    }
+
 # ------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -373,8 +502,10 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c1', choices=['c1', 'c4'])
+    ap.add_argument('--workload', default='c1', choices=['c1', 'c2', 'c4'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--mini-batch', type=int, default=16, help='c4: images per forward graph')
+    ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
     args = ap.parse_args()
     rank, world, local = dist_setup(args.gpus)
 
@@ -399,10 +530,13 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline')
-    res = run_c4(args, rank, world, local) if args.workload == 'c4' else run_c1(args, rank, world, local)
+    res = {'c1': run_c1, 'c2': run_c2, 'c4': run_c4}[args.workload](args, rank, world, local)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
             model, cores = cpu_info()
+            if args.workload == 'c2':
+                print(json.dumps(res))
+                return
             if args.workload == 'c4':
                 ips, n, dt = c4_cpu_sample()
                 res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',

@@ -58,7 +58,7 @@ int kad_nhwc_to_nchw(const void* src, void* dst, int B, int C, int H, int W, int
  *   act     KAD_ACT_*
  *   y       [B,H,W,Cout] float32 if y_f32 else dtype
  *   gap_partial  NULL, or float32 [B][gap_tiles][Cout]: per-tile sums of y over pixels, in a fixed order
- *                (deterministic); gap_tiles = kad_dsc_gap_tiles(H, W, path).
+ *                (deterministic); gap_tiles = kad_dsc_gap_tiles(H, W, Cin, Cout, path).
  */
 typedef struct KadDscArgs {
     const void* x; const void* offset; const void* mask; const void* weight;
@@ -70,7 +70,7 @@ typedef struct KadDscArgs {
     int* status;         /* device int[4], zeroed by the caller; the tensor path records a wait that gave up here */
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);
-int kad_dsc_gap_tiles(int H, int W, int path);
+int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path);
 /* 1 if the tcgen05 path can run this shape: dtype f16/bf16, Cin % 32 == 0, Cout % 16 == 0, Cout <= 256. */
 int kad_dsc_tc_supported(int Cin, int Cout, int dtype);
 /* Packs W[Cout][Cin][3][3] (float32, the layout of DSC.weight) into the tensor path's K-major
@@ -150,6 +150,17 @@ typedef struct KadMergeArgs {
     int B, H, W, C, dtype;
 } KadMergeArgs;
 int kad_merge_upsample_residual(const KadMergeArgs* args, void* stream);
+
+/* Batched detection post-processing, one launch for the whole batch. Replaces non_max_suppression
+ * (KAD-CNet/utils/general.py:881-990: confidence filter, xywh->xyxy, best class, sort by confidence, class-shifted
+ * torchvision.ops.nms at :972, max_det cap) for multi_label = False, agnostic = False.
+ *   pred   [B][4+nc][A] dtype: rows 0-3 = cx, cy, w, h in pixels, rows 4.. = class scores (DDetect's y)
+ *   dets   float32 [B][max_det][6]: x1, y1, x2, y2, confidence, class, in decreasing confidence; counts int32 [B]
+ *   A <= kad_nms_max_anchors() (the sort runs in shared memory), max_det <= 1024; max_wh is the per-class shift (7680).
+ * Equal scores keep the lower anchor index first, so the result is deterministic. */
+int kad_nms_max_anchors(void);
+int kad_nms_batched(const void* pred, int B, int nc, int A, float conf_thres, float iou_thres, int max_det,
+                    float max_wh, float* dets, int* counts, int dtype, void* stream);
 
 /* 1x1 convolution as a tcgen05 GEMM with bias and activation, TMA-fed operands:
  *   y[m, n] = act( sum_k x[m, k] * w[n, k] + bias[n] ),  m over B*H*W pixels.

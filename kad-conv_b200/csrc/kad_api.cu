@@ -21,7 +21,7 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-int dsc_simt_tiles(int H, int W);
+int dsc_simt_tiles(int H, int W, int Cin, int Cout);
 int launch_dsc_simt(const KadDscArgs& a, cudaStream_t st);
 int dsc_tc_tiles(int H, int W);
 int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st);
@@ -34,9 +34,9 @@ extern "C" int kad_version(void) { return 100; }
 
 extern "C" const char* kad_last_error_string(void) { return last_error().c_str(); }
 
-extern "C" int kad_dsc_gap_tiles(int H, int W, int path) {
-    if (H <= 0 || W <= 0) return 0;
-    return path == 1 ? dsc_tc_tiles(H, W) : dsc_simt_tiles(H, W);
+extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {
+    if (H <= 0 || W <= 0 || Cin <= 0 || Cout <= 0) return 0;
+    return path == 1 ? dsc_tc_tiles(H, W) : dsc_simt_tiles(H, W, Cin, Cout);
 }
 
 extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {

@@ -50,7 +50,7 @@ using namespace sm100;
 
 constexpr int BM = 128;                 // rows (pixels) per tile
 constexpr int UNIT = 32;                // channels per K unit
-constexpr int NA = 3;                   // A stages
+constexpr int NA_MAX = 4;               // A stages: 3 for one CTA per tile pair, 4 for the CTA-pair kernel
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int WIN_PX_MAX = 704;         // pixels per window buffer
 constexpr int WIN_BYTES = WIN_PX_MAX * 64;
@@ -70,7 +70,8 @@ struct TcParams {
     int th, tw, tiles_x, tiles_y, ntiles;       // tile rectangle and tile counts (per image: tiles_x*tiles_y)
     int halo, wh, ww;                           // window geometry
     int units, stages, nchunks;                 // K structure
-    int nb, b_stage_bytes;                      // B ring
+    int na, nb, b_stage_bytes;                  // A and B rings
+    int npairs;                                 // CTA-pair kernel: number of tile pairs
     int offset_f32, mask_f32, y_f32, act, fmt;
     int dbg;
     long long* trace;
@@ -82,7 +83,8 @@ struct SmemLayout {
 
 // Barrier indices inside the barrier block.
 struct Bars {
-    uint64_t a_full[NA], a_empty[NA];
+    uint64_t a_full[NA_MAX], a_empty[NA_MAX];
+    uint64_t peer_full[NA_MAX], peer_acc[2];   // CTA-pair kernel: the peer's stage / accumulator hand-offs to the leader
     uint64_t b_full[4], b_empty[4];
     uint64_t win_full[NWIN], win_empty[NWIN];
     uint64_t acc_full[2], acc_empty[2];
@@ -158,7 +160,7 @@ __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t parity, int l
 }
 
 // AFFINE: the epilogue applies scale/shift/activation/post; otherwise it only converts and stores.
-template <typename T, bool AFFINE>
+template <typename T, bool AFFINE, bool PAIR>
 __global__ void __launch_bounds__(NTHREADS_TC, 1)
 dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const TcParams p, const SmemLayout L) {
@@ -168,9 +170,19 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     volatile int* abort_flag = &bars->abort_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = p.tiles_x * p.tiles_y;
+    const uint32_t NA = (uint32_t)p.na;
+    // Tile schedule. One CTA per SM: CTA c takes tiles c, c + grid, ... In the CTA-pair kernel the two CTAs of cluster q
+    // take tiles 2k and 2k+1 of pair k = q, q + clusters, ...; the last pair may hold one tile past the end, which is
+    // produced as zeros and not stored.
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int sched0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, sched_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int sched_n = PAIR ? p.npairs : p.ntiles;
+    const int niter = sched0 < sched_n ? (sched_n - sched0 + sched_step - 1) / sched_step : 0;
+    auto tile_at = [&](int it_) { const int k = sched0 + it_ * sched_step; return PAIR ? 2 * k + (int)rank : k; };
 
     if (tid == 0) {
-        for (int i = 0; i < NA; ++i) { mbar_init(&bars->a_full[i], GROUP_WARPS); mbar_init(&bars->a_empty[i], 1); }
+        for (int i = 0; i < NA_MAX; ++i) { mbar_init(&bars->a_full[i], GROUP_WARPS); mbar_init(&bars->a_empty[i], 1); mbar_init(&bars->peer_full[i], 1); }
+        for (int i = 0; i < 2; ++i) mbar_init(&bars->peer_acc[i], 1);
         for (int i = 0; i < 4; ++i) { mbar_init(&bars->b_full[i], 1); mbar_init(&bars->b_empty[i], 1); }
         for (int i = 0; i < NWIN; ++i) { mbar_init(&bars->win_full[i], 1); mbar_init(&bars->win_empty[i], PROD_WARPS); }
         for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], EPI_WARPS * 32); }
@@ -179,7 +191,10 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         bars->abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == WARP_MMA) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+    if (warp == WARP_MMA) {
+        if (PAIR) { tmem_alloc_pair(&bars->tmem_base, 512); tmem_relinquish_pair(); }
+        else { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+    }
     // epilogue parameters: scale | shift | post, float[256] each
     float* epi = reinterpret_cast<float*>(smem + L.epi);
     for (int i = tid; i < 256; i += NTHREADS_TC) {
@@ -190,6 +205,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();     // the peer's barriers exist before anything arrives on them remotely
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
@@ -198,7 +214,10 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         float* gsum = epi + 768;   // [4 warps][256] column sums for the SE squeeze
         int it = 0;
         int etr = 0;
-        for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
+        for (; it < niter; ++it) {
+            const int tile_raw = tile_at(it);
+            const bool tile_ok = tile_raw < p.ntiles;
+            const int tile = tile_ok ? tile_raw : p.ntiles - 1;
             const int buf = it & 1;
             if (tid == 0) KAD_TR(2, etr);
             if (!mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag)) { report(p.status, 1, it); break; }
@@ -209,7 +228,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             const int r = warp * 32 + lane;
             const int ry = r / p.tw, rx = r - ry * p.tw;
             const int py = ty0 + ry, px = tx0 + rx;
-            const bool live = (r < p.th * p.tw) && py < p.H && px < p.W;
+            const bool live = tile_ok && (r < p.th * p.tw) && py < p.H && px < p.W;
             const size_t obase = (((size_t)b * p.H + py) * p.W + px) * p.N;
             for (int c0 = 0; c0 < p.N; c0 += 32) {
                 const int nc = min(32, p.N - c0);   // 32 or 16
@@ -274,7 +293,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[buf]);
             if (tid == 0) KAD_TR(2, etr);
-            if (p.gap_partial) {
+            if (p.gap_partial && tile_ok) {
                 if (!group_sync(&bars->gap_ready, it & 1, lane, abort_flag)) { report(p.status, 10, it); break; }
                 for (int c = tid; c < p.N; c += EPI_WARPS * 32)
                     p.gap_partial[((size_t)b * tiles_per_img + tr) * p.N + c] =
@@ -284,37 +303,63 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
     } else if (warp == WARP_MMA) {
         // =========================================================================== MMA issuer
-        const uint32_t idesc = instr_desc_f16(p.fmt, p.N);
-        const uint32_t a_base = smem_u32(smem + L.a), b_base = smem_u32(smem + L.b);
-        int it = 0;
-        uint32_t ia = 0;            // stage counter, shared numbering of the A and B rings
+        // This warp's instruction stream is one dependent chain per stage (nothing else hides its latency), so the loop
+        // keeps ring slots and phases in wrapping counters (no divisions) and the operand descriptors precomputed.
+        const uint32_t idesc = PAIR ? instr_desc_f16_pair(p.fmt, p.N) : instr_desc_f16(p.fmt, p.N);
+        const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem + L.a)), bdesc0 = smem_desc_sw128(smem_u32(smem + L.b));
+        const uint32_t a_step = A_STAGE_BYTES >> 4, b_step = (uint32_t)p.b_stage_bytes >> 4;   // descriptor address units of 16 bytes
+        const uint32_t nbr = (uint32_t)p.nb;
+        uint32_t sa = 0, pa = 0, sb = 0, pb = 0;     // slot and phase parity of the A and B rings
         bool ok = true;
         int trc = 0;
-        for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+        for (int it = 0; it < niter && ok; ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { report(p.status, 2, it); break; }
+            if (PAIR) {
+                // the leader also needs the peer's accumulator buffer drained; the peer's MMA warp passes that on
+                if (rank == 1) { __syncwarp(); if (lane == 0) mbar_arrive_remote(&bars->peer_acc[buf], 0); }
+                else if (!mbar_wait_cluster(&bars->peer_acc[buf], (it >> 1) & 1, abort_flag)) { report(p.status, 14, it); break; }
+            }
             tc_fence_after();
             if (lane == 0) KAD_TR(1, trc);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * ACC_COLS);
-            for (int s = 0; s < p.stages; ++s, ++ia) {
-                const uint32_t sa = ia % NA, sb = ia % (uint32_t)p.nb;
-                // lane 0 waits for the A stage, lane 1 for the B stage: the two waits overlap
+            const int last = p.stages - 1;
+            const int nk_last = (p.units & 1) ? 2 : 4;   // a trailing single unit fills half a stage
+            for (int s = 0; s <= last; ++s) {
+                // lane 0 waits for the A stage, lane 1 for the B stage (lane 2: the peer's stage): the waits overlap
                 bool okw = true;
-                if (lane == 0 && !(p.dbg & 32)) okw = mbar_wait(&bars->a_full[sa], (ia / NA) & 1, abort_flag);
-                else if (lane == 1 && !(p.dbg & 2)) okw = mbar_wait(&bars->b_full[sb], (ia / (uint32_t)p.nb) & 1, abort_flag);
+                if (lane == 0 && !(p.dbg & 32)) okw = mbar_wait(&bars->a_full[sa], pa, abort_flag);
+                else if (lane == 1 && !(p.dbg & 2)) okw = mbar_wait(&bars->b_full[sb], pb, abort_flag);
+                else if (PAIR && lane == 2 && rank == 0) okw = mbar_wait_cluster(&bars->peer_full[sa], pa, abort_flag);
                 if (!__all_sync(0xffffffffu, okw)) { report(p.status, 3, s); ok = false; break; }
-                tc_fence_after();
+                // no tcgen05 fence here: the operands come through shared memory (mbarrier + proxy fence order them);
+                // only the accumulator hand-off above involves TMEM
                 if (lane == 0) KAD_TR(1, trc);
-                if (lane == 0) {
-                    const int nk = (2 * s + 1 < p.units) ? 4 : 2;   // a trailing single unit fills half a stage
-                    const uint32_t aaddr = a_base + sa * A_STAGE_BYTES, baddr = b_base + sb * p.b_stage_bytes;
-                    if (!(p.dbg & 4))
-                    for (int k = 0; k < nk; ++k)
-                        umma_f16(tacc, smem_desc_sw128(aaddr + k * 32), smem_desc_sw128(baddr + k * 32), idesc, (s | k) ? 1u : 0u);
-                    umma_commit(&bars->a_empty[sa]);
-                    if (!(p.dbg & 128)) umma_commit(&bars->b_empty[sb]);
-                    if (s == p.stages - 1) umma_commit(&bars->acc_full[buf]);
+                if (PAIR && rank == 1) {
+                    // peer CTA: its A and B halves of this stage are in place; tell the leader, which issues for both
+                    if (lane == 0) mbar_arrive_remote(&bars->peer_full[sa], 0);
+                } else if (lane == 0) {
+                    const uint64_t ad = adesc0 + (uint64_t)(sa * a_step), bd = bdesc0 + (uint64_t)(sb * b_step);
+                    const int nk = (s == last) ? nk_last : 4;
+                    if (!(p.dbg & 4)) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (k < nk) {
+                                if (PAIR) umma_f16_pair(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
+                                else umma_f16(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
+                            }
+                        }
+                    }
+                    if (PAIR) {
+                        umma_commit_pair(&bars->a_empty[sa]);
+                        if (s == last) umma_commit_pair(&bars->acc_full[buf]);
+                    } else {
+                        umma_commit(&bars->a_empty[sa]);
+                        if (s == last) umma_commit(&bars->acc_full[buf]);
+                    }
                 }
+                if (++sa == NA) { sa = 0; pa ^= 1; }
+                if (++sb == nbr) { sb = 0; pb ^= 1; }
                 __syncwarp();
             }
         }
@@ -322,14 +367,22 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         // =========================================================================== weights
         if (lane == 0 && !(p.dbg & 2)) {
             tma_prefetch_desc(&map_w);
-            uint32_t ib = 0;
+            uint32_t ib = 0, sb = 0;
+            uint32_t ja = 0, jp = 0;                  // ring slot / phase parity of the stage whose completion frees the slot
+            const uint32_t nbr = (uint32_t)p.nb;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
+            for (int it = 0; it < niter && ok; ++it) {
                 for (int s = 0; s < p.stages; ++s, ++ib) {
-                    const uint32_t sb = ib % (uint32_t)p.nb;
-                    if (!mbar_wait(&bars->b_empty[sb], ((ib / (uint32_t)p.nb) & 1) ^ 1, abort_flag)) { report(p.status, 5, s); ok = false; break; }
+                    if (ib >= nbr) {
+                        // The slot is free once the MMAs of stage j = ib - nb are done. That is the event the A ring's
+                        // a_empty[j % NA] barrier already records (one tcgen05.commit per stage serves both rings); with
+                        // nb <= NA that barrier cannot run a further phase ahead before this load is issued.
+                        if (!mbar_wait(&bars->a_empty[ja], jp, abort_flag)) { report(p.status, 5, s); ok = false; break; }
+                        if (++ja == NA) { ja = 0; jp ^= 1u; }
+                    }
                     mbar_arrive_expect_tx(&bars->b_full[sb], (uint32_t)p.b_stage_bytes);
-                    tma_load_2d(smem + L.b + sb * p.b_stage_bytes, &map_w, 0, s * p.N, &bars->b_full[sb]);
+                    tma_load_2d(smem + L.b + sb * p.b_stage_bytes, &map_w, 0, s * p.N + (PAIR ? (int)rank * (p.N >> 1) : 0), &bars->b_full[sb]);
+                    if (++sb == nbr) sb = 0;
                 }
             }
             if (!ok || *abort_flag) {   // let copies in flight land before the CTA goes away
@@ -346,7 +399,8 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             uint32_t iw = 0;
             bool ok = true;
             const uint32_t win_bytes = (uint32_t)(p.wh * p.ww * 64);
-            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
+            for (int it = 0; it < niter && ok; ++it) {
+                const int tile = min(tile_at(it), p.ntiles - 1);
                 const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
                 const int wy0 = (tr / p.tiles_x) * p.th - 1 - p.halo, wx0 = (tr % p.tiles_x) * p.tw - 1 - p.halo;
                 for (int cc = 0; cc < p.nchunks; ++cc, ++iw) {
@@ -395,7 +449,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             for (int i = 0; i < TAB_ITERS; ++i) {
                 const int e = ptid + i * PROD_WARPS * 32;
                 pf[i][0] = 0.f; pf[i][1] = 0.f; pf[i][2] = 1.f;
-                if (e < BM * 9 && tile_ < p.ntiles) {
+                if (e < BM * 9 && tile_ < p.ntiles && tile_ >= 0) {
                     const int r = e / 9, k = e - r * 9;
                     const int ry = r / p.tw, rx = r - ry * p.tw;
                     const int py = ty0_ + ry, px = tx0_ + rx;
@@ -410,9 +464,13 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
         bool ok = true;
         int it = 0;
+        uint32_t cur_ia = 0, sa = 0, pa = 0;          // stage counter of this group and its ring slot / phase parity
         int trc = 0; const bool trp = (pw == 0 && lane == 0);
-        prefetch(blockIdx.x);
-        for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+        prefetch(niter > 0 ? tile_at(0) : -1);
+        for (; it < niter && ok; ++it) {
+            const int tile_raw = tile_at(it);
+            const bool tile_ok = tile_raw < p.ntiles;
+            const int tile = tile_ok ? tile_raw : p.ntiles - 1;
             const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
             const int ty0 = (tr / p.tiles_x) * p.th, tx0 = (tr % p.tiles_x) * p.tw;
             const int wy0 = ty0 - 1 - p.halo, wx0 = tx0 - 1 - p.halo;
@@ -432,7 +490,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     const int py = ty0 + ry, px = tx0 + rx;
                     float w00 = 0.f, w01 = 0.f, w10 = 0.f, w11 = 0.f;
                     uint32_t word = 0, pos = 0;
-                    if (r < p.th * p.tw && py < p.H && px < p.W) {
+                    if (tile_ok && r < p.th * p.tw && py < p.H && px < p.W) {
                         const float sy = (float)(py + k / 3 - 1) + pf[i][0], sx = (float)(px + k % 3 - 1) + pf[i][1];
                         if (sy > -1.f && sy < (float)p.H && sx > -1.f && sx < (float)p.W) {
                             const float m = pf[i][2];
@@ -464,14 +522,17 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             if (trp) KAD_TR(0, trc);
             if (!group_sync(&bars->tab_ready, it & 1, lane, abort_flag)) { report(p.status, 13, it); break; }
             if (trp) KAD_TR(0, trc);
-            prefetch(tile + (int)gridDim.x);         // next tile's offsets and mask arrive while this tile is gathered
+            prefetch(it + 1 < niter ? tile_at(it + 1) : -1);   // next tile's offsets and mask arrive while this tile is gathered
 
             int have_cc = -1;                        // chunks whose window this thread has already waited for
             const uint32_t ia0 = (uint32_t)it * (uint32_t)p.stages, iw0 = (uint32_t)it * (uint32_t)p.nchunks;
             for (int s = grp; s < p.stages && ok; s += PROD_GROUPS) {
-                const uint32_t ia = ia0 + (uint32_t)s;
-                const uint32_t sa = ia % NA;
-                if (!mbar_wait(&bars->a_empty[sa], ((ia / NA) & 1) ^ 1, abort_flag)) { report(p.status, 7, s); ok = false; break; }
+                {   // move the ring position (slot sa, phase parity pa) forward to this stage without dividing
+                    const uint32_t target = ia0 + (uint32_t)s;
+                    sa += target - cur_ia; cur_ia = target;
+                    while (sa >= NA) { sa -= NA; pa ^= 1u; }
+                }
+                if (!mbar_wait(&bars->a_empty[sa], pa ^ 1u, abort_flag)) { report(p.status, 7, s); ok = false; break; }
                 if (trp) KAD_TR(0, trc);
                 const uint32_t a_stage = a_base + sa * A_STAGE_BYTES;
                 const int nu = (2 * s + 1 < p.units) ? 2 : 1;     // a trailing single unit is produced twice (harmless)
@@ -560,7 +621,8 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     // ------------------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (PAIR) cluster_sync_all();     // the leader's MMAs read the peer's shared memory: leave together
+    if (warp == WARP_MMA) { tc_fence_after(); if (PAIR) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512); }
     if (tid == 0 && *abort_flag) report(p.status, 9, 0);
 }
 
@@ -641,24 +703,32 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     { const char* e = getenv("KAD_DSC_TC_DEBUG"); p.dbg = e ? atoi(e) : 0; }
     { const char* e = getenv("KAD_DSC_TC_TRACE"); p.trace = e ? (long long*)strtoull(e, nullptr, 16) : nullptr; }
 
+    // One CTA per tile, or a CTA pair (cluster of 2, tcgen05 cta_group::2) per two tiles: the pair splits the weight
+    // operand by N between the two CTAs' shared memories, which halves the weight bytes every SM has to stage.
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    bool pair = a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2;
+    { const char* e = getenv("KAD_DSC_TC_PAIR"); if (e) pair = pair && atoi(e) != 0; }
+    p.npairs = (p.ntiles + 1) / 2;
+    p.na = pair ? 4 : 3;
+    p.b_stage_bytes = (pair ? a.Cout / 2 : a.Cout) * 128;      // multiple of 2048
+
     // shared-memory carve-up (offsets from a 1024-byte aligned base)
     SmemLayout L{};
     uint32_t off = 0;
-    L.a = off; off += NA * A_STAGE_BYTES;
+    L.a = off; off += p.na * A_STAGE_BYTES;
     L.b = off;
     uint32_t fixed_after = NWIN * WIN_BYTES + TABLE_BYTES + (768 + 1024) * 4 + 1024;
     int nb = (int)((SMEM_LIMIT - 1024 - (int)off - (int)fixed_after) / p.b_stage_bytes);
-    if (nb > 4) nb = 4;
+    if (nb > p.na) nb = p.na;   // the weight ring is released through the A ring's barriers, which needs nb <= na
     KAD_CHECK_ARG(nb >= 2, "kad_dsc_forward: no room for two weight stages");
     p.nb = nb;
-    off += nb * ((p.b_stage_bytes + 1023) & ~1023);
-    p.b_stage_bytes = a.Cout * 128;
+    off += nb * p.b_stage_bytes;
     L.win = off; off += NWIN * WIN_BYTES;
     L.table = off; off += TABLE_BYTES;
     L.epi = off; off += (768 + 1024) * 4;
     L.bars = off; off += 1024;
-    // B stages are placed at multiples of the 1024-aligned stage pitch
-    int b_pitch = (p.b_stage_bytes + 1023) & ~1023;
     size_t smem = off + 1024;   // slack for the runtime alignment of the dynamic segment
 
     // tensor maps
@@ -676,25 +746,48 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     {
         cuuint64_t dims[2] = {64, (cuuint64_t)p.stages * a.Cout};
         cuuint64_t strides[1] = {128};
-        cuuint32_t box[2] = {64, (cuuint32_t)a.Cout};
+        cuuint32_t box[2] = {64, (cuuint32_t)(pair ? a.Cout / 2 : a.Cout)};
         cuuint32_t es[2] = {1, 1};
         CUresult r = enc(&map_w, dt, 2, const_cast<void*>(a.weight), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(KAD_ERR_CUDA, "tensor map for the weights failed (CUresult %d)", (int)r);
     }
-    p.b_stage_bytes = b_pitch;   // ring pitch; the TMA box still transfers Cout*128 bytes
 
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = p.ntiles < sms ? p.ntiles : sms;
     const bool affine = a.scale || a.shift || a.post || a.act != KAD_ACT_NONE;
     void (*kern)(const CUtensorMap, const CUtensorMap, const TcParams, const SmemLayout);
-    if (a.dtype == KAD_F16) kern = affine ? dsc_tc_kernel<__half, true> : dsc_tc_kernel<__half, false>;
-    else kern = affine ? dsc_tc_kernel<__nv_bfloat16, true> : dsc_tc_kernel<__nv_bfloat16, false>;
+    if (a.dtype == KAD_F16) {
+        kern = pair ? (affine ? dsc_tc_kernel<__half, true, true> : dsc_tc_kernel<__half, false, true>)
+                    : (affine ? dsc_tc_kernel<__half, true, false> : dsc_tc_kernel<__half, false, false>);
+    } else {
+        kern = pair ? (affine ? dsc_tc_kernel<__nv_bfloat16, true, true> : dsc_tc_kernel<__nv_bfloat16, false, true>)
+                    : (affine ? dsc_tc_kernel<__nv_bfloat16, true, false> : dsc_tc_kernel<__nv_bfloat16, false, false>);
+    }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_tc smem attribute (%zu bytes): %s", smem, cudaGetErrorString(e));
-    kern<<<grid, NTHREADS_TC, smem, st>>>(map_x, map_w, p, L);
+    if (pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (sms / 2)); cfg.blockDim = dim3(NTHREADS_TC); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        // The schedule is static and every CTA needs a whole SM: launch only as many pairs as can be resident together
+        // (an SM whose partner is unavailable cannot host a pair), otherwise the excess pairs would run as a second wave.
+        static int resident_pairs[64][2] = {};
+        int& cached = resident_pairs[dev < 64 ? dev : 0][affine ? 1 : 0];
+        if (cached == 0) {
+            int n = 0;
+            cudaError_t eq = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+            cached = (eq == cudaSuccess && n > 0) ? n : sms / 2;
+        }
+        int clusters = p.npairs < cached ? p.npairs : cached;
+        cfg.gridDim = dim3(2 * clusters);
+        e = cudaLaunchKernelEx(&cfg, kern, map_x, map_w, p, L);
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_tc_kernel (CTA pair) launch: %s", cudaGetErrorString(e));
+    } else {
+        int grid = p.ntiles < sms ? p.ntiles : sms;
+        kern<<<grid, NTHREADS_TC, smem, st>>>(map_x, map_w, p, L);
+    }
     KAD_CHECK_LAUNCH("dsc_tc_kernel");
     return KAD_OK;
 }

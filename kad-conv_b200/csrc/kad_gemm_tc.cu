@@ -115,7 +115,6 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (int s = 0; s < p.ksteps; ++s, ++is) {
                 const int slot = (int)(is % GSTAGES);
                 if (!mbar_wait(&bars->full[slot], (uint32_t)((is / GSTAGES) & 1), abort_flag)) { greport(p.status, 3, s); ok = false; break; }
-                tc_fence_after();
                 if (lane == 0) {
                     const uint32_t aaddr = a_base + slot * G_A_BYTES, baddr = b_base + slot * p.b_stage_bytes;
                     // K beyond the tensor extent is zero-filled in both operands, so a full stage is always safe

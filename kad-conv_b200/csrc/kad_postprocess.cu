@@ -1,0 +1,159 @@
+// Batched detection post-processing on the device: per image, best class per anchor, confidence filter, sort by
+// confidence, class-aware greedy NMS and the max_det cap, in one kernel launch for the whole batch (one CTA per
+// image). Semantics follow non_max_suppression of the reference project (KAD-CNet/utils/general.py:881-990) in
+// the configuration its inference scripts use (multi_label off, agnostic off): boxes are shifted by class * max_wh
+// so that only boxes of the same class suppress each other; a box is dropped when its IoU with an already kept,
+// higher-scoring box exceeds the threshold; ties in score keep the lower anchor index first (deterministic).
+#include "kad_common.cuh"
+
+namespace kad {
+namespace {
+
+constexpr int NMS_THREADS = 1024;
+constexpr int NMS_MAX_ANCHORS = 16384;   // sort buffer in shared memory: 16384 x 8 bytes
+constexpr int NMS_CHUNK = 64;
+constexpr int NMS_MAX_DET = 1024;
+
+__device__ __forceinline__ bool iou_exceeds(const float4& a, const float4& b, float thr) {
+    const float left = fmaxf(a.x, b.x), right = fminf(a.z, b.z), top = fmaxf(a.y, b.y), bottom = fminf(a.w, b.w);
+    const float w = fmaxf(right - left, 0.f), h = fmaxf(bottom - top, 0.f);
+    const float inter = w * h;
+    const float sa = (a.z - a.x) * (a.w - a.y), sb = (b.z - b.x) * (b.w - b.y);
+    return inter / (sa + sb - inter) > thr;
+}
+
+// pred [B][4+nc][A]; dets [B][max_det][6]; counts [B]
+template <typename T>
+__global__ void __launch_bounds__(NMS_THREADS, 1)
+nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thres, float iou_thres, int max_det, float max_wh,
+           float* __restrict__ dets, int* __restrict__ counts) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw);          // [npow2] (ordered conf << 32) | ~index
+    float4* kept = reinterpret_cast<float4*>(keys + npow2);                              // [max_det] class-shifted boxes
+    float4* cbox = kept + max_det;                                                       // [64] shifted boxes of the chunk
+    float4* craw = cbox + NMS_CHUNK;                                                     // [64] boxes as reported
+    float2* cmeta = reinterpret_cast<float2*>(craw + NMS_CHUNK);                         // [64] (conf, class)
+    unsigned long long* cmask = reinterpret_cast<unsigned long long*>(cmeta + NMS_CHUNK);   // [64] intra-chunk suppression
+    unsigned int* csupp = reinterpret_cast<unsigned int*>(cmask + NMS_CHUNK);            // [64] suppressed by a kept box
+    __shared__ int s_ncand, s_nkept;
+
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const T* pb = pred + (size_t)b * (4 + nc) * A;
+    if (tid == 0) { s_ncand = 0; s_nkept = 0; }
+    __syncthreads();
+
+    // 1. best class score per anchor -> sortable key
+    int local = 0;
+    for (int a = tid; a < npow2; a += NMS_THREADS) {
+        unsigned long long key = 0ull;
+        if (a < A) {
+            float best = to_f<T>(pb[(size_t)4 * A + a]);
+            for (int c = 1; c < nc; ++c) best = fmaxf(best, to_f<T>(pb[(size_t)(4 + c) * A + a]));
+            if (best > conf_thres) {
+                unsigned int u = __float_as_uint(best);
+                u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                key = ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)a);
+                ++local;
+            }
+        }
+        keys[a] = key;
+    }
+    if (local) atomicAdd(&s_ncand, local);
+    __syncthreads();
+    const int ncand = s_ncand;
+
+    // 2. bitonic sort, descending
+    for (int k = 2; k <= npow2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < npow2; i += NMS_THREADS) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long x = keys[i], y = keys[ixj];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (x < y) : (x > y)) { keys[i] = y; keys[ixj] = x; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // 3. greedy NMS over chunks of 64 candidates in score order
+    float* out = dets + (size_t)b * max_det * 6;
+    for (int c0 = 0; c0 < ncand; c0 += NMS_CHUNK) {
+        if (s_nkept >= max_det) break;
+        const int nch = min(NMS_CHUNK, ncand - c0);
+        if (tid < NMS_CHUNK) {
+            cmask[tid] = 0ull;
+            csupp[tid] = tid < nch ? 0u : 1u;
+            if (tid < nch) {
+                const int a = (int)(0xFFFFFFFFu - (unsigned int)(keys[c0 + tid] & 0xFFFFFFFFull));
+                // box corners are formed in the storage type, as the reference does before it widens to float32
+                const float cx = to_f<T>(pb[a]), cy = to_f<T>(pb[(size_t)A + a]);
+                const float hw = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)2 * A + a]) * 0.5f)), hh = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)3 * A + a]) * 0.5f));
+                float4 r;
+                r.x = to_f<T>(from_f<T>(cx - hw)); r.y = to_f<T>(from_f<T>(cy - hh));
+                r.z = to_f<T>(from_f<T>(cx + hw)); r.w = to_f<T>(from_f<T>(cy + hh));
+                float best = to_f<T>(pb[(size_t)4 * A + a]); int cls = 0;
+                for (int c = 1; c < nc; ++c) { const float v = to_f<T>(pb[(size_t)(4 + c) * A + a]); if (v > best) { best = v; cls = c; } }
+                const float sh = (float)cls * max_wh;
+                craw[tid] = r;
+                cbox[tid] = make_float4(r.x + sh, r.y + sh, r.z + sh, r.w + sh);
+                cmeta[tid] = make_float2(best, (float)cls);
+            }
+        }
+        __syncthreads();
+        const int nk = s_nkept;
+        for (int p = tid; p < nk * NMS_CHUNK; p += NMS_THREADS) {
+            const int k = p / NMS_CHUNK, c = p % NMS_CHUNK;
+            if (c < nch && iou_exceeds(kept[k], cbox[c], iou_thres)) atomicOr(&csupp[c], 1u);
+        }
+        for (int p = tid; p < NMS_CHUNK * NMS_CHUNK; p += NMS_THREADS) {
+            const int i = p / NMS_CHUNK, j = p % NMS_CHUNK;
+            if (j > i && j < nch && iou_exceeds(cbox[i], cbox[j], iou_thres)) atomicOr(&cmask[i], 1ull << j);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long dead = 0ull;
+            int n = nk;
+            for (int c = 0; c < nch && n < max_det; ++c) {
+                if (csupp[c] || ((dead >> c) & 1ull)) continue;
+                kept[n] = cbox[c];
+                float* o = out + (size_t)n * 6;
+                o[0] = craw[c].x; o[1] = craw[c].y; o[2] = craw[c].z; o[3] = craw[c].w; o[4] = cmeta[c].x; o[5] = cmeta[c].y;
+                dead |= cmask[c];
+                ++n;
+            }
+            s_nkept = n;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) counts[b] = s_nkept;
+}
+
+}  // namespace
+}  // namespace kad
+
+using namespace kad;
+
+extern "C" int kad_nms_max_anchors(void) { return NMS_MAX_ANCHORS; }
+
+extern "C" int kad_nms_batched(const void* pred, int B, int nc, int A, float conf_thres, float iou_thres, int max_det,
+                               float max_wh, float* dets, int* counts, int dtype, void* stream) {
+    KAD_CHECK_ARG(pred && dets && counts, "kad_nms_batched: null pointer");
+    KAD_CHECK_ARG(B > 0 && nc > 0 && A > 0, "kad_nms_batched: bad shape");
+    KAD_CHECK_ARG(max_det > 0 && max_det <= NMS_MAX_DET, "kad_nms_batched: max_det must lie in [1, %d]", NMS_MAX_DET);
+    KAD_CHECK_ARG(conf_thres >= 0.f && conf_thres <= 1.f && iou_thres >= 0.f && iou_thres <= 1.f, "kad_nms_batched: thresholds must lie in [0, 1]");
+    if (A > NMS_MAX_ANCHORS)
+        return fail(KAD_ERR_UNSUPPORTED, "kad_nms_batched: %d anchors exceed the %d the in-shared-memory sort holds", A, NMS_MAX_ANCHORS);
+    int npow2 = 64;
+    while (npow2 < A) npow2 <<= 1;
+    size_t smem = (size_t)npow2 * 8 + (size_t)max_det * 16 + NMS_CHUNK * (16 + 16 + 8 + 8 + 4) + 64;
+    KAD_DISPATCH_DTYPE(dtype, {
+        auto kern = nms_kernel<T>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "nms smem attribute: %s", cudaGetErrorString(e));
+        kern<<<B, NMS_THREADS, smem, (cudaStream_t)stream>>>((const T*)pred, nc, A, npow2, conf_thres, iou_thres, max_det, max_wh, dets, counts);
+    });
+    KAD_CHECK_LAUNCH("nms_kernel");
+    return KAD_OK;
+}

@@ -258,12 +258,23 @@ inline int pick_cout_tile(int Cout) {
 
 }  // namespace
 
-int dsc_simt_tiles(int H, int W) { return (H * W + TP - 1) / TP; }
+int dsc_px_blocks(int H, int W);
+bool dsc_px_supported(int Cin, int Cout);
+int launch_dsc_px(const KadDscArgs& a, cudaStream_t st);
+bool pool_project_px_supported(int Cin, int Cout);
+int launch_pool_project_px(const void* x, const float* w, const float* bias, void* y, int B, int H, int W, int Cin, int Cout,
+                           int pool, int act, int x_cs, int y_cs, int dtype, cudaStream_t st);
+
+// number of per-image partial sums the SIMT path writes for the SE squeeze
+int dsc_simt_tiles(int H, int W, int Cin, int Cout) {
+    return dsc_px_supported(Cin, Cout) ? dsc_px_blocks(H, W) : (H * W + TP - 1) / TP;
+}
 
 int launch_dsc_simt(const KadDscArgs& a, cudaStream_t st) {
+    if (dsc_px_supported(a.Cin, a.Cout)) return launch_dsc_px(a, st);     // small channel counts: pixel-per-thread kernel
     int coutT = pick_cout_tile(a.Cout);
     size_t smem = sizeof(float) * ((size_t)TP * KPAD + (size_t)KC * coutT + TP * 9 * 4) + sizeof(int) * TP * 9 * 2;
-    dim3 grid(dsc_simt_tiles(a.H, a.W), (a.Cout + coutT - 1) / coutT, a.B);
+    dim3 grid((a.H * a.W + TP - 1) / TP, (a.Cout + coutT - 1) / coutT, a.B);
     KAD_DISPATCH_DTYPE(a.dtype, {
         auto kern = dsc_simt_kernel<T>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -286,6 +297,8 @@ extern "C" int kad_pool_project(const void* x, const float* w, const float* bias
     KAD_CHECK_ARG(B > 0 && H > 0 && W > 0 && Cin > 0 && Cout > 0, "kad_pool_project: bad shape");
     KAD_CHECK_ARG(pool >= 1 && H / pool > 0 && W / pool > 0, "kad_pool_project: pool %d leaves no output for %dx%d", pool, H, W);
     KAD_CHECK_ARG(x_cstride >= Cin && y_cstride >= Cout, "kad_pool_project: channel stride smaller than channel count");
+    if (pool_project_px_supported(Cin, Cout))
+        return launch_pool_project_px(x, w, bias, y, B, H, W, Cin, Cout, pool, act, x_cstride, y_cstride, dtype, (cudaStream_t)stream);
     int Ho = H / pool, Wo = W / pool;
     int coutT = pick_cout_tile(Cout);
     size_t smem = sizeof(float) * ((size_t)TP * KPAD + (size_t)KC * coutT);

@@ -50,3 +50,14 @@ def non_max_suppression(prediction, conf_thres=0.25, iou_thres=0.45, classes=Non
         i = _nms(x[:, :4] + c, x[:, 4], iou_thres)
         output[xi] = x[i[:max_det]]
     return output
+
+
+def non_max_suppression_device(prediction, conf_thres=0.25, iou_thres=0.45, max_det=300):
+    """Same result structure as non_max_suppression, computed by one batched CUDA kernel (kad_nms_batched):
+    no per-image Python loop and no host synchronisation before the final read of the counts."""
+    from kadconv import ops
+    if isinstance(prediction, (list, tuple)):
+        prediction = prediction[0]
+    dets, counts = ops.nms_batched(prediction.contiguous(), conf_thres, iou_thres, max_det)
+    counts = counts.tolist()
+    return [dets[i, :n] for i, n in enumerate(counts)]

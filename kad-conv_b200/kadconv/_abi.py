@@ -36,7 +36,7 @@ SIGNATURES = {
     'kad_nchw_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_nhwc_to_nchw': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_dsc_forward': (c_int, [POINTER(KadDscArgs), c_void_p]),
-    'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int]),
+    'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_tc_supported': (c_int, [c_int, c_int, c_int]),
     'kad_dsc_pack_weight_tc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     'kad_dsc_packed_weight_bytes': (c_size_t, [c_int, c_int, c_int]),
@@ -53,6 +53,8 @@ SIGNATURES = {
     'kad_se_squeeze': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_se_rescale': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_merge_upsample_residual': (c_int, [POINTER(KadMergeArgs), c_void_p]),
+    'kad_nms_max_anchors': (c_int, []),
+    'kad_nms_batched': (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]),
     'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
     'kad_gemm1x1_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p]),

@@ -155,7 +155,7 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
     y = torch.empty((B, H, W, Cout), dtype=torch.float32 if y_f32 else x.dtype, device=x.device)
     gap = None
     if want_gap:
-        tiles = lib.kad_dsc_gap_tiles(H, W, path)
+        tiles = lib.kad_dsc_gap_tiles(H, W, Cin, Cout, path)
         gap = torch.empty((B, tiles, Cout), dtype=torch.float32, device=x.device)
         a.gap_partial = gap.data_ptr()
     a.y = y.data_ptr()
@@ -292,3 +292,14 @@ def gemm1x1_bias_act_raw(src, shape, w, bias, act, k, out=None, out_coff=0):
                                                 ctypes.c_void_p(dst.data_ptr()), M, k, N, Cx, ldy, act, _DT[w.dtype],
                                                 _ptr(status_word(w.device)), _stream()), 'kad_gemm1x1_bias_act')
     return out
+
+
+def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0):
+    """pred [B,4+nc,A] (DDetect's y) -> (dets [B,max_det,6] float32, counts [B] int32), all on the device, one launch."""
+    pred = _cuda(pred, 'pred')
+    B, no, A = pred.shape
+    dets = torch.zeros((B, max_det, 6), dtype=torch.float32, device=pred.device)
+    counts = torch.zeros(B, dtype=torch.int32, device=pred.device)
+    _abi.check(_abi.load().kad_nms_batched(_ptr(pred), B, no - 4, A, ctypes.c_float(conf_thres), ctypes.c_float(iou_thres), max_det,
+                                           ctypes.c_float(max_wh), _ptr(dets), _ptr(counts), dtype_code(pred), _stream()), 'kad_nms_batched')
+    return dets, counts

@@ -286,10 +286,10 @@ def non_max_suppression(pred, conf_thres=0.001, iou_thres=0.65, max_det=300, max
         box = torch.stack((x[:, 0] - x[:, 2] / 2, x[:, 1] - x[:, 3] / 2,
                            x[:, 0] + x[:, 2] / 2, x[:, 1] + x[:, 3] / 2), 1)
         conf, j = x[:, 4:].max(1, keepdim=True)
-        x = torch.cat((box, conf, j.to(x.dtype)), 1)[conf.view(-1) > conf_thres]
+        x = torch.cat((box, conf, j.float()), 1)[conf.view(-1) > conf_thres]     # float32 from here on, as in the reference
         if not x.shape[0]:
             out.append(torch.zeros(0, 6, dtype=pred.dtype)); continue
-        x = x[x[:, 4].argsort(descending=True)[:max_nms]]
+        x = x[x[:, 4].argsort(descending=True, stable=True)[:max_nms]]   # equal scores: lower anchor index first
         keep = greedy_nms(x[:, :4] + x[:, 5:6] * max_wh, x[:, 4], iou_thres)[:max_det]
         out.append(x[keep])
     return out
