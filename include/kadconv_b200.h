@@ -94,6 +94,10 @@ int kad_pool_project(const void* x, const float* w, const float* bias, void* y,
                      int B, int H, int W, int Cin, int Cout, int pool, int act,
                      int x_cstride, int y_cstride, int dtype, void* stream);
 
+/* Average pool, kernel = stride = pool, floor mode, NHWC: F.avg_pool2d as used for the branch pyramid
+ * (KAD-Conv/kadconv/kad_conv.py:115) when the pooled tensor feeds the tensor-core 1x1 GEMM. */
+int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, int dtype, void* stream);
+
 /* LCSA, step 1: row sums [B,H,C] (over x) and column sums [B,W,C] (over y) of x[B,H,W,C], float32.
  * Replaces pool_h / pool_w of LCSA.forward (kad_conv.py:27-28,:39). */
 int kad_lcsa_sums(const void* x, float* rowsum, float* colsum, int B, int H, int W, int C, int dtype, void* stream);

@@ -50,7 +50,7 @@ using namespace sm100;
 
 constexpr int BM = 128;                 // rows (pixels) per tile
 constexpr int UNIT = 32;                // channels per K unit
-constexpr int NA_MAX = 4;               // A stages: 3 for one CTA per tile pair, 4 for the CTA-pair kernel
+constexpr int NA_MAX = 5;               // A stages: 3 for one CTA per tile pair, 4 for the CTA-pair kernel
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int WIN_PX_MAX = 704;         // pixels per window buffer
 constexpr int WIN_BYTES = WIN_PX_MAX * 64;
@@ -711,7 +711,7 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     bool pair = a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2;
     { const char* e = getenv("KAD_DSC_TC_PAIR"); if (e) pair = pair && atoi(e) != 0; }
     p.npairs = (p.ntiles + 1) / 2;
-    p.na = pair ? 4 : 3;
+    p.na = pair ? 5 : 3;
     p.b_stage_bytes = (pair ? a.Cout / 2 : a.Cout) * 128;      // multiple of 2048
 
     // shared-memory carve-up (offsets from a 1024-byte aligned base)

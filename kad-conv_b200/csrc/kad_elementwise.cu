@@ -89,39 +89,50 @@ __global__ void lcsa_prep_kernel(const float* __restrict__ colsum, const float* 
     if (b == 0) Sm[(size_t)c * W + w] = S * m;
 }
 
-// grid (ceil(W/128), H, B), 128 threads; each thread one pixel.
+// grid (ceil(W/128), H, B), 128 threads; each thread one pixel. Per channel the 11 row means, the 11 vertical taps
+// and the 9 projection weights are staged as padded rows of 12 floats, so the inner loop reads 9 broadcast float4s.
 template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                  const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
                  const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int mask_f32) {
-    extern __shared__ float sm[];
-    float* rm = sm;               // [11][C] row means of rows h-5..h+5 (0 outside the image)
-    float* sw2 = rm + 11 * C;     // [C][11]
-    float* sw3 = sw2 + 11 * C;    // [9][C]
-    float* sb2 = sw3 + 9 * C;     // [C]
+    extern __shared__ __align__(16) float sm[];
+    float* rm = sm;               // [C][12] row means of rows h-5..h+5 (0 outside the image), pad 0
+    float* sw2 = rm + 12 * C;     // [C][12] 11x1 taps (0 for rows outside the image), slot 11 = bias b2
+    float* sw3 = sw2 + 12 * C;    // [C][12] 1x1 weights of the 9 outputs, pad 0
     int b = blockIdx.z, h = blockIdx.y, t = threadIdx.x;
     float invW = 1.f / (float)W;
-    for (int e = t; e < 11 * C; e += 128) {
-        int k = e / C, c = e - k * C, hh = h + k - 5;
-        rm[e] = (hh >= 0 && hh < H) ? rowsum[((size_t)b * H + hh) * C + c] * invW : 0.f;
-        sw2[e] = w2[e];
+    for (int e = t; e < 12 * C; e += 128) {
+        int c = e / 12, k = e - c * 12, hh = h + k - 5;
+        bool in = k < 11 && hh >= 0 && hh < H;
+        rm[e] = in ? rowsum[((size_t)b * H + hh) * C + c] * invW : 0.f;
+        sw2[e] = in ? w2[c * 11 + k] : (k == 11 ? b2[c] : 0.f);
+        sw3[e] = k < 9 ? w3[k * C + c] : 0.f;
     }
-    for (int e = t; e < 9 * C; e += 128) sw3[e] = w3[e];
-    for (int e = t; e < C; e += 128) sb2[e] = b2[e];
     __syncthreads();
     int w = blockIdx.x * 128 + t;
     if (w >= W) return;
-    int k0 = max(0, 5 - h), k1 = min(11, H + 5 - h);   // taps whose row lies inside the image
     float logit[9];
 #pragma unroll
     for (int j = 0; j < 9; ++j) logit[j] = b3[j];
+    const float4* rm4 = reinterpret_cast<const float4*>(rm);
+    const float4* w24 = reinterpret_cast<const float4*>(sw2);
+    const float4* w34 = reinterpret_cast<const float4*>(sw3);
     for (int c = 0; c < C; ++c) {
-        float a = A[((size_t)b * C + c) * W + w], s = Sm[(size_t)c * W + w];
-        float v = sb2[c];
-        for (int k = k0; k < k1; ++k) v = fmaf(sw2[c * 11 + k], fmaxf(fmaf(rm[k * C + c], s, a), 0.f), v);
-#pragma unroll
-        for (int j = 0; j < 9; ++j) logit[j] = fmaf(sw3[j * C + c], v, logit[j]);
+        const float a = A[((size_t)b * C + c) * W + w], s = Sm[(size_t)c * W + w];
+        const float4 r0 = rm4[3 * c], r1 = rm4[3 * c + 1], r2 = rm4[3 * c + 2];
+        const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
+        float v = u2.w;           // bias of the 11x1 convolution
+        v = fmaf(u0.x, fmaxf(fmaf(r0.x, s, a), 0.f), v); v = fmaf(u0.y, fmaxf(fmaf(r0.y, s, a), 0.f), v);
+        v = fmaf(u0.z, fmaxf(fmaf(r0.z, s, a), 0.f), v); v = fmaf(u0.w, fmaxf(fmaf(r0.w, s, a), 0.f), v);
+        v = fmaf(u1.x, fmaxf(fmaf(r1.x, s, a), 0.f), v); v = fmaf(u1.y, fmaxf(fmaf(r1.y, s, a), 0.f), v);
+        v = fmaf(u1.z, fmaxf(fmaf(r1.z, s, a), 0.f), v); v = fmaf(u1.w, fmaxf(fmaf(r1.w, s, a), 0.f), v);
+        v = fmaf(u2.x, fmaxf(fmaf(r2.x, s, a), 0.f), v); v = fmaf(u2.y, fmaxf(fmaf(r2.y, s, a), 0.f), v);
+        v = fmaf(u2.z, fmaxf(fmaf(r2.z, s, a), 0.f), v);
+        const float4 p0 = w34[3 * c], p1 = w34[3 * c + 1], p2 = w34[3 * c + 2];
+        logit[0] = fmaf(p0.x, v, logit[0]); logit[1] = fmaf(p0.y, v, logit[1]); logit[2] = fmaf(p0.z, v, logit[2]);
+        logit[3] = fmaf(p0.w, v, logit[3]); logit[4] = fmaf(p1.x, v, logit[4]); logit[5] = fmaf(p1.y, v, logit[5]);
+        logit[6] = fmaf(p1.z, v, logit[6]); logit[7] = fmaf(p1.w, v, logit[7]); logit[8] = fmaf(p2.x, v, logit[8]);
     }
     size_t o = (((size_t)b * H + h) * W + w) * 9;
 #pragma unroll
@@ -225,32 +236,57 @@ __device__ __forceinline__ void src_index(int d, float scale, int in, int& i0, i
     l1 = s - (float)i0;
 }
 
+// blockDim = 256 = (pixel lanes) x (channels rounded up to a multiple of 32): a thread keeps its channel (so its branch,
+// its attention scalar and its source tensor are fixed per image) and walks over pixels; consecutive threads touch
+// consecutive channels of the same pixel, i.e. consecutive addresses of x, out and the branch tensor.
 template <typename T>
-__global__ void merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, size_t n) {
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
-        int c = (int)(e % p.C);
-        size_t pix = e / p.C;
-        int xw = (int)(pix % p.W);
-        size_t r = pix / p.W;
-        int yh = (int)(r % p.H), b = (int)(r / p.H);
+__global__ void __launch_bounds__(256)
+merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp, int pix_per_block) {
+    const int cl0 = threadIdx.x % Cp, pl = threadIdx.x / Cp, PL = 256 / Cp;
+    const int b = blockIdx.y;
+    const int HW = p.H * p.W;
+    const int pix0 = blockIdx.x * pix_per_block, pix1 = min(HW, pix0 + pix_per_block);
+    for (int c = cl0; c < p.C; c += Cp) {
         int i = 0, cl = c;
         if (cl >= p.c[0]) { cl -= p.c[0]; i = 1; if (cl >= p.c[1]) { cl -= p.c[1]; i = 2; } }
-        const T* yi = reinterpret_cast<const T*>(p.y[i]);
-        int ci = p.c[i], hi = p.h[i], wi = p.w[i];
-        float a = p.att[i][(size_t)b * ci + cl];
-        float v;
-        if (hi == p.H && wi == p.W) {
-            v = to_f<T>(yi[(((size_t)b * hi + yh) * wi + xw) * ci + cl]);
-        } else {
-            int y0, y1, x0, x1; float ly, lx;
-            src_index(yh, p.sy[i], hi, y0, y1, ly);
-            src_index(xw, p.sx[i], wi, x0, x1, lx);
-            const T* base = yi + (size_t)b * hi * wi * ci + cl;
-            float v00 = to_f<T>(base[((size_t)y0 * wi + x0) * ci]), v01 = to_f<T>(base[((size_t)y0 * wi + x1) * ci]);
-            float v10 = to_f<T>(base[((size_t)y1 * wi + x0) * ci]), v11 = to_f<T>(base[((size_t)y1 * wi + x1) * ci]);
-            v = (1.f - ly) * ((1.f - lx) * v00 + lx * v01) + ly * ((1.f - lx) * v10 + lx * v11);
+        const int ci = p.c[i], hi = p.h[i], wi = p.w[i];
+        const T* yi = reinterpret_cast<const T*>(p.y[i]) + (size_t)b * hi * wi * ci + cl;
+        const float a = p.att[i][(size_t)b * ci + cl];
+        const bool same = (hi == p.H && wi == p.W);
+        const float sy = p.sy[i], sx = p.sx[i];
+        for (int pix = pix0 + pl; pix < pix1; pix += PL) {
+            const int yh = pix / p.W, xw = pix - yh * p.W;
+            float v;
+            if (same) {
+                v = to_f<T>(yi[(size_t)pix * ci]);
+            } else {
+                int y0, y1, x0, x1; float ly, lx;
+                src_index(yh, sy, hi, y0, y1, ly);
+                src_index(xw, sx, wi, x0, x1, lx);
+                const float v00 = to_f<T>(yi[((size_t)y0 * wi + x0) * ci]), v01 = to_f<T>(yi[((size_t)y0 * wi + x1) * ci]);
+                const float v10 = to_f<T>(yi[((size_t)y1 * wi + x0) * ci]), v11 = to_f<T>(yi[((size_t)y1 * wi + x1) * ci]);
+                v = (1.f - ly) * ((1.f - lx) * v00 + lx * v01) + ly * ((1.f - lx) * v10 + lx * v11);
+            }
+            const size_t e = ((size_t)b * HW + pix) * p.C + c;
+            out[e] = from_f<T>(fmaf(v, a, to_f<T>(x[e])));
         }
-        out[e] = from_f<T>(fmaf(v, a, to_f<T>(x[e])));
+    }
+}
+
+// avg-pool (pool x pool, stride pool, floor), NHWC; one thread per output pixel and channel.
+template <typename T>
+__global__ void avg_pool_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int Ho, int Wo, int C, int pool, size_t n) {
+    const float inv = 1.f / (float)(pool * pool);
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % C);
+        size_t r = e / C;
+        const int xo = (int)(r % Wo); r /= Wo;
+        const int yo = (int)(r % Ho); const int b = (int)(r / Ho);
+        const T* base = x + (((size_t)b * H + yo * pool) * W + xo * pool) * C + c;
+        float s = 0.f;
+        for (int dy = 0; dy < pool; ++dy)
+            for (int dx = 0; dx < pool; ++dx) s += to_f<T>(base[((size_t)dy * W + dx) * C]);
+        y[e] = from_f<T>(s * inv);
     }
 }
 
@@ -311,7 +347,7 @@ extern "C" int kad_lcsa_mask(const float* rowsum, const float* colsum,
     KAD_CHECK_ARG(rowsum && colsum && w1 && b1 && bn_scale && bn_shift && w2 && b2 && w3 && b3 && scratch && mask,
                   "kad_lcsa_mask: null pointer");
     KAD_CHECK_ARG(B > 0 && H > 0 && W > 0 && C > 0 && B <= 65535 && H <= 65535, "kad_lcsa_mask: bad shape");
-    size_t smem = sizeof(float) * (size_t)(11 + 11 + 9 + 1) * C;
+    size_t smem = sizeof(float) * (size_t)36 * C;
     KAD_CHECK_ARG(smem <= 200 * 1024, "kad_lcsa_mask: %d channels exceed the shared-memory staging", C);
     cudaStream_t st = (cudaStream_t)stream;
     float* A = scratch;
@@ -385,9 +421,14 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
         p.sy[i] = (float)a->h[i] / (float)a->H; p.sx[i] = (float)a->w[i] / (float)a->W;
     }
     p.H = a->H; p.W = a->W; p.C = a->C;
-    size_t n = (size_t)a->B * a->H * a->W * a->C;
+    KAD_CHECK_ARG(a->B <= 65535, "kad_merge_upsample_residual: batch %d too large", a->B);
+    int Cp = ((a->C + 31) / 32) * 32;
+    if (Cp > 256) Cp = 256;
+    const int HW = a->H * a->W;
+    int pix_per_block = 64 * (256 / Cp);
+    dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
     KAD_DISPATCH_DTYPE(a->dtype, {
-        merge_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)a->x, (T*)a->out, p, n);
+        merge_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);
     });
     KAD_CHECK_LAUNCH("merge_kernel");
     return KAD_OK;
@@ -440,4 +481,17 @@ extern "C" int kad_lcsa_mask_noalloc(const float* rowsum, const float* colsum,
     }
     // Every element of scratch[0, need) is overwritten before it is read, so stale contents of an earlier call are harmless.
     return kad_lcsa_mask(rowsum, colsum, w1, b1, bn_scale, bn_shift, w2, b2, w3, b3, scratch, mask, B, H, W, C, mask_f32, dtype, stream);
+}
+
+
+extern "C" int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, int dtype, void* stream) {
+    KAD_CHECK_ARG(x && y && B > 0 && H > 0 && W > 0 && C > 0, "kad_avg_pool: bad argument");
+    KAD_CHECK_ARG(pool >= 1 && H / pool > 0 && W / pool > 0, "kad_avg_pool: pool %d leaves no output for %dx%d", pool, H, W);
+    const int Ho = H / pool, Wo = W / pool;
+    const size_t n = (size_t)B * Ho * Wo * C;
+    KAD_DISPATCH_DTYPE(dtype, {
+        avg_pool_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)y, H, W, Ho, Wo, C, pool, n);
+    });
+    KAD_CHECK_LAUNCH("avg_pool_kernel");
+    return KAD_OK;
 }

@@ -39,6 +39,8 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
 
     const int b = blockIdx.x, tid = threadIdx.x;
     const T* pb = pred + (size_t)b * (4 + nc) * A;
+    // the reference compares scores in the tensor's own type, i.e. against the threshold rounded to that type
+    conf_thres = to_f<T>(from_f<T>(conf_thres));
     if (tid == 0) { s_ncand = 0; s_nkept = 0; }
     __syncthreads();
 

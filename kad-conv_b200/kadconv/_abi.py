@@ -43,6 +43,7 @@ SIGNATURES = {
     'kad_dsc_pack_weight_simt': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kad_pool_project': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_void_p]),
+    'kad_avg_pool': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask': (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask_noalloc_max_floats': (c_size_t, []),

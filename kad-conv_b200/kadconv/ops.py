@@ -303,3 +303,12 @@ def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0):
     _abi.check(_abi.load().kad_nms_batched(_ptr(pred), B, no - 4, A, ctypes.c_float(conf_thres), ctypes.c_float(iou_thres), max_det,
                                            ctypes.c_float(max_wh), _ptr(dets), _ptr(counts), dtype_code(pred), _stream()), 'kad_nms_batched')
     return dets, counts
+
+
+def avg_pool(x, pool):
+    """NHWC average pool, kernel = stride = pool, floor mode."""
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    y = torch.empty((B, H // pool, W // pool, C), dtype=x.dtype, device=x.device)
+    _abi.check(_abi.load().kad_avg_pool(_ptr(x), _ptr(y), B, H, W, C, pool, dtype_code(x), _stream()), 'kad_avg_pool')
+    return y

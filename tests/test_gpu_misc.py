@@ -123,3 +123,13 @@ def test_gemm1x1_slices_in_place():
     ops.check_status(torch.device('cuda', 0))
     assert rel_err(out[:, 16:56].float().cpu(), ref) <= 1e-2
     assert out[:, :16].abs().max().item() == 0 and out[:, 56:].abs().max().item() == 0
+
+
+def test_avg_pool():
+    from kadconv import ops
+    for dtype in (torch.float32, torch.bfloat16):
+        x = round_to(_rand((2, 24, 13, 18), 40), dtype)
+        for pool in (2, 4):
+            ref = F.avg_pool2d(x, pool)
+            y = ops.avg_pool(nhwc(x).cuda().to(dtype), pool).float().cpu().permute(0, 3, 1, 2)
+            assert rel_err(y, ref) <= (1e-6 if dtype == torch.float32 else 1e-2)
