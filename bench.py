@@ -462,6 +462,9 @@ def run_c2(args, rank, world, local):
     clocks = sampler.stop()
     launches = _abi.KERNELS_LAUNCHED[0] - k0
     ms_total = max_over_ranks(e0.elapsed_time(e1), world, device)
+    if args.profile:
+        return {'metric': 'KAD-Conv downsampling composition (bf16) feature maps/s', 'value': world * B * args.steps / (ms_total * 1e-3),
+                'unit': 'images/s', 'n_gpus': world, 'config': {'workload': 'c2 profile run'}, 'e2e': None, 'gpu_launches': launches}
     with OpTimer(ops) as tm:
         for i in range(4):
             step(i)

@@ -181,7 +181,8 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     auto tile_at = [&](int it_) { const int k = sched0 + it_ * sched_step; return PAIR ? 2 * k + (int)rank : k; };
 
     if (tid == 0) {
-        for (int i = 0; i < NA_MAX; ++i) { mbar_init(&bars->a_full[i], GROUP_WARPS); mbar_init(&bars->a_empty[i], 1); mbar_init(&bars->peer_full[i], 1); }
+        // CTA pair: the peer's producers arrive directly on the leader's a_full (8 local + 8 remote warps per stage)
+        for (int i = 0; i < NA_MAX; ++i) { mbar_init(&bars->a_full[i], PAIR ? 2 * GROUP_WARPS : GROUP_WARPS); mbar_init(&bars->a_empty[i], 1); mbar_init(&bars->peer_full[i], 1); }
         for (int i = 0; i < 2; ++i) mbar_init(&bars->peer_acc[i], 1);
         for (int i = 0; i < 4; ++i) { mbar_init(&bars->b_full[i], 1); mbar_init(&bars->b_empty[i], 1); }
         for (int i = 0; i < NWIN; ++i) { mbar_init(&bars->win_full[i], 1); mbar_init(&bars->win_empty[i], PROD_WARPS); }
@@ -311,7 +312,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         const uint32_t nbr = (uint32_t)p.nb;
         uint32_t sa = 0, pa = 0, sb = 0, pb = 0;     // slot and phase parity of the A and B rings
         bool ok = true;
-        int trc = 0;
+        int trc = 0, trl = 0;
         for (int it = 0; it < niter && ok; ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { report(p.status, 2, it); break; }
@@ -328,15 +329,17 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             for (int s = 0; s <= last; ++s) {
                 // lane 0 waits for the A stage, lane 1 for the B stage (lane 2: the peer's stage): the waits overlap
                 bool okw = true;
-                if (lane == 0 && !(p.dbg & 32)) okw = mbar_wait(&bars->a_full[sa], pa, abort_flag);
-                else if (lane == 1 && !(p.dbg & 2)) okw = mbar_wait(&bars->b_full[sb], pb, abort_flag);
-                else if (PAIR && lane == 2 && rank == 0) okw = mbar_wait_cluster(&bars->peer_full[sa], pa, abort_flag);
+                if (lane == 0 && !(p.dbg & 32) && !(PAIR && rank == 1)) {      // A stage (both CTAs' halves in pair mode)
+                    okw = PAIR ? mbar_wait_cluster(&bars->a_full[sa], pa, abort_flag) : mbar_wait(&bars->a_full[sa], pa, abort_flag);
+                    KAD_TR(3, trl);
+                } else if (lane == 1 && !(p.dbg & 2)) { okw = mbar_wait(&bars->b_full[sb], pb, abort_flag); KAD_TR(4, trl); }
+                else if (PAIR && lane == 2 && rank == 0) { okw = mbar_wait_cluster(&bars->peer_full[sa], pa, abort_flag); KAD_TR(5, trl); }
                 if (!__all_sync(0xffffffffu, okw)) { report(p.status, 3, s); ok = false; break; }
                 // no tcgen05 fence here: the operands come through shared memory (mbarrier + proxy fence order them);
                 // only the accumulator hand-off above involves TMEM
                 if (lane == 0) KAD_TR(1, trc);
                 if (PAIR && rank == 1) {
-                    // peer CTA: its A and B halves of this stage are in place; tell the leader, which issues for both
+                    // peer CTA: its half of the weights for this stage has landed; tell the leader, which issues for both
                     if (lane == 0) mbar_arrive_remote(&bars->peer_full[sa], 0);
                 } else if (lane == 0) {
                     const uint64_t ad = adesc0 + (uint64_t)(sa * a_step), bd = bdesc0 + (uint64_t)(sb * b_step);
@@ -350,6 +353,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                             }
                         }
                     }
+                    KAD_TR(1, trc);
                     if (PAIR) {
                         umma_commit_pair(&bars->a_empty[sa]);
                         if (s == last) umma_commit_pair(&bars->acc_full[buf]);
@@ -357,6 +361,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                         umma_commit(&bars->a_empty[sa]);
                         if (s == last) umma_commit(&bars->acc_full[buf]);
                     }
+                    KAD_TR(1, trc);
                 }
                 if (++sa == NA) { sa = 0; pa ^= 1; }
                 if (++sb == nbr) { sb = 0; pb ^= 1; }
@@ -612,7 +617,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 }
                 if (!(p.dbg & 64)) fence_proxy_async();          // generic-proxy stores -> visible to the tensor core
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->a_full[sa]);
+                if (lane == 0) { if (PAIR && rank == 1) mbar_arrive_remote(&bars->a_full[sa], 0); else mbar_arrive(&bars->a_full[sa]); }
                 if (trp) KAD_TR(0, trc);
             }
         }
@@ -708,10 +713,13 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    bool pair = a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2;
-    { const char* e = getenv("KAD_DSC_TC_PAIR"); if (e) pair = pair && atoi(e) != 0; }
+    // The pair kernel is selectable (KAD_DSC_TC_PAIR=1) but not the default: on C1 it measured 370-380 us against
+    // 310-320 us for one CTA per tile, because the weight ring and the hand-off between the two CTAs add latency that
+    // the four A stages which fit in shared memory do not cover.
+    bool pair = false;
+    { const char* e = getenv("KAD_DSC_TC_PAIR"); if (e && atoi(e) != 0) pair = a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2; }
     p.npairs = (p.ntiles + 1) / 2;
-    p.na = pair ? 5 : 3;
+    p.na = pair ? 4 : 3;
     p.b_stage_bytes = (pair ? a.Cout / 2 : a.Cout) * 128;      // multiple of 2048
 
     // shared-memory carve-up (offsets from a 1024-byte aligned base)

@@ -484,14 +484,48 @@ extern "C" int kad_lcsa_mask_noalloc(const float* rowsum, const float* colsum,
 }
 
 
+namespace kad { namespace {
+// 8 x 16-bit channels per thread (C % 8 == 0)
+template <typename T>
+__global__ void avg_pool_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int Ho, int Wo, int C8, int pool, size_t n) {
+    const float inv = 1.f / (float)(pool * pool);
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % C8);
+        size_t r = e / C8;
+        const int xo = (int)(r % Wo); r /= Wo;
+        const int yo = (int)(r % Ho); const int b = (int)(r / Ho);
+        const uint4* base = x + (((size_t)b * H + yo * pool) * W + xo * pool) * C8 + c;
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int dy = 0; dy < pool; ++dy)
+            for (int dx = 0; dx < pool; ++dx) {
+                const uint4 v = base[((size_t)dy * W + dx) * C8];
+                const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] += to_f<T>(h[i]);
+            }
+        uint4 o;
+        T* ho = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ho[i] = from_f<T>(s[i] * inv);
+        y[e] = o;
+    }
+}
+} }
+
 extern "C" int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, int dtype, void* stream) {
     KAD_CHECK_ARG(x && y && B > 0 && H > 0 && W > 0 && C > 0, "kad_avg_pool: bad argument");
     KAD_CHECK_ARG(pool >= 1 && H / pool > 0 && W / pool > 0, "kad_avg_pool: pool %d leaves no output for %dx%d", pool, H, W);
     const int Ho = H / pool, Wo = W / pool;
     const size_t n = (size_t)B * Ho * Wo * C;
-    KAD_DISPATCH_DTYPE(dtype, {
-        avg_pool_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)y, H, W, Ho, Wo, C, pool, n);
-    });
+    if (dtype != KAD_F32 && C % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+        const size_t nv = n / 8;
+        if (dtype == KAD_F16) avg_pool_vec8_kernel<__half><<<grid_for(nv, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, H, W, Ho, Wo, C / 8, pool, nv);
+        else avg_pool_vec8_kernel<__nv_bfloat16><<<grid_for(nv, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, H, W, Ho, Wo, C / 8, pool, nv);
+    } else {
+        KAD_DISPATCH_DTYPE(dtype, {
+            avg_pool_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)y, H, W, Ho, Wo, C, pool, n);
+        });
+    }
     KAD_CHECK_LAUNCH("avg_pool_kernel");
     return KAD_OK;
 }

@@ -5,7 +5,8 @@
 // Both operands are K-major in global memory already (NHWC activations, [Cout][Cin] weights), so
 // each pipeline stage is two plain tiled TMA loads (128 x 64 of x, Nt x 64 of w, 128-byte swizzle;
 // out-of-range K and N are zero-filled by TMA). One persistent CTA per SM:
-//   warps 0-3 epilogue (TMEM -> bias/activation -> NHWC store), warp 4 MMA issuer, warp 5 TMA.
+//   warps 0-7 epilogue (TMEM -> bias/activation -> NHWC store; warps w and w+4 share a TMEM lane quadrant and split
+//   the columns), warp 8 MMA issuer, warp 9 TMA.
 // The op is HBM-bound at the detector's shapes (K <= 512): the design goal is to keep enough bytes
 // in flight, which the 4-stage ring and the double-buffered accumulator do.
 #include "kad_common.cuh"
@@ -18,7 +19,8 @@ using namespace sm100;
 constexpr int GBM = 128;
 constexpr int GSTAGES = 4;
 constexpr int G_A_BYTES = GBM * 128;
-constexpr int G_THREADS = 192;
+constexpr int G_THREADS = 320;
+constexpr int G_EPI_WARPS = 8, G_WARP_MMA = 8, G_WARP_TMA = 9;
 constexpr int G_ACC_COLS = 256;
 
 struct GemmParams {
@@ -54,17 +56,21 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     if (tid == 0) {
         for (int i = 0; i < GSTAGES; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], G_EPI_WARPS * 32); }
         bars->abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+    if (warp == G_WARP_MMA) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+    // bias of every output channel, padded with zeros to the tile grid
+    float* sbias = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + ((sizeof(GemmBars) + 15) & ~size_t(15)));   // 16-byte aligned: read as float4
+    for (int i = tid; i < p.n_tiles * p.nt; i += G_THREADS) sbias[i] = (p.bias && i < p.N) ? p.bias[i] : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
-    if (warp < 4) {
+    if (warp < G_EPI_WARPS) {
+        const int quad = warp & 3, half = warp >> 2;       // TMEM lane quadrant; which half of the column chunks
         int it = 0;
         for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
             const int buf = it & 1;
@@ -72,26 +78,40 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const long long mt = tile / p.n_tiles;
             const int n0 = (int)(tile - mt * p.n_tiles) * p.nt;
-            const long long row = mt * GBM + warp * 32 + lane;
+            const long long row = mt * GBM + quad * 32 + lane;
             const bool live = row < p.M;
-            for (int c0 = 0; c0 < p.nt; c0 += 32) {
+            const int nchunks = (p.nt + 31) / 32;
+            for (int ch = half; ch < nchunks; ch += 2) {
+                const int c0 = ch * 32;
                 const int nc = min(32, p.nt - c0);
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + (uint32_t)(buf * G_ACC_COLS + c0) + ((uint32_t)(warp * 32) << 16);
+                const uint32_t taddr = tmem_base + (uint32_t)(buf * G_ACC_COLS + c0) + ((uint32_t)(quad * 32) << 16);
                 if (nc == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
                 tmem_ld_wait();
                 if (live) {
                     T* dst = reinterpret_cast<T*>(p.y) + row * p.ldy + n0 + c0;
+                    const float4* b4 = reinterpret_cast<const float4*>(sbias + n0 + c0);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int n = n0 + c0 + 8 * j;
                         if (8 * j < nc && n < p.N) {      // N % 8 == 0: a group of 8 is all in or all out
+                            const float4 ba = b4[2 * j], bb = b4[2 * j + 1];
+                            float a[8] = {__uint_as_float(v[8 * j + 0]) + ba.x, __uint_as_float(v[8 * j + 1]) + ba.y,
+                                          __uint_as_float(v[8 * j + 2]) + ba.z, __uint_as_float(v[8 * j + 3]) + ba.w,
+                                          __uint_as_float(v[8 * j + 4]) + bb.x, __uint_as_float(v[8 * j + 5]) + bb.y,
+                                          __uint_as_float(v[8 * j + 6]) + bb.z, __uint_as_float(v[8 * j + 7]) + bb.w};
                             uint4 w;
                             T* h = reinterpret_cast<T*>(&w);
+                            if (p.act == KAD_ACT_SILU) {
+                                // the result is rounded to 16 bits: the fast exponential / division (about 1e-6 relative) is ample
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                float a = __uint_as_float(v[8 * j + e]) + (p.bias ? p.bias[n + e] : 0.f);
-                                h[e] = from_f<T>(apply_act(a, p.act));
+                                for (int e = 0; e < 8; ++e) h[e] = from_f<T>(__fdividef(a[e], 1.f + __expf(-a[e])));
+                            } else if (p.act == KAD_ACT_RELU) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) h[e] = from_f<T>(fmaxf(a[e], 0.f));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) h[e] = from_f<T>(a[e]);
                             }
                             *reinterpret_cast<uint4*>(dst + 8 * j) = w;
                         }
@@ -101,7 +121,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[buf]);
         }
-    } else if (warp == 4) {
+    } else if (warp == G_WARP_MMA) {
         const uint32_t idesc = instr_desc_f16(p.fmt, p.nt);
         const uint32_t a_base = smem_u32(sa), b_base = smem_u32(sb);
         int it = 0;
@@ -156,7 +176,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == G_WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
     if (tid == 0 && *abort_flag) greport(p.status, 9, 0);
 }
 
@@ -211,7 +231,7 @@ extern "C" int kad_gemm1x1_bias_act(const void* x, const void* w, const float* b
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(KAD_ERR_CUDA, "tensor map for w failed (CUresult %d)", (int)r);
     }
-    size_t smem = (size_t)GSTAGES * (G_A_BYTES + p.b_stage_bytes) + sizeof(GemmBars) + 1024 + 128;
+    size_t smem = (size_t)GSTAGES * (G_A_BYTES + p.b_stage_bytes) + sizeof(GemmBars) + (size_t)n_tiles * nt * 4 + 1024 + 128;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
