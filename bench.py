@@ -508,7 +508,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='c1', choices=['c1', 'c2', 'c4'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--mini-batch', type=int, default=16, help='c4: images per forward graph')
+    ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
     ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
     args = ap.parse_args()
     rank, world, local = dist_setup(args.gpus)

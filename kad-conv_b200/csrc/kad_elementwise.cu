@@ -425,7 +425,7 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     int Cp = ((a->C + 31) / 32) * 32;
     if (Cp > 256) Cp = 256;
     const int HW = a->H * a->W;
-    int pix_per_block = 64 * (256 / Cp);
+    int pix_per_block = 4 * (256 / Cp);     // four pixels per thread: enough blocks to fill the GPU on small feature maps
     dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
     KAD_DISPATCH_DTYPE(a->dtype, {
         merge_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);
