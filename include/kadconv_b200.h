@@ -66,7 +66,8 @@ typedef struct KadDscArgs {
     void* y; float* gap_partial;
     int B, H, W, Cin, Cout;
     int dtype, offset_f32, mask_f32, y_f32, act;
-    int path;            /* 0 = SIMT (any shape, any dtype); 1 = tcgen05 implicit GEMM (see kad_dsc_tc_supported) */
+    int path;            /* 0 = SIMT (any shape, any dtype); 1 = tcgen05 implicit GEMM (see kad_dsc_tc_supported);
+                            2 = the same on CTA pairs (tcgen05 cta_group::2, cluster of 2; needs Cout % 32 == 0) */
     int* status;         /* device int[4], zeroed by the caller; the tensor path records a wait that gave up here */
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);

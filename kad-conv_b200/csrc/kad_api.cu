@@ -36,7 +36,7 @@ extern "C" const char* kad_last_error_string(void) { return last_error().c_str()
 
 extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {
     if (H <= 0 || W <= 0 || Cin <= 0 || Cout <= 0) return 0;
-    return path == 1 ? dsc_tc_tiles(H, W) : dsc_simt_tiles(H, W, Cin, Cout);
+    return (path == 1 || path == 2) ? dsc_tc_tiles(H, W) : dsc_simt_tiles(H, W, Cin, Cout);
 }
 
 extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
@@ -49,7 +49,7 @@ extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
     KAD_CHECK_ARG(a->dtype == KAD_F32 || a->dtype == KAD_F16 || a->dtype == KAD_BF16, "kad_dsc_forward: unknown dtype %d", a->dtype);
     KAD_CHECK_ARG(a->act == KAD_ACT_NONE || a->act == KAD_ACT_SILU || a->act == KAD_ACT_RELU, "kad_dsc_forward: unknown activation %d", a->act);
     if (a->path == 0) return launch_dsc_simt(*a, (cudaStream_t)stream);
-    if (a->path == 1) {
+    if (a->path == 1 || a->path == 2) {
         if (!kad_dsc_tc_supported(a->Cin, a->Cout, a->dtype))
             return fail(KAD_ERR_UNSUPPORTED, "kad_dsc_forward: tensor path needs f16/bf16, Cin %% 32 == 0, Cout %% 16 == 0, Cout <= 256 (got Cin=%d Cout=%d dtype=%d)",
                         a->Cin, a->Cout, a->dtype);

@@ -23,7 +23,6 @@
 // role leaves its loop, outstanding TMA copies are waited for (bounded), TMEM is freed and the
 // kernel returns with a code in the caller's status word.
 #include <mutex>
-#include <stdlib.h>
 
 #include "kad_common.cuh"
 #include "kad_sm100.cuh"
@@ -73,8 +72,6 @@ struct TcParams {
     int na, nb, b_stage_bytes;                  // A and B rings
     int npairs;                                 // CTA-pair kernel: number of tile pairs
     int offset_f32, mask_f32, y_f32, act, fmt;
-    int dbg;
-    long long* trace;
 };
 
 struct SmemLayout {
@@ -145,9 +142,6 @@ __device__ __forceinline__ uint4 interp8<__nv_bfloat16>(uint4 a, uint4 b, uint4 
     return r;
 }
 
-// Development trace: role r of CTA 0 appends clock64 stamps to trace[r*4096 ...].
-#define KAD_TR(role, cnt) do { if (p.trace && blockIdx.x == 0 && (cnt) < 4096) p.trace[(role) * 4096 + (cnt)++] = clock64(); } while (0)
-
 __device__ __forceinline__ void report(int* status, int code, int detail) {
     if (atomicCAS(status, 0, code) == 0) { status[1] = detail; status[2] = blockIdx.x; }
 }
@@ -214,16 +208,13 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         // =========================================================================== epilogue
         float* gsum = epi + 768;   // [4 warps][256] column sums for the SE squeeze
         int it = 0;
-        int etr = 0;
         for (; it < niter; ++it) {
             const int tile_raw = tile_at(it);
             const bool tile_ok = tile_raw < p.ntiles;
             const int tile = tile_ok ? tile_raw : p.ntiles - 1;
             const int buf = it & 1;
-            if (tid == 0) KAD_TR(2, etr);
             if (!mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag)) { report(p.status, 1, it); break; }
             tc_fence_after();
-            if (tid == 0) KAD_TR(2, etr);
             const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
             const int ty0 = (tr / p.tiles_x) * p.th, tx0 = (tr % p.tiles_x) * p.tw;
             const int r = warp * 32 + lane;
@@ -293,7 +284,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             }
             tc_fence_before();
             mbar_arrive(&bars->acc_empty[buf]);
-            if (tid == 0) KAD_TR(2, etr);
             if (p.gap_partial && tile_ok) {
                 if (!group_sync(&bars->gap_ready, it & 1, lane, abort_flag)) { report(p.status, 10, it); break; }
                 for (int c = tid; c < p.N; c += EPI_WARPS * 32)
@@ -312,7 +302,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         const uint32_t nbr = (uint32_t)p.nb;
         uint32_t sa = 0, pa = 0, sb = 0, pb = 0;     // slot and phase parity of the A and B rings
         bool ok = true;
-        int trc = 0, trl = 0;
         for (int it = 0; it < niter && ok; ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { report(p.status, 2, it); break; }
@@ -322,38 +311,32 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 else if (!mbar_wait_cluster(&bars->peer_acc[buf], (it >> 1) & 1, abort_flag)) { report(p.status, 14, it); break; }
             }
             tc_fence_after();
-            if (lane == 0) KAD_TR(1, trc);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * ACC_COLS);
             const int last = p.stages - 1;
             const int nk_last = (p.units & 1) ? 2 : 4;   // a trailing single unit fills half a stage
             for (int s = 0; s <= last; ++s) {
                 // lane 0 waits for the A stage, lane 1 for the B stage (lane 2: the peer's stage): the waits overlap
                 bool okw = true;
-                if (lane == 0 && !(p.dbg & 32) && !(PAIR && rank == 1)) {      // A stage (both CTAs' halves in pair mode)
+                if (lane == 0 && !(PAIR && rank == 1)) {      // A stage (both CTAs' halves in pair mode)
                     okw = PAIR ? mbar_wait_cluster(&bars->a_full[sa], pa, abort_flag) : mbar_wait(&bars->a_full[sa], pa, abort_flag);
-                    KAD_TR(3, trl);
-                } else if (lane == 1 && !(p.dbg & 2)) { okw = mbar_wait(&bars->b_full[sb], pb, abort_flag); KAD_TR(4, trl); }
-                else if (PAIR && lane == 2 && rank == 0) { okw = mbar_wait_cluster(&bars->peer_full[sa], pa, abort_flag); KAD_TR(5, trl); }
+                } else if (lane == 1) { okw = mbar_wait(&bars->b_full[sb], pb, abort_flag); }
+                else if (PAIR && lane == 2 && rank == 0) { okw = mbar_wait_cluster(&bars->peer_full[sa], pa, abort_flag); }
                 if (!__all_sync(0xffffffffu, okw)) { report(p.status, 3, s); ok = false; break; }
                 // no tcgen05 fence here: the operands come through shared memory (mbarrier + proxy fence order them);
                 // only the accumulator hand-off above involves TMEM
-                if (lane == 0) KAD_TR(1, trc);
                 if (PAIR && rank == 1) {
                     // peer CTA: its half of the weights for this stage has landed; tell the leader, which issues for both
                     if (lane == 0) mbar_arrive_remote(&bars->peer_full[sa], 0);
                 } else if (lane == 0) {
                     const uint64_t ad = adesc0 + (uint64_t)(sa * a_step), bd = bdesc0 + (uint64_t)(sb * b_step);
                     const int nk = (s == last) ? nk_last : 4;
-                    if (!(p.dbg & 4)) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            if (k < nk) {
-                                if (PAIR) umma_f16_pair(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
-                                else umma_f16(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
-                            }
+                    for (int k = 0; k < 4; ++k) {
+                        if (k < nk) {
+                            if (PAIR) umma_f16_pair(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
+                            else umma_f16(tacc, ad + 2u * k, bd + 2u * k, idesc, (s | k) ? 1u : 0u);
                         }
                     }
-                    KAD_TR(1, trc);
                     if (PAIR) {
                         umma_commit_pair(&bars->a_empty[sa]);
                         if (s == last) umma_commit_pair(&bars->acc_full[buf]);
@@ -361,7 +344,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                         umma_commit(&bars->a_empty[sa]);
                         if (s == last) umma_commit(&bars->acc_full[buf]);
                     }
-                    KAD_TR(1, trc);
                 }
                 if (++sa == NA) { sa = 0; pa ^= 1; }
                 if (++sb == nbr) { sb = 0; pb ^= 1; }
@@ -370,7 +352,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
     } else if (warp == WARP_TMA_B) {
         // =========================================================================== weights
-        if (lane == 0 && !(p.dbg & 2)) {
+        if (lane == 0) {
             tma_prefetch_desc(&map_w);
             uint32_t ib = 0, sb = 0;
             uint32_t ja = 0, jp = 0;                  // ring slot / phase parity of the stage whose completion frees the slot
@@ -399,7 +381,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
     } else if (warp == WARP_TMA_WIN) {
         // =========================================================================== input windows
-        if (lane == 0 && !(p.dbg & 8)) {
+        if (lane == 0) {
             tma_prefetch_desc(&map_x);
             uint32_t iw = 0;
             bool ok = true;
@@ -470,7 +452,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         bool ok = true;
         int it = 0;
         uint32_t cur_ia = 0, sa = 0, pa = 0;          // stage counter of this group and its ring slot / phase parity
-        int trc = 0; const bool trp = (pw == 0 && lane == 0);
         prefetch(niter > 0 ? tile_at(0) : -1);
         for (; it < niter && ok; ++it) {
             const int tile_raw = tile_at(it);
@@ -479,7 +460,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             const int b = tile / tiles_per_img, tr = tile - b * tiles_per_img;
             const int ty0 = (tr / p.tiles_x) * p.th, tx0 = (tr % p.tiles_x) * p.tw;
             const int wy0 = ty0 - 1 - p.halo, wx0 = tx0 - 1 - p.halo;
-            if (trp) KAD_TR(0, trc);
             // everybody is done reading the previous table
             if (!group_sync(&bars->tab_free, it & 1, lane, abort_flag)) { report(p.status, 12, it); break; }
             // ---- sample table [row][tap] -> {w_first|w_second, w_first_below|w_second_below, window offset|flags, y0<<16|x0}
@@ -524,9 +504,7 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     table[e] = ent;
                 }
             }
-            if (trp) KAD_TR(0, trc);
             if (!group_sync(&bars->tab_ready, it & 1, lane, abort_flag)) { report(p.status, 13, it); break; }
-            if (trp) KAD_TR(0, trc);
             prefetch(it + 1 < niter ? tile_at(it + 1) : -1);   // next tile's offsets and mask arrive while this tile is gathered
 
             int have_cc = -1;                        // chunks whose window this thread has already waited for
@@ -538,7 +516,6 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     while (sa >= NA) { sa -= NA; pa ^= 1u; }
                 }
                 if (!mbar_wait(&bars->a_empty[sa], pa ^ 1u, abort_flag)) { report(p.status, 7, s); ok = false; break; }
-                if (trp) KAD_TR(0, trc);
                 const uint32_t a_stage = a_base + sa * A_STAGE_BYTES;
                 const int nu = (2 * s + 1 < p.units) ? 2 : 1;     // a trailing single unit is produced twice (harmless)
                 int tapj[2], ccj[2];
@@ -549,14 +526,13 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     ccj[j] = u / 9; tapj[j] = u - ccj[j] * 9;
                     const uint32_t iwc = iw0 + (uint32_t)ccj[j];     // window counter of this chunk
                     const uint32_t sw = iwc % NWIN;
-                    if (ccj[j] > have_cc && !(p.dbg & 8)) {          // first use of this chunk: its window must have landed
+                    if (ccj[j] > have_cc) {          // first use of this chunk: its window must have landed
                         if (!mbar_wait(&bars->win_full[sw], (iwc / NWIN) & 1, abort_flag)) { report(p.status, 8, u); ok = false; }
                         have_cc = ccj[j];
                     }
                     winj[j] = win_base + sw * WIN_BYTES + sub * 16;
                 }
                 if (!ok) break;
-                if (!(p.dbg & 1)) {
 #pragma unroll
                 for (int pass = 0; pass < 2; ++pass) {
                     // two independent tasks (the stage's two units of one row): table reads, then eight corner
@@ -602,11 +578,10 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                         sts128(a_stage + st_off[pass][j], res);
                     }
                 }
-                }
                 // release a chunk's window after this group's last stage that reads it
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    if (j < nu && (j == nu - 1 || ccj[j + 1 < 2 ? j + 1 : j] != ccj[j]) && !(p.dbg & 8)) {
+                    if (j < nu && (j == nu - 1 || ccj[j + 1 < 2 ? j + 1 : j] != ccj[j])) {
                         const int Lc = (9 * ccj[j] + 8) >> 1;                 // last stage holding a unit of the chunk
                         const int Lg = Lc - ((Lc - grp) & 1);                 // ... that belongs to this group
                         if (s == Lg) {
@@ -615,10 +590,9 @@ dsc_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                         }
                     }
                 }
-                if (!(p.dbg & 64)) fence_proxy_async();          // generic-proxy stores -> visible to the tensor core
+                fence_proxy_async();                             // generic-proxy stores -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) { if (PAIR && rank == 1) mbar_arrive_remote(&bars->a_full[sa], 0); else mbar_arrive(&bars->a_full[sa]); }
-                if (trp) KAD_TR(0, trc);
             }
         }
     }
@@ -705,19 +679,17 @@ int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st) {
     p.b_stage_bytes = a.Cout * 128;
     p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
     p.fmt = a.dtype == KAD_BF16 ? 1 : 0;
-    { const char* e = getenv("KAD_DSC_TC_DEBUG"); p.dbg = e ? atoi(e) : 0; }
-    { const char* e = getenv("KAD_DSC_TC_TRACE"); p.trace = e ? (long long*)strtoull(e, nullptr, 16) : nullptr; }
 
     // One CTA per tile, or a CTA pair (cluster of 2, tcgen05 cta_group::2) per two tiles: the pair splits the weight
     // operand by N between the two CTAs' shared memories, which halves the weight bytes every SM has to stage.
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // The pair kernel is selectable (KAD_DSC_TC_PAIR=1) but not the default: on C1 it measured 370-380 us against
-    // 310-320 us for one CTA per tile, because the weight ring and the hand-off between the two CTAs add latency that
-    // the four A stages which fit in shared memory do not cover.
-    bool pair = false;
-    { const char* e = getenv("KAD_DSC_TC_PAIR"); if (e && atoi(e) != 0) pair = a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2; }
+    // path 2 selects the pair kernel. It is not what path 1 uses: on C1 it measured 370-380 us against 310-320 us for
+    // one CTA per tile, because the weight ring and the hand-off between the two CTAs add latency that the four A
+    // stages which fit in shared memory do not cover.
+    const bool pair = a.path == 2;
+    if (pair) KAD_CHECK_ARG(a.Cout % 32 == 0 && p.ntiles >= 2 && sms >= 2, "kad_dsc_forward: the CTA-pair kernel needs Cout %% 32 == 0 and at least two tiles");
     p.npairs = (p.ntiles + 1) / 2;
     p.na = pair ? 4 : 3;
     p.b_stage_bytes = (pair ? a.Cout / 2 : a.Cout) * 128;      // multiple of 2048

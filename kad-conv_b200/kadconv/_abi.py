@@ -11,7 +11,7 @@ _LIB_PATH = Path(__file__).resolve().parent / '_lib' / 'libkadconv_b200.so'
 
 KAD_F32, KAD_F16, KAD_BF16 = 0, 1, 2
 ACT_NONE, ACT_SILU, ACT_RELU = 0, 1, 2
-PATH_SIMT, PATH_TC = 0, 1
+PATH_SIMT, PATH_TC, PATH_TC_PAIR = 0, 1, 2
 
 
 class KadDscArgs(Structure):

@@ -8,7 +8,7 @@ import ctypes
 import torch
 
 from . import _abi
-from ._abi import ACT_NONE, ACT_RELU, ACT_SILU, KAD_BF16, KAD_F16, KAD_F32, PATH_SIMT, PATH_TC
+from ._abi import ACT_NONE, ACT_RELU, ACT_SILU, KAD_BF16, KAD_F16, KAD_F32, PATH_SIMT, PATH_TC, PATH_TC_PAIR
 
 _DT = {torch.float32: KAD_F32, torch.float16: KAD_F16, torch.bfloat16: KAD_BF16}
 

@@ -16,7 +16,7 @@ def _run(x, off, msk, w, b, dtype, path, act=0, scale=None, post=None, want_gap=
     og = None if off is None else nhwc(off).to(dev, off_dtype)
     mg = None if msk is None else nhwc(msk).to(dev, off_dtype)
     Cout, Cin = w.shape[:2]
-    if path == ops.PATH_TC:
+    if path in (ops.PATH_TC, ops.PATH_TC_PAIR):
         wp = ops.pack_dsc_weight_tc(w.to(dev), dtype)
     else:
         wp = ops.pack_dsc_weight_simt(w.to(dev))
@@ -135,3 +135,19 @@ def test_linearity_at_full_c1_size():
     ref = ko.deform_conv2d(xi, off[3:4].half().float().permute(0, 3, 1, 2).cpu(), w1.cpu(), None,
                            msk[3:4].half().float().permute(0, 3, 1, 2).cpu())
     assert rel_err(ys[0][3:4].cpu().permute(0, 3, 1, 2), ref) <= 1e-2
+
+
+@pytest.mark.parametrize('shape', [(2, 64, 64, 20, 25), (1, 96, 256, 13, 30), (3, 128, 96, 10, 11), (1, 32, 32, 9, 7)])
+def test_tc_pair_kernel_matches_single(shape):
+    """The CTA-pair variant (tcgen05 cta_group::2) gives bit-identical results to the one-CTA kernel,
+    including an odd tile count (one CTA of the last pair has no tile)."""
+    B, Cin, Cout, H, W = shape
+    x, off, msk, w, b = dcn_inputs(B, Cin, Cout, H, W, seed=sum(shape) + 1)
+    x, w = round_to(x, torch.float16), round_to(w, torch.float16)
+    g = np.random.default_rng(4)
+    scale = torch.from_numpy(g.uniform(0.5, 1.5, Cout).astype(np.float32))
+    y1, g1 = _run(x, off, msk, w, b, torch.float16, 1, act=2, scale=scale, want_gap=True)
+    y2, g2 = _run(x, off, msk, w, b, torch.float16, 2, act=2, scale=scale, want_gap=True)
+    assert torch.equal(y1, y2) and torch.equal(g1, g2)
+    ref = torch.relu(ko.deform_conv2d(x, off, w, None, msk) * scale.view(1, -1, 1, 1) + (b * scale).view(1, -1, 1, 1))
+    assert rel_err(y2.float().cpu().permute(0, 3, 1, 2), ref) <= 1e-2
