@@ -156,6 +156,38 @@ typedef struct KadMergeArgs {
 } KadMergeArgs;
 int kad_merge_upsample_residual(const KadMergeArgs* args, void* stream);
 
+/* A whole KAD-Conv layer in one call: out = KADConv.forward(x) (KAD-Conv/kadconv/kad_conv.py:112-121,
+ * == KADC4.forward, KAD-CNet/models/module/KADC/module.py:50-62) for n = 3 branches, BatchNorm folded.
+ * The call issues the kernels declared above for the three branches on three streams (the caller's stream and
+ * two side streams the library creates once per device on the first call; fork and join by events), so the
+ * branches overlap; under stream capture this becomes three parallel chains of the captured graph.
+ * Counterpart of the reference's multi-stream branch schedulers (kadc_fused_parallel.py:268-286).
+ *   x, out [B,H,W,dim] dtype (NHWC); branch i works at (H >> i) x (W >> i) with c_i channels
+ *   (c_0 = dim - 2*(dim/3), c_1 = c_2 = dim/3); parameters float32 as named below;
+ *   w_off: kad_dsc_pack_weight_simt of conv_offset.weight; w_dsc_simt: the same of DSC.weight;
+ *   w_dsc_tc: kad_dsc_pack_weight_tc of DSC.weight in dtype, or NULL (then, or when the shape does not
+ *   qualify, the SIMT kernel runs); ep_scale/ep_shift/ep_post: folded BatchNorm (+ conv bias) and branch scale;
+ *   workspace: kad_kadconv_workspace_bytes(B,H,W,dim,dtype,tc_branches) bytes, 256-byte aligned, where bit i of
+ *   tc_branches says that branch i passes w_dsc_tc and qualifies for it; status: device int[4] as for kad_dsc_forward.
+ * Calls for one device must not be issued concurrently from several host threads (they share the side streams). */
+typedef struct KadBranchParams {
+    const float* w_proj; const float* b_proj;                       /* [c][dim], [c] */
+    const float* lcsa_w1; const float* lcsa_b1; const float* lcsa_bn_scale; const float* lcsa_bn_shift;
+    const float* lcsa_w2; const float* lcsa_b2; const float* lcsa_w3; const float* lcsa_b3;
+    const float* w_off; const float* b_off;                         /* [9][c][18], [18] */
+    const float* w_dsc_simt; const void* w_dsc_tc;
+    const float* ep_scale; const float* ep_shift; const float* ep_post;
+    const float* fc_w1; const float* fc_b1; const float* fc_w2; const float* fc_b2;   /* [hidden][c], [hidden], [c][hidden], [c] */
+    int c, hidden;
+} KadBranchParams;
+typedef struct KadLayerArgs {
+    const void* x; void* out; void* workspace; size_t workspace_bytes; int* status;
+    int B, H, W, dim, dtype;
+    KadBranchParams br[3];
+} KadLayerArgs;
+size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches);
+int kad_kadconv_forward(const KadLayerArgs* args, void* stream);
+
 /* Batched detection post-processing, one launch for the whole batch. Replaces non_max_suppression
  * (KAD-CNet/utils/general.py:881-990: confidence filter, xywh->xyxy, best class, sort by confidence, class-shifted
  * torchvision.ops.nms at :972, max_det cap) for multi_label = False, agnostic = False.

@@ -425,7 +425,12 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     int Cp = ((a->C + 31) / 32) * 32;
     if (Cp > 256) Cp = 256;
     const int HW = a->H * a->W;
-    int pix_per_block = 4 * (256 / Cp);     // four pixels per thread: enough blocks to fill the GPU on small feature maps
+    // pixels per thread: 4 on small feature maps (enough blocks to fill the GPU), up to 32 on large ones (amortises the
+    // per-thread channel set-up)
+    const int PL = 256 / Cp;
+    long long want = ((long long)HW * a->B) / ((long long)PL * 148 * 8);
+    int iters = want < 4 ? 4 : (want > 32 ? 32 : (int)want);
+    int pix_per_block = iters * PL;
     dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
     KAD_DISPATCH_DTYPE(a->dtype, {
         merge_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);

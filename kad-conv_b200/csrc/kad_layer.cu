@@ -1,0 +1,157 @@
+// One C-ABI call for a whole KAD-Conv layer (KADConv.forward of the reference, KAD-Conv/kadconv/kad_conv.py:112-121):
+// the three branches are independent until the final concat, so they are issued on three streams (the caller's stream
+// and two library-owned side streams, forked and joined with events) and run concurrently; under stream capture
+// the fork/join becomes three parallel chains of one CUDA graph. All intermediate tensors live in a workspace the
+// caller provides, so nothing is allocated per call.
+#include <mutex>
+
+#include "kad_common.cuh"
+
+namespace kad {
+namespace {
+
+struct SideStreams {
+    cudaStream_t s[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
+    bool ready = false;
+};
+constexpr int MAX_DEVICES = 64;
+SideStreams g_side[MAX_DEVICES];
+std::mutex g_side_mutex;
+
+int side_streams(int dev, SideStreams** out) {
+    std::lock_guard<std::mutex> lock(g_side_mutex);
+    SideStreams& ss = g_side[dev];
+    if (!ss.ready) {
+        for (int i = 0; i < 2; ++i) {
+            cudaError_t e = cudaStreamCreateWithFlags(&ss.s[i], cudaStreamNonBlocking);
+            if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: side stream: %s", cudaGetErrorString(e));
+            e = cudaEventCreateWithFlags(&ss.join[i], cudaEventDisableTiming);
+            if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: event: %s", cudaGetErrorString(e));
+        }
+        cudaError_t e = cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: event: %s", cudaGetErrorString(e));
+        ss.ready = true;
+    }
+    *out = &ss;
+    return KAD_OK;
+}
+
+inline size_t align_up(size_t v) { return (v + 255) & ~size_t(255); }
+
+struct BranchWs {
+    size_t t, rows, cols, scratch, mask, offset, y, gap, att, end;
+};
+
+BranchWs plan_branch(size_t base, int B, int h, int w, int c, size_t es, int gap_tiles) {
+    BranchWs p;
+    size_t o = base;
+    p.t = o; o = align_up(o + (size_t)B * h * w * c * es);
+    p.rows = o; o = align_up(o + (size_t)B * h * c * 4);
+    p.cols = o; o = align_up(o + (size_t)B * w * c * 4);
+    p.scratch = o; o = align_up(o + ((size_t)B * w * c + (size_t)w * c) * 4);
+    p.mask = o; o = align_up(o + (size_t)B * h * w * 9 * 4);
+    p.offset = o; o = align_up(o + (size_t)B * h * w * 18 * 4);
+    p.y = o; o = align_up(o + (size_t)B * h * w * c * es);
+    p.gap = o; o = align_up(o + (size_t)B * gap_tiles * c * 4);
+    p.att = o; o = align_up(o + (size_t)B * c * 4);
+    p.end = o;
+    return p;
+}
+
+int branch_path(const KadBranchParams& br, int dtype) {
+    return (br.w_dsc_tc && kad_dsc_tc_supported(br.c, br.c, dtype)) ? 1 : 0;
+}
+
+}  // namespace
+}  // namespace kad
+
+using namespace kad;
+
+extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches) {
+    if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
+    const size_t es = dtype_size(dtype);
+    const int widths[3] = {dim - (dim / 3) * 2, dim / 3, dim / 3};
+    size_t o = 0;
+    for (int i = 0; i < 3; ++i) {
+        const int h = H >> i, w = W >> i;
+        const int path = ((tc_branches >> i) & 1) ? 1 : 0;
+        o = plan_branch(o, B, h, w, widths[i], es, kad_dsc_gap_tiles(h, w, widths[i], widths[i], path)).end;
+    }
+    return o;
+}
+
+extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
+    KAD_CHECK_ARG(a && a->x && a->out && a->workspace && a->status, "kad_kadconv_forward: null pointer");
+    KAD_CHECK_ARG(a->B > 0 && a->H >= 4 && a->W >= 4 && a->dim >= 3, "kad_kadconv_forward: bad shape B=%d H=%d W=%d dim=%d", a->B, a->H, a->W, a->dim);
+    const int widths[3] = {a->dim - (a->dim / 3) * 2, a->dim / 3, a->dim / 3};
+    int tc_mask = 0;
+    for (int i = 0; i < 3; ++i) {
+        KAD_CHECK_ARG(a->br[i].c == widths[i], "kad_kadconv_forward: branch %d has %d channels, expected %d", i, a->br[i].c, widths[i]);
+        if (branch_path(a->br[i], a->dtype)) tc_mask |= 1 << i;
+    }
+    KAD_CHECK_ARG(a->workspace_bytes >= kad_kadconv_workspace_bytes(a->B, a->H, a->W, a->dim, a->dtype, tc_mask),
+                  "kad_kadconv_forward: workspace of %zu bytes is too small", a->workspace_bytes);
+    KAD_CHECK_ARG((uintptr_t)a->workspace % 256 == 0, "kad_kadconv_forward: workspace must be 256-byte aligned");
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: cudaGetDevice: %s", cudaGetErrorString(e));
+    KAD_CHECK_ARG(dev >= 0 && dev < MAX_DEVICES, "kad_kadconv_forward: device index %d out of range", dev);
+    SideStreams* ss = nullptr;
+    int rc = side_streams(dev, &ss);
+    if (rc) return rc;
+    cudaStream_t main_s = (cudaStream_t)stream;
+    cudaStream_t st[3] = {main_s, ss->s[0], ss->s[1]};
+
+    // fork
+    if ((e = cudaEventRecord(ss->fork, main_s)) != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: fork: %s", cudaGetErrorString(e));
+    for (int i = 1; i < 3; ++i)
+        if ((e = cudaStreamWaitEvent(st[i], ss->fork, 0)) != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: fork wait: %s", cudaGetErrorString(e));
+
+    const size_t es = dtype_size(a->dtype);
+    unsigned char* ws = reinterpret_cast<unsigned char*>(a->workspace);
+    KadMergeArgs m{};
+    m.x = a->x; m.out = a->out; m.B = a->B; m.H = a->H; m.W = a->W; m.C = a->dim; m.dtype = a->dtype;
+    size_t o = 0;
+    for (int i = 0; i < 3 && rc == KAD_OK; ++i) {
+        const KadBranchParams& br = a->br[i];
+        const int h = a->H >> i, w = a->W >> i, c = br.c;
+        const int path = (tc_mask >> i) & 1;
+        const int tiles = kad_dsc_gap_tiles(h, w, c, c, path);
+        const BranchWs p = plan_branch(o, a->B, h, w, c, es, tiles);
+        o = p.end;
+        void* s = (void*)st[i];
+        rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
+        if (rc) break;
+        rc = kad_lcsa_sums(ws + p.t, (float*)(ws + p.rows), (float*)(ws + p.cols), a->B, h, w, c, a->dtype, s);
+        if (rc) break;
+        rc = kad_lcsa_mask((const float*)(ws + p.rows), (const float*)(ws + p.cols), br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift,
+                           br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3, (float*)(ws + p.scratch), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
+        if (rc) break;
+        KadDscArgs d{};
+        d.x = ws + p.t; d.weight = br.w_off; d.shift = br.b_off; d.y = ws + p.offset;
+        d.B = a->B; d.H = h; d.W = w; d.Cin = c; d.Cout = 18; d.dtype = a->dtype; d.y_f32 = 1; d.act = KAD_ACT_NONE; d.path = 0; d.status = a->status;
+        rc = kad_dsc_forward(&d, s);
+        if (rc) break;
+        KadDscArgs q{};
+        q.x = ws + p.t; q.offset = ws + p.offset; q.mask = ws + p.mask; q.offset_f32 = 1; q.mask_f32 = 1;
+        q.weight = path ? br.w_dsc_tc : (const void*)br.w_dsc_simt;
+        q.scale = br.ep_scale; q.shift = br.ep_shift; q.post = br.ep_post; q.y = ws + p.y; q.gap_partial = (float*)(ws + p.gap);
+        q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;
+        rc = kad_dsc_forward(&q, s);
+        if (rc) break;
+        rc = kad_se_excite((const float*)(ws + p.gap), tiles, 1.0f / (float)(h * w), br.fc_w1, br.fc_b1, br.fc_w2, br.fc_b2, (float*)(ws + p.att),
+                           a->B, c, br.hidden, s);
+        if (rc) break;
+        m.y[i] = ws + p.y; m.att[i] = (const float*)(ws + p.att); m.c[i] = c; m.h[i] = h; m.w[i] = w;
+    }
+    // join (always, so that a capture in progress is left well-formed even after an argument error)
+    for (int i = 1; i < 3; ++i) {
+        cudaError_t e1 = cudaEventRecord(ss->join[i - 1], st[i]);
+        cudaError_t e2 = cudaStreamWaitEvent(main_s, ss->join[i - 1], 0);
+        if (rc == KAD_OK && (e1 != cudaSuccess || e2 != cudaSuccess))
+            rc = fail(KAD_ERR_CUDA, "kad_kadconv_forward: join: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    }
+    if (rc) return rc;
+    return kad_merge_upsample_residual(&m, stream);
+}

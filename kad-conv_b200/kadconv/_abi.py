@@ -29,6 +29,17 @@ class KadMergeArgs(Structure):
                 ('B', c_int), ('H', c_int), ('W', c_int), ('C', c_int), ('dtype', c_int)]
 
 
+class KadBranchParams(Structure):
+    _fields_ = [(n, c_void_p) for n in ('w_proj', 'b_proj', 'lcsa_w1', 'lcsa_b1', 'lcsa_bn_scale', 'lcsa_bn_shift', 'lcsa_w2', 'lcsa_b2',
+                                        'lcsa_w3', 'lcsa_b3', 'w_off', 'b_off', 'w_dsc_simt', 'w_dsc_tc', 'ep_scale', 'ep_shift', 'ep_post',
+                                        'fc_w1', 'fc_b1', 'fc_w2', 'fc_b2')] + [('c', c_int), ('hidden', c_int)]
+
+
+class KadLayerArgs(Structure):
+    _fields_ = [('x', c_void_p), ('out', c_void_p), ('workspace', c_void_p), ('workspace_bytes', c_size_t), ('status', c_void_p),
+                ('B', c_int), ('H', c_int), ('W', c_int), ('dim', c_int), ('dtype', c_int), ('br', KadBranchParams * 3)]
+
+
 # name -> (restype, argtypes); every symbol declared in include/kadconv_b200.h
 SIGNATURES = {
     'kad_version': (c_int, []),
@@ -54,6 +65,8 @@ SIGNATURES = {
     'kad_se_squeeze': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_se_rescale': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_merge_upsample_residual': (c_int, [POINTER(KadMergeArgs), c_void_p]),
+    'kad_kadconv_workspace_bytes': (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    'kad_kadconv_forward': (c_int, [POINTER(KadLayerArgs), c_void_p]),
     'kad_nms_max_anchors': (c_int, []),
     'kad_nms_batched': (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]),
     'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
@@ -89,7 +102,7 @@ def load():
 
 # Number of kernels launched through this binding so far (a plain counter the benchmark reads).
 KERNELS_LAUNCHED = [0]
-_KERNELS_PER_CALL = {'kad_lcsa_sums': 2, 'kad_lcsa_mask': 2}
+_KERNELS_PER_CALL = {'kad_lcsa_sums': 2, 'kad_lcsa_mask': 2, 'kad_kadconv_forward': 25}
 
 
 def check(code, what):

@@ -74,13 +74,60 @@ def _prepare(layer, device):
     return st
 
 
+def _layer_args(layer, st, dtype):
+    """ctypes argument block of kad_kadconv_forward for this layer and activation dtype (built once, then reused)."""
+    import ctypes
+    from . import _abi
+    key = ('args', dtype)
+    if key not in st:
+        a = _abi.KadLayerArgs()
+        tc_mask = 0
+        keep = []
+        for i, br in enumerate(st['branches']):
+            p = a.br[i]
+            path, w = br.dsc_weight(dtype)
+            fields = dict(w_proj=br.w_proj, b_proj=br.b_proj, lcsa_w1=br.lcsa['w1'], lcsa_b1=br.lcsa['b1'], lcsa_bn_scale=br.lcsa['bn_m'],
+                          lcsa_bn_shift=br.lcsa['bn_a'], lcsa_w2=br.lcsa['w2'], lcsa_b2=br.lcsa['b2'], lcsa_w3=br.lcsa['w3'], lcsa_b3=br.lcsa['b3'],
+                          w_off=br.w_off, b_off=br.b_off, w_dsc_simt=br.w_dsc_simt, ep_scale=br.ep_scale, ep_shift=br.ep_shift,
+                          ep_post=br.ep_post, fc_w1=br.fc_w1, fc_b1=br.fc_b1, fc_w2=br.fc_w2, fc_b2=br.fc_b2)
+            for name, t in fields.items():
+                setattr(p, name, t.data_ptr())
+            if path == ops.PATH_TC:
+                p.w_dsc_tc = w.data_ptr(); keep.append(w); tc_mask |= 1 << i
+            p.c, p.hidden = br.c, br.fc_w1.shape[0]
+        a.dtype = ops._DT[dtype]
+        st[key] = (a, tc_mask, keep)
+    return st[key]
+
+
 def kadconv_forward_nhwc(layer, x):
-    """The accelerated KADConv forward on a contiguous NHWC tensor; returns NHWC."""
+    """The accelerated KADConv forward on a contiguous NHWC tensor; returns NHWC. One C-ABI call per layer
+    (kad_kadconv_forward): the three branches run on three streams and all intermediates live in one workspace."""
+    import ctypes
+    from . import _abi
     if layer.n != 3:
         raise RuntimeError('the B200 pipeline implements the 3-branch KAD-Conv (n=3)')
+    x = ops._cuda(x, 'x')
     B, H, W, C = x.shape
     if H < 4 or W < 4:
         raise RuntimeError(f'KAD-Conv needs H, W >= 4 for its 1/4-resolution branch, got {H}x{W}')
+    st = _prepare(layer, x.device)
+    a, tc_mask, _ = _layer_args(layer, st, x.dtype)
+    lib = _abi.load()
+    nbytes = lib.kad_kadconv_workspace_bytes(B, H, W, C, a.dtype, tc_mask)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    out = torch.empty_like(x)
+    a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes
+    a.status = ops.status_word(x.device).data_ptr()
+    a.B, a.H, a.W, a.dim = B, H, W, C
+    _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward')
+    return out
+
+
+def kadconv_forward_nhwc_stepwise(layer, x):
+    """The same computation issued kernel by kernel from Python on the current stream (kept for tests that
+    look at intermediate tensors)."""
+    B, H, W, C = x.shape
     st = _prepare(layer, x.device)
     ys, atts = [], []
     for i, br in enumerate(st['branches']):

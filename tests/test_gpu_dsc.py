@@ -137,7 +137,7 @@ def test_linearity_at_full_c1_size():
     assert rel_err(ys[0][3:4].cpu().permute(0, 3, 1, 2), ref) <= 1e-2
 
 
-@pytest.mark.parametrize('shape', [(2, 64, 64, 20, 25), (1, 96, 256, 13, 30), (3, 128, 96, 10, 11), (1, 32, 32, 9, 7)])
+@pytest.mark.parametrize('shape', [(2, 64, 64, 20, 25), (1, 96, 256, 13, 30), (3, 128, 96, 10, 11), (1, 32, 32, 19, 17)])
 def test_tc_pair_kernel_matches_single(shape):
     """The CTA-pair variant (tcgen05 cta_group::2) gives bit-identical results to the one-CTA kernel,
     including an odd tile count (one CTA of the last pair has no tile)."""

@@ -100,3 +100,33 @@ def test_fast_mode_refuses_cpu_and_training():
     layer.eval()
     kadconv.disable_fast_inference(layer)
     assert 'forward' not in vars(layer)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+def test_layer_call_matches_stepwise_kernels(dtype):
+    """kad_kadconv_forward (one call, three streams, one workspace) is bit-identical to issuing the same kernels one
+    by one on a single stream, also when called twice in a row and inside a CUDA graph."""
+    import kadconv
+    from kadconv import fast, ops
+    layer, _ = _layer(48, 31, dtype=dtype)
+    kadconv.enable_fast_inference(layer.cuda())
+    x = round_to(seeding.seeded_input((3, 27, 22, 48), seed=31), dtype).cuda().to(dtype)     # NHWC
+    ref = fast.kadconv_forward_nhwc_stepwise(layer, x)
+    a = fast.kadconv_forward_nhwc(layer, x)
+    b = fast.kadconv_forward_nhwc(layer, x)
+    torch.cuda.synchronize()
+    assert torch.equal(a, ref) and torch.equal(b, ref)
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fast.kadconv_forward_nhwc(layer, x)
+    torch.cuda.current_stream().wait_stream(s)
+    with torch.cuda.graph(g, stream=s):
+        out = fast.kadconv_forward_nhwc(layer, x)
+        out2 = fast.kadconv_forward_nhwc(layer, out)      # a second fork/join inside the same capture
+    g.replay(); g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    assert torch.equal(out2, fast.kadconv_forward_nhwc_stepwise(layer, ref))
+    ops.check_status(x.device)
