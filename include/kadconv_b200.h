@@ -99,6 +99,16 @@ int kad_pool_project(const void* x, const float* w, const float* bias, void* y,
  * (KAD-Conv/kadconv/kad_conv.py:115) when the pooled tensor feeds the tensor-core 1x1 GEMM. */
 int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, int dtype, void* stream);
 
+/* Detector glue (KAD-CNet-S outside its KAD-Conv layers), NHWC:
+ *  kad_avg_pool2x2s1    avg_pool2d(x, 2, 1, 0) of AConv.forward (KAD-CNet/models/common.py:65-66): [B,H,W,C] -> [B,H-1,W-1,C]
+ *  kad_bias_act_inplace y = act(y + bias[c]) on [M][C]: the bias + SiLU of Conv.forward_fuse (common.py:56-57) after a
+ *                       bias-free 3x3 convolution (counterpart of bias_silu_float4_kernel, kadc_gemm_silu.cu:67-88)
+ *  kad_image_to_nhwc    uint8 [B,C,H,W] image batch -> dtype [B,H,W,Cp], value * scale, channels C..Cp-1 zero: the
+ *                       `/255` normalisation of KAD-CNet/inference/infer_dior.py:39-46 fused with the layout change */
+int kad_avg_pool2x2s1(const void* x, void* y, int B, int H, int W, int C, int dtype, void* stream);
+int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act, int dtype, void* stream);
+int kad_image_to_nhwc(const void* img_u8, void* y, int B, int C, int H, int W, int Cp, float scale, int dtype, void* stream);
+
 /* LCSA, step 1: row sums [B,H,C] (over x) and column sums [B,W,C] (over y) of x[B,H,W,C], float32.
  * Replaces pool_h / pool_w of LCSA.forward (kad_conv.py:27-28,:39). */
 int kad_lcsa_sums(const void* x, float* rowsum, float* colsum, int B, int H, int W, int C, int dtype, void* stream);

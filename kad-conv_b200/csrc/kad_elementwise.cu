@@ -534,3 +534,117 @@ extern "C" int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, 
     KAD_CHECK_LAUNCH("avg_pool_kernel");
     return KAD_OK;
 }
+
+
+// ------------------------------------------------------------------------------ detector glue kernels
+namespace kad { namespace {
+
+// 2x2 average pool with stride 1 (AConv's pre-pool, KAD-CNet/models/common.py:65): y[b,y,x,:] = mean of the 2x2 block at (y,x).
+template <typename T>
+__global__ void avg_pool2x2s1_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int C8, size_t n) {
+    const int Ho = H - 1, Wo = W - 1;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % C8);
+        size_t r = e / C8;
+        const int xo = (int)(r % Wo); r /= Wo;
+        const int yo = (int)(r % Ho); const int b = (int)(r / Ho);
+        const uint4* base = x + (((size_t)b * H + yo) * W + xo) * C8 + c;
+        const uint4 v00 = base[0], v01 = base[C8], v10 = base[(size_t)W * C8], v11 = base[(size_t)(W + 1) * C8];
+        const T* a = reinterpret_cast<const T*>(&v00); const T* bq = reinterpret_cast<const T*>(&v01);
+        const T* cq = reinterpret_cast<const T*>(&v10); const T* d = reinterpret_cast<const T*>(&v11);
+        uint4 o; T* ho = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ho[i] = from_f<T>((to_f<T>(a[i]) + to_f<T>(bq[i]) + to_f<T>(cq[i]) + to_f<T>(d[i])) * 0.25f);
+        y[e] = o;
+    }
+}
+template <typename T>
+__global__ void avg_pool2x2s1_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int C, size_t n) {
+    const int Ho = H - 1, Wo = W - 1;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % C);
+        size_t r = e / C;
+        const int xo = (int)(r % Wo); r /= Wo;
+        const int yo = (int)(r % Ho); const int b = (int)(r / Ho);
+        const T* base = x + (((size_t)b * H + yo) * W + xo) * C + c;
+        y[e] = from_f<T>((to_f<T>(base[0]) + to_f<T>(base[C]) + to_f<T>(base[(size_t)W * C]) + to_f<T>(base[(size_t)(W + 1) * C])) * 0.25f);
+    }
+}
+
+// y = act(y + bias[c]) in place on an [M][C] tensor
+template <typename T>
+__global__ void bias_act_vec8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, int C8, size_t n, int act) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % C8);
+        uint4 v = y[e];
+        T* h = reinterpret_cast<T*>(&v);
+        const float4 b0 = bias ? reinterpret_cast<const float4*>(bias)[2 * c] : make_float4(0, 0, 0, 0);
+        const float4 b1 = bias ? reinterpret_cast<const float4*>(bias)[2 * c + 1] : make_float4(0, 0, 0, 0);
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a = to_f<T>(h[i]) + bb[i];
+            h[i] = from_f<T>(act == KAD_ACT_SILU ? __fdividef(a, 1.f + __expf(-a)) : (act == KAD_ACT_RELU ? fmaxf(a, 0.f) : a));
+        }
+        y[e] = v;
+    }
+}
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bias, int C, size_t n, int act) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const float a = to_f<T>(y[e]) + (bias ? bias[e % C] : 0.f);
+        y[e] = from_f<T>(apply_act(a, act));
+    }
+}
+
+// uint8 NCHW image batch -> T NHWC, value * scale, channels zero-padded from C to Cp (Cp * sizeof(T) == 16 here)
+template <typename T>
+__global__ void image_to_nhwc_kernel(const unsigned char* __restrict__ img, T* __restrict__ y, int C, int Cp, size_t HW, size_t n, float scale) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t b = e / HW, p = e - b * HW;
+        const unsigned char* src = img + b * C * HW + p;
+        T* dst = y + e * Cp;
+        for (int c = 0; c < Cp; ++c) dst[c] = from_f<T>(c < C ? (float)src[(size_t)c * HW] * scale : 0.f);
+    }
+}
+} }
+
+extern "C" int kad_avg_pool2x2s1(const void* x, void* y, int B, int H, int W, int C, int dtype, void* stream) {
+    KAD_CHECK_ARG(x && y && B > 0 && H > 1 && W > 1 && C > 0, "kad_avg_pool2x2s1: bad argument");
+    const size_t n = (size_t)B * (H - 1) * (W - 1) * C;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != KAD_F32 && C % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+        const size_t nv = n / 8;
+        if (dtype == KAD_F16) avg_pool2x2s1_vec8_kernel<__half><<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, H, W, C / 8, nv);
+        else avg_pool2x2s1_vec8_kernel<__nv_bfloat16><<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, H, W, C / 8, nv);
+    } else {
+        KAD_DISPATCH_DTYPE(dtype, { avg_pool2x2s1_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)x, (T*)y, H, W, C, n); });
+    }
+    KAD_CHECK_LAUNCH("avg_pool2x2s1_kernel");
+    return KAD_OK;
+}
+
+extern "C" int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act, int dtype, void* stream) {
+    KAD_CHECK_ARG(y && M > 0 && C > 0, "kad_bias_act_inplace: bad argument");
+    const size_t n = (size_t)M * C;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != KAD_F32 && C % 8 == 0 && (uintptr_t)y % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0)) {
+        const size_t nv = n / 8;
+        if (dtype == KAD_F16) bias_act_vec8_kernel<__half><<<grid_for(nv, 256), 256, 0, st>>>((uint4*)y, bias, C / 8, nv, act);
+        else bias_act_vec8_kernel<__nv_bfloat16><<<grid_for(nv, 256), 256, 0, st>>>((uint4*)y, bias, C / 8, nv, act);
+    } else {
+        KAD_DISPATCH_DTYPE(dtype, { bias_act_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((T*)y, bias, C, n, act); });
+    }
+    KAD_CHECK_LAUNCH("bias_act_kernel");
+    return KAD_OK;
+}
+
+extern "C" int kad_image_to_nhwc(const void* img_u8, void* y, int B, int C, int H, int W, int Cp, float scale, int dtype, void* stream) {
+    KAD_CHECK_ARG(img_u8 && y && B > 0 && C > 0 && H > 0 && W > 0 && Cp >= C, "kad_image_to_nhwc: bad argument");
+    const size_t HW = (size_t)H * W, n = (size_t)B * HW;
+    KAD_DISPATCH_DTYPE(dtype, {
+        image_to_nhwc_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const unsigned char*)img_u8, (T*)y, C, Cp, HW, n, scale);
+    });
+    KAD_CHECK_LAUNCH("image_to_nhwc_kernel");
+    return KAD_OK;
+}

@@ -53,20 +53,23 @@ class _Conv1x1:
 
 
 class _ConvKxK:
-    """3x3 (or grouped / strided) convolution + bias + SiLU through the library on a channels_last view."""
+    """3x3 (or grouped / strided) convolution through the library on a channels_last view, without bias; the bias and
+    the SiLU are applied in place by one kadconv kernel. `cin_pad` zero-pads the input channels of the weight (the
+    first layer reads the image padded from 3 to 8 channels so that a tensor-core kernel can be chosen)."""
 
-    def __init__(self, conv_mod, dtype, device):
+    def __init__(self, conv_mod, dtype, device, cin_pad=None):
         conv = conv_mod.conv if hasattr(conv_mod, 'conv') else conv_mod
-        self.w = conv.weight.detach().to(device, dtype).contiguous(memory_format=torch.channels_last)
-        self.b = conv.bias.detach().to(device, dtype)
+        w = conv.weight.detach().to(device, dtype)
+        if cin_pad is not None and cin_pad > w.shape[1]:
+            w = F.pad(w, (0, 0, 0, 0, 0, cin_pad - w.shape[1]))
+        self.w = w.contiguous(memory_format=torch.channels_last)
+        self.b = conv.bias.detach().float().contiguous().to(device)
         self.stride, self.padding, self.groups = conv.stride, conv.padding, conv.groups
-        self.silu = hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)
+        self.act = ops.ACT_SILU if (hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)) else ops.ACT_NONE
 
     def __call__(self, x):
-        y = F.conv2d(_nchw_view(x), self.w, self.b, self.stride, self.padding, 1, self.groups)
-        if self.silu:
-            y = F.silu(y, inplace=True)
-        return _nhwc(y)
+        y = _nhwc(F.conv2d(_nchw_view(x), self.w, None, self.stride, self.padding, 1, self.groups))
+        return ops.bias_act_(y, self.b, self.act)
 
 
 def _conv(conv_mod, dtype, device):
@@ -96,11 +99,11 @@ class FastDetector(torch.nn.Module):
     def _compile(self, m):
         dt, dev = self.dtype, self.device
         if isinstance(m, M.Conv):
-            c = _conv(m, dt, dev)
+            c = _ConvKxK(m, dt, dev, cin_pad=8) if (m.i == 0 and m.conv.in_channels < 8 and m.conv.kernel_size != (1, 1)) else _conv(m, dt, dev)
             return lambda x: c(x)
         if isinstance(m, M.AConv):
             c = _ConvKxK(m.cv1, dt, dev)
-            return lambda x: c(_nhwc(F.avg_pool2d(_nchw_view(x), 2, 1, 0, False, True)))
+            return lambda x: c(ops.avg_pool2x2s1(x))
         if isinstance(m, M.ELAN1):
             cv1, cv2, cv3, cv4 = (_conv(t, dt, dev) for t in (m.cv1, m.cv2, m.cv3, m.cv4))
             half = m.c
@@ -193,9 +196,18 @@ class FastDetector(torch.nn.Module):
     # ---- forward -------------------------------------------------------------------------------
     @torch.no_grad()
     def forward(self, x):
+        """x: float [B,3,H,W] in [0,1] (any float dtype), or a uint8 image batch [B,3,H,W] in [0,255], which is
+        normalised by 1/255 on the way in (the `/255` of the reference's inference scripts)."""
         if not x.is_cuda:
             raise RuntimeError('FastDetector has no CPU path: move the input to the GPU')
-        x = ops.to_nhwc(x.to(self.dtype))
+        first = self.model.model[0]
+        pad8 = isinstance(first, M.Conv) and first.conv.in_channels < 8 and first.conv.kernel_size != (1, 1)
+        if x.dtype == torch.uint8:
+            x = ops.image_to_nhwc(x.contiguous(), self.dtype, cpad=8 if pad8 else x.shape[1])
+        else:
+            x = ops.to_nhwc(x.to(self.dtype))
+            if pad8:
+                x = F.pad(x, (0, 8 - x.shape[-1]))
         ys = []
         save = self.model.save
         for m, fn in zip(self.model.model, self.plan):

@@ -55,6 +55,9 @@ SIGNATURES = {
     'kad_pool_project': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_void_p]),
     'kad_avg_pool': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_avg_pool2x2s1': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_bias_act_inplace': (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]),
+    'kad_image_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask': (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask_noalloc_max_floats': (c_size_t, []),

@@ -312,3 +312,33 @@ def avg_pool(x, pool):
     y = torch.empty((B, H // pool, W // pool, C), dtype=x.dtype, device=x.device)
     _abi.check(_abi.load().kad_avg_pool(_ptr(x), _ptr(y), B, H, W, C, pool, dtype_code(x), _stream()), 'kad_avg_pool')
     return y
+
+
+def avg_pool2x2s1(x):
+    """NHWC 2x2 average pool with stride 1 (no padding)."""
+    x = _cuda(x, 'x')
+    B, H, W, C = x.shape
+    y = torch.empty((B, H - 1, W - 1, C), dtype=x.dtype, device=x.device)
+    _abi.check(_abi.load().kad_avg_pool2x2s1(_ptr(x), _ptr(y), B, H, W, C, dtype_code(x), _stream()), 'kad_avg_pool2x2s1')
+    return y
+
+
+def bias_act_(y, bias, act=ACT_SILU):
+    """In place y = act(y + bias) over the last dimension of a contiguous tensor."""
+    y = _cuda(y, 'y')
+    C = y.shape[-1]
+    _abi.check(_abi.load().kad_bias_act_inplace(_ptr(y), _ptr(_f32(bias, 'bias')), y.numel() // C, C, act, dtype_code(y), _stream()),
+               'kad_bias_act_inplace')
+    return y
+
+
+def image_to_nhwc(img_u8, dtype, cpad=8, scale=1.0 / 255.0):
+    """uint8 [B,C,H,W] -> dtype [B,H,W,cpad], scaled, extra channels zero."""
+    img_u8 = _cuda(img_u8, 'img')
+    if img_u8.dtype != torch.uint8:
+        raise TypeError('image_to_nhwc expects a uint8 tensor')
+    B, C, H, W = img_u8.shape
+    y = torch.empty((B, H, W, cpad), dtype=dtype, device=img_u8.device)
+    _abi.check(_abi.load().kad_image_to_nhwc(_ptr(img_u8), _ptr(y), B, C, H, W, cpad, ctypes.c_float(scale), _DT[dtype], _stream()),
+               'kad_image_to_nhwc')
+    return y

@@ -98,3 +98,14 @@ def test_batched_nms_kernel_matches_oracle(golden_dir, dtype):
     assert all(c.shape[0] == min(7, r.shape[0]) and torch.equal(c.cpu(), r[:7].float()) for c, r in zip(capped, ref))
     if dtype == torch.float32:
         assert torch.equal(out[0].cpu(), torch.from_numpy(g['det']))
+
+
+def test_engine_uint8_input_equals_float_input(golden_dir):
+    """The uint8 entry (image -> /255 -> NHWC in one kernel) gives the same result as feeding the normalised float image."""
+    import kadcnet
+    g, sd = _sd(golden_dir)
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    img = seeding.seeded_input((2, 3, 160, 192), seed=9, kind='image').cuda()
+    y8, _ = fast(img)
+    yf, _ = fast((img.float() / 255).half())
+    assert torch.equal(y8, yf)

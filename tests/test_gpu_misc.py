@@ -133,3 +133,19 @@ def test_avg_pool():
             ref = F.avg_pool2d(x, pool)
             y = ops.avg_pool(nhwc(x).cuda().to(dtype), pool).float().cpu().permute(0, 3, 1, 2)
             assert rel_err(y, ref) <= (1e-6 if dtype == torch.float32 else 1e-2)
+
+
+def test_detector_glue_kernels():
+    from kadconv import ops
+    for dtype in (torch.float32, torch.float16):
+        x = round_to(_rand((2, 24, 9, 14), 50), dtype)
+        ref = F.avg_pool2d(x, 2, 1, 0, False, True)
+        y = ops.avg_pool2x2s1(nhwc(x).cuda().to(dtype)).float().cpu().permute(0, 3, 1, 2)
+        assert rel_err(y, ref) <= (1e-6 if dtype == torch.float32 else 2e-3)
+        t = round_to(_rand((5, 7, 16), 51), dtype); b = _rand((16,), 52, 0.3)
+        out = ops.bias_act_(t.cuda().to(dtype).clone(), b.cuda(), ops.ACT_SILU).float().cpu()
+        assert rel_err(out, F.silu(t + b)) <= (1e-5 if dtype == torch.float32 else 2e-3)
+    img = torch.from_numpy(np.random.default_rng(3).integers(0, 256, (2, 3, 11, 13), dtype=np.uint8))
+    y = ops.image_to_nhwc(img.cuda(), torch.float16, cpad=8).cpu()
+    ref = (img.float() / 255).half().permute(0, 2, 3, 1)
+    assert torch.equal(y[..., :3], ref) and y[..., 3:].abs().max().item() == 0
