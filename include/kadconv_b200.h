@@ -67,13 +67,24 @@ typedef struct KadDscArgs {
     int B, H, W, Cin, Cout;
     int dtype, offset_f32, mask_f32, y_f32, act;
     int path;            /* 0 = SIMT (any shape, any dtype); 1 = tcgen05 implicit GEMM (see kad_dsc_tc_supported);
-                            2 = the same on CTA pairs (tcgen05 cta_group::2, cluster of 2; needs Cout % 32 == 0) */
+                            2 = the same on CTA pairs (tcgen05 cta_group::2, cluster of 2; needs Cout % 32 == 0);
+                            3 = warp-level tensor-core kernel for small channel counts (see kad_dsc_mma_supported):
+                                weight in the SIMT layout, operands rounded to dtype, float32 accumulation */
     int* status;         /* device int[4], zeroed by the caller; the tensor path records a wait that gave up here */
+    /* path 3 only, optional: weights of the offset convolution (float32 [9][Cin][18], kad_dsc_pack_weight_simt of
+       DSC.conv_offset.weight) and its bias (float32 [18] or NULL). When offset_weight is set, `offset` is ignored and
+       the kernel computes the offsets of its own pixels itself (kad_conv.py:64 fused into :66-67): the offset
+       tensor is never written to memory. */
+    const float* offset_weight; const float* offset_bias;
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);
 int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path);
 /* 1 if the tcgen05 path can run this shape: dtype f16/bf16, Cin % 32 == 0, Cout % 16 == 0, Cout <= 256. */
 int kad_dsc_tc_supported(int Cin, int Cout, int dtype);
+/* 1 if path 3 can run this shape: dtype f16/bf16, 4 <= Cin <= 64, Cout <= 64, and the image rows a group of 256
+ * pixels touches (W * Cin * 2 bytes each) fit in shared memory beside the kernel's tables. x must be 16-byte aligned.
+ * Path 3 writes its channel sums per group of 256 pixels: kad_dsc_gap_tiles(..., 3) = ceil(H*W / 256). */
+int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
 /* Packs W[Cout][Cin][3][3] (float32, the layout of DSC.weight) into the tensor path's K-major
  * operand: dst is dtype [9*Cin/64 (rounded up)][Cout][64]; K index = (ci/32)*288 + tap*32 + ci%32. */
 int kad_dsc_pack_weight_tc(const float* w_oihw, void* dst, int Cin, int Cout, int dtype, void* stream);

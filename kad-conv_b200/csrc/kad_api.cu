@@ -1,5 +1,5 @@
 // C-ABI plumbing: error strings, version, and the dispatch of kad_dsc_forward between the SIMT
-// kernel and the tcgen05 implicit GEMM.
+// kernels, the tcgen05 implicit GEMM and the warp-MMA kernel for small channel counts.
 #include <stdarg.h>
 
 #include "kad_common.cuh"
@@ -25,6 +25,9 @@ int dsc_simt_tiles(int H, int W, int Cin, int Cout);
 int launch_dsc_simt(const KadDscArgs& a, cudaStream_t st);
 int dsc_tc_tiles(int H, int W);
 int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st);
+int dsc_mma_tiles(int H, int W);
+bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
+int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st);
 
 }  // namespace kad
 
@@ -36,8 +39,11 @@ extern "C" const char* kad_last_error_string(void) { return last_error().c_str()
 
 extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {
     if (H <= 0 || W <= 0 || Cin <= 0 || Cout <= 0) return 0;
+    if (path == 3) return dsc_mma_tiles(H, W);
     return (path == 1 || path == 2) ? dsc_tc_tiles(H, W) : dsc_simt_tiles(H, W, Cin, Cout);
 }
+
+extern "C" int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) { return dsc_mma_supported(Cin, Cout, dtype, H, W) ? 1 : 0; }
 
 extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
     KAD_CHECK_ARG(a != nullptr, "kad_dsc_forward: null args");
@@ -55,6 +61,12 @@ extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
                         a->Cin, a->Cout, a->dtype);
         KAD_CHECK_ARG(a->status != nullptr, "kad_dsc_forward: the tensor path needs a device status word");
         return launch_dsc_tc(*a, (cudaStream_t)stream);
+    }
+    if (a->path == 3) {
+        if (!dsc_mma_supported(a->Cin, a->Cout, a->dtype, a->H, a->W))
+            return fail(KAD_ERR_UNSUPPORTED, "kad_dsc_forward: the warp-MMA path needs f16/bf16, 4 <= Cin <= 64, Cout <= 64 and image rows that fit in shared memory "
+                        "(got Cin=%d Cout=%d dtype=%d H=%d W=%d)", a->Cin, a->Cout, a->dtype, a->H, a->W);
+        return launch_dsc_mma(*a, (cudaStream_t)stream);
     }
     return fail(KAD_ERR_INVALID, "kad_dsc_forward: unknown path %d", a->path);
 }

@@ -1,0 +1,565 @@
+// Deformable 3x3 convolution for SMALL channel counts (the detector's DSCs have 10-44 channels) on the warp-level
+// tensor-core instruction (mma.sync m16n8k16, fp16/bf16 operands, fp32 accumulators), NHWC.
+//
+// Why not the tcgen05 implicit GEMM: with K = 9 taps x 10..44 channels and N <= 64 the contraction is tiny; what costs
+// is the bilinear gather. So the A operand is never staged as a matrix: the four lanes that share an accumulator row
+// gather four channels each (one 8-byte load per corner) straight into the A-fragment registers. The bilinear
+// interpolation itself is folded into the contraction: a sample is sum_corner w_corner * x[corner], so every corner
+// contributes one MMA with A = w_corner * x[corner] (one packed multiply per register) against the same weight
+// fragment; products are rounded to the storage type, the sum over corners, taps and channels is fp32.
+//
+// Blocks are persistent (two per SM for the narrow variants) and walk over (image, group of 256 consecutive pixels);
+// a warp owns 32 pixels of the group (two 16-row MMA tiles). The image rows a group can reach (its own rows, one row of
+// 3x3 halo, a margin for the learned offsets) are one CONTIGUOUS range of the NHWC tensor; it is copied to shared
+// memory with 16-byte cp.async, so HBM sees one coalesced pass over x and the gathers are shared-memory loads with
+// 32-bit addresses. Lane l computes the sampling geometry of pixel l, one kernel row (3 taps) at a time, into a
+// warp-private table: per corner the shared-memory address of the pixel (the address of a block of zeros when the
+// corner leaves the image) and the mask-scaled weight. The gathering lanes then run straight-line code: address +
+// channel offset, one load, multiply, MMA. A tap in which some lane's sample leaves the staged rows (a warp vote)
+// takes a slower variant of the same code that reads those corners from global memory.
+// Results leave through shared memory as well, so that a warp writes its 32 pixels as one contiguous run.
+//
+// Modes:  plain   offset == NULL: ordinary zero-padded 3x3 convolution (the offset convolution, c -> 18)
+//         deform  offsets and modulation mask read from global memory
+//         fused   the offset convolution runs first on the same pixels and its 18 outputs go through shared memory
+//                 straight into the sampling geometry: the offset tensor never exists in global memory.
+#include "kad_common.cuh"
+
+namespace kad {
+namespace {
+
+constexpr int MMA_THREADS = 256;
+constexpr int MMA_WARPS = 8;
+constexpr int MMA_MAX_BLOCKS_PER_IMAGE = 64;
+constexpr int OFF_PITCH = 19;           // floats per pixel of the staged offsets (18, padded against bank conflicts)
+constexpr int NT_OFF = 3;               // n-tiles of the offset convolution (18 outputs -> 24)
+
+struct MmaParams {
+    const void* x; const void* offset; const void* mask;
+    const float* Wt;                    // [9][Cin][Cout] fp32
+    const float* Woff;                  // [9][Cin][18] fp32 (fused mode)
+    const float* boff;                  // [18] (fused mode)
+    const float* scale; const float* shift; const float* post;
+    void* y; float* gap_partial;
+    int H, W, Cin, Cout, KC, align;
+    int offset_f32, mask_f32, y_f32, act;
+    int B, win_margin;                  // win_margin: rows staged above / below the 3x3 halo for the learned offsets
+};
+
+constexpr int SCRATCH_PER_WARP = 4224;  // sampling table (3 taps x 32 pixels x 32 bytes), later the warp's output tile (+ 16 bytes of shift)
+constexpr int ZERO_BYTES = 160;         // block of zeros in shared memory that out-of-image corners point at
+constexpr uint32_t OUTSIDE = 0x80000000u;   // table address flag: the corner is not staged; low bits = image element offset
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T> __device__ __forceinline__ uint32_t mul2(uint32_t x, uint32_t w);
+template <> __device__ __forceinline__ uint32_t mul2<__half>(uint32_t x, uint32_t w) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&x), *reinterpret_cast<__half2*>(&w)); return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t mul2<__nv_bfloat16>(uint32_t x, uint32_t w) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&x), *reinterpret_cast<__nv_bfloat162*>(&w)); return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b);
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+}
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+}
+
+
+// Eight bytes (four consecutive 16-bit channels) at byte offset `off` of the block's shared memory, whose address is
+// known to be ALIGN-byte aligned. ALIGN = 2 reads the three aligned words around the span and shifts the bytes outside
+// it away (the staged window has slack on both sides for exactly this).
+template <int ALIGN>
+__device__ __forceinline__ uint2 lds8(const unsigned char* smem, uint32_t off) {
+    if (ALIGN == 8) return *reinterpret_cast<const uint2*>(smem + off);
+    if (ALIGN == 4) { const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + off); return make_uint2(q[0], q[1]); }
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + (off & ~3u));
+    const uint32_t sh = (off & 2u) * 8u;
+    return make_uint2(__funnelshift_r(q[0], q[1], sh), __funnelshift_r(q[1], q[2], sh));
+}
+// The same through a global pointer; here the word after the span is only read when the span ends inside it.
+template <int ALIGN>
+__device__ __forceinline__ uint2 ldg8(const unsigned char* p) {
+    if (ALIGN == 8) return __ldg(reinterpret_cast<const uint2*>(p));
+    if (ALIGN == 4) { const uint32_t* q = reinterpret_cast<const uint32_t*>(p); return make_uint2(__ldg(q), __ldg(q + 1)); }
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
+    const bool odd = (a & 2) != 0;
+    const uint32_t w0 = __ldg(q), w1 = __ldg(q + 1), w2 = odd ? __ldg(q + 2) : 0u;
+    return odd ? make_uint2(__funnelshift_r(w0, w1, 16), __funnelshift_r(w1, w2, 16)) : make_uint2(w0, w1);
+}
+
+// Which four channels lane t gathers in 16-channel chunk kc: normally ch = kc*16 + 4t .. ch+3. In the last, partial
+// chunk a lane with only 1-3 existing channels loads the LAST four channels of the pixel instead, and a lane with none
+// re-reads channels 0-3; the weight fragments (stage_weights) carry zeros for every slot that would count a channel
+// twice, so no lane ever reads past its pixel and no masking is needed in the gather.
+__device__ __forceinline__ int lane_first_channel(int kc, int t, int Cin) {
+    const int ch = kc * 16 + 4 * t, nv = Cin - ch;
+    return nv >= 4 ? ch : (nv <= 0 ? 0 : Cin - 4);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// Weight fragments for mma.sync: lane (g = lane / 4, t = lane % 4) of n-tile nt holds output channel nt*8 + g and four
+// input channels (the K order inside a 16-chunk is permuted so that a lane's four A values are four CONSECUTIVE
+// channels: logical k = 2t, 2t+1, 2t+8, 2t+9  <->  slot 0..3 = channel first + 0..3, first = lane_first_channel()).
+template <typename T>
+__device__ __forceinline__ void stage_weights(uint2* dst, const float* __restrict__ Wt, int Cin, int Cout, int KC, int NT, int tid) {
+    const int total = 9 * KC * NT * 32;
+    for (int e = tid; e < total; e += MMA_THREADS) {
+        const int lane = e & 31, f = e >> 5, nt = f % NT, kc = (f / NT) % KC, k = f / (NT * KC);
+        const int n = nt * 8 + (lane >> 2), t = lane & 3, ch = kc * 16 + 4 * t;
+        const int first = lane_first_channel(kc, t, Cin);
+        float w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = first + j;
+            w[j] = (n < Cout && c >= ch && c < Cin) ? Wt[((size_t)k * Cin + c) * Cout + n] : 0.f;
+        }
+        dst[e] = make_uint2(pack2<T>(w[0], w[1]), pack2<T>(w[2], w[3]));
+    }
+}
+
+// Ordinary 3x3 convolution of this lane's four accumulator rows over all taps and chunks, out of the staged rows.
+// so[j] = shared-memory address of row j's pixel, vm[j] = which of its 9 neighbours lie inside the image.
+template <typename T, int NTP, int ALIGN>
+__device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsigned char* smem, const uint32_t (&so)[4], const uint32_t (&vm)[4],
+                                           uint32_t zoff, const uint2* __restrict__ Bs, int KC, int Cin, int W, int lane) {
+    const int t = lane & 3;
+#pragma unroll 1
+    for (int k = 0; k < 9; ++k) {
+        const int step = ((k / 3 - 1) * W + (k % 3 - 1)) * Cin * 2;
+        uint32_t q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = ((vm[j] >> k) & 1u) ? so[j] + step : zoff;
+#pragma unroll 1
+        for (int kc = 0; kc < KC; ++kc) {
+            const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
+            uint2 bf[NTP];
+#pragma unroll
+            for (int nt = 0; nt < NTP; ++nt) bf[nt] = Bs[((k * KC + kc) * NTP + nt) * 32 + lane];
+            uint2 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = lds8<ALIGN>(smem, q[j] + coff);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NTP; ++nt) mma16816<T>(acc[mt][nt], v[2 * mt].x, v[2 * mt + 1].x, v[2 * mt].y, v[2 * mt + 1].y, bf[nt]);
+        }
+    }
+}
+
+// One tap of the deformable pass for one 16-row tile: A = corner weight * gathered channels, four corners, all chunks.
+// SLOW: some address in the warp carries the OUTSIDE flag and is read from global memory instead.
+template <typename T, int NT, int ALIGN, bool SLOW>
+__device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned char* smem, const unsigned char* gimg, const uint4* tw, const uint4* ta,
+                                           int row0, const uint2* __restrict__ Bs, int k, int KC, int Cin, int lane) {
+    const int t = lane & 3;
+    uint32_t w[2][4], a[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint4 wq = tw[row0 + 8 * h], aq = ta[row0 + 8 * h];
+        w[h][0] = wq.x; w[h][1] = wq.y; w[h][2] = wq.z; w[h][3] = wq.w;
+        a[h][0] = aq.x; a[h][1] = aq.y; a[h][2] = aq.z; a[h][3] = aq.w;
+    }
+#pragma unroll 1
+    for (int kc = 0; kc < KC; ++kc) {
+        const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
+        uint2 bf[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) bf[nt] = Bs[((k * KC + kc) * NT + nt) * 32 + lane];
+        uint2 v[2][4];
+#pragma unroll
+        for (int cr = 0; cr < 4; ++cr)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (SLOW && (a[h][cr] & OUTSIDE)) v[h][cr] = ldg8<ALIGN>(gimg + 2 * (size_t)(a[h][cr] & ~OUTSIDE) + coff);
+                else v[h][cr] = lds8<ALIGN>(smem, a[h][cr] + coff);
+            }
+#pragma unroll
+        for (int cr = 0; cr < 4; ++cr) {
+            const uint32_t a0 = mul2<T>(v[0][cr].x, w[0][cr]), a2 = mul2<T>(v[0][cr].y, w[0][cr]);
+            const uint32_t a1 = mul2<T>(v[1][cr].x, w[1][cr]), a3 = mul2<T>(v[1][cr].y, w[1][cr]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816<T>(acc[nt], a0, a1, a2, a3, bf[nt]);
+        }
+    }
+}
+
+template <typename T, int NT, int MODE, int ALIGN>      // MODE 0 plain, 1 deform, 2 fused
+__global__ void __launch_bounds__(MMA_THREADS, NT <= 4 ? 2 : 1)
+dsc_mma_kernel(const MmaParams p) {
+    constexpr int COP = NT * 8;
+    extern __shared__ __align__(16) unsigned char smem_mma[];
+    const int KC = p.KC;
+    uint2* Bs = reinterpret_cast<uint2*>(smem_mma);                                   // [9][KC][NT][32]
+    uint2* Bo = Bs + 9 * KC * NT * 32;                                                // [9][KC][3][32]   (fused)
+    unsigned char* cur = reinterpret_cast<unsigned char*>(Bo + (MODE == 2 ? 9 * KC * NT_OFF * 32 : 0));
+    unsigned char* scratch = cur; cur += MMA_WARPS * SCRATCH_PER_WARP;
+    float* ep = reinterpret_cast<float*>(cur); cur += 3 * COP * 4;                    // scale | shift | post
+    float* red = reinterpret_cast<float*>(cur); cur += MMA_WARPS * COP * 4;
+    float* offs = reinterpret_cast<float*>(cur); cur += (MODE == 2 ? MMA_WARPS * 32 * OFF_PITCH * 4 : 0);
+    float* boffs = reinterpret_cast<float*>(cur); cur += (MODE == 2 ? 32 * 4 : 0);    // [24] (fused)
+    const uint32_t zoff = static_cast<uint32_t>(cur - smem_mma); cur += ZERO_BYTES;   // the block of zeros
+    const uint32_t wdata = static_cast<uint32_t>(cur - smem_mma) + 16;                // staged rows start here (16 bytes of slack in front)
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int H = p.H, W = p.W, HW = H * W, Cin = p.Cin, Cout = p.Cout;
+    const int gpi = (HW + MMA_THREADS - 1) / MMA_THREADS, total = gpi * p.B;      // groups per image, groups in all
+
+    uint4* my_w = reinterpret_cast<uint4*>(scratch + warp * SCRATCH_PER_WARP);    // [3][32] corner weights, each a duplicated pair
+    uint4* my_a = my_w + 96;                                                          // [3][32] corner addresses
+    unsigned char* my_tile = scratch + warp * SCRATCH_PER_WARP;                       // output tile (after the taps are done)
+    float* my_offs = offs + warp * 32 * OFF_PITCH;
+    const float relu_floor = p.act == KAD_ACT_RELU ? 0.f : -INFINITY;
+
+    bool first = true;
+    for (int gi = blockIdx.x; gi < total; gi += gridDim.x) {
+        const int b = gi / gpi, grp = gi - b * gpi, base = grp * MMA_THREADS;
+        const unsigned char* gimg = reinterpret_cast<const unsigned char*>(p.x) + (size_t)b * HW * Cin * 2;
+        // ---- stage the rows this group can reach -------------------------------------------------------------
+        __syncthreads();                                       // every warp is done with the previous rows, tiles and sums
+        const int last = min(HW, base + MMA_THREADS) - 1;
+        const int wy0 = max(0, base / W - 1 - p.win_margin), wy1 = min(H - 1, last / W + 1 + p.win_margin);
+        const int e_lo = wy0 * W * Cin, e_hi = (wy1 + 1) * W * Cin;                  // staged image elements [e_lo, e_hi)
+        const uintptr_t a_lo = reinterpret_cast<uintptr_t>(gimg) + 2 * (size_t)e_lo, a16 = a_lo & ~uintptr_t(15);
+        const uintptr_t a_hi = reinterpret_cast<uintptr_t>(gimg) + 2 * (size_t)e_hi;
+        {
+            const int nbytes = static_cast<int>(a_hi - a16), nvec = nbytes >> 4, ntail = (nbytes & 15) >> 1;
+            unsigned char* dst = smem_mma + wdata;
+            for (int i = tid; i < nvec; i += MMA_THREADS) cp_async16(dst + 16 * i, reinterpret_cast<const void*>(a16 + 16 * (size_t)i));
+            if (tid < ntail)
+                *reinterpret_cast<uint16_t*>(dst + 16 * nvec + 2 * tid) = *reinterpret_cast<const uint16_t*>(a16 + 16 * (size_t)nvec + 2 * tid);
+        }
+        // shared-memory address of image element e: sel0 + 2*e
+        const int sel0 = static_cast<int>(wdata) - static_cast<int>(static_cast<ptrdiff_t>(a16) - static_cast<ptrdiff_t>(reinterpret_cast<uintptr_t>(gimg)));
+        if (first) {
+            stage_weights<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
+            if (MODE == 2) {
+                stage_weights<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
+                if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
+            }
+            for (int e = tid; e < COP; e += MMA_THREADS) {
+                const bool on = e < Cout;
+                ep[e] = (on && p.scale) ? p.scale[e] : 1.f;
+                ep[COP + e] = (on && p.shift) ? p.shift[e] : 0.f;
+                ep[2 * COP + e] = (on && p.post) ? p.post[e] : 1.f;
+            }
+            if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(smem_mma + zoff)[tid] = 0u;
+            first = false;
+        }
+        // lane l describes pixel wbase + l; its modulation mask is fetched while the copy is in flight
+        const int wbase = base + warp * 32;
+        const int mypix = wbase + lane;
+        const bool mylive = mypix < HW;
+        const int mpy = mypix / W, mpx = mypix - mpy * W;
+        const size_t gp = (size_t)b * HW + mypix;
+        float mk[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) mk[k] = (MODE != 0 && mylive && p.mask) ? load_mixed<T>(p.mask, gp * 9 + k, p.mask_f32) : 1.f;
+        uint32_t myvm = 0;                                     // which 3x3 neighbours of my pixel are inside the image
+        if (mylive) {
+#pragma unroll
+            for (int k = 0; k < 9; ++k) {
+                const int yy = mpy + k / 3 - 1, xx = mpx + k % 3 - 1;
+                if (yy >= 0 && yy < H && xx >= 0 && xx < W) myvm |= 1u << k;
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+
+        float psum[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) psum[nt][0] = psum[nt][1] = 0.f;
+        if (wbase < HW) {
+            // the four accumulator rows of this lane: j = mt*2 + half -> pixel wbase + mt*16 + g + 8*half
+            uint32_t so[4], vm[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = (j >> 1) * 16 + g + 8 * (j & 1);
+                vm[j] = __shfl_sync(0xffffffffu, myvm, r);
+                so[j] = static_cast<uint32_t>(sel0 + 2 * (wbase + r) * Cin);
+            }
+            float acc[2][NT][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+
+            if (MODE == 0) {
+                plain_pass<T, NT, ALIGN>(acc, smem_mma, so, vm, zoff, Bs, KC, Cin, W, lane);
+            } else {
+                if (MODE == 2) {
+                    // offset convolution of the warp's 32 pixels -> shared memory [32][18]
+                    float oacc[2][NT_OFF][4];
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                        for (int nt = 0; nt < NT_OFF; ++nt)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) oacc[mt][nt][i] = 0.f;
+                    plain_pass<T, NT_OFF, ALIGN>(oacc, smem_mma, so, vm, zoff, Bo, KC, Cin, W, lane);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int nt = 0; nt < NT_OFF; ++nt) {
+                            const int co = nt * 8 + 2 * t, row = (j >> 1) * 16 + g + 8 * (j & 1);
+                            if (co < 18) {
+                                my_offs[row * OFF_PITCH + co] = oacc[j >> 1][nt][2 * (j & 1)] + boffs[co];
+                                my_offs[row * OFF_PITCH + co + 1] = oacc[j >> 1][nt][2 * (j & 1) + 1] + boffs[co + 1];
+                            }
+                        }
+                }
+#pragma unroll 1
+                for (int r = 0; r < 3; ++r) {
+                    __syncwarp();                              // readers of the previous row's table are done; offsets are visible
+                    uint32_t slow = 0;                         // bit kk: some lane's sample of tap kk leaves the staged rows
+#pragma unroll
+                    for (int kk = 0; kk < 3; ++kk) {
+                        const int k = 3 * r + kk;
+                        uint4 wq = make_uint4(0u, 0u, 0u, 0u), aq = make_uint4(zoff, zoff, zoff, zoff);
+                        bool out = false;
+                        if (mylive) {
+                            float dy, dx;
+                            if (MODE == 2) { dy = my_offs[lane * OFF_PITCH + 2 * k]; dx = my_offs[lane * OFF_PITCH + 2 * k + 1]; }
+                            else { dy = load_mixed<T>(p.offset, gp * 18 + 2 * k, p.offset_f32); dx = load_mixed<T>(p.offset, gp * 18 + 2 * k + 1, p.offset_f32); }
+                            const float m = r == 0 ? mk[kk] : (r == 1 ? mk[3 + kk] : mk[6 + kk]);
+                            const float sy = (float)(mpy + r - 1) + dy, sx = (float)(mpx + kk - 1) + dx;
+                            if (sy > -1.f && sy < (float)H && sx > -1.f && sx < (float)W) {
+                                const float fy = floorf(sy), fx = floorf(sx);
+                                const int y0 = (int)fy, x0 = (int)fx;
+                                const float ly = sy - fy, lx = sx - fx, hy = 1.f - ly, hx = 1.f - lx;
+                                const bool yl = y0 >= 0, yh = y0 + 1 < H, xl = x0 >= 0, xh = x0 + 1 < W;
+                                const int o00 = (y0 * W + x0) * Cin, o10 = o00 + W * Cin;
+                                // rows y0 and y0+1 are staged as a whole or not at all
+                                const bool in0 = o00 - x0 * Cin >= e_lo && o00 - x0 * Cin < e_hi, in1 = o10 - x0 * Cin >= e_lo && o10 - x0 * Cin < e_hi;
+                                if (yl && xl) aq.x = in0 ? static_cast<uint32_t>(sel0 + 2 * o00) : (OUTSIDE | static_cast<uint32_t>(o00));
+                                if (yl && xh) aq.y = in0 ? static_cast<uint32_t>(sel0 + 2 * (o00 + Cin)) : (OUTSIDE | static_cast<uint32_t>(o00 + Cin));
+                                if (yh && xl) aq.z = in1 ? static_cast<uint32_t>(sel0 + 2 * o10) : (OUTSIDE | static_cast<uint32_t>(o10));
+                                if (yh && xh) aq.w = in1 ? static_cast<uint32_t>(sel0 + 2 * (o10 + Cin)) : (OUTSIDE | static_cast<uint32_t>(o10 + Cin));
+                                out = (yl && !in0) || (yh && !in1);
+                                const float w00 = hy * hx * m, w01 = hy * lx * m, w10 = ly * hx * m, w11 = ly * lx * m;
+                                wq = make_uint4(pack2<T>(w00, w00), pack2<T>(w01, w01), pack2<T>(w10, w10), pack2<T>(w11, w11));
+                            }
+                        }
+                        my_w[kk * 32 + lane] = wq;
+                        my_a[kk * 32 + lane] = aq;
+                        if (__any_sync(0xffffffffu, out)) slow |= 1u << kk;
+                    }
+                    __syncwarp();
+#pragma unroll 1
+                    for (int kk = 0; kk < 3; ++kk) {
+                        const int k = 3 * r + kk;
+                        if ((slow >> kk) & 1u) {
+#pragma unroll
+                            for (int mt = 0; mt < 2; ++mt)
+                                deform_tap<T, NT, ALIGN, true>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                        } else {
+#pragma unroll
+                            for (int mt = 0; mt < 2; ++mt)
+                                deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                        }
+                    }
+                }
+            }
+
+            // ---- epilogue: affine, activation, post scale; the warp's 32 pixels leave as one contiguous run --------
+            const int es = p.y_f32 ? 4 : 2;
+            const int npx = min(32, HW - wbase);
+            const bool tiled = 32 * Cout * es + 16 <= SCRATCH_PER_WARP;
+            unsigned char* ydst = reinterpret_cast<unsigned char*>(p.y) + ((size_t)b * HW + wbase) * Cout * es;
+            // the tile sits in shared memory at the same offset from a 16-byte boundary as its destination
+            const int mis = static_cast<int>(reinterpret_cast<uintptr_t>(ydst) & 15);
+            unsigned char* tile = tiled ? my_tile + mis : ydst;
+            const bool pair_ok = !(Cout & 1) && !(mis & 3);
+            __syncwarp();                                      // the table is no longer read
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int row = (j >> 1) * 16 + g + 8 * (j & 1);
+                if (row >= npx) continue;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int co = nt * 8 + 2 * t;
+                    if (co >= Cout) continue;
+                    float v0 = fmaf(acc[j >> 1][nt][2 * (j & 1)], ep[co], ep[COP + co]);
+                    float v1 = fmaf(acc[j >> 1][nt][2 * (j & 1) + 1], ep[co + 1], ep[COP + co + 1]);
+                    if (p.act == KAD_ACT_SILU) { v0 = v0 * sigmoidf_(v0); v1 = v1 * sigmoidf_(v1); }
+                    v0 = fmaxf(v0, relu_floor) * ep[2 * COP + co];
+                    v1 = fmaxf(v1, relu_floor) * ep[2 * COP + co + 1];
+                    const bool two = co + 1 < Cout;
+                    const size_t idx = (size_t)row * Cout + co;
+                    if (p.y_f32) {
+                        float* yo = reinterpret_cast<float*>(tile) + idx;
+                        yo[0] = v0; if (two) yo[1] = v1;
+                    } else {
+                        T* yo = reinterpret_cast<T*>(tile) + idx;
+                        if (pair_ok) *reinterpret_cast<uint32_t*>(yo) = pack2<T>(v0, v1);
+                        else { yo[0] = from_f<T>(v0); if (two) yo[1] = from_f<T>(v1); }
+                        v0 = to_f<T>(from_f<T>(v0)); v1 = to_f<T>(from_f<T>(v1));     // sums of what the next kernel reads back
+                    }
+                    psum[nt][0] += v0;
+                    if (two) psum[nt][1] += v1;
+                }
+            }
+            if (tiled) {
+                __syncwarp();
+                const int nb = npx * Cout * es;
+                const int head = min(nb, (16 - mis) & 15), body = (nb - head) >> 4, tail = nb - head - (body << 4);
+                const uint4* src = reinterpret_cast<const uint4*>(tile + head);
+                uint4* dst = reinterpret_cast<uint4*>(ydst + head);
+                for (int i = lane; i < body; i += 32) dst[i] = src[i];
+                if (lane < (head >> 1)) reinterpret_cast<uint16_t*>(ydst)[lane] = reinterpret_cast<const uint16_t*>(tile)[lane];
+                else if (lane >= 16 && lane - 16 < (tail >> 1))
+                    reinterpret_cast<uint16_t*>(ydst + head + (body << 4))[lane - 16] = reinterpret_cast<const uint16_t*>(tile + head + (body << 4))[lane - 16];
+            }
+        }
+
+        // ---- channel sums of the group (squeeze-excite mean), deterministic -------------------------------------------
+        if (p.gap_partial) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float v = psum[nt][i];
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 16);
+                    if (g == 0) red[warp * COP + nt * 8 + 2 * t + i] = v;
+                }
+            __syncthreads();
+            if (tid < Cout) {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < MMA_WARPS; ++w) s += red[w * COP + tid];
+                p.gap_partial[((size_t)b * gpi + grp) * Cout + tid] = s;
+            }
+        }
+    }
+}
+
+inline int pick_nt(int Cout) {
+    const int n = (Cout + 7) / 8;
+    return n <= 2 ? 2 : n <= 3 ? 3 : n <= 4 ? 4 : n <= 6 ? 6 : 8;
+}
+
+// Shared memory of one block without the staged rows.
+inline size_t fixed_smem(int KC, int nt, int mode) {
+    size_t s = (size_t)9 * KC * nt * 32 * 8 + (size_t)MMA_WARPS * SCRATCH_PER_WARP + (size_t)3 * nt * 8 * 4 + (size_t)MMA_WARPS * nt * 8 * 4 + ZERO_BYTES;
+    if (mode == 2) s += (size_t)9 * KC * NT_OFF * 32 * 8 + (size_t)MMA_WARPS * 32 * OFF_PITCH * 4 + 32 * 4;
+    return s;
+}
+// Bytes for the staged rows with `margin` rows for the learned offsets (incl. alignment slack on both sides).
+inline size_t window_smem(int H, int W, int Cin, int margin) {
+    int rows = (W + MMA_THREADS - 2) / W + 1 + 2 + 2 * margin;      // rows 256 consecutive pixels span + halo + margin
+    if (rows > H) rows = H;
+    return (size_t)rows * W * Cin * 2 + 16 + 16 + 32;
+}
+constexpr size_t SMEM_ONE_BLOCK = 224 * 1024, SMEM_TWO_BLOCKS = 112 * 1024;
+
+template <typename T, int NT, int MODE>
+int launch_mma_align(const MmaParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+#define KAD_MMA_LAUNCH(A)                                                                                             \
+    {                                                                                                                 \
+        auto kern = dsc_mma_kernel<T, NT, MODE, A>;                                                                   \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_mma smem attribute: %s", cudaGetErrorString(e));         \
+        kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
+    }
+    if (p.align == 8) KAD_MMA_LAUNCH(8) else if (p.align == 4) KAD_MMA_LAUNCH(4) else KAD_MMA_LAUNCH(2)
+#undef KAD_MMA_LAUNCH
+    return KAD_OK;
+}
+
+template <typename T, int NT>
+int launch_mma_mode(const MmaParams& p, int mode, dim3 grid, size_t smem, cudaStream_t st) {
+    if (mode == 0) return launch_mma_align<T, NT, 0>(p, grid, smem, st);
+    if (mode == 1) return launch_mma_align<T, NT, 1>(p, grid, smem, st);
+    return launch_mma_align<T, NT, 2>(p, grid, smem, st);
+}
+
+template <typename T>
+int launch_mma_nt(const MmaParams& p, int nt, int mode, dim3 grid, size_t smem, cudaStream_t st) {
+    switch (nt) {
+        case 2: return launch_mma_mode<T, 2>(p, mode, grid, smem, st);
+        case 3: return launch_mma_mode<T, 3>(p, mode, grid, smem, st);
+        case 4: return launch_mma_mode<T, 4>(p, mode, grid, smem, st);
+        case 6: return launch_mma_mode<T, 6>(p, mode, grid, smem, st);
+        default: return launch_mma_mode<T, 8>(p, mode, grid, smem, st);
+    }
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace
+
+// channel sums are written per group of 256 pixels
+int dsc_mma_tiles(int H, int W) { return (H * W + MMA_THREADS - 1) / MMA_THREADS; }
+
+// The fused mode (the largest footprint) must fit with at least the 3x3 halo staged.
+bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) {
+    if (!((dtype == KAD_F16 || dtype == KAD_BF16) && Cin >= 4 && Cin <= 64 && Cout >= 1 && Cout <= 64 && H >= 1 && W >= 1)) return false;
+    if ((long long)H * W * Cin >= (1ll << 30)) return false;
+    const int nt = pick_nt(Cout);
+    return fixed_smem((Cin + 15) / 16, nt, 2) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
+}
+
+int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
+    const bool fused = a.offset_weight != nullptr;
+    const int mode = fused ? 2 : (a.offset ? 1 : 0);
+    KAD_CHECK_ARG(mode != 0 || a.mask == nullptr, "kad_dsc_forward: the warp-MMA path takes a mask only together with offsets");
+    KAD_CHECK_ARG((uintptr_t)a.x % 16 == 0, "kad_dsc_forward: the warp-MMA path needs x aligned to 16 bytes");
+    KAD_CHECK_ARG((uintptr_t)a.y % 4 == 0, "kad_dsc_forward: the warp-MMA path needs y aligned to 4 bytes");
+    MmaParams p{};
+    p.x = a.x; p.offset = fused ? nullptr : a.offset; p.mask = a.mask; p.Wt = (const float*)a.weight;
+    p.Woff = a.offset_weight; p.boff = a.offset_bias;
+    p.scale = a.scale; p.shift = a.shift; p.post = a.post; p.y = a.y; p.gap_partial = a.gap_partial;
+    p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KC = (a.Cin + 15) / 16; p.B = a.B;
+    p.align = a.Cin % 4 == 0 ? 8 : (a.Cin % 2 == 0 ? 4 : 2);
+    p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
+    const int nt = pick_nt(a.Cout);
+    size_t smem = fixed_smem(p.KC, nt, mode);
+    // rows of margin for the learned offsets: as many as fit, at most 2 (none for the plain convolution); the narrow
+    // variants (128 registers) keep two blocks per SM when the halo alone allows it
+    const size_t soft = (nt <= 4 && smem + window_smem(a.H, a.W, a.Cin, 0) <= SMEM_TWO_BLOCKS) ? SMEM_TWO_BLOCKS : SMEM_ONE_BLOCK;
+    p.win_margin = 0;
+    for (int m = (mode == 0 ? 0 : 2); m > 0; --m)
+        if (smem + window_smem(a.H, a.W, a.Cin, m) <= soft) { p.win_margin = m; break; }
+    smem += window_smem(a.H, a.W, a.Cin, p.win_margin);
+    const long long groups = (long long)dsc_mma_tiles(a.H, a.W) * a.B;
+    const long long resident = (long long)sm_count() * (soft == SMEM_TWO_BLOCKS ? 2 : 1);
+    dim3 grid((unsigned)(groups < resident ? groups : resident), 1, 1);
+    const int rc = a.dtype == KAD_F16 ? launch_mma_nt<__half>(p, nt, mode, grid, smem, st) : launch_mma_nt<__nv_bfloat16>(p, nt, mode, grid, smem, st);
+    if (rc) return rc;
+    KAD_CHECK_LAUNCH("dsc_mma_kernel");
+    return KAD_OK;
+}
+
+}  // namespace kad

@@ -236,39 +236,62 @@ __device__ __forceinline__ void src_index(int d, float scale, int in, int& i0, i
     l1 = s - (float)i0;
 }
 
-// blockDim = 256 = (pixel lanes) x (channels rounded up to a multiple of 32): a thread keeps its channel (so its branch,
-// its attention scalar and its source tensor are fixed per image) and walks over pixels; consecutive threads touch
-// consecutive channels of the same pixel, i.e. consecutive addresses of x, out and the branch tensor.
-template <typename T>
+// V consecutive channels as floats (V = 1, or V = 2 for 16-bit types: one 32-bit access)
+template <typename T, int V> struct MergeIO {
+    static __device__ __forceinline__ void ld(const T* p, float (&o)[V]) { o[0] = to_f<T>(*p); }
+    static __device__ __forceinline__ void st(T* p, const float (&v)[V]) { *p = from_f<T>(v[0]); }
+};
+template <> struct MergeIO<__half, 2> {
+    static __device__ __forceinline__ void ld(const __half* p, float (&o)[2]) { float2 f = __half22float2(*reinterpret_cast<const __half2*>(p)); o[0] = f.x; o[1] = f.y; }
+    static __device__ __forceinline__ void st(__half* p, const float (&v)[2]) { *reinterpret_cast<__half2*>(p) = __floats2half2_rn(v[0], v[1]); }
+};
+template <> struct MergeIO<__nv_bfloat16, 2> {
+    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&o)[2]) { float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); o[0] = f.x; o[1] = f.y; }
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[2]) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]); }
+};
+
+// blockDim = 256 = (pixel lanes) x (channel groups rounded up to a multiple of 32): a thread keeps its V channels (so its
+// branch, its attention scalars and its source tensor are fixed per image) and walks over pixels; consecutive threads
+// touch consecutive channels of the same pixel, i.e. consecutive addresses of x, out and the branch tensor.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp, int pix_per_block) {
     const int cl0 = threadIdx.x % Cp, pl = threadIdx.x / Cp, PL = 256 / Cp;
     const int b = blockIdx.y;
     const int HW = p.H * p.W;
     const int pix0 = blockIdx.x * pix_per_block, pix1 = min(HW, pix0 + pix_per_block);
-    for (int c = cl0; c < p.C; c += Cp) {
+    for (int c = cl0 * V; c < p.C; c += Cp * V) {
         int i = 0, cl = c;
         if (cl >= p.c[0]) { cl -= p.c[0]; i = 1; if (cl >= p.c[1]) { cl -= p.c[1]; i = 2; } }
         const int ci = p.c[i], hi = p.h[i], wi = p.w[i];
         const T* yi = reinterpret_cast<const T*>(p.y[i]) + (size_t)b * hi * wi * ci + cl;
-        const float a = p.att[i][(size_t)b * ci + cl];
+        float a[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) a[v] = p.att[i][(size_t)b * ci + cl + v];
         const bool same = (hi == p.H && wi == p.W);
         const float sy = p.sy[i], sx = p.sx[i];
         for (int pix = pix0 + pl; pix < pix1; pix += PL) {
             const int yh = pix / p.W, xw = pix - yh * p.W;
-            float v;
+            float val[V];
             if (same) {
-                v = to_f<T>(yi[(size_t)pix * ci]);
+                MergeIO<T, V>::ld(yi + (size_t)pix * ci, val);
             } else {
                 int y0, y1, x0, x1; float ly, lx;
                 src_index(yh, sy, hi, y0, y1, ly);
                 src_index(xw, sx, wi, x0, x1, lx);
-                const float v00 = to_f<T>(yi[((size_t)y0 * wi + x0) * ci]), v01 = to_f<T>(yi[((size_t)y0 * wi + x1) * ci]);
-                const float v10 = to_f<T>(yi[((size_t)y1 * wi + x0) * ci]), v11 = to_f<T>(yi[((size_t)y1 * wi + x1) * ci]);
-                v = (1.f - ly) * ((1.f - lx) * v00 + lx * v01) + ly * ((1.f - lx) * v10 + lx * v11);
+                float v00[V], v01[V], v10[V], v11[V];
+                MergeIO<T, V>::ld(yi + ((size_t)y0 * wi + x0) * ci, v00); MergeIO<T, V>::ld(yi + ((size_t)y0 * wi + x1) * ci, v01);
+                MergeIO<T, V>::ld(yi + ((size_t)y1 * wi + x0) * ci, v10); MergeIO<T, V>::ld(yi + ((size_t)y1 * wi + x1) * ci, v11);
+#pragma unroll
+                for (int v = 0; v < V; ++v)
+                    val[v] = (1.f - ly) * ((1.f - lx) * v00[v] + lx * v01[v]) + ly * ((1.f - lx) * v10[v] + lx * v11[v]);
             }
             const size_t e = ((size_t)b * HW + pix) * p.C + c;
-            out[e] = from_f<T>(fmaf(v, a, to_f<T>(x[e])));
+            float xin[V], o[V];
+            MergeIO<T, V>::ld(x + e, xin);
+#pragma unroll
+            for (int v = 0; v < V; ++v) o[v] = fmaf(val[v], a[v], xin[v]);
+            MergeIO<T, V>::st(out + e, o);
         }
     }
 }
@@ -422,7 +445,12 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     }
     p.H = a->H; p.W = a->W; p.C = a->C;
     KAD_CHECK_ARG(a->B <= 65535, "kad_merge_upsample_residual: batch %d too large", a->B);
-    int Cp = ((a->C + 31) / 32) * 32;
+    // two channels per thread (one 32-bit access) for 16-bit storage when every branch width is even
+    const bool pairs = a->dtype != KAD_F32 && a->c[0] % 2 == 0 && a->c[1] % 2 == 0 && a->c[2] % 2 == 0 &&
+                       (uintptr_t)a->x % 4 == 0 && (uintptr_t)a->out % 4 == 0 && (uintptr_t)a->y[0] % 4 == 0 &&
+                       (uintptr_t)a->y[1] % 4 == 0 && (uintptr_t)a->y[2] % 4 == 0;
+    const int groups = pairs ? a->C / 2 : a->C;
+    int Cp = ((groups + 31) / 32) * 32;
     if (Cp > 256) Cp = 256;
     const int HW = a->H * a->W;
     // pixels per thread: 4 on small feature maps (enough blocks to fill the GPU), up to 32 on large ones (amortises the
@@ -432,9 +460,14 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     int iters = want < 4 ? 4 : (want > 32 ? 32 : (int)want);
     int pix_per_block = iters * PL;
     dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
-    KAD_DISPATCH_DTYPE(a->dtype, {
-        merge_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);
-    });
+    cudaStream_t st = (cudaStream_t)stream;
+    if (pairs && a->dtype == KAD_F16) merge_kernel<__half, 2><<<grid, 256, 0, st>>>((const __half*)a->x, (__half*)a->out, p, Cp, pix_per_block);
+    else if (pairs) merge_kernel<__nv_bfloat16, 2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a->x, (__nv_bfloat16*)a->out, p, Cp, pix_per_block);
+    else {
+        KAD_DISPATCH_DTYPE(a->dtype, {
+            merge_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);
+        });
+    }
     KAD_CHECK_LAUNCH("merge_kernel");
     return KAD_OK;
 }

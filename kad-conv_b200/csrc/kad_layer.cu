@@ -59,8 +59,10 @@ BranchWs plan_branch(size_t base, int B, int h, int w, int c, size_t es, int gap
     return p;
 }
 
-int branch_path(const KadBranchParams& br, int dtype) {
-    return (br.w_dsc_tc && kad_dsc_tc_supported(br.c, br.c, dtype)) ? 1 : 0;
+// 1 = tcgen05 implicit GEMM, 3 = warp-MMA kernel with the offset convolution fused in, 0 = SIMT
+int branch_path(const KadBranchParams& br, int dtype, int h, int w) {
+    if (br.w_dsc_tc && kad_dsc_tc_supported(br.c, br.c, dtype)) return 1;
+    return kad_dsc_mma_supported(br.c, br.c, dtype, h, w) ? 3 : 0;
 }
 
 }  // namespace
@@ -75,7 +77,7 @@ extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int 
     size_t o = 0;
     for (int i = 0; i < 3; ++i) {
         const int h = H >> i, w = W >> i;
-        const int path = ((tc_branches >> i) & 1) ? 1 : 0;
+        const int path = ((tc_branches >> i) & 1) ? 1 : (kad_dsc_mma_supported(widths[i], widths[i], dtype, h, w) ? 3 : 0);
         o = plan_branch(o, B, h, w, widths[i], es, kad_dsc_gap_tiles(h, w, widths[i], widths[i], path)).end;
     }
     return o;
@@ -88,7 +90,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     int tc_mask = 0;
     for (int i = 0; i < 3; ++i) {
         KAD_CHECK_ARG(a->br[i].c == widths[i], "kad_kadconv_forward: branch %d has %d channels, expected %d", i, a->br[i].c, widths[i]);
-        if (branch_path(a->br[i], a->dtype)) tc_mask |= 1 << i;
+        if (branch_path(a->br[i], a->dtype, a->H >> i, a->W >> i) == 1) tc_mask |= 1 << i;
     }
     KAD_CHECK_ARG(a->workspace_bytes >= kad_kadconv_workspace_bytes(a->B, a->H, a->W, a->dim, a->dtype, tc_mask),
                   "kad_kadconv_forward: workspace of %zu bytes is too small", a->workspace_bytes);
@@ -116,7 +118,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     for (int i = 0; i < 3 && rc == KAD_OK; ++i) {
         const KadBranchParams& br = a->br[i];
         const int h = a->H >> i, w = a->W >> i, c = br.c;
-        const int path = (tc_mask >> i) & 1;
+        const int path = branch_path(br, a->dtype, h, w);
         const int tiles = kad_dsc_gap_tiles(h, w, c, c, path);
         const BranchWs p = plan_branch(o, a->B, h, w, c, es, tiles);
         o = p.end;
@@ -128,14 +130,20 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         rc = kad_lcsa_mask((const float*)(ws + p.rows), (const float*)(ws + p.cols), br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift,
                            br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3, (float*)(ws + p.scratch), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
         if (rc) break;
-        KadDscArgs d{};
-        d.x = ws + p.t; d.weight = br.w_off; d.shift = br.b_off; d.y = ws + p.offset;
-        d.B = a->B; d.H = h; d.W = w; d.Cin = c; d.Cout = 18; d.dtype = a->dtype; d.y_f32 = 1; d.act = KAD_ACT_NONE; d.path = 0; d.status = a->status;
-        rc = kad_dsc_forward(&d, s);
-        if (rc) break;
         KadDscArgs q{};
-        q.x = ws + p.t; q.offset = ws + p.offset; q.mask = ws + p.mask; q.offset_f32 = 1; q.mask_f32 = 1;
-        q.weight = path ? br.w_dsc_tc : (const void*)br.w_dsc_simt;
+        if (path == 3) {
+            q.offset_weight = br.w_off; q.offset_bias = br.b_off;       // offsets computed inside the DSC kernel
+        } else {
+            KadDscArgs d{};
+            d.x = ws + p.t; d.weight = br.w_off; d.shift = br.b_off; d.y = ws + p.offset;
+            d.B = a->B; d.H = h; d.W = w; d.Cin = c; d.Cout = 18; d.dtype = a->dtype; d.y_f32 = 1; d.act = KAD_ACT_NONE; d.status = a->status;
+            d.path = kad_dsc_mma_supported(c, 18, a->dtype, h, w) ? 3 : 0;
+            rc = kad_dsc_forward(&d, s);
+            if (rc) break;
+            q.offset = ws + p.offset; q.offset_f32 = 1;
+        }
+        q.x = ws + p.t; q.mask = ws + p.mask; q.mask_f32 = 1;
+        q.weight = path == 1 ? br.w_dsc_tc : (const void*)br.w_dsc_simt;
         q.scale = br.ep_scale; q.shift = br.ep_shift; q.post = br.ep_post; q.y = ws + p.y; q.gap_partial = (float*)(ws + p.gap);
         q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;
         rc = kad_dsc_forward(&q, s);

@@ -11,7 +11,7 @@ _LIB_PATH = Path(__file__).resolve().parent / '_lib' / 'libkadconv_b200.so'
 
 KAD_F32, KAD_F16, KAD_BF16 = 0, 1, 2
 ACT_NONE, ACT_SILU, ACT_RELU = 0, 1, 2
-PATH_SIMT, PATH_TC, PATH_TC_PAIR = 0, 1, 2
+PATH_SIMT, PATH_TC, PATH_TC_PAIR, PATH_MMA = 0, 1, 2, 3
 
 
 class KadDscArgs(Structure):
@@ -20,7 +20,8 @@ class KadDscArgs(Structure):
                 ('y', c_void_p), ('gap_partial', c_void_p),
                 ('B', c_int), ('H', c_int), ('W', c_int), ('Cin', c_int), ('Cout', c_int),
                 ('dtype', c_int), ('offset_f32', c_int), ('mask_f32', c_int), ('y_f32', c_int), ('act', c_int),
-                ('path', c_int), ('status', c_void_p)]
+                ('path', c_int), ('status', c_void_p),
+                ('offset_weight', c_void_p), ('offset_bias', c_void_p)]
 
 
 class KadMergeArgs(Structure):
@@ -49,6 +50,7 @@ SIGNATURES = {
     'kad_dsc_forward': (c_int, [POINTER(KadDscArgs), c_void_p]),
     'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_tc_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_dsc_mma_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_pack_weight_tc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     'kad_dsc_packed_weight_bytes': (c_size_t, [c_int, c_int, c_int]),
     'kad_dsc_pack_weight_simt': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
@@ -108,8 +110,8 @@ KERNELS_LAUNCHED = [0]
 _KERNELS_PER_CALL = {'kad_lcsa_sums': 2, 'kad_lcsa_mask': 2, 'kad_kadconv_forward': 25}
 
 
-def check(code, what):
-    KERNELS_LAUNCHED[0] += _KERNELS_PER_CALL.get(what, 1)
+def check(code, what, launches=None):
+    KERNELS_LAUNCHED[0] += _KERNELS_PER_CALL.get(what, 1) if launches is None else launches
     if code != 0:
         msg = load().kad_last_error_string().decode(errors='replace')
         raise RuntimeError(f'{what} failed ({code}): {msg}')

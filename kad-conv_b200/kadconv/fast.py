@@ -56,12 +56,14 @@ class _BranchParams:
         self.fc_w1, self.fc_b1 = f(fc[0].weight), f(fc[0].bias)
         self.fc_w2, self.fc_b2 = f(fc[2].weight), f(fc[2].bias)
 
-    def dsc_weight(self, dtype):
-        """(path, packed weight) for activations of `dtype`."""
+    def dsc_weight(self, dtype, h, w):
+        """(path, packed weight) for activations of `dtype` on an h x w map."""
         if dtype != torch.float32 and ops.dsc_tc_supported(self.c, self.c, dtype):
             if dtype not in self.w_dsc_tc:
                 self.w_dsc_tc[dtype] = ops.pack_dsc_weight_tc(self.dsc_weight_raw, dtype)
             return ops.PATH_TC, self.w_dsc_tc[dtype]
+        if ops.dsc_mma_supported(self.c, self.c, dtype, h, w):
+            return ops.PATH_MMA, self.w_dsc_simt
         return ops.PATH_SIMT, self.w_dsc_simt
 
 
@@ -74,18 +76,18 @@ def _prepare(layer, device):
     return st
 
 
-def _layer_args(layer, st, dtype):
-    """ctypes argument block of kad_kadconv_forward for this layer and activation dtype (built once, then reused)."""
+def _layer_args(layer, st, dtype, H, W):
+    """ctypes argument block of kad_kadconv_forward for this layer, activation dtype and map size (built once, then reused)."""
     import ctypes
     from . import _abi
-    key = ('args', dtype)
+    key = ('args', dtype, H, W)
     if key not in st:
         a = _abi.KadLayerArgs()
         tc_mask = 0
         keep = []
         for i, br in enumerate(st['branches']):
             p = a.br[i]
-            path, w = br.dsc_weight(dtype)
+            path, w = br.dsc_weight(dtype, H >> i, W >> i)
             fields = dict(w_proj=br.w_proj, b_proj=br.b_proj, lcsa_w1=br.lcsa['w1'], lcsa_b1=br.lcsa['b1'], lcsa_bn_scale=br.lcsa['bn_m'],
                           lcsa_bn_shift=br.lcsa['bn_a'], lcsa_w2=br.lcsa['w2'], lcsa_b2=br.lcsa['b2'], lcsa_w3=br.lcsa['w3'], lcsa_b3=br.lcsa['b3'],
                           w_off=br.w_off, b_off=br.b_off, w_dsc_simt=br.w_dsc_simt, ep_scale=br.ep_scale, ep_shift=br.ep_shift,
@@ -96,7 +98,8 @@ def _layer_args(layer, st, dtype):
                 p.w_dsc_tc = w.data_ptr(); keep.append(w); tc_mask |= 1 << i
             p.c, p.hidden = br.c, br.fc_w1.shape[0]
         a.dtype = ops._DT[dtype]
-        st[key] = (a, tc_mask, keep)
+        launches = 25 - sum(1 for i, br in enumerate(st['branches']) if br.dsc_weight(dtype, H >> i, W >> i)[0] == ops.PATH_MMA)
+        st[key] = (a, tc_mask, keep, launches)
     return st[key]
 
 
@@ -112,7 +115,7 @@ def kadconv_forward_nhwc(layer, x):
     if H < 4 or W < 4:
         raise RuntimeError(f'KAD-Conv needs H, W >= 4 for its 1/4-resolution branch, got {H}x{W}')
     st = _prepare(layer, x.device)
-    a, tc_mask, _ = _layer_args(layer, st, x.dtype)
+    a, tc_mask, _, launches = _layer_args(layer, st, x.dtype, H, W)
     lib = _abi.load()
     nbytes = lib.kad_kadconv_workspace_bytes(B, H, W, C, a.dtype, tc_mask)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
@@ -120,7 +123,7 @@ def kadconv_forward_nhwc(layer, x):
     a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes
     a.status = ops.status_word(x.device).data_ptr()
     a.B, a.H, a.W, a.dim = B, H, W, C
-    _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward')
+    _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward', launches)
     return out
 
 
@@ -133,10 +136,15 @@ def kadconv_forward_nhwc_stepwise(layer, x):
     for i, br in enumerate(st['branches']):
         t = ops.pool_project(x, br.w_proj, br.b_proj, pool=2 ** i)
         mask = ops.lcsa_mask(t, br.lcsa, mask_f32=True)
-        offset = ops.dsc_forward(t, br.w_off, shift=br.b_off, y_f32=True)
-        path, w = br.dsc_weight(t.dtype)
-        y, gap = ops.dsc_forward(t, w, offset, mask, scale=br.ep_scale, shift=br.ep_shift, post=br.ep_post,
-                                 act=ops.ACT_RELU, path=path, want_gap=True, cout=br.c)
+        path, w = br.dsc_weight(t.dtype, t.shape[1], t.shape[2])
+        if path == ops.PATH_MMA:      # the offset convolution runs inside the DSC kernel
+            y, gap = ops.dsc_forward(t, w, None, mask, scale=br.ep_scale, shift=br.ep_shift, post=br.ep_post, act=ops.ACT_RELU,
+                                     path=path, want_gap=True, offset_weight=br.w_off, offset_bias=br.b_off)
+        else:
+            off_path = ops.PATH_MMA if ops.dsc_mma_supported(br.c, 18, t.dtype, t.shape[1], t.shape[2]) else ops.PATH_SIMT
+            offset = ops.dsc_forward(t, br.w_off, shift=br.b_off, y_f32=True, path=off_path)
+            y, gap = ops.dsc_forward(t, w, offset, mask, scale=br.ep_scale, shift=br.ep_shift, post=br.ep_post,
+                                     act=ops.ACT_RELU, path=path, want_gap=True, cout=br.c)
         atts.append(ops.se_excite(gap, t.shape[1] * t.shape[2], br.fc_w1, br.fc_b1, br.fc_w2, br.fc_b2))
         ys.append(y)
     return ops.merge_upsample_residual(x, ys, atts)

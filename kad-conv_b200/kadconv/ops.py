@@ -8,7 +8,7 @@ import ctypes
 import torch
 
 from . import _abi
-from ._abi import ACT_NONE, ACT_RELU, ACT_SILU, KAD_BF16, KAD_F16, KAD_F32, PATH_SIMT, PATH_TC, PATH_TC_PAIR
+from ._abi import ACT_NONE, ACT_RELU, ACT_SILU, KAD_BF16, KAD_F16, KAD_F32, PATH_MMA, PATH_SIMT, PATH_TC, PATH_TC_PAIR
 
 _DT = {torch.float32: KAD_F32, torch.float16: KAD_F16, torch.bfloat16: KAD_BF16}
 
@@ -80,6 +80,10 @@ def dsc_tc_supported(Cin, Cout, dtype):
     return bool(_abi.load().kad_dsc_tc_supported(Cin, Cout, _DT[dtype]))
 
 
+def dsc_mma_supported(Cin, Cout, dtype, H, W):
+    return dtype in _DT and bool(_abi.load().kad_dsc_mma_supported(Cin, Cout, _DT[dtype], H, W))
+
+
 def pack_dsc_weight_tc(w, dtype):
     """[Cout,Cin,3,3] -> the tensor path's packed K-major operand in `dtype`."""
     w = _cuda(w.detach().float().contiguous(), 'weight')
@@ -113,17 +117,19 @@ def check_status(device):
 
 
 def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=None, act=ACT_NONE,
-                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None):
+                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None, offset_weight=None, offset_bias=None):
     """Deformable 3x3 convolution with fused epilogue on NHWC tensors.
 
     x [B,H,W,Cin]; offset [B,H,W,18] (float32 or x.dtype) or None; mask [B,H,W,9] or None;
-    weight: pack_dsc_weight_simt(...) for PATH_SIMT or pack_dsc_weight_tc(...) for PATH_TC.
+    weight: pack_dsc_weight_simt(...) for PATH_SIMT / PATH_MMA or pack_dsc_weight_tc(...) for PATH_TC.
+    PATH_MMA only: offset_weight (pack_dsc_weight_simt of the offset convolution's weight, [9,Cin,18]) and
+    offset_bias ([18]) make the kernel compute the offsets itself instead of reading `offset`.
     Returns y [B,H,W,Cout] (and the per-tile channel sums [B,tiles,Cout] when want_gap).
     """
     lib = _abi.load()
     x = _cuda(x, 'x')
     B, H, W, Cin = x.shape
-    if path == PATH_SIMT:
+    if path in (PATH_SIMT, PATH_MMA):
         if weight.dim() != 3 or weight.shape[0] != 9 or weight.shape[1] != Cin or weight.dtype != torch.float32:
             raise ValueError('SIMT path expects weight packed as float32 [9,Cin,Cout]')
         Cout = weight.shape[2]
@@ -147,6 +153,16 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
         a.mask = mask.data_ptr(); a.mask_f32 = int(mask.dtype == torch.float32)
         if not a.mask_f32 and mask.dtype != x.dtype:
             raise TypeError('mask must be float32 or the activation dtype')
+    if offset_weight is not None:
+        if path != PATH_MMA:
+            raise ValueError('offset_weight is an option of PATH_MMA')
+        if tuple(_f32(offset_weight, 'offset_weight').shape) != (9, Cin, 18):
+            raise ValueError('offset_weight must be float32 [9,Cin,18]')
+        a.offset_weight = offset_weight.data_ptr()
+        if offset_bias is not None:
+            if _f32(offset_bias, 'offset_bias').numel() != 18:
+                raise ValueError('offset_bias must have 18 elements')
+            a.offset_bias = offset_bias.data_ptr()
     for name, t in (('scale', scale), ('shift', shift), ('post', post)):
         if t is not None:
             if _f32(t, name).numel() != Cout:

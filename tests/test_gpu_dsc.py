@@ -151,3 +151,101 @@ def test_tc_pair_kernel_matches_single(shape):
     assert torch.equal(y1, y2) and torch.equal(g1, g2)
     ref = torch.relu(ko.deform_conv2d(x, off, w, None, msk) * scale.view(1, -1, 1, 1) + (b * scale).view(1, -1, 1, 1))
     assert rel_err(y2.float().cpu().permute(0, 3, 1, 2), ref) <= 1e-2
+
+
+# ---- path 3: warp-level tensor-core kernel for small channel counts --------------------------------------------
+
+@pytest.mark.parametrize('shape,dtype', [((2, 12, 12, 20, 25), torch.float16), ((1, 10, 10, 9, 7), torch.float16),
+                                         ((2, 21, 21, 13, 30), torch.float16), ((1, 22, 22, 50, 50), torch.float16),
+                                         ((1, 44, 43, 16, 16), torch.float16), ((2, 64, 64, 10, 11), torch.float16),
+                                         ((1, 7, 5, 33, 9), torch.float16), ((2, 21, 21, 12, 10), torch.bfloat16),
+                                         ((1, 32, 18, 17, 19), torch.bfloat16)])
+def test_mma_matches_oracle(shape, dtype):
+    """Odd channel counts (2-byte aligned pixels), partial 16-channel chunks, pixel counts that do not fill a warp."""
+    from kadconv import ops
+    B, Cin, Cout, H, W = shape
+    x, off, msk, w, b = dcn_inputs(B, Cin, Cout, H, W, seed=sum(shape) + 3)
+    x, w = round_to(x, dtype), round_to(w, dtype)
+    ref = ko.deform_conv2d(x, off, w, b, msk)
+    y = _run(x, off, msk, w, b, dtype, ops.PATH_MMA).float().cpu().permute(0, 3, 1, 2)
+    assert rel_err(y, ref) <= 1e-2
+
+
+def test_mma_plain_conv_mode_epilogue_and_large_offsets():
+    from kadconv import ops
+    dtype = torch.float16
+    x, off, msk, w, b = dcn_inputs(2, 12, 18, 11, 8, seed=5, offset_std=6.0)
+    x, w = round_to(x, dtype), round_to(w, dtype)
+    g = np.random.default_rng(1)
+    scale = torch.from_numpy(g.uniform(0.5, 1.5, 18).astype(np.float32))
+    post = torch.from_numpy(g.uniform(0.5, 1.5, 18).astype(np.float32))
+    # offset = mask = NULL: ordinary convolution, float32 output (the offset convolution's configuration)
+    ref = torch.nn.functional.conv2d(x, w, b, padding=1)
+    from kadconv import ops as _ops
+    xg = nhwc(x).cuda().half()
+    y = _ops.dsc_forward(xg, _ops.pack_dsc_weight_simt(w.cuda()), shift=b.cuda(), path=ops.PATH_MMA, y_f32=True)
+    assert y.dtype == torch.float32
+    assert rel_err(y.cpu().permute(0, 3, 1, 2), ref) <= 2e-3
+    # deformable with offsets N(0,6) (most samples partly or fully outside), fused scale/shift/ReLU/post, SE sums
+    ref2 = torch.relu(ko.deform_conv2d(x, off, w, None, msk) * scale.view(1, -1, 1, 1) + (b * scale).view(1, -1, 1, 1)) * post.view(1, -1, 1, 1)
+    y2, gap = _run(x, off, msk, w, b, dtype, ops.PATH_MMA, act=2, scale=scale, post=post, want_gap=True)
+    y2 = y2.float().cpu().permute(0, 3, 1, 2)
+    assert rel_err(y2, ref2) <= 1e-2
+    assert rel_err(gap.sum(1).cpu(), y2.sum((2, 3))) <= 1e-3
+    a = _run(x, off, msk, w, b, dtype, ops.PATH_MMA)
+    c = _run(x, off, msk, w, b, dtype, ops.PATH_MMA)
+    assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 12, 12, 20, 25), torch.float16), ((1, 21, 21, 31, 18), torch.float16),
+                                         ((1, 44, 44, 12, 12), torch.float16), ((2, 10, 10, 9, 14), torch.bfloat16)])
+def test_mma_fused_offset_convolution(shape, dtype):
+    """With offset_weight the kernel computes offsets = conv3x3(x) + bias itself (DSC.forward, kad_conv.py:64-67)."""
+    from kadconv import ops
+    B, Cin, Cout, H, W = shape
+    x, _, msk, w, b = dcn_inputs(B, Cin, Cout, H, W, seed=sum(shape) + 11)
+    g = np.random.default_rng(sum(shape))
+    w_off = round_to(torch.from_numpy((g.standard_normal((18, Cin, 3, 3)) * (1.5 / np.sqrt(9 * Cin))).astype(np.float32)), dtype)
+    b_off = torch.from_numpy(g.standard_normal(18).astype(np.float32) * 0.5)
+    x, w = round_to(x, dtype), round_to(w, dtype)
+    off = torch.nn.functional.conv2d(x, w_off, b_off, padding=1)
+    ref = ko.deform_conv2d(x, off, w, b, msk)
+    xg = nhwc(x).cuda().to(dtype)
+    mg = nhwc(msk).cuda()
+    y, gap = ops.dsc_forward(xg, ops.pack_dsc_weight_simt(w.cuda()), None, mg, shift=b.cuda(), path=ops.PATH_MMA, want_gap=True,
+                             offset_weight=ops.pack_dsc_weight_simt(w_off.cuda()), offset_bias=b_off.cuda())
+    y = y.float().cpu().permute(0, 3, 1, 2)
+    assert rel_err(y, ref) <= 1e-2
+    assert rel_err(gap.sum(1).cpu(), y.sum((2, 3))) <= 1e-3
+    # and it agrees with the two-kernel sequence on the same path
+    offg = ops.dsc_forward(xg, ops.pack_dsc_weight_simt(w_off.cuda()), shift=b_off.cuda(), path=ops.PATH_MMA, y_f32=True)
+    y2 = ops.dsc_forward(xg, ops.pack_dsc_weight_simt(w.cuda()), offg, mg, shift=b.cuda(), path=ops.PATH_MMA)
+    assert rel_err(y2.float().cpu().permute(0, 3, 1, 2), y) <= 2e-3
+
+
+@pytest.mark.parametrize('shape,dtype', [((1, 12, 12, 70, 20), torch.float16), ((2, 21, 22, 90, 33), torch.float16),
+                                         ((1, 10, 10, 64, 50), torch.bfloat16)])
+def test_mma_samples_outside_the_staged_rows(shape, dtype):
+    """Tall images with offsets N(0, 8): many samples leave the rows staged in shared memory and are read from global
+    memory (the per-tap slow variant), many leave the image."""
+    from kadconv import ops
+    B, Cin, Cout, H, W = shape
+    x, off, msk, w, b = dcn_inputs(B, Cin, Cout, H, W, seed=sum(shape) + 5, offset_std=8.0)
+    x, w = round_to(x, dtype), round_to(w, dtype)
+    ref = ko.deform_conv2d(x, off, w, b, msk)
+    y = _run(x, off, msk, w, b, dtype, ops.PATH_MMA).float().cpu().permute(0, 3, 1, 2)
+    assert rel_err(y, ref) <= 1e-2
+
+
+def test_mma_rejects_what_it_cannot_run():
+    from kadconv import ops
+    x = torch.zeros((1, 8, 8, 80), device='cuda', dtype=torch.float16)
+    with pytest.raises(RuntimeError, match='warp-MMA'):
+        ops.dsc_forward(x, torch.zeros((9, 80, 8), device='cuda'), path=ops.PATH_MMA)
+    with pytest.raises(RuntimeError, match='warp-MMA'):
+        ops.dsc_forward(x[..., :8].contiguous().float(), torch.zeros((9, 8, 8), device='cuda'), path=ops.PATH_MMA)
+    # rows too long for shared memory
+    assert not ops.dsc_mma_supported(64, 64, torch.float16, 8, 4000)
+    assert ops.dsc_mma_supported(44, 44, torch.bfloat16, 200, 200)
+    with pytest.raises(RuntimeError, match='warp-MMA'):
+        ops.dsc_forward(torch.zeros((1, 4, 4000, 64), device='cuda', dtype=torch.float16), torch.zeros((9, 64, 64), device='cuda'), path=ops.PATH_MMA)
