@@ -168,12 +168,19 @@ int kad_se_rescale(const void* x, const float* att, void* y, int B, int H, int W
 /* Tail of KADConv.forward (kad_conv.py:117-121): out = cat_i( upsample_i( y_i * att_i ) ) + x with bilinear
  * upsampling, align_corners = False. Counterpart of k_upsample_bilinear_att / k_cat_residual_att0
  * (kadc_fused_sm75.py:1245-1331).
- *   x, out [B,H,W,C] dtype; y_i [B,H_i,W_i,c_i] dtype, att_i float32 [B][c_i], i = 0..2, sum c_i = C. */
+ *   x, out [B,H,W,C] dtype; y_i [B,H_i,W_i,c_i] dtype, att_i float32 [B][c_i], i = 0..2, sum c_i = C.
+ * Optional (set gap[0..2] or none): the channel attention fc (kad_conv.py:104-108,:118) is evaluated inside the
+ * kernel from the channel sums the DSC kernels wrote (gap[i] float32 [B][gap_tiles[i]][c_i], mean = sum / (h_i*w_i)),
+ * exactly as kad_se_excite does; att[i] must then still point to B*c_i floats, which general shapes use as scratch.
+ * out_cstride (0 = C): elements per pixel of `out`, so the result can land in a channel slice of a wider tensor. */
 typedef struct KadMergeArgs {
     const void* x; void* out;
     const void* y[3]; const float* att[3];
     int c[3], h[3], w[3];
     int B, H, W, C, dtype;
+    const float* gap[3]; const float* fc_w1[3]; const float* fc_b1[3]; const float* fc_w2[3]; const float* fc_b2[3];
+    int gap_tiles[3], hidden[3];
+    int out_cstride;
 } KadMergeArgs;
 int kad_merge_upsample_residual(const KadMergeArgs* args, void* stream);
 

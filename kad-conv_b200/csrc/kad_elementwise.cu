@@ -140,27 +140,47 @@ lcsa_mask_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, 
 }
 
 // ------------------------------------------------------------------------------ SE
-__global__ void se_excite_kernel(const float* __restrict__ gap_partial, int tiles, float inv_count,
-                                 const float* __restrict__ w1, const float* __restrict__ b1,
-                                 const float* __restrict__ w2, const float* __restrict__ b2,
-                                 float* __restrict__ att, int C, int Hd) {
-    extern __shared__ float sm[];
-    float* mean = sm;        // [C]
-    float* hid = sm + C;     // [Hd]
-    int b = blockIdx.x, t = threadIdx.x;
-    for (int c = t; c < C; c += blockDim.x) {
+// Channel means from per-tile sums, by all 256 threads of a block and in a fixed order: K tiles are summed side by side
+// (thread = (tile residue, channel), coalesced), then the K partial sums of a channel are added in order.
+__device__ __forceinline__ int se_parallel_tiles(int tiles, int C) { return max(1, min(tiles, 256 / max(C, 1))); }
+__device__ __forceinline__ void se_partial_sums(const float* __restrict__ gap_b, int tiles, int C, float* part, int tid) {
+    const int K = se_parallel_tiles(tiles, C);
+    for (int idx = tid; idx < K * C; idx += 256) {
+        const int k0 = idx / C, c = idx - k0 * C;
         float s = 0.f;
-        for (int i = 0; i < tiles; ++i) s += gap_partial[((size_t)b * tiles + i) * C + c];
-        mean[c] = s * inv_count;
+        for (int k = k0; k < tiles; k += K) s += gap_b[(size_t)k * C + c];
+        part[idx] = s;
     }
+}
+__device__ __forceinline__ float se_mean_of(const float* part, int tiles, int C, int c, float inv_count) {
+    const int K = se_parallel_tiles(tiles, C);
+    float s = 0.f;
+    for (int k0 = 0; k0 < K; ++k0) s += part[k0 * C + c];
+    return s * inv_count;
+}
+
+// 256 threads per image
+__global__ void __launch_bounds__(256)
+se_excite_kernel(const float* __restrict__ gap_partial, int tiles, float inv_count,
+                 const float* __restrict__ w1, const float* __restrict__ b1,
+                 const float* __restrict__ w2, const float* __restrict__ b2,
+                 float* __restrict__ att, int C, int Hd) {
+    extern __shared__ float sm[];
+    float* mean = sm;                    // [C]
+    float* hid = sm + C;                 // [Hd]
+    float* part = hid + Hd;              // [max(256, C)]
+    int b = blockIdx.x, t = threadIdx.x;
+    se_partial_sums(gap_partial + (size_t)b * tiles * C, tiles, C, part, t);
     __syncthreads();
-    for (int h = t; h < Hd; h += blockDim.x) {
+    for (int c = t; c < C; c += 256) mean[c] = se_mean_of(part, tiles, C, c, inv_count);
+    __syncthreads();
+    for (int h = t; h < Hd; h += 256) {
         float s = b1[h];
         for (int c = 0; c < C; ++c) s = fmaf(w1[(size_t)h * C + c], mean[c], s);
         hid[h] = fmaxf(s, 0.f);
     }
     __syncthreads();
-    for (int c = t; c < C; c += blockDim.x) {
+    for (int c = t; c < C; c += 256) {
         float s = b2[c];
         for (int h = 0; h < Hd; ++h) s = fmaf(w2[(size_t)c * Hd + h], hid[h], s);
         att[(size_t)b * C + c] = sigmoidf_(s);
@@ -250,12 +270,12 @@ template <> struct MergeIO<__nv_bfloat16, 2> {
     static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[2]) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]); }
 };
 
-// blockDim = 256 = (pixel lanes) x (channel groups rounded up to a multiple of 32): a thread keeps its V channels (so its
+// blockDim = 256 = (pixel lanes) x (channel groups rounded up to a power of two): a thread keeps its V channels (so its
 // branch, its attention scalars and its source tensor are fixed per image) and walks over pixels; consecutive threads
 // touch consecutive channels of the same pixel, i.e. consecutive addresses of x, out and the branch tensor.
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
-merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp, int pix_per_block) {
+merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp, int pix_per_block, int out_ld) {
     const int cl0 = threadIdx.x % Cp, pl = threadIdx.x / Cp, PL = 256 / Cp;
     const int b = blockIdx.y;
     const int HW = p.H * p.W;
@@ -263,13 +283,16 @@ merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp
     for (int c = cl0 * V; c < p.C; c += Cp * V) {
         int i = 0, cl = c;
         if (cl >= p.c[0]) { cl -= p.c[0]; i = 1; if (cl >= p.c[1]) { cl -= p.c[1]; i = 2; } }
-        const int ci = p.c[i], hi = p.h[i], wi = p.w[i];
-        const T* yi = reinterpret_cast<const T*>(p.y[i]) + (size_t)b * hi * wi * ci + cl;
+        // (selected by value: indexing the parameter arrays with a run-time i would move them to local memory)
+        const int ci = i == 0 ? p.c[0] : (i == 1 ? p.c[1] : p.c[2]), hi = i == 0 ? p.h[0] : (i == 1 ? p.h[1] : p.h[2]);
+        const int wi = i == 0 ? p.w[0] : (i == 1 ? p.w[1] : p.w[2]);
+        const T* yi = reinterpret_cast<const T*>(i == 0 ? p.y[0] : (i == 1 ? p.y[1] : p.y[2])) + (size_t)b * hi * wi * ci + cl;
+        const float* ai = i == 0 ? p.att[0] : (i == 1 ? p.att[1] : p.att[2]);
         float a[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) a[v] = p.att[i][(size_t)b * ci + cl + v];
+        for (int v = 0; v < V; ++v) a[v] = ai[(size_t)b * ci + cl + v];
         const bool same = (hi == p.H && wi == p.W);
-        const float sy = p.sy[i], sx = p.sx[i];
+        const float sy = i == 0 ? p.sy[0] : (i == 1 ? p.sy[1] : p.sy[2]), sx = i == 0 ? p.sx[0] : (i == 1 ? p.sx[1] : p.sx[2]);
         for (int pix = pix0 + pl; pix < pix1; pix += PL) {
             const int yh = pix / p.W, xw = pix - yh * p.W;
             float val[V];
@@ -291,8 +314,281 @@ merge_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int Cp
             MergeIO<T, V>::ld(x + e, xin);
 #pragma unroll
             for (int v = 0; v < V; ++v) o[v] = fmaf(val[v], a[v], xin[v]);
-            MergeIO<T, V>::st(out + e, o);
+            MergeIO<T, V>::st(out + ((size_t)b * HW + pix) * out_ld + c, o);
         }
+    }
+}
+
+// The same tail for 16-bit tensors with C % 8 == 0: a thread owns one 16-byte vector (8 channels of one pixel) of x and
+// out, so both are read and written fully coalesced; the branch values are gathered per channel (2-byte loads that hit
+// L1: neighbouring pixels share their sources). Optionally the squeeze-excite MLP of the three branches is evaluated at
+// the head of every block (a few hundred FMAs) from the channel sums the DSC kernels left behind, in the same order of
+// operations as se_excite_kernel, so the attention never makes a trip through memory or a launch of its own.
+struct MergeSe {
+    const float* gap[3]; const float* w1[3]; const float* b1[3]; const float* w2[3]; const float* b2[3];
+    int tiles[3], hidden[3];
+    float inv[3];
+};
+
+// Attention of the three branches of one image into att_s[C] (channel order of the concatenation): either copied from
+// memory, or the squeeze-excite MLP evaluated here from the channel sums, with the arithmetic of se_excite_kernel.
+// scratch: mean[C] | hid[hidden0 + hidden1 + hidden2] | part[3][256]; every branch width <= 256.
+__device__ __forceinline__ void merge_attention(const MergeParams& p, const MergeSe& se, int use_se, int b, float* att_s, float* scratch, int tid) {
+    const int c0 = p.c[0], c1 = p.c[1], c2 = p.c[2];
+    if (!use_se) {
+        for (int c = tid; c < c0; c += 256) att_s[c] = p.att[0][(size_t)b * c0 + c];
+        for (int c = tid; c < c1; c += 256) att_s[c0 + c] = p.att[1][(size_t)b * c1 + c];
+        for (int c = tid; c < c2; c += 256) att_s[c0 + c1 + c] = p.att[2][(size_t)b * c2 + c];
+        __syncthreads();
+        return;
+    }
+    float* mean = scratch;
+    float* hid = mean + p.C;
+    float* part = hid + se.hidden[0] + se.hidden[1] + se.hidden[2];
+    se_partial_sums(se.gap[0] + (size_t)b * se.tiles[0] * c0, se.tiles[0], c0, part, tid);
+    se_partial_sums(se.gap[1] + (size_t)b * se.tiles[1] * c1, se.tiles[1], c1, part + 256, tid);
+    se_partial_sums(se.gap[2] + (size_t)b * se.tiles[2] * c2, se.tiles[2], c2, part + 512, tid);
+    __syncthreads();
+    for (int c = tid; c < p.C; c += 256) {
+        if (c < c0) mean[c] = se_mean_of(part, se.tiles[0], c0, c, se.inv[0]);
+        else if (c < c0 + c1) mean[c] = se_mean_of(part + 256, se.tiles[1], c1, c - c0, se.inv[1]);
+        else mean[c] = se_mean_of(part + 512, se.tiles[2], c2, c - c0 - c1, se.inv[2]);
+    }
+    __syncthreads();
+    const int h0 = se.hidden[0], h1 = se.hidden[1], h2 = se.hidden[2];
+    for (int h = tid; h < h0 + h1 + h2; h += 256) {
+        const int i = h < h0 ? 0 : (h < h0 + h1 ? 1 : 2);
+        const int hl = i == 0 ? h : (i == 1 ? h - h0 : h - h0 - h1), ci = i == 0 ? c0 : (i == 1 ? c1 : c2), cb = i == 0 ? 0 : (i == 1 ? c0 : c0 + c1);
+        const float* w1 = i == 0 ? se.w1[0] : (i == 1 ? se.w1[1] : se.w1[2]);
+        const float* b1 = i == 0 ? se.b1[0] : (i == 1 ? se.b1[1] : se.b1[2]);
+        float s = b1[hl];
+        for (int c = 0; c < ci; ++c) s = fmaf(w1[(size_t)hl * ci + c], mean[cb + c], s);
+        hid[h] = fmaxf(s, 0.f);
+    }
+    __syncthreads();
+    for (int c = tid; c < p.C; c += 256) {
+        const int i = c < c0 ? 0 : (c < c0 + c1 ? 1 : 2);
+        const int cl = i == 0 ? c : (i == 1 ? c - c0 : c - c0 - c1), Hd = i == 0 ? h0 : (i == 1 ? h1 : h2), hb = i == 0 ? 0 : (i == 1 ? h0 : h0 + h1);
+        const float* w2 = i == 0 ? se.w2[0] : (i == 1 ? se.w2[1] : se.w2[2]);
+        const float* b2 = i == 0 ? se.b2[0] : (i == 1 ? se.b2[1] : se.b2[2]);
+        float s = b2[cl];
+        for (int h = 0; h < Hd; ++h) s = fmaf(w2[(size_t)cl * Hd + h], hid[hb + h], s);
+        att_s[c] = sigmoidf_(s);
+    }
+    __syncthreads();
+}
+
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+template <typename T> __device__ __forceinline__ uint32_t pack2f(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2f<__half>(float a, float b) { __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
+template <> __device__ __forceinline__ uint32_t pack2f<__nv_bfloat16>(float a, float b) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
+
+struct BranchTap { int o00, o01, o10, o11; float ly, lx; };
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+merge_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, MergeParams p, MergeSe se, int use_se, int G, int PL,
+                  int pix_per_block, int out_ld8) {
+    extern __shared__ float sm_merge[];
+    float* att_s = sm_merge;             // [C] attention of this image, channel order of the concatenation
+    const int b = blockIdx.y, tid = threadIdx.x;
+    merge_attention(p, se, use_se, b, att_s, att_s + p.C, tid);
+    const int grp = tid % G, pl = tid / G;
+    if (pl >= PL) return;
+    const int HW = p.H * p.W;
+    // the 8 channels of this thread: branch, channel inside the branch, attention
+    int bi[8], cl[8]; float at[8];
+    int uses = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int c = grp * 8 + j, i = 0;
+        at[j] = att_s[c];
+        if (c >= p.c[0]) { c -= p.c[0]; i = 1; if (c >= p.c[1]) { c -= p.c[1]; i = 2; } }
+        bi[j] = i; cl[j] = c; uses |= 1 << i;
+    }
+    const T* yb[3]; int cc[3]; bool same[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        cc[i] = p.c[i];
+        yb[i] = reinterpret_cast<const T*>(p.y[i]) + (size_t)b * p.h[i] * p.w[i] * cc[i];
+        same[i] = p.h[i] == p.H && p.w[i] == p.W;
+    }
+    const int pix0 = blockIdx.x * pix_per_block, pix1 = min(HW, pix0 + pix_per_block);
+    for (int pix = pix0 + pl; pix < pix1; pix += PL) {
+        const int yh = pix / p.W, xw = pix - yh * p.W;
+        const uint4 xv = x[((size_t)b * HW + pix) * G + grp];
+        BranchTap bt[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            if (!((uses >> i) & 1)) continue;
+            if (same[i]) { bt[i].o00 = bt[i].o01 = bt[i].o10 = bt[i].o11 = pix * cc[i]; bt[i].ly = bt[i].lx = 0.f; continue; }
+            int y0, y1, x0, x1;
+            src_index(yh, p.sy[i], p.h[i], y0, y1, bt[i].ly);
+            src_index(xw, p.sx[i], p.w[i], x0, x1, bt[i].lx);
+            bt[i].o00 = (y0 * p.w[i] + x0) * cc[i]; bt[i].o01 = (y0 * p.w[i] + x1) * cc[i];
+            bt[i].o10 = (y1 * p.w[i] + x0) * cc[i]; bt[i].o11 = (y1 * p.w[i] + x1) * cc[i];
+        }
+        float val[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // (values are selected, never references: the per-branch state has to stay in registers)
+            const int i = bi[j];
+            const int o00 = i == 0 ? bt[0].o00 : (i == 1 ? bt[1].o00 : bt[2].o00), o01 = i == 0 ? bt[0].o01 : (i == 1 ? bt[1].o01 : bt[2].o01);
+            const int o10 = i == 0 ? bt[0].o10 : (i == 1 ? bt[1].o10 : bt[2].o10), o11 = i == 0 ? bt[0].o11 : (i == 1 ? bt[1].o11 : bt[2].o11);
+            const float ly = i == 0 ? bt[0].ly : (i == 1 ? bt[1].ly : bt[2].ly), lx = i == 0 ? bt[0].lx : (i == 1 ? bt[1].lx : bt[2].lx);
+            const T* yi = (i == 0 ? yb[0] : (i == 1 ? yb[1] : yb[2])) + cl[j];
+            const bool sm_ = i == 0 ? same[0] : (i == 1 ? same[1] : same[2]);
+            if (sm_) {
+                val[j] = to_f<T>(yi[o00]);
+            } else {
+                const float v00 = to_f<T>(yi[o00]), v01 = to_f<T>(yi[o01]), v10 = to_f<T>(yi[o10]), v11 = to_f<T>(yi[o11]);
+                val[j] = (1.f - ly) * ((1.f - lx) * v00 + lx * v01) + ly * ((1.f - lx) * v10 + lx * v11);
+            }
+        }
+        const float2 x0 = unpack2<T>(xv.x), x1 = unpack2<T>(xv.y), x2 = unpack2<T>(xv.z), x3 = unpack2<T>(xv.w);
+        uint4 o;
+        o.x = pack2f<T>(fmaf(val[0], at[0], x0.x), fmaf(val[1], at[1], x0.y));
+        o.y = pack2f<T>(fmaf(val[2], at[2], x1.x), fmaf(val[3], at[3], x1.y));
+        o.z = pack2f<T>(fmaf(val[4], at[4], x2.x), fmaf(val[5], at[5], x2.y));
+        o.w = pack2f<T>(fmaf(val[6], at[6], x3.x), fmaf(val[7], at[7], x3.y));
+        out[((size_t)b * HW + pix) * out_ld8 + grp] = o;
+    }
+}
+
+// The tail for 16-bit tensors with the branch rows staged in shared memory, in two phases. A block owns R consecutive
+// output rows of one image. The source rows those outputs interpolate from are, for every branch, ONE contiguous run of
+// the NHWC branch tensor, copied to shared memory with 16-byte accesses (the run keeps its offset from a 16-byte
+// boundary, the ragged ends go as 2-byte elements).
+//   phase 0  the x rows are copied into an output tile in shared memory (coalesced)
+//   phase 1  one work item per (branch, pixel): the interpolation geometry is computed once and reused for all channels
+//            of the branch; tile = tile + att * upsample(y), formed in fp32
+//   phase 2  the tile leaves coalesced (out may be a channel slice of a wider tensor).
+// PAIRS: every branch width is even, so channels are handled two at a time with 4-byte accesses.
+struct MergeStage { int off[3]; int cap_rows[3]; int tile_off; };     // byte offsets of the branch regions and the tile
+
+__device__ __forceinline__ void copy_run_to_smem(unsigned char* dst, const unsigned char* src, int nbytes, int tid) {
+    // dst and src have the same offset from a 16-byte boundary; nbytes is even
+    const int head = min(nbytes, static_cast<int>((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15));
+    const int body = (nbytes - head) >> 4, tail = nbytes - head - (body << 4);
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
+    uint4* d4 = reinterpret_cast<uint4*>(dst + head);
+    for (int i = tid; i < body; i += 256) d4[i] = __ldg(s4 + i);
+    if (tid < (head >> 1)) reinterpret_cast<uint16_t*>(dst)[tid] = reinterpret_cast<const uint16_t*>(src)[tid];
+    else if (tid >= 32 && tid - 32 < (tail >> 1))
+        reinterpret_cast<uint16_t*>(dst + head + (body << 4))[tid - 32] = reinterpret_cast<const uint16_t*>(src + head + (body << 4))[tid - 32];
+}
+
+// One branch of phase 1 (i is a compile-time constant at every call site, so nothing is indexed at run time).
+template <typename T, bool PAIRS>
+__device__ __forceinline__ void merge_branch(const T* __restrict__ ysrc, T* __restrict__ tile, const float* __restrict__ att,
+                                             int c, int cbase, int hi, int wi, float sy, float sx, int lo, bool same,
+                                             int pitch, int W, int row0, int npx, int tid) {
+    for (int q = tid; q < npx; q += 256) {
+        const int yh = row0 + q / W, xw = q % W;
+        int o00, o01, o10, o11; float ly = 0.f, lx = 0.f;
+        if (same) { o00 = o01 = o10 = o11 = ((yh - lo) * wi + xw) * c; }
+        else {
+            int y0, y1, x0, x1;
+            src_index(yh, sy, hi, y0, y1, ly);
+            src_index(xw, sx, wi, x0, x1, lx);
+            y0 -= lo; y1 -= lo;
+            o00 = (y0 * wi + x0) * c; o01 = (y0 * wi + x1) * c; o10 = (y1 * wi + x0) * c; o11 = (y1 * wi + x1) * c;
+        }
+        T* tp = tile + (size_t)q * pitch + cbase;      // holds x on entry, out on exit
+        if (PAIRS) {
+            for (int ch = 0; ch < c; ch += 2) {
+                const float2 xin = unpack2<T>(*reinterpret_cast<const uint32_t*>(tp + ch));
+                float2 v;
+                if (same) v = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o00 + ch));
+                else {
+                    const float2 a = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o00 + ch)), b = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o01 + ch));
+                    const float2 d = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o10 + ch)), e = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o11 + ch));
+                    v.x = (1.f - ly) * ((1.f - lx) * a.x + lx * b.x) + ly * ((1.f - lx) * d.x + lx * e.x);
+                    v.y = (1.f - ly) * ((1.f - lx) * a.y + lx * b.y) + ly * ((1.f - lx) * d.y + lx * e.y);
+                }
+                *reinterpret_cast<uint32_t*>(tp + ch) = pack2f<T>(fmaf(v.x, att[ch], xin.x), fmaf(v.y, att[ch + 1], xin.y));
+            }
+        } else {
+            for (int ch = 0; ch < c; ++ch) {
+                const float xin = to_f<T>(tp[ch]);
+                float v;
+                if (same) v = to_f<T>(ysrc[o00 + ch]);
+                else v = (1.f - ly) * ((1.f - lx) * to_f<T>(ysrc[o00 + ch]) + lx * to_f<T>(ysrc[o01 + ch])) +
+                         ly * ((1.f - lx) * to_f<T>(ysrc[o10 + ch]) + lx * to_f<T>(ysrc[o11 + ch]));
+                tp[ch] = from_f<T>(fmaf(v, att[ch], xin));
+            }
+        }
+    }
+}
+
+template <typename T, bool PAIRS>
+__global__ void __launch_bounds__(256)
+merge_tile_kernel(const T* __restrict__ x, uint4* __restrict__ out, MergeParams p, MergeSe se, MergeStage stg, int use_se, int R, int out_ld8,
+                  int se_floats) {
+    extern __shared__ __align__(16) unsigned char sm_rows[];
+    float* att_s = reinterpret_cast<float*>(sm_rows);      // [C], then the scratch of merge_attention
+    unsigned char* stage = sm_rows + se_floats * 4;
+    T* tile = reinterpret_cast<T*>(stage + stg.tile_off);
+    const int b = blockIdx.y, tid = threadIdx.x;
+    const int row0 = blockIdx.x * R, row1 = min(p.H, row0 + R);
+    const int HW = p.H * p.W, npx = (row1 - row0) * p.W;
+
+    // x rows -> the output tile. A pixel of the tile is C/2 + 1 words long: phase 1 runs one thread per pixel, and an odd
+    // pitch keeps its 32 lanes on 32 different banks (a pitch of C/2 words would be a 16- or 32-way conflict).
+    const int Cw = p.C >> 1, pitch_w = Cw + 1, pitch = 2 * pitch_w;
+    const bool pow2 = (Cw & (Cw - 1)) == 0;
+    const int sh = 31 - __clz(Cw);
+    {
+        const uint32_t* xs = reinterpret_cast<const uint32_t*>(x + ((size_t)b * HW + (size_t)row0 * p.W) * p.C);
+        uint32_t* tw = reinterpret_cast<uint32_t*>(tile);
+        for (int w = tid; w < npx * Cw; w += 256) {
+            const int q = pow2 ? (w >> sh) : (w / Cw);
+            tw[q * pitch_w + (w - q * Cw)] = __ldg(xs + w);
+        }
+    }
+    // source rows of every branch -> shared memory
+    const T* src[3]; int lo[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int hi_ = p.h[i], wi = p.w[i], ci = p.c[i];
+        const bool same = hi_ == p.H && wi == p.W;
+        int first, last;
+        if (same) { first = row0; last = row1 - 1; }
+        else {
+            int a0, a1, b0, b1; float l;
+            src_index(row0, p.sy[i], hi_, a0, a1, l);
+            src_index(row1 - 1, p.sy[i], hi_, b0, b1, l);
+            first = a0; last = b1;
+        }
+        const T* g = reinterpret_cast<const T*>(p.y[i]) + (size_t)b * hi_ * wi * ci;
+        if (last - first + 1 <= stg.cap_rows[i]) {
+            const unsigned char* run = reinterpret_cast<const unsigned char*>(g + (size_t)first * wi * ci);
+            unsigned char* dst = stage + stg.off[i] + (reinterpret_cast<uintptr_t>(run) & 15);
+            copy_run_to_smem(dst, run, (last - first + 1) * wi * ci * 2, tid);
+            src[i] = reinterpret_cast<const T*>(dst); lo[i] = first;
+        } else {                                            // (never with the capacities the host computes)
+            src[i] = g; lo[i] = 0;
+        }
+    }
+    merge_attention(p, se, use_se, b, att_s, att_s + p.C, tid);
+    int cbase;
+
+    cbase = 0;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        merge_branch<T, PAIRS>(src[i], tile, att_s + cbase, p.c[i], cbase, p.h[i], p.w[i], p.sy[i], p.sx[i], lo[i],
+                               p.h[i] == p.H && p.w[i] == p.W, pitch, p.W, row0, npx, tid);
+        cbase += p.c[i];
+    }
+    __syncthreads();
+    const uint32_t* tr = reinterpret_cast<const uint32_t*>(tile);
+    uint32_t* orow = reinterpret_cast<uint32_t*>(out + ((size_t)b * HW + (size_t)row0 * p.W) * out_ld8);
+    const int out_w = out_ld8 * 4;                          // words per pixel of out
+    for (int w = tid; w < npx * Cw; w += 256) {
+        const int q = pow2 ? (w >> sh) : (w / Cw), k = w - q * Cw;
+        orow[(size_t)q * out_w + k] = tr[q * pitch_w + k];
     }
 }
 
@@ -393,7 +689,7 @@ extern "C" int kad_se_excite(const float* gap_partial, int tiles, float inv_coun
                              float* att, int B, int C, int Hd, void* stream) {
     KAD_CHECK_ARG(gap_partial && w1 && b1 && w2 && b2 && att, "kad_se_excite: null pointer");
     KAD_CHECK_ARG(B > 0 && C > 0 && Hd > 0 && tiles > 0, "kad_se_excite: bad shape");
-    size_t smem = sizeof(float) * (size_t)(C + Hd);
+    size_t smem = sizeof(float) * (size_t)(C + Hd + (C > 256 ? C : 256));
     KAD_CHECK_ARG(smem <= 48 * 1024, "kad_se_excite: C + hidden = %d too large", C + Hd);
     se_excite_kernel<<<B, 256, smem, (cudaStream_t)stream>>>(gap_partial, tiles, inv_count, w1, b1, w2, b2, att, C, Hd);
     KAD_CHECK_LAUNCH("se_excite_kernel");
@@ -437,22 +733,97 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     KAD_CHECK_ARG(a->B > 0 && a->H > 0 && a->W > 0 && a->C > 0, "kad_merge_upsample_residual: bad shape");
     KAD_CHECK_ARG(a->c[0] + a->c[1] + a->c[2] == a->C, "kad_merge_upsample_residual: branch widths %d+%d+%d != %d",
                   a->c[0], a->c[1], a->c[2], a->C);
+    const bool use_se = a->gap[0] != nullptr;
+    const int out_ld = a->out_cstride ? a->out_cstride : a->C;
+    KAD_CHECK_ARG(out_ld >= a->C, "kad_merge_upsample_residual: out_cstride %d < C %d", out_ld, a->C);
     MergeParams p;
+    MergeSe se{};
+    int hmax = 1;
     for (int i = 0; i < 3; ++i) {
-        KAD_CHECK_ARG(a->y[i] && a->att[i] && a->h[i] > 0 && a->w[i] > 0, "kad_merge_upsample_residual: bad branch %d", i);
+        KAD_CHECK_ARG(a->y[i] && a->h[i] > 0 && a->w[i] > 0 && a->c[i] > 0, "kad_merge_upsample_residual: bad branch %d", i);
+        KAD_CHECK_ARG(a->att[i], "kad_merge_upsample_residual: att[%d] is null (with gap[] it is scratch of B * c floats)", i);
         p.y[i] = a->y[i]; p.att[i] = a->att[i]; p.c[i] = a->c[i]; p.h[i] = a->h[i]; p.w[i] = a->w[i];
         p.sy[i] = (float)a->h[i] / (float)a->H; p.sx[i] = (float)a->w[i] / (float)a->W;
+        if (use_se) {
+            KAD_CHECK_ARG(a->gap[i] && a->fc_w1[i] && a->fc_b1[i] && a->fc_w2[i] && a->fc_b2[i] && a->gap_tiles[i] > 0 && a->hidden[i] > 0,
+                          "kad_merge_upsample_residual: incomplete squeeze-excite arguments for branch %d", i);
+            se.gap[i] = a->gap[i]; se.w1[i] = a->fc_w1[i]; se.b1[i] = a->fc_b1[i]; se.w2[i] = a->fc_w2[i]; se.b2[i] = a->fc_b2[i];
+            se.tiles[i] = a->gap_tiles[i]; se.hidden[i] = a->hidden[i]; se.inv[i] = 1.0f / (float)(a->h[i] * a->w[i]);
+            if (a->hidden[i] > hmax) hmax = a->hidden[i];
+        }
     }
     p.H = a->H; p.W = a->W; p.C = a->C;
     KAD_CHECK_ARG(a->B <= 65535, "kad_merge_upsample_residual: batch %d too large", a->B);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int HW = a->H * a->W;
+    const size_t se_smem = sizeof(float) * (size_t)(2 * a->C + 3 * hmax + 768);
+    const bool vec8 = a->dtype != KAD_F32 && a->C % 8 == 0 && a->C <= 2048 && out_ld % 8 == 0 && (uintptr_t)a->x % 16 == 0 &&
+                      (uintptr_t)a->out % 16 == 0 && se_smem <= 48 * 1024 && a->c[0] <= 256 && a->c[1] <= 256 && a->c[2] <= 256;
+    if (vec8) {
+        const int G = a->C / 8, PL = 256 / G;
+        const int se_floats = ((2 * a->C + 3 * hmax + 768 + 3) / 4) * 4;
+        // rows per block for the staged kernel: enough blocks for two per SM, at most 16 rows, at most ~56 KB of shared memory
+        auto stage_bytes = [&](int R, MergeStage* stg) {
+            size_t o = 0;
+            for (int i = 0; i < 3; ++i) {
+                const bool same = a->h[i] == a->H && a->w[i] == a->W;
+                int rows = same ? R : (int)((float)R * p.sy[i]) + 3;
+                if (rows > a->h[i]) rows = a->h[i];
+                if (stg) { stg->off[i] = (int)o; stg->cap_rows[i] = rows; }
+                o += (((size_t)rows * a->w[i] * a->c[i] * 2 + 15) / 16) * 16 + 32;
+            }
+            if (stg) stg->tile_off = (int)o;
+            return o + (size_t)R * a->W * (a->C + 2) * 2;
+        };
+        int R = (int)(((long long)a->H * a->B) / 296);
+        R = R < 1 ? 1 : (R > 16 ? 16 : R);
+        while (R > 1 && stage_bytes(R, nullptr) > 56 * 1024) --R;
+        MergeStage stg{};
+        const size_t sb = stage_bytes(R, &stg);
+        bool aligned = true;
+        for (int i = 0; i < 3; ++i) aligned = aligned && ((uintptr_t)a->y[i] % 4 == 0);
+        if (sb + (size_t)se_floats * 4 <= 110 * 1024 && aligned) {
+            const size_t smem = sb + (size_t)se_floats * 4;
+            const bool pairs = a->c[0] % 2 == 0 && a->c[1] % 2 == 0 && a->c[2] % 2 == 0;
+            dim3 grid((a->H + R - 1) / R, a->B);
+#define KAD_MERGE_TILE(TT, PP)                                                                                          \
+            {                                                                                                             \
+                auto kern = merge_tile_kernel<TT, PP>;                                                                    \
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+                if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "merge smem attribute: %s", cudaGetErrorString(e));       \
+                kern<<<grid, 256, smem, st>>>((const TT*)a->x, (uint4*)a->out, p, se, stg, use_se ? 1 : 0, R, out_ld / 8, se_floats); \
+            }
+            if (a->dtype == KAD_F16) { if (pairs) KAD_MERGE_TILE(__half, true) else KAD_MERGE_TILE(__half, false) }
+            else { if (pairs) KAD_MERGE_TILE(__nv_bfloat16, true) else KAD_MERGE_TILE(__nv_bfloat16, false) }
+#undef KAD_MERGE_TILE
+            KAD_CHECK_LAUNCH("merge_tile_kernel");
+            return KAD_OK;
+        }
+        long long want = ((long long)HW * a->B) / ((long long)PL * 148 * 8);
+        const int iters = want < 2 ? 2 : (want > 16 ? 16 : (int)want);
+        const int pix_per_block = iters * PL;
+        dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
+        if (a->dtype == KAD_F16)
+            merge_vec8_kernel<__half><<<grid, 256, se_smem, st>>>((const uint4*)a->x, (uint4*)a->out, p, se, use_se ? 1 : 0, G, PL, pix_per_block, out_ld / 8);
+        else
+            merge_vec8_kernel<__nv_bfloat16><<<grid, 256, se_smem, st>>>((const uint4*)a->x, (uint4*)a->out, p, se, use_se ? 1 : 0, G, PL, pix_per_block, out_ld / 8);
+        KAD_CHECK_LAUNCH("merge_vec8_kernel");
+        return KAD_OK;
+    }
+    if (use_se) {      // general shapes: the attention takes its own small launches into the att[] scratch
+        for (int i = 0; i < 3; ++i) {
+            const int rc = kad_se_excite(a->gap[i], a->gap_tiles[i], se.inv[i], a->fc_w1[i], a->fc_b1[i], a->fc_w2[i], a->fc_b2[i],
+                                         const_cast<float*>(a->att[i]), a->B, a->c[i], a->hidden[i], stream);
+            if (rc) return rc;
+        }
+    }
     // two channels per thread (one 32-bit access) for 16-bit storage when every branch width is even
-    const bool pairs = a->dtype != KAD_F32 && a->c[0] % 2 == 0 && a->c[1] % 2 == 0 && a->c[2] % 2 == 0 &&
+    const bool pairs = a->dtype != KAD_F32 && a->c[0] % 2 == 0 && a->c[1] % 2 == 0 && a->c[2] % 2 == 0 && out_ld % 2 == 0 &&
                        (uintptr_t)a->x % 4 == 0 && (uintptr_t)a->out % 4 == 0 && (uintptr_t)a->y[0] % 4 == 0 &&
                        (uintptr_t)a->y[1] % 4 == 0 && (uintptr_t)a->y[2] % 4 == 0;
     const int groups = pairs ? a->C / 2 : a->C;
-    int Cp = ((groups + 31) / 32) * 32;
-    if (Cp > 256) Cp = 256;
-    const int HW = a->H * a->W;
+    int Cp = 8;
+    while (Cp < groups && Cp < 256) Cp <<= 1;          // channel groups per pixel lane, a power of two
     // pixels per thread: 4 on small feature maps (enough blocks to fill the GPU), up to 32 on large ones (amortises the
     // per-thread channel set-up)
     const int PL = 256 / Cp;
@@ -460,12 +831,11 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     int iters = want < 4 ? 4 : (want > 32 ? 32 : (int)want);
     int pix_per_block = iters * PL;
     dim3 grid((HW + pix_per_block - 1) / pix_per_block, a->B);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (pairs && a->dtype == KAD_F16) merge_kernel<__half, 2><<<grid, 256, 0, st>>>((const __half*)a->x, (__half*)a->out, p, Cp, pix_per_block);
-    else if (pairs) merge_kernel<__nv_bfloat16, 2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a->x, (__nv_bfloat16*)a->out, p, Cp, pix_per_block);
+    if (pairs && a->dtype == KAD_F16) merge_kernel<__half, 2><<<grid, 256, 0, st>>>((const __half*)a->x, (__half*)a->out, p, Cp, pix_per_block, out_ld);
+    else if (pairs) merge_kernel<__nv_bfloat16, 2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a->x, (__nv_bfloat16*)a->out, p, Cp, pix_per_block, out_ld);
     else {
         KAD_DISPATCH_DTYPE(a->dtype, {
-            merge_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block);
+            merge_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)a->x, (T*)a->out, p, Cp, pix_per_block, out_ld);
         });
     }
     KAD_CHECK_LAUNCH("merge_kernel");

@@ -148,10 +148,10 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;
         rc = kad_dsc_forward(&q, s);
         if (rc) break;
-        rc = kad_se_excite((const float*)(ws + p.gap), tiles, 1.0f / (float)(h * w), br.fc_w1, br.fc_b1, br.fc_w2, br.fc_b2, (float*)(ws + p.att),
-                           a->B, c, br.hidden, s);
-        if (rc) break;
+        // the channel attention is evaluated by the merge kernel from the sums the DSC kernel wrote
         m.y[i] = ws + p.y; m.att[i] = (const float*)(ws + p.att); m.c[i] = c; m.h[i] = h; m.w[i] = w;
+        m.gap[i] = (const float*)(ws + p.gap); m.gap_tiles[i] = tiles; m.hidden[i] = br.hidden;
+        m.fc_w1[i] = br.fc_w1; m.fc_b1[i] = br.fc_b1; m.fc_w2[i] = br.fc_w2; m.fc_b2[i] = br.fc_b2;
     }
     // join (always, so that a capture in progress is left well-formed even after an argument error)
     for (int i = 1; i < 3; ++i) {

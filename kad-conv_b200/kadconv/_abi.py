@@ -27,7 +27,9 @@ class KadDscArgs(Structure):
 class KadMergeArgs(Structure):
     _fields_ = [('x', c_void_p), ('out', c_void_p), ('y', c_void_p * 3), ('att', c_void_p * 3),
                 ('c', c_int * 3), ('h', c_int * 3), ('w', c_int * 3),
-                ('B', c_int), ('H', c_int), ('W', c_int), ('C', c_int), ('dtype', c_int)]
+                ('B', c_int), ('H', c_int), ('W', c_int), ('C', c_int), ('dtype', c_int),
+                ('gap', c_void_p * 3), ('fc_w1', c_void_p * 3), ('fc_b1', c_void_p * 3), ('fc_w2', c_void_p * 3), ('fc_b2', c_void_p * 3),
+                ('gap_tiles', c_int * 3), ('hidden', c_int * 3), ('out_cstride', c_int)]
 
 
 class KadBranchParams(Structure):

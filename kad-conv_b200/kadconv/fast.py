@@ -98,7 +98,11 @@ def _layer_args(layer, st, dtype, H, W):
                 p.w_dsc_tc = w.data_ptr(); keep.append(w); tc_mask |= 1 << i
             p.c, p.hidden = br.c, br.fc_w1.shape[0]
         a.dtype = ops._DT[dtype]
+        # per branch: project, 2 LCSA sums, 2 LCSA mask, offset conv (unless fused), DSC, SE (unless inside the merge); + merge
+        dim = sum(br.c for br in st['branches'])
         launches = 25 - sum(1 for i, br in enumerate(st['branches']) if br.dsc_weight(dtype, H >> i, W >> i)[0] == ops.PATH_MMA)
+        if dtype != torch.float32 and dim % 8 == 0:
+            launches -= 3
         st[key] = (a, tc_mask, keep, launches)
     return st[key]
 

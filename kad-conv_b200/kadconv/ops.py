@@ -251,17 +251,39 @@ def se_rescale(x, att):
     return y
 
 
-def merge_upsample_residual(x, ys, atts):
-    """out = cat_i(upsample(ys[i] * atts[i])) + x, all NHWC."""
+def merge_upsample_residual(x, ys, atts=None, se=None, out=None, out_coff=0):
+    """out = cat_i(upsample(ys[i] * att_i)) + x, all NHWC. The attentions are either given (atts[i] float32 [B,c_i]) or
+    computed inside the kernel from se[i] = (gap [B,tiles,c_i], fc_w1, fc_b1, fc_w2, fc_b2), the channel sums of
+    dsc_forward(want_gap=True) and the weights of the branch's fc. With `out` ([B,H,W,Cy]) the result is written into
+    its channels [out_coff, out_coff + C) in place."""
     x = _cuda(x, 'x')
     B, H, W, C = x.shape
-    out = torch.empty_like(x)
     a = _abi.KadMergeArgs()
-    a.x = x.data_ptr(); a.out = out.data_ptr()
+    if out is None:
+        out = torch.empty_like(x)
+        a.out = out.data_ptr()
+    else:
+        if out.shape[:3] != x.shape[:3] or out.dtype != x.dtype or not out.is_contiguous() or out_coff + C > out.shape[3]:
+            raise ValueError('out must be a contiguous [B,H,W,Cy] tensor of the same dtype with room for C channels at out_coff')
+        a.out = out.data_ptr() + out_coff * out.element_size(); a.out_cstride = out.shape[3]
+    a.x = x.data_ptr()
+    keep = []
     for i in range(3):
         yi = _cuda(ys[i], f'y{i}')
-        a.y[i] = yi.data_ptr(); a.att[i] = _f32(atts[i], f'att{i}').data_ptr()
+        a.y[i] = yi.data_ptr()
         a.c[i], a.h[i], a.w[i] = yi.shape[3], yi.shape[1], yi.shape[2]
+        if se is not None:
+            gap, w1, b1, w2, b2 = se[i]
+            if tuple(gap.shape) != (B, gap.shape[1], yi.shape[3]):
+                raise ValueError(f'gap{i} must be [B,tiles,{yi.shape[3]}]')
+            a.gap[i] = _f32(gap, 'gap').data_ptr(); a.gap_tiles[i] = gap.shape[1]; a.hidden[i] = w1.shape[0]
+            a.fc_w1[i] = _f32(w1, 'fc_w1').data_ptr(); a.fc_b1[i] = _f32(b1, 'fc_b1').data_ptr()
+            a.fc_w2[i] = _f32(w2, 'fc_w2').data_ptr(); a.fc_b2[i] = _f32(b2, 'fc_b2').data_ptr()
+            att = torch.empty((B, yi.shape[3]), dtype=torch.float32, device=x.device)
+            keep.append(att)
+        else:
+            att = _f32(atts[i], f'att{i}')
+        a.att[i] = att.data_ptr()
     a.B, a.H, a.W, a.C, a.dtype = B, H, W, C, dtype_code(x)
     _abi.check(_abi.load().kad_merge_upsample_residual(ctypes.byref(a), _stream()), 'kad_merge_upsample_residual')
     return out

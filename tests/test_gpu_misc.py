@@ -98,6 +98,64 @@ def test_merge_upsample_residual():
     assert (out.cpu().permute(0, 3, 1, 2) - ref).abs().max().item() <= 1e-5
 
 
+@pytest.mark.parametrize('dim,dtype', [(32, torch.float16), (64, torch.float16), (16, torch.bfloat16), (128, torch.bfloat16)])
+def test_merge_vectorised_with_attention_inside(dim, dtype):
+    """16-bit, C % 8 == 0: the kernel that owns 8-channel vectors. The squeeze-excite MLP evaluated inside the kernel
+    gives bit-identical results to kad_se_excite + a merge with given attentions; out may be a channel slice."""
+    from kadconv import ops
+    B, H, W = 3, 26, 19
+    cs = (dim - 2 * (dim // 3), dim // 3, dim // 3)
+    x = round_to(_rand((B, dim, H, W), 12), dtype)
+    ys = [round_to(_rand((B, c, H >> i, W >> i), 13 + i), dtype) for i, c in enumerate(cs)]
+    tiles = (5, 3, 2)
+    gaps = [_rand((B, tiles[i], c), 40 + i, 30.0) for i, c in enumerate(cs)]
+    hid = [max(c // 4, 2) for c in cs]
+    fcs = [(_rand((hid[i], c), 50 + i, 0.3), _rand((hid[i],), 54 + i, 0.1), _rand((c, hid[i]), 58 + i, 0.3), _rand((c,), 62 + i, 0.1)) for i, c in enumerate(cs)]
+    atts, feats = [], []
+    for i in range(3):
+        mean = gaps[i].sum(1) / ((H >> i) * (W >> i))
+        a = torch.sigmoid(F.linear(F.relu(F.linear(mean, fcs[i][0], fcs[i][1])), fcs[i][2], fcs[i][3]))
+        atts.append(a)
+        t = ys[i] * a.view(B, -1, 1, 1)
+        if i:
+            t = F.interpolate(t, size=(H, W), mode='bilinear', align_corners=False)
+        feats.append(t)
+    ref = torch.cat(feats, 1) + x
+    xg = nhwc(x).cuda().to(dtype)
+    yg = [nhwc(t).cuda().to(dtype) for t in ys]
+    se = [(gaps[i].cuda(),) + tuple(t.cuda() for t in fcs[i]) for i in range(3)]
+    out = ops.merge_upsample_residual(xg, yg, se=se)
+    assert rel_err(out.float().cpu().permute(0, 3, 1, 2), ref) <= 1e-2
+    att_dev = [ops.se_excite(se[i][0], (H >> i) * (W >> i), *se[i][1:]) for i in range(3)]
+    for i in range(3):
+        assert (att_dev[i].cpu() - atts[i]).abs().max().item() <= 1e-5
+    out2 = ops.merge_upsample_residual(xg, yg, att_dev)
+    assert torch.equal(out, out2)
+    wide = torch.full((B, H, W, 2 * dim + 8), 7.0, dtype=dtype, device='cuda')
+    ops.merge_upsample_residual(xg, yg, se=se, out=wide, out_coff=8)
+    assert torch.equal(wide[..., 8:8 + dim], out) and bool((wide[..., :8] == 7).all()) and bool((wide[..., 8 + dim:] == 7).all())
+
+
+def test_merge_general_shapes_with_attention_arguments():
+    """float32 / C % 8 != 0 take the general kernel; the attention arguments then run kad_se_excite into att[]."""
+    from kadconv import ops
+    B, H, W, dim = 2, 13, 9, 20
+    cs = (8, 6, 6)
+    x = _rand((B, dim, H, W), 12)
+    ys = [_rand((B, c, H >> i, W >> i), 13 + i) for i, c in enumerate(cs)]
+    gaps = [_rand((B, 2, c), 40 + i, 10.0) for i, c in enumerate(cs)]
+    fcs = [(_rand((3, c), 50 + i, 0.3), _rand((3,), 54 + i, 0.1), _rand((c, 3), 58 + i, 0.3), _rand((c,), 62 + i, 0.1)) for i, c in enumerate(cs)]
+    feats = []
+    for i in range(3):
+        a = torch.sigmoid(F.linear(F.relu(F.linear(gaps[i].sum(1) / ((H >> i) * (W >> i)), fcs[i][0], fcs[i][1])), fcs[i][2], fcs[i][3]))
+        t = ys[i] * a.view(B, -1, 1, 1)
+        feats.append(F.interpolate(t, size=(H, W), mode='bilinear', align_corners=False) if i else t)
+    ref = torch.cat(feats, 1) + x
+    se = [(gaps[i].cuda(),) + tuple(t.cuda() for t in fcs[i]) for i in range(3)]
+    out = ops.merge_upsample_residual(nhwc(x).cuda(), [nhwc(t).cuda() for t in ys], se=se)
+    assert (out.cpu().permute(0, 3, 1, 2) - ref).abs().max().item() <= 1e-5
+
+
 @pytest.mark.parametrize('M,K,N,dtype', [(1000, 128, 256, torch.bfloat16), (333, 72, 64, torch.float16), (5000, 360, 128, torch.float16),
                                          (777, 512, 288, torch.float16), (129, 64, 32, torch.bfloat16), (4096, 96, 48, torch.float16)])
 def test_gemm1x1_bias_silu(M, K, N, dtype):
