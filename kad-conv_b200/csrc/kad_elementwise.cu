@@ -466,15 +466,27 @@ merge_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, MergePar
 //            of the branch; tile = tile + att * upsample(y), formed in fp32
 //   phase 2  the tile leaves coalesced (out may be a channel slice of a wider tensor).
 // PAIRS: every branch width is even, so channels are handled two at a time with 4-byte accesses.
+constexpr int MERGE_CHUNK = 12;     // channels per work item of phase 1 (even)
 struct MergeStage { int off[3]; int cap_rows[3]; int tile_off; };     // byte offsets of the branch regions and the tile
 
+__device__ __forceinline__ void cp_async_bytes16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_bytes4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_everything() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// (asynchronous: the caller waits with cp_async_wait_everything() and a barrier)
 __device__ __forceinline__ void copy_run_to_smem(unsigned char* dst, const unsigned char* src, int nbytes, int tid) {
     // dst and src have the same offset from a 16-byte boundary; nbytes is even
     const int head = min(nbytes, static_cast<int>((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15));
     const int body = (nbytes - head) >> 4, tail = nbytes - head - (body << 4);
     const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
     uint4* d4 = reinterpret_cast<uint4*>(dst + head);
-    for (int i = tid; i < body; i += 256) d4[i] = __ldg(s4 + i);
+    for (int i = tid; i < body; i += 256) cp_async_bytes16(d4 + i, s4 + i);
     if (tid < (head >> 1)) reinterpret_cast<uint16_t*>(dst)[tid] = reinterpret_cast<const uint16_t*>(src)[tid];
     else if (tid >= 32 && tid - 32 < (tail >> 1))
         reinterpret_cast<uint16_t*>(dst + head + (body << 4))[tid - 32] = reinterpret_cast<const uint16_t*>(src + head + (body << 4))[tid - 32];
@@ -485,7 +497,11 @@ template <typename T, bool PAIRS>
 __device__ __forceinline__ void merge_branch(const T* __restrict__ ysrc, T* __restrict__ tile, const float* __restrict__ att,
                                              int c, int cbase, int hi, int wi, float sy, float sx, int lo, bool same,
                                              int pitch, int W, int row0, int npx, int tid) {
-    for (int q = tid; q < npx; q += 256) {
+    // work item = (pixel, chunk of MERGE_CHUNK channels): consecutive lanes take consecutive pixels
+    const int nchunk = (c + MERGE_CHUNK - 1) / MERGE_CHUNK;
+    for (int item = tid; item < npx * nchunk; item += 256) {
+        const int chunk = item / npx, q = item - chunk * npx;
+        const int ch_lo = chunk * MERGE_CHUNK, ch_hi = min(c, ch_lo + MERGE_CHUNK);
         const int yh = row0 + q / W, xw = q % W;
         int o00, o01, o10, o11; float ly = 0.f, lx = 0.f;
         if (same) { o00 = o01 = o10 = o11 = ((yh - lo) * wi + xw) * c; }
@@ -498,7 +514,7 @@ __device__ __forceinline__ void merge_branch(const T* __restrict__ ysrc, T* __re
         }
         T* tp = tile + (size_t)q * pitch + cbase;      // holds x on entry, out on exit
         if (PAIRS) {
-            for (int ch = 0; ch < c; ch += 2) {
+            for (int ch = ch_lo; ch < ch_hi; ch += 2) {
                 const float2 xin = unpack2<T>(*reinterpret_cast<const uint32_t*>(tp + ch));
                 float2 v;
                 if (same) v = unpack2<T>(*reinterpret_cast<const uint32_t*>(ysrc + o00 + ch));
@@ -511,7 +527,7 @@ __device__ __forceinline__ void merge_branch(const T* __restrict__ ysrc, T* __re
                 *reinterpret_cast<uint32_t*>(tp + ch) = pack2f<T>(fmaf(v.x, att[ch], xin.x), fmaf(v.y, att[ch + 1], xin.y));
             }
         } else {
-            for (int ch = 0; ch < c; ++ch) {
+            for (int ch = ch_lo; ch < ch_hi; ++ch) {
                 const float xin = to_f<T>(tp[ch]);
                 float v;
                 if (same) v = to_f<T>(ysrc[o00 + ch]);
@@ -545,7 +561,7 @@ merge_tile_kernel(const T* __restrict__ x, uint4* __restrict__ out, MergeParams 
         uint32_t* tw = reinterpret_cast<uint32_t*>(tile);
         for (int w = tid; w < npx * Cw; w += 256) {
             const int q = pow2 ? (w >> sh) : (w / Cw);
-            tw[q * pitch_w + (w - q * Cw)] = __ldg(xs + w);
+            cp_async_bytes4(tw + q * pitch_w + (w - q * Cw), xs + w);
         }
     }
     // source rows of every branch -> shared memory
@@ -572,7 +588,9 @@ merge_tile_kernel(const T* __restrict__ x, uint4* __restrict__ out, MergeParams 
             src[i] = g; lo[i] = 0;
         }
     }
-    merge_attention(p, se, use_se, b, att_s, att_s + p.C, tid);
+    merge_attention(p, se, use_se, b, att_s, att_s + p.C, tid);      // (overlaps the copies in flight)
+    cp_async_wait_everything();
+    __syncthreads();
     int cbase;
 
     cbase = 0;
