@@ -117,7 +117,23 @@ int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, i
  *  kad_image_to_nhwc    uint8 [B,C,H,W] image batch -> dtype [B,H,W,Cp], value * scale, channels C..Cp-1 zero: the
  *                       `/255` normalisation of KAD-CNet/inference/infer_dior.py:39-46 fused with the layout change */
 int kad_avg_pool2x2s1(const void* x, void* y, int B, int H, int W, int C, int dtype, void* stream);
+/* The detector's first layer on raw images, in one kernel: uint8 [B,Cin,H,W] -> 3x3 convolution with stride 2 and
+ * padding 1 -> * scale + bias -> activation -> [B,(H-1)/2+1,(W-1)/2+1,Cout] dtype (NHWC). Replaces the `/255`
+ * of KAD-CNet/inference/infer_dior.py:39-46 followed by Conv.forward_fuse of layer 0 (KAD-CNet/models/common.py:56-57;
+ * yaml: [-1, 1, Conv, [32, 3, 2]]). w float32 [Cout][Cin][3][3] (BatchNorm folded), bias float32 [Cout] or NULL.
+ * kad_stem_conv_supported: dtype f16/bf16, Cin <= 4, Cout % 8 == 0, Cout <= 64. */
+int kad_stem_conv_supported(int Cin, int Cout, int dtype);
+int kad_stem_conv_u8(const void* img_u8, const float* w_oihw, const float* bias, void* y,
+                     int B, int Cin, int H, int W, int Cout, float scale, int act, int dtype, void* stream);
 int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act, int dtype, void* stream);
+/* The same out of place: out[m][0..C) = act(y[m][0..C) + bias) with out rows out_cstride (0 = C) elements apart, so the
+ * result of a convolution lands in its channel slice of a concatenation (the torch.cat of ELAN1.forward /
+ * RepNCSPELAN4.forward, KAD-CNet/models/common.py) without a copy of its own. */
+int kad_bias_act_to(const void* y, const float* bias, void* out, long long M, int C, int out_cstride, int act, int dtype, void* stream);
+/* nn.Upsample(scale_factor=2, mode='nearest') followed by Concat([upsampled, skip]) (the top-down path of the neck,
+ * yaml: [-1, 1, nn.Upsample, [None, 2, 'nearest']], [[-1, k], 1, Concat, [1]]) in one pass:
+ *   low [B,h,w,C1], skip [B,2h,2w,C2] -> out [B,2h,2w,C1+C2], all NHWC dtype. */
+int kad_upsample2x_concat(const void* low, const void* skip, void* out, int B, int h, int w, int C1, int C2, int dtype, void* stream);
 int kad_image_to_nhwc(const void* img_u8, void* y, int B, int C, int H, int W, int Cp, float scale, int dtype, void* stream);
 
 /* LCSA, step 1: row sums [B,H,C] (over x) and column sums [B,W,C] (over y) of x[B,H,W,C], float32.
@@ -212,6 +228,7 @@ typedef struct KadLayerArgs {
     const void* x; void* out; void* workspace; size_t workspace_bytes; int* status;
     int B, H, W, dim, dtype;
     KadBranchParams br[3];
+    int out_cstride;     /* elements per pixel of `out` (0 = dim): the layer can write into a channel slice of a wider tensor */
 } KadLayerArgs;
 size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches);
 int kad_kadconv_forward(const KadLayerArgs* args, void* stream);

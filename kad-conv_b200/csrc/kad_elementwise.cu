@@ -992,29 +992,81 @@ __global__ void avg_pool2x2s1_kernel(const T* __restrict__ x, T* __restrict__ y,
     }
 }
 
-// y = act(y + bias[c]) in place on an [M][C] tensor
+__device__ __forceinline__ float silu_tanh(float v) {      // v * sigmoid(v) with one special-function instruction
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * v));
+    return v * fmaf(0.5f, th, 0.5f);
+}
+
+// out[m][0..C) = act(y[m][0..C) + bias), 8 channels per thread; out rows are out_ld8 vectors apart (out may be y itself,
+// or a channel slice of a wider tensor). Two vectors per thread are in flight.
 template <typename T>
-__global__ void bias_act_vec8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, int C8, size_t n, int act) {
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
-        const int c = (int)(e % C8);
-        uint4 v = y[e];
-        T* h = reinterpret_cast<T*>(&v);
-        const float4 b0 = bias ? reinterpret_cast<const float4*>(bias)[2 * c] : make_float4(0, 0, 0, 0);
-        const float4 b1 = bias ? reinterpret_cast<const float4*>(bias)[2 * c + 1] : make_float4(0, 0, 0, 0);
-        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+__global__ void __launch_bounds__(256)
+bias_act_vec8_kernel(const uint4* __restrict__ y, uint4* __restrict__ out, const float* __restrict__ bias, unsigned C8, unsigned out_ld8,
+                     unsigned long long n, int act) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * 256;
+    for (unsigned long long e0 = (unsigned long long)blockIdx.x * 256 + threadIdx.x; e0 < n; e0 += 2 * stride) {
+        const unsigned long long e1 = e0 + stride;
+        const bool two = e1 < n;
+        uint4 v[2];
+        v[0] = y[e0];
+        if (two) v[1] = y[e1];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float a = to_f<T>(h[i]) + bb[i];
-            h[i] = from_f<T>(act == KAD_ACT_SILU ? __fdividef(a, 1.f + __expf(-a)) : (act == KAD_ACT_RELU ? fmaxf(a, 0.f) : a));
+        for (int k = 0; k < 2; ++k) {
+            if (k == 1 && !two) break;
+            const unsigned long long e = k ? e1 : e0;
+            const unsigned long long m = n <= 0xffffffffull ? (unsigned long long)((unsigned)e / C8) : e / C8;
+            const unsigned c = (unsigned)(e - m * C8);
+            T* h = reinterpret_cast<T*>(&v[k]);
+            const float4 b0 = bias ? reinterpret_cast<const float4*>(bias)[2 * c] : make_float4(0, 0, 0, 0);
+            const float4 b1 = bias ? reinterpret_cast<const float4*>(bias)[2 * c + 1] : make_float4(0, 0, 0, 0);
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float a = to_f<T>(h[i]) + bb[i];
+                h[i] = from_f<T>(act == KAD_ACT_SILU ? silu_tanh(a) : (act == KAD_ACT_RELU ? fmaxf(a, 0.f) : a));
+            }
+            out[m * out_ld8 + c] = v[k];
         }
-        y[e] = v;
     }
 }
 template <typename T>
-__global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bias, int C, size_t n, int act) {
+__global__ void bias_act_kernel(const T* __restrict__ y, T* __restrict__ out, const float* __restrict__ bias, int C, int out_ld, size_t n, int act) {
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
-        const float a = to_f<T>(y[e]) + (bias ? bias[e % C] : 0.f);
-        y[e] = from_f<T>(apply_act(a, act));
+        const size_t m = e / C; const int c = (int)(e - m * C);
+        const float a = to_f<T>(y[e]) + (bias ? bias[c] : 0.f);
+        out[m * out_ld + c] = from_f<T>(apply_act(a, act));
+    }
+}
+
+// out[b][y][x][0..C1) = low[b][y/2][x/2][:], out[b][y][x][C1..C1+C2) = skip[b][y][x][:]: nearest-neighbour 2x upsampling
+// and channel concatenation in one pass, 8 channels per thread.
+__global__ void __launch_bounds__(256)
+upsample2x_concat_vec8_kernel(const uint4* __restrict__ low, const uint4* __restrict__ skip, uint4* __restrict__ out,
+                              int h, int w, unsigned G1, unsigned G2, unsigned long long n) {
+    const unsigned G = G1 + G2;
+    const int W = 2 * w;
+    for (unsigned long long e = (unsigned long long)blockIdx.x * 256 + threadIdx.x; e < n; e += (unsigned long long)gridDim.x * 256) {
+        const unsigned long long pix = e / G;                 // b*H*W + y*W + x
+        const unsigned g = (unsigned)(e - pix * G);
+        if (g >= G1) { out[e] = __ldg(skip + pix * G2 + (g - G1)); continue; }
+        const unsigned long long row = pix / W;               // b*H + y
+        const int x = (int)(pix - row * W);
+        const unsigned long long bimg = row / (2 * h);
+        const int y = (int)(row - bimg * 2 * h);
+        out[e] = __ldg(low + ((bimg * h + (y >> 1)) * w + (x >> 1)) * G1 + g);
+    }
+}
+template <typename T>
+__global__ void upsample2x_concat_kernel(const T* __restrict__ low, const T* __restrict__ skip, T* __restrict__ out,
+                                         int h, int w, int C1, int C2, size_t n) {
+    const int C = C1 + C2, W = 2 * w;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t pix = e / C; const int c = (int)(e - pix * C);
+        if (c >= C1) { out[e] = skip[pix * C2 + (c - C1)]; continue; }
+        const size_t row = pix / W; const int x = (int)(pix - row * W);
+        const size_t bimg = row / (2 * h); const int y = (int)(row - bimg * 2 * h);
+        out[e] = low[((bimg * h + (y >> 1)) * w + (x >> 1)) * C1 + c];
     }
 }
 
@@ -1045,18 +1097,40 @@ extern "C" int kad_avg_pool2x2s1(const void* x, void* y, int B, int H, int W, in
     return KAD_OK;
 }
 
-extern "C" int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act, int dtype, void* stream) {
-    KAD_CHECK_ARG(y && M > 0 && C > 0, "kad_bias_act_inplace: bad argument");
+extern "C" int kad_bias_act_to(const void* y, const float* bias, void* out, long long M, int C, int out_cstride, int act, int dtype, void* stream) {
+    KAD_CHECK_ARG(y && out && M > 0 && C > 0, "kad_bias_act_to: bad argument");
+    const int out_ld = out_cstride ? out_cstride : C;
+    KAD_CHECK_ARG(out_ld >= C, "kad_bias_act_to: out_cstride %d < C %d", out_ld, C);
     const size_t n = (size_t)M * C;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype != KAD_F32 && C % 8 == 0 && (uintptr_t)y % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0)) {
+    if (dtype != KAD_F32 && C % 8 == 0 && out_ld % 8 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0)) {
         const size_t nv = n / 8;
-        if (dtype == KAD_F16) bias_act_vec8_kernel<__half><<<grid_for(nv, 256), 256, 0, st>>>((uint4*)y, bias, C / 8, nv, act);
-        else bias_act_vec8_kernel<__nv_bfloat16><<<grid_for(nv, 256), 256, 0, st>>>((uint4*)y, bias, C / 8, nv, act);
+        size_t blocks = (nv + 511) / 512;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (dtype == KAD_F16) bias_act_vec8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
+        else bias_act_vec8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
     } else {
-        KAD_DISPATCH_DTYPE(dtype, { bias_act_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((T*)y, bias, C, n, act); });
+        KAD_DISPATCH_DTYPE(dtype, { bias_act_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)y, (T*)out, bias, C, out_ld, n, act); });
     }
     KAD_CHECK_LAUNCH("bias_act_kernel");
+    return KAD_OK;
+}
+
+extern "C" int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act, int dtype, void* stream) {
+    return kad_bias_act_to(y, bias, y, M, C, C, act, dtype, stream);
+}
+
+extern "C" int kad_upsample2x_concat(const void* low, const void* skip, void* out, int B, int h, int w, int C1, int C2, int dtype, void* stream) {
+    KAD_CHECK_ARG(low && skip && out && B > 0 && h > 0 && w > 0 && C1 > 0 && C2 > 0, "kad_upsample2x_concat: bad argument");
+    const size_t n = (size_t)B * 4 * h * w * (C1 + C2);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != KAD_F32 && C1 % 8 == 0 && C2 % 8 == 0 && (uintptr_t)low % 16 == 0 && (uintptr_t)skip % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t nv = n / 8;
+        upsample2x_concat_vec8_kernel<<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)low, (const uint4*)skip, (uint4*)out, h, w, C1 / 8, C2 / 8, nv);
+    } else {
+        KAD_DISPATCH_DTYPE(dtype, { upsample2x_concat_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)low, (const T*)skip, (T*)out, h, w, C1, C2, n); });
+    }
+    KAD_CHECK_LAUNCH("upsample2x_concat_kernel");
     return KAD_OK;
 }
 

@@ -113,7 +113,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     const size_t es = dtype_size(a->dtype);
     unsigned char* ws = reinterpret_cast<unsigned char*>(a->workspace);
     KadMergeArgs m{};
-    m.x = a->x; m.out = a->out; m.B = a->B; m.H = a->H; m.W = a->W; m.C = a->dim; m.dtype = a->dtype;
+    m.x = a->x; m.out = a->out; m.B = a->B; m.H = a->H; m.W = a->W; m.C = a->dim; m.dtype = a->dtype; m.out_cstride = a->out_cstride;
     size_t o = 0;
     for (int i = 0; i < 3 && rc == KAD_OK; ++i) {
         const KadBranchParams& br = a->br[i];

@@ -67,9 +67,11 @@ class _ConvKxK:
         self.stride, self.padding, self.groups = conv.stride, conv.padding, conv.groups
         self.act = ops.ACT_SILU if (hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)) else ops.ACT_NONE
 
-    def __call__(self, x):
+    def __call__(self, x, out=None, out_coff=0):
         y = _nhwc(F.conv2d(_nchw_view(x), self.w, None, self.stride, self.padding, 1, self.groups))
-        return ops.bias_act_(y, self.b, self.act)
+        if out is None:
+            return ops.bias_act_(y, self.b, self.act)
+        return ops.bias_act_to(y, self.b, out, out_coff, self.act)    # lands in its slice of a concatenation
 
 
 def _conv(conv_mod, dtype, device):
@@ -93,7 +95,18 @@ class FastDetector(torch.nn.Module):
             raise ValueError('move the model to a CUDA device first (there is no CPU path)')
         self.model, self.dtype, self.device = model, dtype, device
         self.stride = model.stride
+        self._fused_up = set()
         self.plan = [self._compile(m) for m in model.model]
+        # raw uint8 images: the first layer (3x3, stride 2) runs as one kernel that also normalises and changes layout
+        self.stem = None
+        first = model.model[0]
+        if isinstance(first, M.Conv):
+            cv = first.conv
+            if (cv.kernel_size == (3, 3) and cv.stride == (2, 2) and cv.padding == (1, 1) and cv.groups == 1 and cv.dilation == (1, 1)
+                    and ops.stem_conv_supported(cv.in_channels, cv.out_channels, dtype)):
+                act = ops.ACT_SILU if isinstance(first.act, torch.nn.SiLU) else (ops.ACT_NONE if isinstance(first.act, torch.nn.Identity) else None)
+                if act is not None:
+                    self.stem = (cv.weight.detach().float().contiguous().to(device), cv.bias.detach().float().contiguous().to(device), act)
 
     # ---- per-module closures -------------------------------------------------------------------
     def _compile(self, m):
@@ -108,11 +121,15 @@ class FastDetector(torch.nn.Module):
             cv1, cv2, cv3, cv4 = (_conv(t, dt, dev) for t in (m.cv1, m.cv2, m.cv3, m.cv4))
             half = m.c
 
+            widths = (m.cv1.conv.out_channels, m.cv2.conv.out_channels, m.cv3.conv.out_channels)
+
             def elan(x):
-                t = cv1(x)
-                y2 = cv2(t[..., half:].contiguous())
-                y3 = cv3(y2)
-                return cv4(torch.cat((t, y2, y3), -1))
+                cat = torch.empty(x.shape[:3] + (sum(widths),), dtype=x.dtype, device=x.device)
+                cv1(x, out=cat, out_coff=0)
+                y2 = cv2(cat[..., half:widths[0]].contiguous())
+                cat[..., widths[0]:widths[0] + widths[1]].copy_(y2)
+                cv3(y2, out=cat, out_coff=widths[0] + widths[1])
+                return cv4(cat)
             return elan
         if isinstance(m, M.RepNCSPELAN4_KADC):
             cv1, cv4 = _conv(m.cv1, dt, dev), _conv(m.cv4, dt, dev)
@@ -120,11 +137,15 @@ class FastDetector(torch.nn.Module):
             b3, c3 = self._csp(m.cv3[0]), _conv(m.cv3[1], dt, dev)
             half = m.c
 
+            wt, w2, w3 = m.cv1.conv.out_channels, m.cv2[1].conv.out_channels, m.cv3[1].conv.out_channels
+
             def gelan(x):
-                t = cv1(x)
-                y2 = c2(b2(t, half))
-                y3 = c3(b3(y2, 0))
-                return cv4(torch.cat((t, y2, y3), -1))
+                # every producer writes its slice of the concatenation; the CSP blocks read their input as a slice of it
+                cat = torch.empty(x.shape[:3] + (wt + w2 + w3,), dtype=x.dtype, device=x.device)
+                cv1(x, out=cat, out_coff=0)
+                c2(b2(cat, half, wt - half), out=cat, out_coff=wt)
+                c3(b3(cat, wt, w2), out=cat, out_coff=wt + w2)
+                return cv4(cat)
             return gelan
         if isinstance(m, M.SPPELAN):
             cv1, cv5 = _conv(m.cv1, dt, dev), _conv(m.cv5, dt, dev)
@@ -136,11 +157,19 @@ class FastDetector(torch.nn.Module):
                 return cv5(torch.cat(ys, -1))
             return spp
         if isinstance(m, torch.nn.Upsample):
+            nxt = self.model.model[m.i + 1] if m.i + 1 < len(self.model.model) else None
+            if (isinstance(nxt, M.Concat) and isinstance(nxt.f, (list, tuple)) and len(nxt.f) == 2 and nxt.f[0] == -1
+                    and m.i not in self.model.save and float(m.scale_factor) == 2.0 and m.mode == 'nearest'):
+                self._fused_up.add(m.i + 1)
+                return lambda x: x           # the Concat that follows upsamples and concatenates in one kernel
+
             def up(x):
                 B, H, W, C = x.shape
                 return x.view(B, H, 1, W, 1, C).expand(B, H, 2, W, 2, C).reshape(B, 2 * H, 2 * W, C)
             return up
         if isinstance(m, M.Concat):
+            if m.i in self._fused_up:
+                return lambda xs: ops.upsample2x_concat(xs[0], xs[1])
             return lambda xs: torch.cat(xs, -1)
         if isinstance(m, M.DDetect):
             return self._head(m)
@@ -152,13 +181,17 @@ class FastDetector(torch.nn.Module):
         cv1, cv2, cv3 = _conv(m.cv1, dt, dev), _conv(m.cv2, dt, dev), _conv(m.cv3, dt, dev)
         layers = list(m.m)
 
-        def csp(x, in_coff):
+        def csp(x, in_coff, cin):
+            """x [B,H,W,Cx]: reads channels [in_coff, in_coff + cin)."""
+            assert cin == cv1.k
             a = cv1(x, in_coff=in_coff)
-            for layer in layers:
-                a = kadconv_forward_nhwc(layer, a)
-            cat = torch.empty(a.shape[:-1] + (2 * a.shape[-1],), dtype=a.dtype, device=a.device)
-            cat[..., :a.shape[-1]].copy_(a)
-            cv2(x, in_coff=in_coff, out=cat, out_coff=a.shape[-1])
+            c = a.shape[-1]
+            cat = torch.empty(a.shape[:-1] + (2 * c,), dtype=a.dtype, device=a.device)
+            for j, layer in enumerate(layers):      # the last KAD-Conv layer writes straight into the concatenation
+                a = kadconv_forward_nhwc(layer, a, out=cat if j == len(layers) - 1 else None)
+            if not layers:
+                cat[..., :c].copy_(a)
+            cv2(x, in_coff=in_coff, out=cat, out_coff=c)
             return cv3(cat)
         return csp
 
@@ -202,7 +235,11 @@ class FastDetector(torch.nn.Module):
             raise RuntimeError('FastDetector has no CPU path: move the input to the GPU')
         first = self.model.model[0]
         pad8 = isinstance(first, M.Conv) and first.conv.in_channels < 8 and first.conv.kernel_size != (1, 1)
-        if x.dtype == torch.uint8:
+        skip_first = False
+        if x.dtype == torch.uint8 and self.stem is not None:
+            x = ops.stem_conv_u8(x.contiguous(), self.stem[0], self.stem[1], self.dtype, act=self.stem[2])
+            skip_first = True
+        elif x.dtype == torch.uint8:
             x = ops.image_to_nhwc(x.contiguous(), self.dtype, cpad=8 if pad8 else x.shape[1])
         else:
             x = ops.to_nhwc(x.to(self.dtype))
@@ -213,6 +250,7 @@ class FastDetector(torch.nn.Module):
         for m, fn in zip(self.model.model, self.plan):
             if m.f != -1:
                 x = ys[m.f] if isinstance(m.f, int) else [x if j == -1 else ys[j] for j in m.f]
-            x = fn(x)
+            if not (skip_first and m.i == 0):
+                x = fn(x)
             ys.append(x if m.i in save else None)
         return x

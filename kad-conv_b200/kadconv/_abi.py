@@ -40,7 +40,8 @@ class KadBranchParams(Structure):
 
 class KadLayerArgs(Structure):
     _fields_ = [('x', c_void_p), ('out', c_void_p), ('workspace', c_void_p), ('workspace_bytes', c_size_t), ('status', c_void_p),
-                ('B', c_int), ('H', c_int), ('W', c_int), ('dim', c_int), ('dtype', c_int), ('br', KadBranchParams * 3)]
+                ('B', c_int), ('H', c_int), ('W', c_int), ('dim', c_int), ('dtype', c_int), ('br', KadBranchParams * 3),
+                ('out_cstride', c_int)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/kadconv_b200.h
@@ -52,6 +53,8 @@ SIGNATURES = {
     'kad_dsc_forward': (c_int, [POINTER(KadDscArgs), c_void_p]),
     'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_tc_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_stem_conv_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_stem_conv_u8': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
     'kad_dsc_mma_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_pack_weight_tc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     'kad_dsc_packed_weight_bytes': (c_size_t, [c_int, c_int, c_int]),
@@ -61,6 +64,8 @@ SIGNATURES = {
     'kad_avg_pool': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_avg_pool2x2s1': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_bias_act_inplace': (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]),
+    'kad_bias_act_to': (c_int, [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_upsample2x_concat': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_image_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_lcsa_mask': (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -107,9 +107,10 @@ def _layer_args(layer, st, dtype, H, W):
     return st[key]
 
 
-def kadconv_forward_nhwc(layer, x):
+def kadconv_forward_nhwc(layer, x, out=None, out_coff=0):
     """The accelerated KADConv forward on a contiguous NHWC tensor; returns NHWC. One C-ABI call per layer
-    (kad_kadconv_forward): the three branches run on three streams and all intermediates live in one workspace."""
+    (kad_kadconv_forward): the three branches run on three streams and all intermediates live in one workspace.
+    With `out` ([B,H,W,Cy], contiguous) the result is written into its channels [out_coff, out_coff + C) in place."""
     import ctypes
     from . import _abi
     if layer.n != 3:
@@ -123,8 +124,14 @@ def kadconv_forward_nhwc(layer, x):
     lib = _abi.load()
     nbytes = lib.kad_kadconv_workspace_bytes(B, H, W, C, a.dtype, tc_mask)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-    out = torch.empty_like(x)
-    a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes
+    if out is None:
+        out = torch.empty_like(x)
+        out_ptr, a.out_cstride = out.data_ptr(), 0
+    else:
+        if out.shape[:3] != x.shape[:3] or out.dtype != x.dtype or not out.is_contiguous() or out_coff + C > out.shape[3]:
+            raise ValueError('out must be a contiguous [B,H,W,Cy] tensor of the same dtype with room for C channels at out_coff')
+        out_ptr, a.out_cstride = out.data_ptr() + out_coff * out.element_size(), out.shape[3]
+    a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out_ptr, ws.data_ptr(), nbytes
     a.status = ops.status_word(x.device).data_ptr()
     a.B, a.H, a.W, a.dim = B, H, W, C
     _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward', launches)

@@ -370,6 +370,29 @@ def bias_act_(y, bias, act=ACT_SILU):
     return y
 
 
+def bias_act_to(y, bias, out, out_coff=0, act=ACT_SILU):
+    """out[..., out_coff:out_coff+C] = act(y + bias) for contiguous y [..., C] and contiguous out [..., Cy] (same leading shape)."""
+    y = _cuda(y, 'y'); out = _cuda(out, 'out')
+    C = y.shape[-1]
+    if out.shape[:-1] != y.shape[:-1] or out.dtype != y.dtype or out_coff + C > out.shape[-1]:
+        raise ValueError('out must have the leading shape and dtype of y and room for C channels at out_coff')
+    _abi.check(_abi.load().kad_bias_act_to(_ptr(y), _ptr(_f32(bias, 'bias')), ctypes.c_void_p(out.data_ptr() + out_coff * out.element_size()),
+                                           y.numel() // C, C, out.shape[-1], act, dtype_code(y), _stream()), 'kad_bias_act_to')
+    return out
+
+
+def upsample2x_concat(low, skip):
+    """cat((nearest-2x-upsample(low), skip), channels): low [B,h,w,C1], skip [B,2h,2w,C2] -> [B,2h,2w,C1+C2], NHWC."""
+    low = _cuda(low, 'low'); skip = _cuda(skip, 'skip')
+    B, h, w, C1 = low.shape
+    if skip.shape[:3] != (B, 2 * h, 2 * w) or skip.dtype != low.dtype:
+        raise ValueError(f'skip must be [B,{2 * h},{2 * w},C2] of the same dtype, got {tuple(skip.shape)}')
+    out = torch.empty((B, 2 * h, 2 * w, C1 + skip.shape[3]), dtype=low.dtype, device=low.device)
+    _abi.check(_abi.load().kad_upsample2x_concat(_ptr(low), _ptr(skip), _ptr(out), B, h, w, C1, skip.shape[3], dtype_code(low), _stream()),
+               'kad_upsample2x_concat')
+    return out
+
+
 def image_to_nhwc(img_u8, dtype, cpad=8, scale=1.0 / 255.0):
     """uint8 [B,C,H,W] -> dtype [B,H,W,cpad], scaled, extra channels zero."""
     img_u8 = _cuda(img_u8, 'img')
@@ -379,4 +402,24 @@ def image_to_nhwc(img_u8, dtype, cpad=8, scale=1.0 / 255.0):
     y = torch.empty((B, H, W, cpad), dtype=dtype, device=img_u8.device)
     _abi.check(_abi.load().kad_image_to_nhwc(_ptr(img_u8), _ptr(y), B, C, H, W, cpad, ctypes.c_float(scale), _DT[dtype], _stream()),
                'kad_image_to_nhwc')
+    return y
+
+
+def stem_conv_supported(cin, cout, dtype):
+    return dtype in _DT and bool(_abi.load().kad_stem_conv_supported(cin, cout, _DT[dtype]))
+
+
+def stem_conv_u8(img_u8, w, bias, dtype, act=ACT_SILU, scale=1.0 / 255.0):
+    """uint8 [B,Cin,H,W] -> act(conv3x3 stride 2 pad 1 (img * scale) + bias) as dtype [B,OH,OW,Cout] (NHWC).
+    w float32 [Cout,Cin,3,3], bias float32 [Cout] or None."""
+    img_u8 = _cuda(img_u8, 'img')
+    if img_u8.dtype != torch.uint8:
+        raise TypeError('stem_conv_u8 expects a uint8 tensor')
+    w = _f32(w, 'w')
+    B, C, H, W = img_u8.shape
+    if tuple(w.shape[1:]) != (C, 3, 3):
+        raise ValueError(f'w must be [Cout,{C},3,3]')
+    y = torch.empty((B, (H - 1) // 2 + 1, (W - 1) // 2 + 1, w.shape[0]), dtype=dtype, device=img_u8.device)
+    _abi.check(_abi.load().kad_stem_conv_u8(_ptr(img_u8), _ptr(w), _ptr(_f32(bias, 'bias')), _ptr(y), B, C, H, W, w.shape[0],
+                                            ctypes.c_float(scale), act, _DT[dtype], _stream()), 'kad_stem_conv_u8')
     return y

@@ -207,3 +207,48 @@ def test_detector_glue_kernels():
     y = ops.image_to_nhwc(img.cuda(), torch.float16, cpad=8).cpu()
     ref = (img.float() / 255).half().permute(0, 2, 3, 1)
     assert torch.equal(y[..., :3], ref) and y[..., 3:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 3, 50, 70, 40), torch.float16), ((1, 3, 33, 47, 32), torch.bfloat16), ((2, 1, 16, 16, 8), torch.float16),
+                                         ((1, 4, 21, 130, 64), torch.float16)])
+def test_stem_conv_on_uint8_images(shape, dtype):
+    """uint8 planes -> /255 -> 3x3 stride-2 convolution + bias + SiLU -> NHWC, against torch in float32 (odd sizes, image
+    borders, widths that do not fill the 32-pixel tiles)."""
+    from kadconv import ops
+    B, Cin, H, W, Cout = shape
+    g = np.random.default_rng(sum(shape))
+    img = torch.from_numpy(g.integers(0, 256, (B, Cin, H, W), dtype=np.uint8))
+    w = round_to(_rand((Cout, Cin, 3, 3), 70, 1.0 / np.sqrt(9 * Cin)), dtype)
+    b = _rand((Cout,), 71, 0.2)
+    ref = F.silu(F.conv2d(img.float() / 255.0, w, b, stride=2, padding=1))
+    y = ops.stem_conv_u8(img.cuda(), w.cuda(), b.cuda(), dtype)
+    assert tuple(y.shape) == (B, ref.shape[2], ref.shape[3], Cout)
+    assert rel_err(y.float().cpu().permute(0, 3, 1, 2), ref) <= (4e-3 if dtype == torch.float16 else 1e-2)
+    y0 = ops.stem_conv_u8(img.cuda(), w.cuda(), None, dtype, act=ops.ACT_NONE, scale=1.0)
+    ref0 = F.conv2d(img.float(), w, None, stride=2, padding=1)
+    assert rel_err(y0.float().cpu().permute(0, 3, 1, 2), ref0) <= (2e-3 if dtype == torch.float16 else 1e-2)
+
+
+@pytest.mark.parametrize('dtype,C1,C2', [(torch.float16, 16, 24), (torch.bfloat16, 216, 288), (torch.float32, 5, 3), (torch.float16, 7, 8)])
+def test_upsample2x_concat(dtype, C1, C2):
+    from kadconv import ops
+    B, h, w = 2, 7, 5
+    low = round_to(_rand((B, C1, h, w), 80), dtype); skip = round_to(_rand((B, C2, 2 * h, 2 * w), 81), dtype)
+    ref = torch.cat((F.interpolate(low, scale_factor=2, mode='nearest'), skip), 1)
+    out = ops.upsample2x_concat(nhwc(low).cuda().to(dtype), nhwc(skip).cuda().to(dtype))
+    assert torch.equal(out.float().cpu().permute(0, 3, 1, 2), ref)
+
+
+@pytest.mark.parametrize('dtype,C,act', [(torch.float16, 40, 1), (torch.bfloat16, 72, 2), (torch.float32, 9, 1), (torch.float16, 12, 0)])
+def test_bias_act_into_a_channel_slice(dtype, C, act):
+    from kadconv import ops
+    y = round_to(_rand((3, 11, 13, C), 90, 2.0), dtype); b = _rand((C,), 91, 0.5)
+    z = y + b
+    ref = F.silu(z) if act == 1 else (F.relu(z) if act == 2 else z)
+    wide = torch.full((3, 11, 13, C + 24), 3.0, dtype=dtype, device='cuda')
+    ops.bias_act_to(y.cuda().to(dtype), b.cuda(), wide, 16, act)
+    tol = 1e-5 if dtype == torch.float32 else (4e-3 if dtype == torch.float16 else 1e-2)
+    assert rel_err(wide[..., 16:16 + C].float().cpu(), ref) <= tol
+    assert bool((wide[..., :16] == 3).all()) and bool((wide[..., 16 + C:] == 3).all())
+    inplace = ops.bias_act_(y.cuda().to(dtype).clone(), b.cuda(), act)
+    assert torch.equal(inplace, wide[..., 16:16 + C])
