@@ -106,6 +106,15 @@ int kad_pool_project(const void* x, const float* w, const float* bias, void* y,
                      int B, int H, int W, int Cin, int Cout, int pool, int act,
                      int x_cstride, int y_cstride, int dtype, void* stream);
 
+/* The whole branch pyramid of a KAD-Conv layer in one pass over x: t[i] = conv1x1_i(avg_pool2d(x, 2^i)) + bias_i, i = 0..2
+ * (KADConv.forward, kad_conv.py:115 with convs[i][0], :101): three calls of kad_pool_project that share their input.
+ *   x [B,H,W,dim] dtype; w[i] float32 [c[i]][dim], bias[i] float32 [c[i]] or NULL; t[i] [B,H>>i,W>>i,c[i]] dtype.
+ * Operands are rounded to dtype (the pooled means as well, as F.avg_pool2d rounds them), accumulation is float32.
+ * kad_pyramid_project_supported: dtype f16/bf16, dim % 8 == 0, widths <= 64, H, W >= 4, a 4-row tile fits shared memory. */
+int kad_pyramid_project_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W);
+int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
+                        int B, int H, int W, int dim, const int* c, int dtype, void* stream);
+
 /* Average pool, kernel = stride = pool, floor mode, NHWC: F.avg_pool2d as used for the branch pyramid
  * (KAD-Conv/kadconv/kad_conv.py:115) when the pooled tensor feeds the tensor-core 1x1 GEMM. */
 int kad_avg_pool(const void* x, void* y, int B, int H, int W, int C, int pool, int dtype, void* stream);

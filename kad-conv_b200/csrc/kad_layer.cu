@@ -105,26 +105,48 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     cudaStream_t main_s = (cudaStream_t)stream;
     cudaStream_t st[3] = {main_s, ss->s[0], ss->s[1]};
 
+    const size_t es = dtype_size(a->dtype);
+    unsigned char* ws = reinterpret_cast<unsigned char*>(a->workspace);
+    BranchWs plan[3]; int paths[3], tiles_of[3];
+    {
+        size_t o = 0;
+        for (int i = 0; i < 3; ++i) {
+            const int h = a->H >> i, w = a->W >> i, c = a->br[i].c;
+            paths[i] = branch_path(a->br[i], a->dtype, h, w);
+            tiles_of[i] = kad_dsc_gap_tiles(h, w, c, c, paths[i]);
+            plan[i] = plan_branch(o, a->B, h, w, c, es, tiles_of[i]);
+            o = plan[i].end;
+        }
+    }
+    // the three pooled projections read the same x: one kernel on the caller's stream, before the branches fork
+    const bool pyramid = kad_pyramid_project_supported(a->dim, widths[0], widths[1], widths[2], a->dtype, a->H, a->W) != 0 &&
+                         (uintptr_t)a->x % 16 == 0;
+    if (pyramid) {
+        const float* w3[3] = {a->br[0].w_proj, a->br[1].w_proj, a->br[2].w_proj};
+        const float* b3[3] = {a->br[0].b_proj, a->br[1].b_proj, a->br[2].b_proj};
+        void* t3[3] = {ws + plan[0].t, ws + plan[1].t, ws + plan[2].t};
+        rc = kad_pyramid_project(a->x, w3, b3, t3, a->B, a->H, a->W, a->dim, widths, a->dtype, stream);
+        if (rc) return rc;
+    }
+
     // fork
     if ((e = cudaEventRecord(ss->fork, main_s)) != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: fork: %s", cudaGetErrorString(e));
     for (int i = 1; i < 3; ++i)
         if ((e = cudaStreamWaitEvent(st[i], ss->fork, 0)) != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: fork wait: %s", cudaGetErrorString(e));
 
-    const size_t es = dtype_size(a->dtype);
-    unsigned char* ws = reinterpret_cast<unsigned char*>(a->workspace);
     KadMergeArgs m{};
     m.x = a->x; m.out = a->out; m.B = a->B; m.H = a->H; m.W = a->W; m.C = a->dim; m.dtype = a->dtype; m.out_cstride = a->out_cstride;
-    size_t o = 0;
     for (int i = 0; i < 3 && rc == KAD_OK; ++i) {
         const KadBranchParams& br = a->br[i];
         const int h = a->H >> i, w = a->W >> i, c = br.c;
-        const int path = branch_path(br, a->dtype, h, w);
-        const int tiles = kad_dsc_gap_tiles(h, w, c, c, path);
-        const BranchWs p = plan_branch(o, a->B, h, w, c, es, tiles);
-        o = p.end;
+        const int path = paths[i];
+        const int tiles = tiles_of[i];
+        const BranchWs p = plan[i];
         void* s = (void*)st[i];
-        rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
-        if (rc) break;
+        if (!pyramid) {
+            rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
+            if (rc) break;
+        }
         rc = kad_lcsa_sums(ws + p.t, (float*)(ws + p.rows), (float*)(ws + p.cols), a->B, h, w, c, a->dtype, s);
         if (rc) break;
         rc = kad_lcsa_mask((const float*)(ws + p.rows), (const float*)(ws + p.cols), br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift,

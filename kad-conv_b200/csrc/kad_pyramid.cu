@@ -1,0 +1,259 @@
+// Branch pyramid of a KAD-Conv layer in one pass over x: t_i = conv1x1_i(avg_pool_{2^i}(x)) + b_i for i = 0, 1, 2
+// (KADConv.forward, KAD-Conv/kadconv/kad_conv.py:115 with convs[i][0]). The three projections read the same tensor; issued
+// as three kernels x crosses HBM three times and each launch is latency-bound. Here a block stages a tile of 4 rows x
+// TW columns of x in shared memory with asynchronous 16-byte copies (everything in flight at once), forms the 2x2 and
+// 4x4 averages from the staged tile (rounded to the storage type, as the reference's avg_pool2d output is), runs the three
+// 1x1 convolutions on the warp-level tensor-core instruction (fp32 accumulation) and writes the three result tiles as
+// contiguous row segments.
+#include "kad_mma.cuh"
+
+namespace kad {
+namespace {
+
+struct PyramidParams {
+    const void* x; const float* w[3]; const float* b[3]; void* t[3];
+    int B, H, W, dim, c[3];
+    int TW, KC, xpitch;           // tile width (a multiple of 4), 16-channel chunks, bytes per staged pixel (dim*2 + 16)
+    int off_p1, off_p2, off_B, off_bias, off_out;   // shared-memory byte offsets
+};
+
+// Weight fragments of a 1x1 convolution w[Cout][Cin] (see stage_weights of the deformable kernel for the slot layout).
+template <typename T>
+__device__ __forceinline__ void stage_weights_1x1(uint2* dst, const float* __restrict__ w, int Cin, int Cout, int KC, int NT, int tid) {
+    for (int e = tid; e < KC * NT * 32; e += MMA_THREADS) {
+        const int lane = e & 31, f = e >> 5, nt = f % NT, kc = f / NT;
+        const int n = nt * 8 + (lane >> 2), t = lane & 3, ch = kc * 16 + 4 * t;
+        const int first = lane_first_channel(kc, t, Cin);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = first + j;
+            v[j] = (n < Cout && c >= ch && c < Cin) ? w[(size_t)n * Cin + c] : 0.f;
+        }
+        dst[e] = make_uint2(pack2<T>(v[0], v[1]), pack2<T>(v[2], v[3]));
+    }
+}
+
+template <typename T> __device__ __forceinline__ float2 up2(uint32_t u);
+template <> __device__ __forceinline__ float2 up2<__half>(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+template <> __device__ __forceinline__ float2 up2<__nv_bfloat16>(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+
+// mean of the N x N staged pixels whose top-left corner is s (rows `rowpitch` bytes apart, pixels `xp` bytes apart), for 8
+// channels: summed in fp32, rounded once (as F.avg_pool2d rounds its output)
+template <typename T, int N>
+__device__ __forceinline__ uint4 mean_block(const unsigned char* s, int xp, size_t rowpitch) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < N; ++r)
+#pragma unroll
+        for (int c = 0; c < N; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(s + r * rowpitch + (size_t)c * xp);
+            const uint32_t* pv = &v.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = up2<T>(pv[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+        }
+    const float inv = 1.f / (float)(N * N);
+    uint4 out; uint32_t* po = &out.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) po[i] = pack2<T>(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+    return out;
+}
+
+template <typename T, int NT>
+__global__ void __launch_bounds__(MMA_THREADS)
+pyramid_project_kernel(const PyramidParams p) {
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int TW = p.TW, dim = p.dim, KC = p.KC, xp = p.xpitch;
+    const int b = blockIdx.z, r0 = blockIdx.y * 4, c0 = blockIdx.x * TW;
+    const int rows = min(4, p.H - r0), cols = min(TW, p.W - c0);
+    unsigned char* xt = sm;                                   // [4][TW] pixels of xp bytes
+    unsigned char* p1 = sm + p.off_p1;                        // [2][TW/2]
+    unsigned char* p2 = sm + p.off_p2;                        // [1][TW/4]
+    uint2* Bs = reinterpret_cast<uint2*>(sm + p.off_B);       // [3][KC][NT][32]
+    float* bias = reinterpret_cast<float*>(sm + p.off_bias);  // [3][NT*8]
+    unsigned char* outs = sm + p.off_out;                     // result tiles of the three branches, one after the other
+
+    // ---- stage x (asynchronous), weights and bias meanwhile ----------------------------------------------------------
+    const int vpp = dim >> 3;                                 // 16-byte vectors per pixel
+    const unsigned char* xb = reinterpret_cast<const unsigned char*>(p.x) + (size_t)b * p.H * p.W * dim * 2;
+    for (int v = tid; v < rows * cols * vpp; v += MMA_THREADS) {
+        const int px = v / vpp, k = v - px * vpp, r = px / cols, c = px - r * cols;
+        cp_async16(xt + (size_t)(r * TW + c) * xp + 16 * k, xb + ((size_t)(r0 + r) * p.W + c0 + c) * dim * 2 + 16 * k);
+    }
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        stage_weights_1x1<T>(Bs + i * KC * NT * 32, p.w[i], dim, p.c[i], KC, NT, tid);
+        for (int e = tid; e < NT * 8; e += MMA_THREADS) bias[i * NT * 8 + e] = (e < p.c[i] && p.b[i]) ? p.b[i][e] : 0.f;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    // ---- 2x2 and 4x4 means (only where all contributing pixels exist: floor-mode pooling) -----------------------------
+    const int h1 = p.H >> 1, w1 = p.W >> 1, h2 = p.H >> 2, w2 = p.W >> 2;
+    const int TW1 = TW >> 1, TW2 = TW >> 2;
+    for (int v = tid; v < 2 * TW1 * vpp; v += MMA_THREADS) {
+        const int px = v / vpp, k = v - px * vpp, r = px / TW1, c = px - r * TW1;
+        if ((r0 >> 1) + r < h1 && (c0 >> 1) + c < w1) {
+            *reinterpret_cast<uint4*>(p1 + (size_t)px * xp + 16 * k) = mean_block<T, 2>(xt + (size_t)((2 * r) * TW + 2 * c) * xp + 16 * k, xp, (size_t)TW * xp);
+        }
+    }
+    for (int v = tid; v < TW2 * vpp; v += MMA_THREADS) {
+        const int c = v / vpp, k = v - c * vpp;
+        if ((r0 >> 2) < h2 && (c0 >> 2) + c < w2)
+            *reinterpret_cast<uint4*>(p2 + (size_t)c * xp + 16 * k) = mean_block<T, 4>(xt + (size_t)(4 * c) * xp + 16 * k, xp, (size_t)TW * xp);
+    }
+    __syncthreads();
+
+    // ---- the three 1x1 convolutions: 16-pixel tiles of [x tile | 2x2 means | 4x4 means] -------------------------------
+    const int n0 = (4 * TW + 15) >> 4, n1 = (2 * TW1 + 15) >> 4, n2 = (TW2 + 15) >> 4;
+    int obase[3]; obase[0] = 0; obase[1] = 4 * TW * p.c[0] * 2; obase[2] = obase[1] + 2 * TW1 * p.c[1] * 2;
+    for (int mt = warp; mt < n0 + n1 + n2; mt += MMA_THREADS / 32) {
+        const int i = mt < n0 ? 0 : (mt < n0 + n1 ? 1 : 2);
+        const int m0 = (i == 0 ? mt : (i == 1 ? mt - n0 : mt - n0 - n1)) * 16;
+        const int npx = i == 0 ? 4 * TW : (i == 1 ? 2 * TW1 : TW2), ci = i == 0 ? p.c[0] : (i == 1 ? p.c[1] : p.c[2]);
+        const unsigned char* src = i == 0 ? xt : (i == 1 ? p1 : p2);
+        const uint2* Bi = Bs + i * KC * NT * 32;
+        const int rlo = min(m0 + g, npx - 1), rhi = min(m0 + g + 8, npx - 1);   // (rows past the end repeat the last pixel, never stored)
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+#pragma unroll 1
+        for (int kc = 0; kc < KC; ++kc) {
+            const int coff = 2 * lane_first_channel(kc, t, dim);
+            const uint2 lo = *reinterpret_cast<const uint2*>(src + (size_t)rlo * xp + coff);
+            const uint2 hi = *reinterpret_cast<const uint2*>(src + (size_t)rhi * xp + coff);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816<T>(acc[nt], lo.x, hi.x, lo.y, hi.y, Bi[(kc * NT + nt) * 32 + lane]);
+        }
+        T* ot = reinterpret_cast<T*>(outs + (i == 0 ? obase[0] : (i == 1 ? obase[1] : obase[2])));
+        const float* bi = bias + i * NT * 8;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int px = m0 + g + 8 * hrow;
+            if (px >= npx) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int co = nt * 8 + 2 * t;
+                if (co >= ci) continue;
+                const float v0 = acc[nt][2 * hrow] + bi[co], v1 = acc[nt][2 * hrow + 1] + bi[co + 1];
+                T* o = ot + (size_t)px * ci + co;
+                if (!(ci & 1)) *reinterpret_cast<uint32_t*>(o) = pack2<T>(v0, v1);
+                else { o[0] = from_f<T>(v0); if (co + 1 < ci) o[1] = from_f<T>(v1); }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- result tiles -> global, row segment by row segment (contiguous) ---------------------------------------------
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int ci = p.c[i], tw = TW >> i, hi_ = p.H >> i, wi = p.W >> i;
+        const int rr0 = r0 >> i, cc0 = c0 >> i, nrows = min(4 >> i, hi_ - rr0), ncols = min(tw, wi - cc0);
+        if (nrows <= 0 || ncols <= 0) continue;
+        const T* ot = reinterpret_cast<const T*>(outs + obase[i]);
+        T* dst = reinterpret_cast<T*>(p.t[i]) + (((size_t)b * hi_ + rr0) * wi + cc0) * ci;
+        const int seg = ncols * ci;                           // elements per row segment
+        if (!(ci & 1)) {
+            const int segw = seg >> 1;
+            for (int e = tid; e < nrows * segw; e += MMA_THREADS) {
+                const int r = e / segw, k = e - r * segw;
+                reinterpret_cast<uint32_t*>(dst + (size_t)r * wi * ci)[k] = reinterpret_cast<const uint32_t*>(ot + (size_t)r * tw * ci)[k];
+            }
+        } else {
+            for (int e = tid; e < nrows * seg; e += MMA_THREADS) {
+                const int r = e / seg, k = e - r * seg;
+                dst[(size_t)r * wi * ci + k] = ot[(size_t)r * tw * ci + k];
+            }
+        }
+    }
+}
+
+inline int pyr_nt(int c) {
+    const int n = (c + 7) / 8;
+    return n <= 2 ? 2 : n <= 3 ? 3 : n <= 4 ? 4 : n <= 6 ? 6 : 8;
+}
+
+// Tile width (multiple of 4) and the shared-memory plan; returns the total bytes, 0 if the shape does not fit.
+size_t pyramid_plan(int W, int dim, const int c[3], PyramidParams* p) {
+    const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
+    const int KC = (dim + 15) / 16, xpitch = dim * 2 + 16;
+    const int Wp = ((W + 3) / 4) * 4;
+    // the x tile gets as much as leaves the block under 112 KB (two blocks per SM), at most 44 KB
+    const int budgets[5] = {44 * 1024, 32 * 1024, 24 * 1024, 16 * 1024, 8 * 1024};
+    for (int bi = 0; bi < 5; ++bi) {
+        int maxTW = ((budgets[bi] / (4 * xpitch)) / 4) * 4;
+        if (maxTW < 4) continue;
+        const int ncol = (Wp + maxTW - 1) / maxTW;
+        const int TW = (((Wp + ncol - 1) / ncol + 3) / 4) * 4;
+        size_t o = (size_t)4 * TW * xpitch;
+        const size_t off_p1 = o; o += (size_t)2 * (TW / 2) * xpitch;
+        const size_t off_p2 = o; o += (size_t)(TW / 4) * xpitch;
+        const size_t off_B = o; o += (size_t)3 * KC * nt * 32 * 8;
+        const size_t off_bias = o; o += (size_t)3 * nt * 8 * 4;
+        o = (o + 15) & ~size_t(15);
+        const size_t off_out = o;
+        o += ((size_t)4 * TW * c[0] + (size_t)2 * (TW / 2) * c[1] + (size_t)(TW / 4) * c[2]) * 2 + 16;
+        if (o > 112 * 1024) continue;
+        if (p) {
+            p->TW = TW; p->KC = KC; p->xpitch = xpitch;
+            p->off_p1 = (int)off_p1; p->off_p2 = (int)off_p2; p->off_B = (int)off_B; p->off_bias = (int)off_bias; p->off_out = (int)off_out;
+        }
+        return o;
+    }
+    return 0;
+}
+
+}  // namespace
+}  // namespace kad
+
+using namespace kad;
+
+extern "C" int kad_pyramid_project_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W) {
+    if (!(dtype == KAD_F16 || dtype == KAD_BF16)) return 0;
+    if (dim < 8 || dim % 8 != 0 || dim > 512 || H < 4 || W < 4) return 0;
+    if (c0 < 1 || c1 < 1 || c2 < 1 || c0 > 64 || c1 > 64 || c2 > 64) return 0;
+    const int c[3] = {c0, c1, c2};
+    return pyramid_plan(W, dim, c, nullptr) != 0;
+}
+
+extern "C" int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
+                                   int B, int H, int W, int dim, const int* c, int dtype, void* stream) {
+    KAD_CHECK_ARG(x && w && bias && t && c, "kad_pyramid_project: null pointer");
+    KAD_CHECK_ARG(B > 0 && B <= 65535, "kad_pyramid_project: bad batch %d", B);
+    if (!kad_pyramid_project_supported(dim, c[0], c[1], c[2], dtype, H, W))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_pyramid_project: needs f16/bf16, dim %% 8 == 0, widths <= 64, H, W >= 4 (got dim=%d c=%d,%d,%d H=%d W=%d dtype=%d)",
+                    dim, c[0], c[1], c[2], H, W, dtype);
+    PyramidParams p{};
+    p.x = x; p.B = B; p.H = H; p.W = W; p.dim = dim;
+    for (int i = 0; i < 3; ++i) {
+        KAD_CHECK_ARG(w[i] && t[i], "kad_pyramid_project: null pointer for branch %d", i);
+        KAD_CHECK_ARG((uintptr_t)t[i] % 4 == 0, "kad_pyramid_project: t[%d] must be 4-byte aligned", i);
+        p.w[i] = w[i]; p.b[i] = bias[i]; p.t[i] = t[i]; p.c[i] = c[i];
+    }
+    KAD_CHECK_ARG((uintptr_t)x % 16 == 0, "kad_pyramid_project: x must be 16-byte aligned");
+    const size_t smem = pyramid_plan(W, dim, c, &p);
+    const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
+    dim3 grid((W + p.TW - 1) / p.TW, (H + 3) / 4, B);
+    KAD_CHECK_ARG(grid.y <= 65535, "kad_pyramid_project: image too tall");
+    cudaStream_t st = (cudaStream_t)stream;
+#define KAD_PYR(TT, N)                                                                                                \
+    {                                                                                                                 \
+        auto kern = pyramid_project_kernel<TT, N>;                                                                    \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "pyramid smem attribute: %s", cudaGetErrorString(e));         \
+        kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
+    }
+#define KAD_PYR_NT(TT)                                                                                                \
+    switch (nt) { case 2: KAD_PYR(TT, 2) break; case 3: KAD_PYR(TT, 3) break; case 4: KAD_PYR(TT, 4) break;          \
+                  case 6: KAD_PYR(TT, 6) break; default: KAD_PYR(TT, 8) break; }
+    if (dtype == KAD_F16) { KAD_PYR_NT(__half) } else { KAD_PYR_NT(__nv_bfloat16) }
+#undef KAD_PYR_NT
+#undef KAD_PYR
+    KAD_CHECK_LAUNCH("pyramid_project_kernel");
+    return KAD_OK;
+}

@@ -53,6 +53,8 @@ SIGNATURES = {
     'kad_dsc_forward': (c_int, [POINTER(KadDscArgs), c_void_p]),
     'kad_dsc_gap_tiles': (c_int, [c_int, c_int, c_int, c_int, c_int]),
     'kad_dsc_tc_supported': (c_int, [c_int, c_int, c_int]),
+    'kad_pyramid_project_supported': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    'kad_pyramid_project': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     'kad_stem_conv_supported': (c_int, [c_int, c_int, c_int]),
     'kad_stem_conv_u8': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
     'kad_dsc_mma_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),

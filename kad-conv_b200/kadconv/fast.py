@@ -103,6 +103,8 @@ def _layer_args(layer, st, dtype, H, W):
         launches = 25 - sum(1 for i, br in enumerate(st['branches']) if br.dsc_weight(dtype, H >> i, W >> i)[0] == ops.PATH_MMA)
         if dtype != torch.float32 and dim % 8 == 0:
             launches -= 3
+        if ops.pyramid_project_supported(dim, [br.c for br in st['branches']], dtype, H, W):
+            launches -= 2
         st[key] = (a, tc_mask, keep, launches)
     return st[key]
 
@@ -144,8 +146,11 @@ def kadconv_forward_nhwc_stepwise(layer, x):
     B, H, W, C = x.shape
     st = _prepare(layer, x.device)
     ys, atts = [], []
-    for i, br in enumerate(st['branches']):
-        t = ops.pool_project(x, br.w_proj, br.b_proj, pool=2 ** i)
+    brs = st['branches']
+    pyramid = ops.pyramid_project_supported(C, [br.c for br in brs], x.dtype, H, W)
+    ts = ops.pyramid_project(x, [br.w_proj for br in brs], [br.b_proj for br in brs]) if pyramid else None
+    for i, br in enumerate(brs):
+        t = ts[i] if pyramid else ops.pool_project(x, br.w_proj, br.b_proj, pool=2 ** i)
         mask = ops.lcsa_mask(t, br.lcsa, mask_f32=True)
         path, w = br.dsc_weight(t.dtype, t.shape[1], t.shape[2])
         if path == ops.PATH_MMA:      # the offset convolution runs inside the DSC kernel

@@ -423,3 +423,23 @@ def stem_conv_u8(img_u8, w, bias, dtype, act=ACT_SILU, scale=1.0 / 255.0):
     _abi.check(_abi.load().kad_stem_conv_u8(_ptr(img_u8), _ptr(w), _ptr(_f32(bias, 'bias')), _ptr(y), B, C, H, W, w.shape[0],
                                             ctypes.c_float(scale), act, _DT[dtype], _stream()), 'kad_stem_conv_u8')
     return y
+
+
+def pyramid_project_supported(dim, cs, dtype, H, W):
+    return dtype in _DT and bool(_abi.load().kad_pyramid_project_supported(dim, cs[0], cs[1], cs[2], _DT[dtype], H, W))
+
+
+def pyramid_project(x, ws, bs):
+    """t[i] = conv1x1(avg_pool2d(x, 2**i), ws[i]) + bs[i] for i = 0, 1, 2 in one kernel. x [B,H,W,dim] NHWC (f16/bf16),
+    ws[i] float32 [c_i, dim], bs[i] float32 [c_i] or None. Returns the three NHWC tensors."""
+    x = _cuda(x, 'x')
+    B, H, W, dim = x.shape
+    cs = [int(w.shape[0]) for w in ws]
+    ts = [torch.empty((B, H >> i, W >> i, cs[i]), dtype=x.dtype, device=x.device) for i in range(3)]
+    P3 = ctypes.c_void_p * 3
+    wp = P3(*[_f32(w, 'w').data_ptr() for w in ws])
+    bp = P3(*[(_f32(b, 'b').data_ptr() if b is not None else None) for b in bs])
+    tp = P3(*[t.data_ptr() for t in ts])
+    cp = (ctypes.c_int * 3)(*cs)
+    _abi.check(_abi.load().kad_pyramid_project(_ptr(x), wp, bp, tp, B, H, W, dim, cp, dtype_code(x), _stream()), 'kad_pyramid_project')
+    return ts

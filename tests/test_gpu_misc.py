@@ -252,3 +252,27 @@ def test_bias_act_into_a_channel_slice(dtype, C, act):
     assert bool((wide[..., :16] == 3).all()) and bool((wide[..., 16 + C:] == 3).all())
     inplace = ops.bias_act_(y.cuda().to(dtype).clone(), b.cuda(), act)
     assert torch.equal(inplace, wide[..., 16:16 + C])
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((1, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
+                                         ((1, 24, 9, 7), torch.float16), ((1, 72, 21, 33), torch.bfloat16)])
+def test_pyramid_projection(shape, dtype):
+    """One kernel for the three pooled 1x1 projections of a KAD-Conv layer: odd sizes (floor-mode pooling drops the
+    last rows / columns), widths with partial 16-channel chunks, several column tiles."""
+    from kadconv import ops
+    B, dim, H, W = shape
+    cs = (dim - 2 * (dim // 3), dim // 3, dim // 3)
+    x = round_to(_rand((B, dim, H, W), 100), dtype)
+    ws = [round_to(_rand((c, dim), 101 + i, 1.0 / np.sqrt(dim)), dtype) for i, c in enumerate(cs)]
+    bs = [_rand((c,), 105 + i, 0.1) for i, c in enumerate(cs)]
+    assert ops.pyramid_project_supported(dim, cs, dtype, H, W)
+    ts = ops.pyramid_project(nhwc(x).cuda().to(dtype), [w.cuda() for w in ws], [b.cuda() for b in bs])
+    for i in range(3):
+        pooled = round_to(F.avg_pool2d(x, 2 ** i), dtype) if i else x
+        ref = F.conv2d(pooled, ws[i].view(cs[i], dim, 1, 1), bs[i])
+        assert tuple(ts[i].shape) == (B, H >> i, W >> i, cs[i])
+        assert rel_err(ts[i].float().cpu().permute(0, 3, 1, 2), ref) <= (2e-3 if dtype == torch.float16 else 1e-2)
+    # agrees with the three single projections
+    for i in range(3):
+        single = ops.pool_project(nhwc(x).cuda().to(dtype), ws[i].cuda(), bs[i].cuda(), pool=2 ** i)
+        assert rel_err(ts[i].float(), single.float()) <= (2e-3 if dtype == torch.float16 else 1e-2)
