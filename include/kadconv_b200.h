@@ -112,8 +112,14 @@ int kad_pool_project(const void* x, const float* w, const float* bias, void* y,
  * Operands are rounded to dtype (the pooled means as well, as F.avg_pool2d rounds them), accumulation is float32.
  * kad_pyramid_project_supported: dtype f16/bf16, dim % 8 == 0, widths <= 64, H, W >= 4, a 4-row tile fits shared memory. */
 int kad_pyramid_project_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W);
+/* Optional by-products (both or neither; NULL to skip) for the LCSA that follows, whose pool_h / pool_w (kad_conv.py:27-28)
+ * are sums over the very tensors this kernel writes: rowpart[i] float32 [B][H>>i][n_col_tiles][c[i]] (sum over the columns
+ * of one tile) and colpart[i] float32 [B][n_row_groups][W>>i][c[i]] (sum over the rows one block covers), of the values as
+ * stored; (n_col_tiles, n_row_groups) from kad_pyramid_partial_dims. kad_lcsa_mask_from_partials consumes them. */
+int kad_pyramid_partial_dims(int B, int H, int W, int dim, int c0, int c1, int c2, int dtype, int* n_col_tiles, int* n_row_groups);
 int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
-                        int B, int H, int W, int dim, const int* c, int dtype, void* stream);
+                        int B, int H, int W, int dim, const int* c, int dtype,
+                        float* const* rowpart, float* const* colpart, void* stream);
 
 /* Average pool, kernel = stride = pool, floor mode, NHWC: F.avg_pool2d as used for the branch pyramid
  * (KAD-Conv/kadconv/kad_conv.py:115) when the pooled tensor feeds the tensor-core 1x1 GEMM. */
@@ -157,6 +163,16 @@ int kad_lcsa_mask(const float* rowsum, const float* colsum,
                   const float* w1, const float* b1, const float* bn_scale, const float* bn_shift,
                   const float* w2, const float* b2, const float* w3, const float* b3,
                   float* scratch, void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
+
+/* LCSA steps 1 + 2 from the partial sums of kad_pyramid_project (no second pass over the branch tensor): the sums over
+ * tiles are finished here (rowsum float32 [B][H][C] is written as a by-product), then the mask as in kad_lcsa_mask.
+ * Works on 128 consecutive pixels per block, so narrow feature maps keep their lanes busy.
+ * kad_lcsa_mask_from_partials_supported: C <= 256 and the per-row operands fit shared memory. */
+int kad_lcsa_mask_from_partials_supported(int H, int W, int C);
+int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles, const float* colpart, int n_row_groups,
+                                const float* w1, const float* b1, const float* bn_scale, const float* bn_shift,
+                                const float* w2, const float* b2, const float* w3, const float* b3,
+                                float* scratch, float* rowsum, void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
 
 /* LCSA step 2 without a scratch argument and without any allocation. No counterpart in the reference project: it
  * exists for hosts that cannot create device memory where they call this library (a server whose own pool took all

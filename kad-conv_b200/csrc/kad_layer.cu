@@ -40,15 +40,17 @@ int side_streams(int dev, SideStreams** out) {
 inline size_t align_up(size_t v) { return (v + 255) & ~size_t(255); }
 
 struct BranchWs {
-    size_t t, rows, cols, scratch, mask, offset, y, gap, att, end;
+    size_t t, rows, cols, rowpart, colpart, scratch, mask, offset, y, gap, att, end;
 };
 
-BranchWs plan_branch(size_t base, int B, int h, int w, int c, size_t es, int gap_tiles) {
+BranchWs plan_branch(size_t base, int B, int h, int w, int c, size_t es, int gap_tiles, int nct, int nrg) {
     BranchWs p;
     size_t o = base;
     p.t = o; o = align_up(o + (size_t)B * h * w * c * es);
     p.rows = o; o = align_up(o + (size_t)B * h * c * 4);
     p.cols = o; o = align_up(o + (size_t)B * w * c * 4);
+    p.rowpart = o; o = align_up(o + (size_t)B * h * nct * c * 4);     // partial sums of the pyramid kernel (nct = 0: unused)
+    p.colpart = o; o = align_up(o + (size_t)B * nrg * w * c * 4);
     p.scratch = o; o = align_up(o + ((size_t)B * w * c + (size_t)w * c) * 4);
     p.mask = o; o = align_up(o + (size_t)B * h * w * 9 * 4);
     p.offset = o; o = align_up(o + (size_t)B * h * w * 18 * 4);
@@ -65,6 +67,36 @@ int branch_path(const KadBranchParams& br, int dtype, int h, int w) {
     return kad_dsc_mma_supported(br.c, br.c, dtype, h, w) ? 3 : 0;
 }
 
+// What the layer call does for this shape, and where everything lives in the workspace.
+struct LayerPlan {
+    BranchWs ws[3];
+    int path[3], tiles[3];
+    bool pyramid, partials;      // one kernel for the three projections; LCSA sums taken from that kernel's partial sums
+    int nct, nrg;
+    size_t bytes;
+};
+
+LayerPlan plan_layer(int B, int H, int W, int dim, int dtype, int tc_mask) {
+    LayerPlan L{};
+    const size_t es = dtype_size(dtype);
+    const int widths[3] = {dim - (dim / 3) * 2, dim / 3, dim / 3};
+    L.pyramid = kad_pyramid_project_supported(dim, widths[0], widths[1], widths[2], dtype, H, W) != 0;
+    L.partials = L.pyramid;
+    for (int i = 0; i < 3; ++i) L.partials = L.partials && kad_lcsa_mask_from_partials_supported(H >> i, W >> i, widths[i]) != 0;
+    if (L.partials && kad_pyramid_partial_dims(B, H, W, dim, widths[0], widths[1], widths[2], dtype, &L.nct, &L.nrg) != KAD_OK) L.partials = false;
+    if (!L.partials) L.nct = L.nrg = 0;
+    size_t o = 0;
+    for (int i = 0; i < 3; ++i) {
+        const int h = H >> i, w = W >> i, c = widths[i];
+        L.path[i] = ((tc_mask >> i) & 1) ? 1 : (kad_dsc_mma_supported(c, c, dtype, h, w) ? 3 : 0);
+        L.tiles[i] = kad_dsc_gap_tiles(h, w, c, c, L.path[i]);
+        L.ws[i] = plan_branch(o, B, h, w, c, es, L.tiles[i], L.nct, L.nrg);
+        o = L.ws[i].end;
+    }
+    L.bytes = o;
+    return L;
+}
+
 }  // namespace
 }  // namespace kad
 
@@ -72,15 +104,7 @@ using namespace kad;
 
 extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches) {
     if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
-    const size_t es = dtype_size(dtype);
-    const int widths[3] = {dim - (dim / 3) * 2, dim / 3, dim / 3};
-    size_t o = 0;
-    for (int i = 0; i < 3; ++i) {
-        const int h = H >> i, w = W >> i;
-        const int path = ((tc_branches >> i) & 1) ? 1 : (kad_dsc_mma_supported(widths[i], widths[i], dtype, h, w) ? 3 : 0);
-        o = plan_branch(o, B, h, w, widths[i], es, kad_dsc_gap_tiles(h, w, widths[i], widths[i], path)).end;
-    }
-    return o;
+    return plan_layer(B, H, W, dim, dtype, tc_branches).bytes;
 }
 
 extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
@@ -105,27 +129,18 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     cudaStream_t main_s = (cudaStream_t)stream;
     cudaStream_t st[3] = {main_s, ss->s[0], ss->s[1]};
 
-    const size_t es = dtype_size(a->dtype);
     unsigned char* ws = reinterpret_cast<unsigned char*>(a->workspace);
-    BranchWs plan[3]; int paths[3], tiles_of[3];
-    {
-        size_t o = 0;
-        for (int i = 0; i < 3; ++i) {
-            const int h = a->H >> i, w = a->W >> i, c = a->br[i].c;
-            paths[i] = branch_path(a->br[i], a->dtype, h, w);
-            tiles_of[i] = kad_dsc_gap_tiles(h, w, c, c, paths[i]);
-            plan[i] = plan_branch(o, a->B, h, w, c, es, tiles_of[i]);
-            o = plan[i].end;
-        }
-    }
+    const LayerPlan L = plan_layer(a->B, a->H, a->W, a->dim, a->dtype, tc_mask);
     // the three pooled projections read the same x: one kernel on the caller's stream, before the branches fork
-    const bool pyramid = kad_pyramid_project_supported(a->dim, widths[0], widths[1], widths[2], a->dtype, a->H, a->W) != 0 &&
-                         (uintptr_t)a->x % 16 == 0;
+    const bool pyramid = L.pyramid && (uintptr_t)a->x % 16 == 0;
+    const bool partials = pyramid && L.partials;
     if (pyramid) {
         const float* w3[3] = {a->br[0].w_proj, a->br[1].w_proj, a->br[2].w_proj};
         const float* b3[3] = {a->br[0].b_proj, a->br[1].b_proj, a->br[2].b_proj};
-        void* t3[3] = {ws + plan[0].t, ws + plan[1].t, ws + plan[2].t};
-        rc = kad_pyramid_project(a->x, w3, b3, t3, a->B, a->H, a->W, a->dim, widths, a->dtype, stream);
+        void* t3[3] = {ws + L.ws[0].t, ws + L.ws[1].t, ws + L.ws[2].t};
+        float* rp[3] = {(float*)(ws + L.ws[0].rowpart), (float*)(ws + L.ws[1].rowpart), (float*)(ws + L.ws[2].rowpart)};
+        float* cp[3] = {(float*)(ws + L.ws[0].colpart), (float*)(ws + L.ws[1].colpart), (float*)(ws + L.ws[2].colpart)};
+        rc = kad_pyramid_project(a->x, w3, b3, t3, a->B, a->H, a->W, a->dim, widths, a->dtype, partials ? rp : nullptr, partials ? cp : nullptr, stream);
         if (rc) return rc;
     }
 
@@ -139,19 +154,26 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     for (int i = 0; i < 3 && rc == KAD_OK; ++i) {
         const KadBranchParams& br = a->br[i];
         const int h = a->H >> i, w = a->W >> i, c = br.c;
-        const int path = paths[i];
-        const int tiles = tiles_of[i];
-        const BranchWs p = plan[i];
+        const int path = L.path[i];
+        const int tiles = L.tiles[i];
+        const BranchWs p = L.ws[i];
         void* s = (void*)st[i];
         if (!pyramid) {
             rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
             if (rc) break;
         }
-        rc = kad_lcsa_sums(ws + p.t, (float*)(ws + p.rows), (float*)(ws + p.cols), a->B, h, w, c, a->dtype, s);
-        if (rc) break;
-        rc = kad_lcsa_mask((const float*)(ws + p.rows), (const float*)(ws + p.cols), br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift,
-                           br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3, (float*)(ws + p.scratch), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
-        if (rc) break;
+        if (partials) {
+            rc = kad_lcsa_mask_from_partials((const float*)(ws + p.rowpart), L.nct, (const float*)(ws + p.colpart), L.nrg,
+                                             br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift, br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3,
+                                             (float*)(ws + p.scratch), (float*)(ws + p.rows), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
+            if (rc) break;
+        } else {
+            rc = kad_lcsa_sums(ws + p.t, (float*)(ws + p.rows), (float*)(ws + p.cols), a->B, h, w, c, a->dtype, s);
+            if (rc) break;
+            rc = kad_lcsa_mask((const float*)(ws + p.rows), (const float*)(ws + p.cols), br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift,
+                               br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3, (float*)(ws + p.scratch), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
+            if (rc) break;
+        }
         KadDscArgs q{};
         if (path == 3) {
             q.offset_weight = br.w_off; q.offset_bias = br.b_off;       // offsets computed inside the DSC kernel

@@ -14,7 +14,12 @@ struct PyramidParams {
     const void* x; const float* w[3]; const float* b[3]; void* t[3];
     int B, H, W, dim, c[3];
     int TW, KC, xpitch;           // tile width (a multiple of 4), 16-channel chunks, bytes per staged pixel (dim*2 + 16)
-    int off_p1, off_p2, off_B, off_bias, off_out;   // shared-memory byte offsets
+    int off_p1, off_p2, off_B, off_bias, off_out, off_colacc, off_part;   // shared-memory byte offsets
+    // optional by-products for the LCSA that follows (kad_conv.py:27-28: means over rows and over columns of every t_i):
+    // rowpart[i] [B][h_i][gridDim.x][c_i]: sum over the columns of this block's tile; colpart[i] [B][gridDim.y][w_i][c_i]:
+    // sum over the rows this block covers (RT consecutive 4-row tiles); sums of the values as stored (rounded to T)
+    float* rowpart[3]; float* colpart[3];
+    int RT;
 };
 
 // Weight fragments of a 1x1 convolution w[Cout][Cin] (see stage_weights of the deformable kernel for the slot layout).
@@ -67,26 +72,37 @@ pyramid_project_kernel(const PyramidParams p) {
     extern __shared__ __align__(16) unsigned char sm[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int TW = p.TW, dim = p.dim, KC = p.KC, xp = p.xpitch;
-    const int b = blockIdx.z, r0 = blockIdx.y * 4, c0 = blockIdx.x * TW;
-    const int rows = min(4, p.H - r0), cols = min(TW, p.W - c0);
+    const int b = blockIdx.z, c0 = blockIdx.x * TW;
+    const int cols = min(TW, p.W - c0);
     unsigned char* xt = sm;                                   // [4][TW] pixels of xp bytes
     unsigned char* p1 = sm + p.off_p1;                        // [2][TW/2]
     unsigned char* p2 = sm + p.off_p2;                        // [1][TW/4]
     uint2* Bs = reinterpret_cast<uint2*>(sm + p.off_B);       // [3][KC][NT][32]
     float* bias = reinterpret_cast<float*>(sm + p.off_bias);  // [3][NT*8]
     unsigned char* outs = sm + p.off_out;                     // result tiles of the three branches, one after the other
+    float* colacc = reinterpret_cast<float*>(sm + p.off_colacc);   // column sums of the three result tiles over this block's row tiles
+    float* part = reinterpret_cast<float*>(sm + p.off_part);       // [768] partial row sums
+    const bool sums = p.rowpart[0] != nullptr;
+    const int ncolacc = TW * p.c[0] + (TW >> 1) * p.c[1] + (TW >> 2) * p.c[2];
+    if (sums) for (int e = tid; e < ncolacc; e += MMA_THREADS) colacc[e] = 0.f;
 
-    // ---- stage x (asynchronous), weights and bias meanwhile ----------------------------------------------------------
     const int vpp = dim >> 3;                                 // 16-byte vectors per pixel
     const unsigned char* xb = reinterpret_cast<const unsigned char*>(p.x) + (size_t)b * p.H * p.W * dim * 2;
+    for (int rt = 0; rt < p.RT; ++rt) {
+    const int r0 = (blockIdx.y * p.RT + rt) * 4;
+    if (r0 >= p.H) break;
+    const int rows = min(4, p.H - r0);
+    // ---- stage x (asynchronous), weights and bias meanwhile ----------------------------------------------------------
     for (int v = tid; v < rows * cols * vpp; v += MMA_THREADS) {
         const int px = v / vpp, k = v - px * vpp, r = px / cols, c = px - r * cols;
         cp_async16(xt + (size_t)(r * TW + c) * xp + 16 * k, xb + ((size_t)(r0 + r) * p.W + c0 + c) * dim * 2 + 16 * k);
     }
+    if (rt == 0) {
 #pragma unroll
-    for (int i = 0; i < 3; ++i) {
-        stage_weights_1x1<T>(Bs + i * KC * NT * 32, p.w[i], dim, p.c[i], KC, NT, tid);
-        for (int e = tid; e < NT * 8; e += MMA_THREADS) bias[i * NT * 8 + e] = (e < p.c[i] && p.b[i]) ? p.b[i][e] : 0.f;
+        for (int i = 0; i < 3; ++i) {
+            stage_weights_1x1<T>(Bs + i * KC * NT * 32, p.w[i], dim, p.c[i], KC, NT, tid);
+            for (int e = tid; e < NT * 8; e += MMA_THREADS) bias[i * NT * 8 + e] = (e < p.c[i] && p.b[i]) ? p.b[i][e] : 0.f;
+        }
     }
     cp_async_wait_all();
     __syncthreads();
@@ -171,6 +187,58 @@ pyramid_project_kernel(const PyramidParams p) {
             }
         }
     }
+
+    // ---- by-products: sums over the tile's columns (per row) and rows (per column), in a fixed order ----------------------
+    if (sums) {
+        int cabase = 0, pbase = 0;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int ci = p.c[i], tw = TW >> i, hi_ = p.H >> i, wi = p.W >> i;
+            const int rr0 = r0 >> i, cc0 = c0 >> i, nrows = max(0, min(4 >> i, hi_ - rr0)), ncols = max(0, min(tw, wi - cc0));
+            const T* ot = reinterpret_cast<const T*>(outs + obase[i]);
+            for (int e = tid; e < ncols * ci; e += MMA_THREADS) {          // e = col*ci + c: consecutive addresses of a tile row
+                float a = 0.f;
+                for (int r = 0; r < nrows; ++r) a += to_f<T>(ot[(size_t)r * tw * ci + e]);
+                colacc[cabase + e] += a;
+            }
+            // row sums: Q threads per (row, channel), each over every Q-th column
+            const int nrc = nrows * ci, Q = nrc > 0 ? max(1, min(8, 256 / nrc)) : 1;
+            for (int e = tid; e < nrc * Q; e += MMA_THREADS) {
+                const int q = e / nrc, rc = e - q * nrc, r = rc / ci, c = rc - r * ci;
+                float a = 0.f;
+                for (int col = q; col < ncols; col += Q) a += to_f<T>(ot[((size_t)r * tw + col) * ci + c]);
+                part[pbase + e] = a;
+            }
+            cabase += tw * ci; pbase += 256;
+        }
+        __syncthreads();
+        pbase = 0;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int ci = p.c[i], hi_ = p.H >> i, rr0 = r0 >> i, nrows = max(0, min(4 >> i, hi_ - rr0));
+            const int nrc = nrows * ci, Q = nrc > 0 ? max(1, min(8, 256 / nrc)) : 1;
+            for (int rc = tid; rc < nrc; rc += MMA_THREADS) {
+                float a = 0.f;
+                for (int q = 0; q < Q; ++q) a += part[pbase + q * nrc + rc];
+                const int r = rc / ci, c = rc - r * ci;
+                p.rowpart[i][(((size_t)b * hi_ + rr0 + r) * gridDim.x + blockIdx.x) * ci + c] = a;
+            }
+            pbase += 256;
+        }
+    }
+    }   // row tiles
+
+    if (sums) {
+        __syncthreads();
+        int cabase = 0;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int ci = p.c[i], tw = TW >> i, wi = p.W >> i, cc0 = c0 >> i, ncols = max(0, min(tw, wi - cc0));
+            for (int e = tid; e < ncols * ci; e += MMA_THREADS)
+                p.colpart[i][(((size_t)b * gridDim.y + blockIdx.y) * wi + cc0) * ci + e] = colacc[cabase + e];
+            cabase += tw * ci;
+        }
+    }
 }
 
 inline int pyr_nt(int c) {
@@ -198,10 +266,14 @@ size_t pyramid_plan(int W, int dim, const int c[3], PyramidParams* p) {
         o = (o + 15) & ~size_t(15);
         const size_t off_out = o;
         o += ((size_t)4 * TW * c[0] + (size_t)2 * (TW / 2) * c[1] + (size_t)(TW / 4) * c[2]) * 2 + 16;
+        o = (o + 15) & ~size_t(15);
+        const size_t off_colacc = o; o += ((size_t)TW * c[0] + (size_t)(TW / 2) * c[1] + (size_t)(TW / 4) * c[2]) * 4;
+        const size_t off_part = o; o += 768 * 4;
         if (o > 112 * 1024) continue;
         if (p) {
             p->TW = TW; p->KC = KC; p->xpitch = xpitch;
             p->off_p1 = (int)off_p1; p->off_p2 = (int)off_p2; p->off_B = (int)off_B; p->off_bias = (int)off_bias; p->off_out = (int)off_out;
+            p->off_colacc = (int)off_colacc; p->off_part = (int)off_part;
         }
         return o;
     }
@@ -221,10 +293,32 @@ extern "C" int kad_pyramid_project_supported(int dim, int c0, int c1, int c2, in
     return pyramid_plan(W, dim, c, nullptr) != 0;
 }
 
+// Row tiles (4 rows each) one block walks through, so that a few hundred blocks remain.
+static int pyramid_row_tiles_per_block(int B, int H, int n_col_tiles) {
+    const long long tiles = (long long)B * ((H + 3) / 4) * n_col_tiles;
+    long long rt = tiles / 592;
+    return rt < 1 ? 1 : (rt > 8 ? 8 : (int)rt);
+}
+
+extern "C" int kad_pyramid_partial_dims(int B, int H, int W, int dim, int c0, int c1, int c2, int dtype, int* n_col_tiles, int* n_row_groups) {
+    KAD_CHECK_ARG(n_col_tiles && n_row_groups, "kad_pyramid_partial_dims: null pointer");
+    if (!kad_pyramid_project_supported(dim, c0, c1, c2, dtype, H, W))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_pyramid_partial_dims: shape not supported by kad_pyramid_project");
+    const int c[3] = {c0, c1, c2};
+    PyramidParams p{};
+    pyramid_plan(W, dim, c, &p);
+    *n_col_tiles = (W + p.TW - 1) / p.TW;
+    const int rt = pyramid_row_tiles_per_block(B, H, *n_col_tiles);
+    *n_row_groups = ((H + 3) / 4 + rt - 1) / rt;
+    return KAD_OK;
+}
+
 extern "C" int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
-                                   int B, int H, int W, int dim, const int* c, int dtype, void* stream) {
+                                   int B, int H, int W, int dim, const int* c, int dtype,
+                                   float* const* rowpart, float* const* colpart, void* stream) {
     KAD_CHECK_ARG(x && w && bias && t && c, "kad_pyramid_project: null pointer");
     KAD_CHECK_ARG(B > 0 && B <= 65535, "kad_pyramid_project: bad batch %d", B);
+    KAD_CHECK_ARG((rowpart == nullptr) == (colpart == nullptr), "kad_pyramid_project: rowpart and colpart go together");
     if (!kad_pyramid_project_supported(dim, c[0], c[1], c[2], dtype, H, W))
         return fail(KAD_ERR_UNSUPPORTED, "kad_pyramid_project: needs f16/bf16, dim %% 8 == 0, widths <= 64, H, W >= 4 (got dim=%d c=%d,%d,%d H=%d W=%d dtype=%d)",
                     dim, c[0], c[1], c[2], H, W, dtype);
@@ -234,11 +328,17 @@ extern "C" int kad_pyramid_project(const void* x, const float* const* w, const f
         KAD_CHECK_ARG(w[i] && t[i], "kad_pyramid_project: null pointer for branch %d", i);
         KAD_CHECK_ARG((uintptr_t)t[i] % 4 == 0, "kad_pyramid_project: t[%d] must be 4-byte aligned", i);
         p.w[i] = w[i]; p.b[i] = bias[i]; p.t[i] = t[i]; p.c[i] = c[i];
+        if (rowpart) {
+            KAD_CHECK_ARG(rowpart[i] && colpart[i], "kad_pyramid_project: null partial-sum pointer for branch %d", i);
+            p.rowpart[i] = rowpart[i]; p.colpart[i] = colpart[i];
+        }
     }
     KAD_CHECK_ARG((uintptr_t)x % 16 == 0, "kad_pyramid_project: x must be 16-byte aligned");
     const size_t smem = pyramid_plan(W, dim, c, &p);
     const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
-    dim3 grid((W + p.TW - 1) / p.TW, (H + 3) / 4, B);
+    const int nct = (W + p.TW - 1) / p.TW;
+    p.RT = pyramid_row_tiles_per_block(B, H, nct);
+    dim3 grid(nct, ((H + 3) / 4 + p.RT - 1) / p.RT, B);
     KAD_CHECK_ARG(grid.y <= 65535, "kad_pyramid_project: image too tall");
     cudaStream_t st = (cudaStream_t)stream;
 #define KAD_PYR(TT, N)                                                                                                \

@@ -105,6 +105,8 @@ def _layer_args(layer, st, dtype, H, W):
             launches -= 3
         if ops.pyramid_project_supported(dim, [br.c for br in st['branches']], dtype, H, W):
             launches -= 2
+            if all(ops.lcsa_mask_from_partials_supported(H >> i, W >> i, br.c) for i, br in enumerate(st['branches'])):
+                launches -= 6      # row/column sums come out of the pyramid kernel
         st[key] = (a, tc_mask, keep, launches)
     return st[key]
 
@@ -148,10 +150,18 @@ def kadconv_forward_nhwc_stepwise(layer, x):
     ys, atts = [], []
     brs = st['branches']
     pyramid = ops.pyramid_project_supported(C, [br.c for br in brs], x.dtype, H, W)
-    ts = ops.pyramid_project(x, [br.w_proj for br in brs], [br.b_proj for br in brs]) if pyramid else None
+    partials = pyramid and all(ops.lcsa_mask_from_partials_supported(H >> i, W >> i, br.c) for i, br in enumerate(brs))
+    ts, parts = None, None
+    if pyramid:
+        ts = ops.pyramid_project(x, [br.w_proj for br in brs], [br.b_proj for br in brs], want_partials=partials)
+        if partials:
+            ts, parts = ts
     for i, br in enumerate(brs):
         t = ts[i] if pyramid else ops.pool_project(x, br.w_proj, br.b_proj, pool=2 ** i)
-        mask = ops.lcsa_mask(t, br.lcsa, mask_f32=True)
+        if partials:
+            mask = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], br.lcsa, t.dtype, mask_f32=True)
+        else:
+            mask = ops.lcsa_mask(t, br.lcsa, mask_f32=True)
         path, w = br.dsc_weight(t.dtype, t.shape[1], t.shape[2])
         if path == ops.PATH_MMA:      # the offset convolution runs inside the DSC kernel
             y, gap = ops.dsc_forward(t, w, None, mask, scale=br.ep_scale, shift=br.ep_shift, post=br.ep_post, act=ops.ACT_RELU,

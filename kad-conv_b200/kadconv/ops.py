@@ -429,17 +429,48 @@ def pyramid_project_supported(dim, cs, dtype, H, W):
     return dtype in _DT and bool(_abi.load().kad_pyramid_project_supported(dim, cs[0], cs[1], cs[2], _DT[dtype], H, W))
 
 
-def pyramid_project(x, ws, bs):
+def pyramid_project(x, ws, bs, want_partials=False):
     """t[i] = conv1x1(avg_pool2d(x, 2**i), ws[i]) + bs[i] for i = 0, 1, 2 in one kernel. x [B,H,W,dim] NHWC (f16/bf16),
-    ws[i] float32 [c_i, dim], bs[i] float32 [c_i] or None. Returns the three NHWC tensors."""
+    ws[i] float32 [c_i, dim], bs[i] float32 [c_i] or None. Returns the three NHWC tensors, and with want_partials also the
+    partial sums for lcsa_mask_from_partials: a list of (rowpart [B,h_i,n_col_tiles,c_i], colpart [B,n_row_groups,w_i,c_i])."""
     x = _cuda(x, 'x')
     B, H, W, dim = x.shape
     cs = [int(w.shape[0]) for w in ws]
+    lib = _abi.load()
     ts = [torch.empty((B, H >> i, W >> i, cs[i]), dtype=x.dtype, device=x.device) for i in range(3)]
     P3 = ctypes.c_void_p * 3
     wp = P3(*[_f32(w, 'w').data_ptr() for w in ws])
     bp = P3(*[(_f32(b, 'b').data_ptr() if b is not None else None) for b in bs])
     tp = P3(*[t.data_ptr() for t in ts])
     cp = (ctypes.c_int * 3)(*cs)
-    _abi.check(_abi.load().kad_pyramid_project(_ptr(x), wp, bp, tp, B, H, W, dim, cp, dtype_code(x), _stream()), 'kad_pyramid_project')
-    return ts
+    parts, rp, cpp = None, None, None
+    if want_partials:
+        nct, nrg = ctypes.c_int(0), ctypes.c_int(0)
+        _abi.check(lib.kad_pyramid_partial_dims(B, H, W, dim, cs[0], cs[1], cs[2], dtype_code(x), ctypes.byref(nct), ctypes.byref(nrg)),
+                   'kad_pyramid_partial_dims', 0)
+        parts = [(torch.empty((B, H >> i, nct.value, cs[i]), dtype=torch.float32, device=x.device),
+                  torch.empty((B, nrg.value, W >> i, cs[i]), dtype=torch.float32, device=x.device)) for i in range(3)]
+        rp = P3(*[p[0].data_ptr() for p in parts]); cpp = P3(*[p[1].data_ptr() for p in parts])
+    _abi.check(lib.kad_pyramid_project(_ptr(x), wp, bp, tp, B, H, W, dim, cp, dtype_code(x), rp, cpp, _stream()), 'kad_pyramid_project')
+    return (ts, parts) if want_partials else ts
+
+
+def lcsa_mask_from_partials_supported(H, W, C):
+    return bool(_abi.load().kad_lcsa_mask_from_partials_supported(H, W, C))
+
+
+def lcsa_mask_from_partials(rowpart, colpart, prm, dtype, mask_f32=False):
+    """LCSA mask [B,H,W,9] from the partial sums of pyramid_project (rowpart [B,H,nct,C], colpart [B,nrg,W,C]);
+    prm as for lcsa_mask. The mask is float32 if mask_f32 else `dtype` (the dtype of the branch tensor)."""
+    rowpart = _f32(rowpart, 'rowpart'); colpart = _f32(colpart, 'colpart')
+    B, H, nct, C = rowpart.shape
+    nrg, W = colpart.shape[1], colpart.shape[2]
+    dev = rowpart.device
+    scratch = torch.empty(B * W * C + W * C, dtype=torch.float32, device=dev)
+    rowsum = torch.empty((B, H, C), dtype=torch.float32, device=dev)
+    mask = torch.empty((B, H, W, 9), dtype=torch.float32 if mask_f32 else dtype, device=dev)
+    _abi.check(_abi.load().kad_lcsa_mask_from_partials(
+        _ptr(rowpart), nct, _ptr(colpart), nrg, _ptr(prm['w1']), _ptr(prm['b1']), _ptr(prm['bn_m']), _ptr(prm['bn_a']),
+        _ptr(prm['w2']), _ptr(prm['b2']), _ptr(prm['w3']), _ptr(prm['b3']), _ptr(scratch), _ptr(rowsum), _ptr(mask),
+        B, H, W, C, int(mask_f32), _DT[dtype], _stream()), 'kad_lcsa_mask_from_partials', 2)
+    return mask

@@ -276,3 +276,28 @@ def test_pyramid_projection(shape, dtype):
     for i in range(3):
         single = ops.pool_project(nhwc(x).cuda().to(dtype), ws[i].cuda(), bs[i].cuda(), pool=2 ** i)
         assert rel_err(ts[i].float(), single.float()) <= (2e-3 if dtype == torch.float16 else 1e-2)
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((1, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
+                                         ((3, 64, 7, 5), torch.float16)])
+def test_lcsa_mask_from_pyramid_partial_sums(shape, dtype):
+    """The row / column sums the pyramid kernel emits as by-products give the same LCSA mask as summing the branch
+    tensors in a second pass (kad_lcsa_sums + kad_lcsa_mask), also on maps narrower than a block."""
+    from kadconv import ops
+    B, dim, H, W = shape
+    cs = (dim - 2 * (dim // 3), dim // 3, dim // 3)
+    x = round_to(_rand((B, dim, H, W), 110), dtype)
+    ws = [_rand((c, dim), 111 + i, 1.0 / np.sqrt(dim)) for i, c in enumerate(cs)]
+    bs = [_rand((c,), 115 + i, 0.1) for i, c in enumerate(cs)]
+    ts, parts = ops.pyramid_project(nhwc(x).cuda().to(dtype), [w.cuda() for w in ws], [b.cuda() for b in bs], want_partials=True)
+    for i, c in enumerate(cs):
+        t = ts[i]
+        assert rel_err(parts[i][0].sum(2).cpu(), t.float().sum(2).cpu()) <= 1e-5
+        assert rel_err(parts[i][1].sum(1).cpu(), t.float().sum(1).cpu()) <= 1e-5
+        f = lambda a: a.cuda()
+        prm = dict(w1=f(_rand((c, 11), 120 + i, 0.3)), b1=f(_rand((c,), 123 + i, 0.1)), bn_m=f(1.0 + _rand((c,), 126 + i, 0.1)), bn_a=f(_rand((c,), 129 + i, 0.1)),
+                   w2=f(_rand((c, 11), 132 + i, 0.3)), b2=f(_rand((c,), 135 + i, 0.1)), w3=f(_rand((9, c), 138 + i, 0.3)), b3=f(_rand((9,), 141 + i, 0.1)))
+        assert ops.lcsa_mask_from_partials_supported(t.shape[1], t.shape[2], c)
+        m1 = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], prm, dtype, mask_f32=True)
+        m0 = ops.lcsa_mask(t, prm, mask_f32=True)
+        assert (m1 - m0).abs().max().item() <= 2e-5
