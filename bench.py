@@ -33,7 +33,7 @@ import torch  # noqa: E402
 C1 = dict(B=16, C=256, H=100, W=100)
 C1_FLOPS = 2.0 * C1['B'] * C1['H'] * C1['W'] * C1['C'] * 9 * C1['C']                    # 188.74 GFLOP
 C1_BYTES = 2.0 * (C1['B'] * C1['H'] * C1['W'] * (2 * C1['C'] + 27) + 9 * C1['C'] * C1['C'])  # 173.66 MB
-NCU_TRAFFIC = {'c1': None}   # DRAM bytes per launch from the committed ncu summary (profiles/), filled below
+NCU_TRAFFIC = {'c1': 129.8e6, 'c4_dsc_mma': None}   # DRAM bytes per launch from the committed ncu summary (profiles/), filled below
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
 
 
@@ -253,6 +253,39 @@ def c4_images(n, seed=0):
     return torch.randint(0, 256, (n, 3, C4['H'], C4['W']), dtype=torch.uint8, generator=g)
 
 
+def c4_dominant_kernel(device, mb, stream, n=20):
+    """The kernel with the largest share of the detector forward, timed alone with CUDA events: the fused offset + deformable
+    convolution of a KAD-Conv branch at the detector's largest KAD-Conv shape (stride 8: 100x100, 12 channels). Two input sets
+    are alternated; one set (x, mask, y) is larger than the L2 at mini-batch 64."""
+    from kadconv import ops
+    B, H, W, c = mb, 100, 100, 12
+    g = torch.Generator(device=device).manual_seed(1)
+    sets = []
+    for _ in range(2):
+        x = torch.randn((B, H, W, c), device=device, generator=g).half()
+        msk = torch.sigmoid(torch.randn((B, H, W, 9), device=device, generator=g))
+        sets.append((x, msk))
+    w = ops.pack_dsc_weight_simt((torch.rand((c, c, 3, 3), device=device, generator=g) * 2 - 1) / (3 * c ** 0.5))
+    wo = ops.pack_dsc_weight_simt((torch.rand((18, c, 3, 3), device=device, generator=g) * 2 - 1) / (3 * c ** 0.5))
+    bo = torch.zeros(18, device=device)
+
+    def launch(i):
+        x, msk = sets[i & 1]
+        return ops.dsc_forward(x, w, None, msk, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo)
+
+    for i in range(3):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(n):
+        launch(i)
+    e1.record(stream); torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / n * 1e3
+    nbytes = B * H * W * (c * 2 + 9 * 4 + c * 2)          # x read, modulation mask read (float32), y written
+    return {'us': us, 'bytes': nbytes, 'gbs': nbytes / (us * 1e-6) / 1e9, 'shape': [B, H, W, c]}
+
+
 def c4_cpu_sample(n_images=2):
     """The plain PyTorch modules (what the reference's raw backend executes) + NMS, fp32, all host cores."""
     import kadcnet
@@ -359,6 +392,7 @@ def run_c4(args, rank, world, local):
     n_total = sum(t.shape[0] for t in all_d) if rank == 0 else None
     pk = peaks()
     ips_fwd = mb / (fwd_ms * 1e-3)
+    dom = c4_dominant_kernel(device, mb, stream)
     return {
         'metric': 'KAD-CNet-S 800x800 images/s', 'value': C4['images'] * args.steps / (ms_total * 1e-3), 'unit': 'images/s',
         'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_total / args.steps,
@@ -367,10 +401,16 @@ def run_c4(args, rank, world, local):
                                'sharded by batch over the ranks, backbone + neck + head + decode + NMS (conf 0.001, IoU 0.65, max_det 300)',
                    'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
                    'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)'},
-        'roofline': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
-                     'frac': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9 / pk['hbm_gbs'], 'traffic': None, 'peak_source': pk['_source'],
-                     'kernel': 'whole forward graph (minimum activation traffic 0.35 GB/image, fp16)',
-                     'forward_ms_per_mini_batch': fwd_ms, 'tensor_frac': ips_fwd * C4_GFLOP_PER_IMAGE / 1e3 / pk['bf16_tflops_sustained']},
+        'roofline': {'bound': 'hbm', 'achieved': dom['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s', 'frac': dom['gbs'] / pk['hbm_gbs'],
+                     'traffic': NCU_TRAFFIC['c4_dsc_mma'], 'peak_source': pk['_source'],
+                     'kernel': 'dsc_mma_kernel (fused offset convolution + deformable convolution of a KAD-Conv branch), the largest share of the '
+                               'forward (about 22 % of its GPU time); timed alone on its largest detector shape', 'shape': dom['shape'],
+                     'us_per_launch': dom['us'], 'algorithmic_bytes': dom['bytes'],
+                     'note': 'bound by instruction issue (bilinear gather geometry), not by HBM: see the ncu summary under profiles/'},
+        'roofline_forward_graph': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+                                   'frac': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9 / pk['hbm_gbs'],
+                                   'kernel': 'whole forward graph (minimum activation traffic 0.35 GB/image, fp16)',
+                                   'forward_ms_per_mini_batch': fwd_ms, 'tensor_frac': ips_fwd * C4_GFLOP_PER_IMAGE / 1e3 / pk['bf16_tflops_sustained']},
         'e2e': {'value': C4['images'] / (e2e_ms * 1e-3), 'unit': 'images/s', 'h2d_bytes_per_step': host.numel(),
                 'd2h_bytes_per_step': int(sum(t.numel() * 4 for t in dets_host)), 'ms_per_step': e2e_ms},
         'gpu_launches': args.steps * (n_local // mb) * kernels_per_mb, 'own_kernels_per_mini_batch': kernels_per_mb,
@@ -506,13 +546,33 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c1', choices=['c1', 'c2', 'c4'])
+    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4'],
+                    help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
     ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
     args = ap.parse_args()
     rank, world, local = dist_setup(args.gpus)
 
+    if args.impl == 'reference' and args.workload == 'c4':
+        if rank == 0:
+            model, cores = cpu_info()
+            vals = []
+            for _ in range(max(1, min(args.steps, 3))):
+                ips, n, dt = c4_cpu_sample()
+                vals.append(ips)
+            v = statistics.median(vals)
+            print(json.dumps({
+                'impl': 'reference', 'metric': 'KAD-CNet-S 800x800 images/s', 'value': v, 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
+                'warmup': args.warmup, 'ms_per_step': 1e3 * C4['images'] / v, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
+                'dtype': 'f32', 'data': 'synthetic',
+                'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 3x800x800 images, backbone + neck + '
+                                       'head + decode + NMS (conf 0.001, IoU 0.65, max_det 300); plain PyTorch modules on the host cores'},
+                'cpu_baseline': {'value': v, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                                 'sample': f'{n} images 3x800x800 per step, fp32 plain PyTorch modules + torchvision deform_conv2d + NMS',
+                                 'cpu': model, 'os_cpu_count': cores},
+                'e2e': {'value': v, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+        return
     if args.impl == 'reference':
         if rank == 0:
             model, cores = cpu_info()
@@ -535,6 +595,13 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline')
     res = {'c1': run_c1, 'c2': run_c2, 'c4': run_c4}[args.workload](args, rank, world, local)
+    if args.workload == 'c4' and not args.profile:
+        # the second half of the metric: the KAD-Conv operator alone (c1), timed in the same run
+        import copy
+        a1 = copy.copy(args); a1.steps = 20; a1.warmup = 3; a1.profile = True
+        op = run_c1(a1, rank, world, local)
+        res['kadconv_op'] = {'workload': op['config']['workload'], 'us_per_op': op['us_per_op'], 'feature_maps_per_s': op['value'],
+                             'roofline': op['roofline']}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             model, cores = cpu_info()

@@ -8,7 +8,7 @@
 //   warps 0-7 epilogue (TMEM -> bias/activation -> NHWC store; warps w and w+4 share a TMEM lane quadrant and split
 //   the columns), warp 8 MMA issuer, warp 9 TMA.
 // The op is HBM-bound at the detector's shapes (K <= 512): the design goal is to keep enough bytes
-// in flight, which the 4-stage ring and the double-buffered accumulator do.
+// in flight, which a ring of 4 to 10 stages (as many as fit beside the weight tile) and the double-buffered accumulator do.
 #include "kad_common.cuh"
 #include "kad_sm100.cuh"
 
@@ -17,10 +17,10 @@ namespace {
 using namespace sm100;
 
 constexpr int GBM = 128;
-constexpr int GSTAGES = 4;
+constexpr int GMAX_STAGES = 10;      // ring depth is chosen per shape: as many stages as fit (narrow outputs get a deeper ring)
 constexpr int G_A_BYTES = GBM * 128;
 constexpr int G_THREADS = 320;
-constexpr int G_EPI_WARPS = 8, G_WARP_MMA = 8, G_WARP_TMA = 9;
+constexpr int G_EPI_WARPS = 8, G_WARP_MMA = 8;      // warp 9 issues the TMA loads
 constexpr int G_ACC_COLS = 256;
 
 struct GemmParams {
@@ -29,10 +29,11 @@ struct GemmParams {
     int nt;            // output-channel tile (multiple of 16, <= 256)
     int n_tiles, m_tiles, ksteps;
     int b_stage_bytes;
+    int stages;
 };
 
 struct GemmBars {
-    uint64_t full[GSTAGES], empty[GSTAGES];
+    uint64_t full[GMAX_STAGES], empty[GMAX_STAGES];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
@@ -48,6 +49,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     unsigned char* sa = smem;
+    const int GSTAGES = p.stages;
     unsigned char* sb = smem + GSTAGES * G_A_BYTES;
     GemmBars* bars = reinterpret_cast<GemmBars*>(sb + GSTAGES * p.b_stage_bytes);
     volatile int* abort_flag = &bars->abort_flag;
@@ -103,9 +105,15 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             uint4 w;
                             T* h = reinterpret_cast<T*>(&w);
                             if (p.act == KAD_ACT_SILU) {
-                                // the result is rounded to 16 bits: the fast exponential / division (about 1e-6 relative) is ample
+                                // x * sigmoid(x) = x * (0.5 * tanh(x / 2) + 0.5): one special-function instruction per element (the
+                                // exponential + division form needs two, and this epilogue would then be bound by that unit);
+                                // tanh.approx is good to about 5e-4 relative, the result is rounded to 16 bits anyway
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) h[e] = from_f<T>(__fdividef(a[e], 1.f + __expf(-a[e])));
+                                for (int e = 0; e < 8; ++e) {
+                                    float th;
+                                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * a[e]));
+                                    h[e] = from_f<T>(a[e] * fmaf(0.5f, th, 0.5f));
+                                }
                             } else if (p.act == KAD_ACT_RELU) {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) h[e] = from_f<T>(fmaxf(a[e], 0.f));
@@ -125,16 +133,15 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t idesc = instr_desc_f16(p.fmt, p.nt);
         const uint32_t a_base = smem_u32(sa), b_base = smem_u32(sb);
         int it = 0;
-        long long is = 0;
+        int slot = 0; uint32_t phase = 0;          // ring position (wrap counters: no division in this loop)
         bool ok = true;
         for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { greport(p.status, 2, it); break; }
             tc_fence_after();
             const uint32_t tacc = tmem_base + (uint32_t)(buf * G_ACC_COLS);
-            for (int s = 0; s < p.ksteps; ++s, ++is) {
-                const int slot = (int)(is % GSTAGES);
-                if (!mbar_wait(&bars->full[slot], (uint32_t)((is / GSTAGES) & 1), abort_flag)) { greport(p.status, 3, s); ok = false; break; }
+            for (int s = 0; s < p.ksteps; ++s) {
+                if (!mbar_wait(&bars->full[slot], phase, abort_flag)) { greport(p.status, 3, s); ok = false; break; }
                 if (lane == 0) {
                     const uint32_t aaddr = a_base + slot * G_A_BYTES, baddr = b_base + slot * p.b_stage_bytes;
                     // K beyond the tensor extent is zero-filled in both operands, so a full stage is always safe
@@ -146,6 +153,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (s == p.ksteps - 1) umma_commit(&bars->acc_full[buf]);
                 }
                 __syncwarp();
+                if (++slot == GSTAGES) { slot = 0; phase ^= 1u; }
             }
         }
     } else {
@@ -153,20 +161,22 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tma_prefetch_desc(&map_a);
             tma_prefetch_desc(&map_b);
             long long is = 0;
+            int slot = 0; uint32_t phase = 0;
             bool ok = true;
             const uint32_t tx = (uint32_t)(G_A_BYTES + p.nt * 128);
             for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 const long long mt = tile / p.n_tiles;
                 const int n0 = (int)(tile - mt * p.n_tiles) * p.nt;
                 for (int s = 0; s < p.ksteps; ++s, ++is) {
-                    const int slot = (int)(is % GSTAGES);
-                    if (!mbar_wait(&bars->empty[slot], (uint32_t)(((is / GSTAGES) & 1) ^ 1), abort_flag)) { greport(p.status, 4, s); ok = false; break; }
+                    if (!mbar_wait(&bars->empty[slot], phase ^ 1u, abort_flag)) { greport(p.status, 4, s); ok = false; break; }
                     mbar_arrive_expect_tx(&bars->full[slot], tx);
                     tma_load_2d(sa + slot * G_A_BYTES, &map_a, s * 64, (int)(mt * GBM), &bars->full[slot]);
                     tma_load_2d(sb + slot * p.b_stage_bytes, &map_b, s * 64, n0, &bars->full[slot]);
+                    if (++slot == GSTAGES) { slot = 0; phase ^= 1u; }
                 }
             }
             if (!ok || *abort_flag) {
+                // the copies already issued must land before the block may exit
                 for (int i = 0; i < GSTAGES && i < is; ++i) {
                     long long j = is - 1 - i;
                     mbar_wait(&bars->full[j % GSTAGES], (uint32_t)((j / GSTAGES) & 1), abort_flag);
@@ -231,7 +241,12 @@ extern "C" int kad_gemm1x1_bias_act(const void* x, const void* w, const float* b
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(KAD_ERR_CUDA, "tensor map for w failed (CUresult %d)", (int)r);
     }
-    size_t smem = (size_t)GSTAGES * (G_A_BYTES + p.b_stage_bytes) + sizeof(GemmBars) + (size_t)n_tiles * nt * 4 + 1024 + 128;
+    // as many stages as fit in ~200 KB (4 for 256 output channels, 10 for 32): HBM-bound shapes need the bytes in flight
+    const size_t fixed = sizeof(GemmBars) + (size_t)n_tiles * nt * 4 + 1024 + 128;
+    int stages = (int)((200 * 1024 - fixed) / (size_t)(G_A_BYTES + p.b_stage_bytes));
+    stages = stages < 2 ? 2 : (stages > GMAX_STAGES ? GMAX_STAGES : stages);
+    p.stages = stages;
+    size_t smem = (size_t)stages * (G_A_BYTES + p.b_stage_bytes) + fixed;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
