@@ -1,17 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the KAD-Conv inference hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c4] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel] [--impl ours|reference]
 
-Prints ONE JSON line (rank 0). Workloads (BASELINE.json configs):
-  c1  KAD-Conv operator: DSC 256->256, [16,256,100,100] fp16, offsets N(0,2) px, mask given
-      (gather + tcgen05 implicit GEMM). One step = one pass over the batch of 16 feature maps.
-  c4  KAD-CNet-S detector, fp16, 3x800x800 synthetic images, batch 64 sharded over the ranks,
-      backbone + neck + head + NMS. One step = one pass over the 64 images.
-`value` is whole-job images/s with inputs resident in HBM; `e2e` is the same metric through the
-public Python API with pinned-host inputs and a host read of the result inside the timed region.
-`--impl reference` times the CPU oracle port (plain PyTorch + torchvision on the host cores) on a
-bounded sample of the same workload.
+Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloads (BASELINE.json configs):
+  c4  (default) KAD-CNet-S detector, fp16, 64 uint8 3x800x800 synthetic images per step sharded over the ranks:
+      backbone + neck + head + decode + NMS. `value` = images/s with the images resident in HBM; `e2e` = the same
+      through the public Python API from pinned host images, detections read back, both copies inside the timed
+      region; `roofline` = the kernel with the largest share of the forward timed alone; `kadconv_op` = the c1
+      measurement below, taken in the same run (the second half of the metric: op microseconds + % of roofline).
+  c1  KAD-Conv operator alone: DSC 256->256, [16,256,100,100] fp16, offsets N(0,2) px, mask given (gather +
+      tcgen05 implicit GEMM). One step = one pass over the batch of 16 feature maps.
+  c2  bf16 KADConv(128) at 200x200 + avg-pool + 1x1 GEMM+SiLU + SE, with a per-kernel-group table.
+  c4-kernel  the detector's dominant kernel alone (small enough to profile).
+`--impl reference` times the plain PyTorch modules + torchvision (what the reference's raw backend executes) on the
+host cores on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -546,12 +549,23 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4'],
+    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel'],
                     help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
     ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
     args = ap.parse_args()
+    # stdout carries exactly one JSON line: anything libraries print while they initialise (NCCL's version banner) goes to stderr
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(obj), flush=True)
+        os.dup2(2, 1)
+
     rank, world, local = dist_setup(args.gpus)
 
     if args.impl == 'reference' and args.workload == 'c4':
@@ -562,7 +576,7 @@ def main():
                 ips, n, dt = c4_cpu_sample()
                 vals.append(ips)
             v = statistics.median(vals)
-            print(json.dumps({
+            emit(({
                 'impl': 'reference', 'metric': 'KAD-CNet-S 800x800 images/s', 'value': v, 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
                 'warmup': args.warmup, 'ms_per_step': 1e3 * C4['images'] / v, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
                 'dtype': 'f32', 'data': 'synthetic',
@@ -582,7 +596,7 @@ def main():
                 vals.append(ips)
             v = statistics.median(vals)
             sample = f'{n} feature maps [1,256,100,100] of the c1 batch per step, fp32, torchvision.ops.deform_conv2d'
-            print(json.dumps({
+            emit(({
                 'impl': 'reference', 'metric': 'KAD-Conv op (DSC 256->256 @100x100 fp16) feature maps/s', 'value': v, 'unit': 'images/s',
                 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * C1['B'] / v, 'higher_is_better': True,
                 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
@@ -594,6 +608,14 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline')
+    if args.workload == 'c4-kernel':
+        # the detector's dominant kernel alone (what the `roofline` object of the c4 line is measured on); small enough for ncu
+        device = torch.device('cuda', local); torch.cuda.set_device(device)
+        dom = c4_dominant_kernel(device, args.mini_batch, torch.cuda.current_stream(), n=max(3, min(args.steps, 20)))
+        if rank == 0:
+            emit(({'metric': 'dsc_mma_kernel us per launch', 'value': dom['us'], 'unit': 'us', 'shape': dom['shape'],
+                              'algorithmic_bytes': dom['bytes'], 'gb_per_s': dom['gbs'], 'gpu_launches': max(3, min(args.steps, 20))}))
+        return
     res = {'c1': run_c1, 'c2': run_c2, 'c4': run_c4}[args.workload](args, rank, world, local)
     if args.workload == 'c4' and not args.profile:
         # the second half of the metric: the KAD-Conv operator alone (c1), timed in the same run
@@ -606,20 +628,20 @@ def main():
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             model, cores = cpu_info()
             if args.workload == 'c2':
-                print(json.dumps(res))
+                emit(res)
                 return
             if args.workload == 'c4':
                 ips, n, dt = c4_cpu_sample()
                 res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                                        'sample': f'{n} images 3x800x800 in {dt:.1f} s, fp32 plain PyTorch modules + torchvision deform_conv2d + NMS',
                                        'cpu': model, 'os_cpu_count': cores}
-                print(json.dumps(res))
+                emit(res)
                 return
             ips, n, dt = c1_cpu_sample()
             res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                                    'sample': f'{n} of the 16 c1 feature maps in {dt:.1f} s, fp32, torchvision.ops.deform_conv2d (the call DSC.forward makes)',
                                    'cpu': model, 'os_cpu_count': cores}
-        print(json.dumps(res))
+        emit(res)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
