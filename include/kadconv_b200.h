@@ -166,7 +166,8 @@ int kad_lcsa_mask(const float* rowsum, const float* colsum,
 
 /* LCSA steps 1 + 2 from the partial sums of kad_pyramid_project (no second pass over the branch tensor): the sums over
  * tiles are finished here (rowsum float32 [B][H][C] is written as a by-product), then the mask as in kad_lcsa_mask.
- * Works on 128 consecutive pixels per block, so narrow feature maps keep their lanes busy.
+ * Works on 128 consecutive pixels per block, so narrow feature maps keep their lanes busy. scratch: float32
+ * [(B + 1) * W * Cp] with Cp = C rounded up to a multiple of 4, 16-byte aligned.
  * kad_lcsa_mask_from_partials_supported: C <= 256 and the per-row operands fit shared memory. */
 int kad_lcsa_mask_from_partials_supported(int H, int W, int C);
 int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles, const float* colpart, int n_row_groups,

@@ -148,7 +148,8 @@ __global__ void __launch_bounds__(256)
 lcsa_prep_partials_kernel(const float* __restrict__ rowpart, int nct, const float* __restrict__ colpart, int nrg,
                           const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ bn_m,
                           const float* __restrict__ bn_a, float* __restrict__ A, float* __restrict__ Sm, float* __restrict__ rowsum,
-                          int H, int W, int C) {
+                          int H, int W, int C, int Cp) {
+    // A [B][W][Cp], Sm [W][Cp] (channels innermost, padded to a multiple of 4: the mask kernel reads them as float4)
     extern __shared__ float colsum_s[];          // [PREP_COLS + 10][C], column w0 - 5 first
     const int b = blockIdx.y, t = threadIdx.x;
     const int w0 = blockIdx.x * PREP_COLS, nw = min(PREP_COLS, W - w0);
@@ -171,21 +172,25 @@ lcsa_prep_partials_kernel(const float* __restrict__ rowpart, int nct, const floa
     }
     __syncthreads();
     const float invH = 1.f / (float)H;
-    for (int e = t; e < nw * C; e += 256) {
-        const int c = e / nw, w = w0 + (e - c * nw);
-        float conv = 0.f, S = 0.f;
+    for (int e = t; e < nw * Cp; e += 256) {
+        const int wl = e / Cp, c = e - wl * Cp, w = w0 + wl;
+        float av = 0.f, sv = 0.f;
+        if (c < C) {
+            float conv = 0.f, S = 0.f;
 #pragma unroll
-        for (int k = 0; k < 11; ++k) {
-            const int ww = w + k - 5;
-            if (ww >= 0 && ww < W) {
-                const float wk = w1[c * 11 + k];
-                conv = fmaf(wk, colsum_s[(ww - (w0 - 5)) * C + c] * invH, conv);
-                S += wk;
+            for (int k = 0; k < 11; ++k) {
+                const int ww = w + k - 5;
+                if (ww >= 0 && ww < W) {
+                    const float wk = w1[c * 11 + k];
+                    conv = fmaf(wk, colsum_s[(ww - (w0 - 5)) * C + c] * invH, conv);
+                    S += wk;
+                }
             }
+            const float m = bn_m[c];
+            av = (conv + b1[c]) * m + bn_a[c]; sv = S * m;
         }
-        const float m = bn_m[c];
-        A[((size_t)b * C + c) * W + w] = (conv + b1[c]) * m + bn_a[c];
-        if (b == 0) Sm[(size_t)c * W + w] = S * m;
+        A[((size_t)b * W + w) * Cp + c] = av;
+        if (b == 0) Sm[(size_t)w * Cp + c] = sv;
     }
 }
 
@@ -195,21 +200,21 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                       const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
-                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int mask_f32) {
+                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int mask_f32) {
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.y, t = threadIdx.x, HW = H * W;
     const int p0 = blockIdx.x * 128, p1 = min(HW, p0 + 128);
     const int r_lo = p0 / W, nrows = (p1 - 1) / W - r_lo + 1;
-    float* sw3 = sm;                     // [C][12] 1x1 weights of the 9 outputs, pad 0
-    float* rm = sw3 + 12 * C;            // [nrows][C][12] row means of rows h-5..h+5 (0 outside the image), pad 0
-    float* sw2 = rm + nrows * 12 * C;    // [nrows][C][12] 11x1 taps (0 for rows outside the image), slot 11 = bias b2
+    float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
+    float* rm = sw3 + 12 * Cp;           // [nrows][Cp][12] row means of rows h-5..h+5 (0 outside the image), pad 0
+    float* sw2 = rm + nrows * 12 * Cp;   // [nrows][Cp][12] 11x1 taps (0 for rows outside the image), slot 11 = bias b2
     const float invW = 1.f / (float)W;
-    for (int e = t; e < 12 * C; e += 128) { const int c = e / 12, k = e - c * 12; sw3[e] = k < 9 ? w3[k * C + c] : 0.f; }
-    for (int e = t; e < nrows * 12 * C; e += 128) {
-        const int r = e / (12 * C), rem = e - r * 12 * C, c = rem / 12, k = rem - c * 12, hh = r_lo + r + k - 5;
-        const bool in = k < 11 && hh >= 0 && hh < H;
+    for (int e = t; e < 12 * Cp; e += 128) { const int c = e / 12, k = e - c * 12; sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f; }
+    for (int e = t; e < nrows * 12 * Cp; e += 128) {
+        const int r = e / (12 * Cp), rem = e - r * 12 * Cp, c = rem / 12, k = rem - c * 12, hh = r_lo + r + k - 5;
+        const bool in = k < 11 && hh >= 0 && hh < H && c < C;
         rm[e] = in ? rowsum[((size_t)b * H + hh) * C + c] * invW : 0.f;
-        sw2[e] = in ? w2[c * 11 + k] : (k == 11 ? b2[c] : 0.f);
+        sw2[e] = in ? w2[c * 11 + k] : ((k == 11 && c < C) ? b2[c] : 0.f);
     }
     __syncthreads();
     const int p = p0 + t;
@@ -218,24 +223,34 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     float logit[9];
 #pragma unroll
     for (int j = 0; j < 9; ++j) logit[j] = b3[j];
-    const float4* rm4 = reinterpret_cast<const float4*>(rm + (size_t)r * 12 * C);
-    const float4* w24 = reinterpret_cast<const float4*>(sw2 + (size_t)r * 12 * C);
+    const float4* rm4 = reinterpret_cast<const float4*>(rm + (size_t)r * 12 * Cp);
+    const float4* w24 = reinterpret_cast<const float4*>(sw2 + (size_t)r * 12 * Cp);
     const float4* w34 = reinterpret_cast<const float4*>(sw3);
-    for (int c = 0; c < C; ++c) {
-        const float a = A[((size_t)b * C + c) * W + w], s = Sm[(size_t)c * W + w];
-        const float4 r0 = rm4[3 * c], r1 = rm4[3 * c + 1], r2 = rm4[3 * c + 2];
-        const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
-        float v = u2.w;           // bias of the 11x1 convolution
-        v = fmaf(u0.x, fmaxf(fmaf(r0.x, s, a), 0.f), v); v = fmaf(u0.y, fmaxf(fmaf(r0.y, s, a), 0.f), v);
-        v = fmaf(u0.z, fmaxf(fmaf(r0.z, s, a), 0.f), v); v = fmaf(u0.w, fmaxf(fmaf(r0.w, s, a), 0.f), v);
-        v = fmaf(u1.x, fmaxf(fmaf(r1.x, s, a), 0.f), v); v = fmaf(u1.y, fmaxf(fmaf(r1.y, s, a), 0.f), v);
-        v = fmaf(u1.z, fmaxf(fmaf(r1.z, s, a), 0.f), v); v = fmaf(u1.w, fmaxf(fmaf(r1.w, s, a), 0.f), v);
-        v = fmaf(u2.x, fmaxf(fmaf(r2.x, s, a), 0.f), v); v = fmaf(u2.y, fmaxf(fmaf(r2.y, s, a), 0.f), v);
-        v = fmaf(u2.z, fmaxf(fmaf(r2.z, s, a), 0.f), v);
-        const float4 q0 = w34[3 * c], q1 = w34[3 * c + 1], q2 = w34[3 * c + 2];
-        logit[0] = fmaf(q0.x, v, logit[0]); logit[1] = fmaf(q0.y, v, logit[1]); logit[2] = fmaf(q0.z, v, logit[2]);
-        logit[3] = fmaf(q0.w, v, logit[3]); logit[4] = fmaf(q1.x, v, logit[4]); logit[5] = fmaf(q1.y, v, logit[5]);
-        logit[6] = fmaf(q1.z, v, logit[6]); logit[7] = fmaf(q1.w, v, logit[7]); logit[8] = fmaf(q2.x, v, logit[8]);
+    // this pixel's column terms for all channels: contiguous, read four channels at a time (no dependent load per channel)
+    const float4* A4 = reinterpret_cast<const float4*>(A + ((size_t)b * W + w) * Cp);
+    const float4* S4 = reinterpret_cast<const float4*>(Sm + (size_t)w * Cp);
+#pragma unroll 2
+    for (int c4 = 0; c4 < (Cp >> 2); ++c4) {
+        const float4 av = __ldg(A4 + c4), sv = __ldg(S4 + c4);
+        const float aa[4] = {av.x, av.y, av.z, av.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            const int c = 4 * c4 + j4;
+            const float a = aa[j4], s = ss[j4];
+            const float4 r0 = rm4[3 * c], r1 = rm4[3 * c + 1], r2 = rm4[3 * c + 2];
+            const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
+            float v = u2.w;           // bias of the 11x1 convolution (0 for a padding channel, whose weights are 0 as well)
+            v = fmaf(u0.x, fmaxf(fmaf(r0.x, s, a), 0.f), v); v = fmaf(u0.y, fmaxf(fmaf(r0.y, s, a), 0.f), v);
+            v = fmaf(u0.z, fmaxf(fmaf(r0.z, s, a), 0.f), v); v = fmaf(u0.w, fmaxf(fmaf(r0.w, s, a), 0.f), v);
+            v = fmaf(u1.x, fmaxf(fmaf(r1.x, s, a), 0.f), v); v = fmaf(u1.y, fmaxf(fmaf(r1.y, s, a), 0.f), v);
+            v = fmaf(u1.z, fmaxf(fmaf(r1.z, s, a), 0.f), v); v = fmaf(u1.w, fmaxf(fmaf(r1.w, s, a), 0.f), v);
+            v = fmaf(u2.x, fmaxf(fmaf(r2.x, s, a), 0.f), v); v = fmaf(u2.y, fmaxf(fmaf(r2.y, s, a), 0.f), v);
+            v = fmaf(u2.z, fmaxf(fmaf(r2.z, s, a), 0.f), v);
+            const float4 q0 = w34[3 * c], q1 = w34[3 * c + 1], q2 = w34[3 * c + 2];
+            logit[0] = fmaf(q0.x, v, logit[0]); logit[1] = fmaf(q0.y, v, logit[1]); logit[2] = fmaf(q0.z, v, logit[2]);
+            logit[3] = fmaf(q0.w, v, logit[3]); logit[4] = fmaf(q1.x, v, logit[4]); logit[5] = fmaf(q1.y, v, logit[5]);
+            logit[6] = fmaf(q1.z, v, logit[6]); logit[7] = fmaf(q1.w, v, logit[7]); logit[8] = fmaf(q2.x, v, logit[8]);
+        }
     }
     const size_t o = ((size_t)b * HW + p) * 9;
 #pragma unroll
@@ -808,7 +823,7 @@ extern "C" int kad_lcsa_mask(const float* rowsum, const float* colsum,
 extern "C" int kad_lcsa_mask_from_partials_supported(int H, int W, int C) {
     if (H <= 0 || W <= 0 || C <= 0) return 0;
     const int nrows = (127 / W + 2) < H ? (127 / W + 2) : H;
-    return C <= 256 && (size_t)(2 * nrows + 1) * 12 * C * 4 <= 96 * 1024;
+    return C <= 256 && (size_t)(2 * nrows + 1) * 12 * ((C + 3) & ~3) * 4 <= 96 * 1024;
 }
 
 extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles, const float* colpart, int n_row_groups,
@@ -821,19 +836,21 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
     if (!kad_lcsa_mask_from_partials_supported(H, W, C))
         return fail(KAD_ERR_UNSUPPORTED, "kad_lcsa_mask_from_partials: C = %d, W = %d exceed the shared-memory staging", C, W);
     cudaStream_t st = (cudaStream_t)stream;
+    const int Cp = (C + 3) & ~3;          // scratch: A [B][W][Cp] then Sm [W][Cp]
+    KAD_CHECK_ARG((uintptr_t)scratch % 16 == 0, "kad_lcsa_mask_from_partials: scratch must be 16-byte aligned");
     float* A = scratch;
-    float* Sm = scratch + (size_t)B * W * C;
+    float* Sm = scratch + (size_t)B * W * Cp;
     lcsa_prep_partials_kernel<<<dim3((W + PREP_COLS - 1) / PREP_COLS, B), 256, sizeof(float) * (size_t)(PREP_COLS + 10) * C, st>>>(
-        rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C);
+        rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C, Cp);
     const int nrows = (127 / W + 2) < H ? (127 / W + 2) : H;
-    const size_t smem = sizeof(float) * (size_t)(2 * nrows + 1) * 12 * C;
+    const size_t smem = sizeof(float) * (size_t)(2 * nrows + 1) * 12 * Cp;
     KAD_DISPATCH_DTYPE(dtype, {
         auto kern = lcsa_mask_flat_kernel<T>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "lcsa_mask smem attribute: %s", cudaGetErrorString(e));
         }
-        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, mask_f32);
+        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32);
     });
     KAD_CHECK_LAUNCH("lcsa_mask_from_partials");
     return KAD_OK;

@@ -51,7 +51,7 @@ BranchWs plan_branch(size_t base, int B, int h, int w, int c, size_t es, int gap
     p.cols = o; o = align_up(o + (size_t)B * w * c * 4);
     p.rowpart = o; o = align_up(o + (size_t)B * h * nct * c * 4);     // partial sums of the pyramid kernel (nct = 0: unused)
     p.colpart = o; o = align_up(o + (size_t)B * nrg * w * c * 4);
-    p.scratch = o; o = align_up(o + ((size_t)B * w * c + (size_t)w * c) * 4);
+    p.scratch = o; o = align_up(o + ((size_t)B + 1) * w * ((c + 3) & ~3) * 4);
     p.mask = o; o = align_up(o + (size_t)B * h * w * 9 * 4);
     p.offset = o; o = align_up(o + (size_t)B * h * w * 18 * 4);
     p.y = o; o = align_up(o + (size_t)B * h * w * c * es);

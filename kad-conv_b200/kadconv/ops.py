@@ -466,7 +466,7 @@ def lcsa_mask_from_partials(rowpart, colpart, prm, dtype, mask_f32=False):
     B, H, nct, C = rowpart.shape
     nrg, W = colpart.shape[1], colpart.shape[2]
     dev = rowpart.device
-    scratch = torch.empty(B * W * C + W * C, dtype=torch.float32, device=dev)
+    scratch = torch.empty((B + 1) * W * ((C + 3) // 4 * 4), dtype=torch.float32, device=dev)
     rowsum = torch.empty((B, H, C), dtype=torch.float32, device=dev)
     mask = torch.empty((B, H, W, 9), dtype=torch.float32 if mask_f32 else dtype, device=dev)
     _abi.check(_abi.load().kad_lcsa_mask_from_partials(
