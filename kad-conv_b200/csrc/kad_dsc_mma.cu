@@ -75,7 +75,7 @@ template <typename T, int NTP, int ALIGN>
 __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsigned char* smem, const uint32_t (&so)[4], const uint32_t (&vm)[4],
                                            uint32_t zoff, const uint2* __restrict__ Bs, int KC, int Cin, int W, int lane) {
     const int t = lane & 3;
-#pragma unroll 1
+#pragma unroll 3
     for (int k = 0; k < 9; ++k) {
         const int step = ((k / 3 - 1) * W + (k % 3 - 1)) * Cin * 2;
         uint32_t q[4];
@@ -298,17 +298,26 @@ dsc_mma_kernel(const MmaParams p) {
                         if (__any_sync(0xffffffffu, out)) slow |= 1u << kk;
                     }
                     __syncwarp();
+                    if (slow == 0) {
+                        // the common case, unrolled over the three taps so that the loads of one tap overlap the MMAs of the previous
+#pragma unroll
+                        for (int kk = 0; kk < 3; ++kk)
+#pragma unroll
+                            for (int mt = 0; mt < 2; ++mt)
+                                deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, 3 * r + kk, KC, Cin, lane);
+                    } else {
 #pragma unroll 1
-                    for (int kk = 0; kk < 3; ++kk) {
-                        const int k = 3 * r + kk;
-                        if ((slow >> kk) & 1u) {
+                        for (int kk = 0; kk < 3; ++kk) {
+                            const int k = 3 * r + kk;
+                            if ((slow >> kk) & 1u) {
 #pragma unroll
-                            for (int mt = 0; mt < 2; ++mt)
-                                deform_tap<T, NT, ALIGN, true>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
-                        } else {
+                                for (int mt = 0; mt < 2; ++mt)
+                                    deform_tap<T, NT, ALIGN, true>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                            } else {
 #pragma unroll
-                            for (int mt = 0; mt < 2; ++mt)
-                                deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                                for (int mt = 0; mt < 2; ++mt)
+                                    deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                            }
                         }
                     }
                 }
