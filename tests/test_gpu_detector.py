@@ -116,3 +116,31 @@ def test_engine_uint8_input_equals_float_input(golden_dir):
     with torch.no_grad():
         yr = raw(img.float() / 255)[0]
     assert rel_err(y8.float(), yr.float()) <= 2e-2 and rel_err(yf.float(), yr.float()) <= 2e-2
+
+
+def test_engine_at_the_full_benchmark_size(golden_dir):
+    """800x800 (the size bench.py runs, too large for the CPU oracle in a test): the fp16 engine on raw uint8 images
+    against the plain fp32 modules executed on the GPU (library kernels only), and the batched NMS kernel against the
+    reference-order NMS on the same predictions. The graph backend replays the same result."""
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression, non_max_suppression_device
+    from kadconv import ops
+    g, sd = _sd(golden_dir)
+    img = seeding.seeded_input((2, 3, 800, 800), seed=21, kind='image').cuda()
+    raw = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
+    with torch.no_grad():
+        ref = raw(img.float() / 255)[0].float()
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    y, _ = fast(img)
+    torch.cuda.synchronize(); ops.check_status(img.device)
+    assert y.shape == ref.shape == (2, 24, 13125)
+    assert rel_err(y[:, :4].float(), ref[:, :4]) <= 1e-2          # boxes (pixels)
+    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 2e-2          # class scores
+    graph = kadcnet.load_model(None, 'graph', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    yg, _ = graph(img)
+    yg2, _ = graph(img)
+    assert torch.equal(yg, yg2) and rel_err(yg.float(), y.float()) <= 1e-3
+    dets = non_max_suppression_device(y, 0.25, 0.65, max_det=300)
+    dets_ref = non_max_suppression(y, 0.25, 0.65, max_det=300)
+    for d, r in zip(dets, dets_ref):
+        assert abs(d.shape[0] - r.shape[0]) <= 2 and match_fraction(d.cpu(), r.cpu().float()) >= 0.97
