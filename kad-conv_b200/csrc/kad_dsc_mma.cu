@@ -29,7 +29,6 @@ namespace kad {
 namespace {
 
 constexpr int MMA_WARPS = 8;
-constexpr int MMA_MAX_BLOCKS_PER_IMAGE = 64;
 constexpr int OFF_PITCH = 19;           // floats per pixel of the staged offsets (18, padded against bank conflicts)
 constexpr int NT_OFF = 3;               // n-tiles of the offset convolution (18 outputs -> 24)
 

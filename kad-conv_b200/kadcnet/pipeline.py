@@ -1,0 +1,83 @@
+"""Streaming inference: host image batches in, per-image detections out, with the copies overlapped.
+
+The counterpart of the loop in the reference's inference script (KAD-CNet/inference/infer_dior.py:39-60: load a batch,
+`/255`, model, non_max_suppression, collect), arranged for throughput on one GPU: the host-to-device copy of batch i+1
+runs on a copy stream while batch i is in the forward graph, the detections come back as one padded tensor plus counts
+(one device-to-host copy per batch, no per-image synchronisation), and the host only waits for batch i-1 while batch i
+is running. There is no CPU path: the model must be a B200 engine (`load_model(..., backend='optimized')`).
+"""
+import torch
+
+from kadconv import ops
+
+from .runtime import StaticGraph
+
+
+class DetectionPipeline:
+    """pipeline = DetectionPipeline(fast_model, (mb, 3, H, W)); for dets in pipeline.run(batches): ...
+
+    `batches`: an iterable of uint8 tensors [mb,3,H,W] in pinned host memory (or already on the device).
+    Yields, per batch and in order, a list of mb float32 tensors [n_i, 6] (x1, y1, x2, y2, confidence, class) on the host.
+    """
+
+    def __init__(self, fast_model, batch_shape, conf_thres=0.25, iou_thres=0.45, max_det=300, device=None):
+        self.device = torch.device(device) if device is not None else fast_model.device
+        if self.device.type != 'cuda':
+            raise RuntimeError('DetectionPipeline needs a CUDA device (there is no CPU path)')
+        self.conf, self.iou, self.max_det = conf_thres, iou_thres, max_det
+        self.shape = tuple(batch_shape)
+        mb = self.shape[0]
+        with torch.cuda.device(self.device):
+            self.stage = [torch.empty(self.shape, dtype=torch.uint8, device=self.device) for _ in range(2)]
+            self.graph = StaticGraph(lambda u8: fast_model(u8)[0], self.stage[0])
+            self.copy_stream = torch.cuda.Stream(self.device)
+            self.out_dets = [torch.empty((mb, max_det, 6), dtype=torch.float32).pin_memory() for _ in range(2)]
+            self.out_counts = [torch.empty((mb,), dtype=torch.int32).pin_memory() for _ in range(2)]
+            self.h2d_done = [torch.cuda.Event() for _ in range(2)]
+            self.stage_free = [torch.cuda.Event() for _ in range(2)]
+            self.result_ready = [torch.cuda.Event() for _ in range(2)]
+
+    def _upload(self, batch, slot):
+        if tuple(batch.shape) != self.shape or batch.dtype != torch.uint8:
+            raise ValueError(f'expected a uint8 batch of shape {self.shape}, got {tuple(batch.shape)} {batch.dtype}')
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.stage_free[slot])        # the previous user of this staging buffer has consumed it
+            self.stage[slot].copy_(batch, non_blocking=True)
+            self.h2d_done[slot].record(self.copy_stream)
+
+    def _collect(self, slot):
+        self.result_ready[slot].synchronize()
+        dets, counts = self.out_dets[slot], self.out_counts[slot].tolist()
+        return [dets[i, :n].clone() for i, n in enumerate(counts)]
+
+    @torch.no_grad()
+    def run(self, batches):
+        main = torch.cuda.current_stream(self.device)
+        for ev in self.stage_free:
+            ev.record(main)
+        it = iter(batches)
+        nxt = next(it, None)
+        if nxt is None:
+            return
+        self._upload(nxt, 0)
+        i, pending = 0, None
+        while nxt is not None:
+            slot = i & 1
+            following = next(it, None)
+            if following is not None:
+                self._upload(following, slot ^ 1)                      # overlaps the forward below
+            main.wait_event(self.h2d_done[slot])
+            self.graph.input.copy_(self.stage[slot], non_blocking=True)
+            self.stage_free[slot].record(main)
+            self.graph.graph.replay()
+            dets, counts = ops.nms_batched(self.graph.output, self.conf, self.iou, self.max_det)
+            if pending is not None:                                    # results of the batch before this one (its slot is `slot ^ 1`)
+                yield self._collect(pending)
+            self.out_dets[slot].copy_(dets, non_blocking=True)
+            self.out_counts[slot].copy_(counts, non_blocking=True)
+            self.result_ready[slot].record(main)
+            pending = slot
+            nxt = following
+            i += 1
+        yield self._collect(pending)
+        ops.check_status(self.device)

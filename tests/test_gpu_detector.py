@@ -144,3 +144,24 @@ def test_engine_at_the_full_benchmark_size(golden_dir):
     dets_ref = non_max_suppression(y, 0.25, 0.65, max_det=300)
     for d, r in zip(dets, dets_ref):
         assert abs(d.shape[0] - r.shape[0]) <= 2 and match_fraction(d.cpu(), r.cpu().float()) >= 0.97
+
+
+def test_streaming_pipeline_matches_direct_calls(golden_dir):
+    """DetectionPipeline (copies overlapped with the forward graph, padded detections + counts) returns, batch by batch and
+    in order, what the direct call + non_max_suppression_device returns."""
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression_device
+    g, sd = _sd(golden_dir)
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    batches = [seeding.seeded_input((2, 3, 160, 192), seed=30 + i, kind='image').pin_memory() for i in range(5)]
+    pipe = kadcnet.DetectionPipeline(fast, (2, 3, 160, 192), 0.25, 0.65, 300)
+    got = list(pipe.run(batches))
+    assert len(got) == 5
+    for b, dets in zip(batches, got):
+        ref = non_max_suppression_device(fast(b.cuda())[0], 0.25, 0.65, max_det=300)
+        assert len(dets) == 2
+        for d, r in zip(dets, ref):
+            assert not d.is_cuda and d.shape == r.shape and torch.equal(d, r.cpu())
+    assert list(pipe.run([])) == []
+    again = list(pipe.run(batches[:1]))
+    assert all(torch.equal(a, b) for a, b in zip(again[0], got[0]))
