@@ -70,9 +70,11 @@ __device__ __forceinline__ void stage_weights(uint2* dst, const float* __restric
 
 // Ordinary 3x3 convolution of this lane's four accumulator rows over all taps and chunks, out of the staged rows.
 // so[j] = shared-memory address of row j's pixel, vm[j] = which of its 9 neighbours lie inside the image.
-template <typename T, int NTP, int ALIGN>
+// KCT: the number of 16-channel chunks when it is known at compile time (1 or 2: the detector's widths), 0 = use KCr.
+template <typename T, int NTP, int ALIGN, int KCT>
 __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsigned char* smem, const uint32_t (&so)[4], const uint32_t (&vm)[4],
-                                           uint32_t zoff, const uint2* __restrict__ Bs, int KC, int Cin, int W, int lane) {
+                                           uint32_t zoff, const uint2* __restrict__ Bs, int KCr, int Cin, int W, int lane) {
+    const int KC = KCT ? KCT : KCr;
     const int t = lane & 3;
 #pragma unroll 3
     for (int k = 0; k < 9; ++k) {
@@ -80,7 +82,7 @@ __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsign
         uint32_t q[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) q[j] = ((vm[j] >> k) & 1u) ? so[j] + step : zoff;
-#pragma unroll 1
+#pragma unroll (KCT ? KCT : 1)
         for (int kc = 0; kc < KC; ++kc) {
             const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
             uint2 bf[NTP];
@@ -99,9 +101,10 @@ __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsign
 
 // One tap of the deformable pass for one 16-row tile: A = corner weight * gathered channels, four corners, all chunks.
 // SLOW: some address in the warp carries the OUTSIDE flag and is read from global memory instead.
-template <typename T, int NT, int ALIGN, bool SLOW>
+template <typename T, int NT, int ALIGN, bool SLOW, int KCT>
 __device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned char* smem, const unsigned char* gimg, const uint4* tw, const uint4* ta,
-                                           int row0, const uint2* __restrict__ Bs, int k, int KC, int Cin, int lane) {
+                                           int row0, const uint2* __restrict__ Bs, int k, int KCr, int Cin, int lane) {
+    const int KC = KCT ? KCT : KCr;
     const int t = lane & 3;
     uint32_t w[2][4], a[2][4];
 #pragma unroll
@@ -110,7 +113,7 @@ __device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned c
         w[h][0] = wq.x; w[h][1] = wq.y; w[h][2] = wq.z; w[h][3] = wq.w;
         a[h][0] = aq.x; a[h][1] = aq.y; a[h][2] = aq.z; a[h][3] = aq.w;
     }
-#pragma unroll 1
+#pragma unroll (KCT ? KCT : 1)
     for (int kc = 0; kc < KC; ++kc) {
         const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
         uint2 bf[NT];
@@ -134,12 +137,12 @@ __device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned c
     }
 }
 
-template <typename T, int NT, int MODE, int ALIGN>      // MODE 0 plain, 1 deform, 2 fused
+template <typename T, int NT, int MODE, int ALIGN, int KCT>      // MODE 0 plain, 1 deform, 2 fused
 __global__ void __launch_bounds__(MMA_THREADS, NT <= 4 ? 2 : 1)
 dsc_mma_kernel(const MmaParams p) {
     constexpr int COP = NT * 8;
     extern __shared__ __align__(16) unsigned char smem_mma[];
-    const int KC = p.KC;
+    const int KC = KCT ? KCT : p.KC;
     uint2* Bs = reinterpret_cast<uint2*>(smem_mma);                                   // [9][KC][NT][32]
     uint2* Bo = Bs + 9 * KC * NT * 32;                                                // [9][KC][3][32]   (fused)
     unsigned char* cur = reinterpret_cast<unsigned char*>(Bo + (MODE == 2 ? 9 * KC * NT_OFF * 32 : 0));
@@ -237,7 +240,7 @@ dsc_mma_kernel(const MmaParams p) {
                     for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
             if (MODE == 0) {
-                plain_pass<T, NT, ALIGN>(acc, smem_mma, so, vm, zoff, Bs, KC, Cin, W, lane);
+                plain_pass<T, NT, ALIGN, KCT>(acc, smem_mma, so, vm, zoff, Bs, KC, Cin, W, lane);
             } else {
                 if (MODE == 2) {
                     // offset convolution of the warp's 32 pixels -> shared memory [32][18]
@@ -248,7 +251,7 @@ dsc_mma_kernel(const MmaParams p) {
                         for (int nt = 0; nt < NT_OFF; ++nt)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) oacc[mt][nt][i] = 0.f;
-                    plain_pass<T, NT_OFF, ALIGN>(oacc, smem_mma, so, vm, zoff, Bo, KC, Cin, W, lane);
+                    plain_pass<T, NT_OFF, ALIGN, KCT>(oacc, smem_mma, so, vm, zoff, Bo, KC, Cin, W, lane);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -260,7 +263,7 @@ dsc_mma_kernel(const MmaParams p) {
                             }
                         }
                 }
-#pragma unroll 1
+#pragma unroll (KCT ? 3 : 1)
                 for (int r = 0; r < 3; ++r) {
                     __syncwarp();                              // readers of the previous row's table are done; offsets are visible
                     uint32_t slow = 0;                         // bit kk: some lane's sample of tap kk leaves the staged rows
@@ -303,7 +306,7 @@ dsc_mma_kernel(const MmaParams p) {
                         for (int kk = 0; kk < 3; ++kk)
 #pragma unroll
                             for (int mt = 0; mt < 2; ++mt)
-                                deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, 3 * r + kk, KC, Cin, lane);
+                                deform_tap<T, NT, ALIGN, false, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, 3 * r + kk, KC, Cin, lane);
                     } else {
 #pragma unroll 1
                         for (int kk = 0; kk < 3; ++kk) {
@@ -311,11 +314,11 @@ dsc_mma_kernel(const MmaParams p) {
                             if ((slow >> kk) & 1u) {
 #pragma unroll
                                 for (int mt = 0; mt < 2; ++mt)
-                                    deform_tap<T, NT, ALIGN, true>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                                    deform_tap<T, NT, ALIGN, true, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
                             } else {
 #pragma unroll
                                 for (int mt = 0; mt < 2; ++mt)
-                                    deform_tap<T, NT, ALIGN, false>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
+                                    deform_tap<T, NT, ALIGN, false, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
                             }
                         }
                     }
@@ -415,11 +418,11 @@ inline size_t window_smem(int H, int W, int Cin, int margin) {
 }
 constexpr size_t SMEM_ONE_BLOCK = 224 * 1024, SMEM_TWO_BLOCKS = 112 * 1024;
 
-template <typename T, int NT, int MODE>
+template <typename T, int NT, int MODE, int KCT>
 int launch_mma_align(const MmaParams& p, dim3 grid, size_t smem, cudaStream_t st) {
 #define KAD_MMA_LAUNCH(A)                                                                                             \
     {                                                                                                                 \
-        auto kern = dsc_mma_kernel<T, NT, MODE, A>;                                                                   \
+        auto kern = dsc_mma_kernel<T, NT, MODE, A, KCT>;                                                              \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_mma smem attribute: %s", cudaGetErrorString(e));         \
         kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
@@ -431,9 +434,13 @@ int launch_mma_align(const MmaParams& p, dim3 grid, size_t smem, cudaStream_t st
 
 template <typename T, int NT>
 int launch_mma_mode(const MmaParams& p, int mode, dim3 grid, size_t smem, cudaStream_t st) {
-    if (mode == 0) return launch_mma_align<T, NT, 0>(p, grid, smem, st);
-    if (mode == 1) return launch_mma_align<T, NT, 1>(p, grid, smem, st);
-    return launch_mma_align<T, NT, 2>(p, grid, smem, st);
+    if (mode == 0) return launch_mma_align<T, NT, 0, 0>(p, grid, smem, st);
+    if (mode == 1) return launch_mma_align<T, NT, 1, 0>(p, grid, smem, st);
+    // the fused kernel at the detector's widths (<= 16 channels: NT 2, one chunk; 17-24 channels: NT 3, two chunks) is
+    // compiled with the chunk count as a constant: index arithmetic folds and the chunk loops unroll
+    if (NT == 2 && p.KC == 1) return launch_mma_align<T, NT, 2, (NT == 2 ? 1 : 0)>(p, grid, smem, st);
+    if (NT == 3 && p.KC == 2) return launch_mma_align<T, NT, 2, (NT == 3 ? 2 : 0)>(p, grid, smem, st);
+    return launch_mma_align<T, NT, 2, 0>(p, grid, smem, st);
 }
 
 template <typename T>
