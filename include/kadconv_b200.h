@@ -281,6 +281,20 @@ int kad_gemm1x1_bias_act(const void* x, const void* w, const float* bias, void* 
                          long long M, int K, int N, int ldx, int ldy, int act, int dtype,
                          int* status, void* stream);
 
+/* 3x3 convolution (padding 1, stride 1 or 2, dilation 1, one group) as a tcgen05 implicit GEMM with bias and activation:
+ *   y[b, yo, xo, n] = act( sum_{ky,kx,c} x[b, s*yo+ky-1, s*xo+kx-1, c] * w[n, ky*3+kx, c] + bias[n] ).
+ * Replaces Conv.forward_fuse for k = 3 (KAD-CNet/models/common.py:56-57 after fuse_conv_and_bn,
+ * utils/torch_utils.py:244-265), AConv's convolution (common.py:60-67) and the 3x3 convolutions of DDetect
+ * (models/yolo.py:95-100); the reference runs them through cuDNN.
+ *   x NHWC [B][H][W][ldx] dtype (Cin valid channels from the pointer on, ldx >= Cin, ldx % 8 == 0),
+ *   w dtype [Cout][9][Cin] (tap = ky*3+kx), bias float32 [Cout] or NULL,
+ *   y NHWC [B][Ho][Wo][ldy] dtype with Ho = (H-1)/s+1, Wo = (W-1)/s+1 (Cout channels written from the pointer on).
+ * Requires dtype f16/bf16, Cin % 8 == 0, Cout % 8 == 0. status: 4 ints, zero on entry, non-zero if a wait gave up. */
+int kad_conv3x3_tc_supported(int Cin, int Cout, int stride, int dtype);
+int kad_conv3x3_bias_act(const void* x, const void* w, const float* bias, void* y,
+                         int B, int H, int W, int Cin, int Cout, int stride, int ldx, int ldy, int act, int dtype,
+                         int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,21 +53,35 @@ class _Conv1x1:
 
 
 class _ConvKxK:
-    """3x3 (or grouped / strided) convolution through the library on a channels_last view, without bias; the bias and
-    the SiLU are applied in place by one kadconv kernel. `cin_pad` zero-pads the input channels of the weight (the
-    first layer reads the image padded from 3 to 8 channels so that a tensor-core kernel can be chosen)."""
+    """3x3 convolution + bias + SiLU. Padding 1, stride 1 or 2, channel counts that are multiples of 8: the tcgen05
+    implicit GEMM of this package (grouped convolutions as the equivalent dense one), reading and writing channel
+    slices in place. Anything else (the first layer on a float image, other kernel sizes): the library convolution on a
+    channels_last view without bias, then one kadconv kernel for bias + SiLU. `cin_pad` zero-pads the input channels of
+    the weight (a float image is padded from 3 to 8 channels)."""
 
     def __init__(self, conv_mod, dtype, device, cin_pad=None):
         conv = conv_mod.conv if hasattr(conv_mod, 'conv') else conv_mod
         w = conv.weight.detach().to(device, dtype)
         if cin_pad is not None and cin_pad > w.shape[1]:
             w = F.pad(w, (0, 0, 0, 0, 0, cin_pad - w.shape[1]))
-        self.w = w.contiguous(memory_format=torch.channels_last)
         self.b = conv.bias.detach().float().contiguous().to(device)
         self.stride, self.padding, self.groups = conv.stride, conv.padding, conv.groups
         self.act = ops.ACT_SILU if (hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)) else ops.ACT_NONE
+        cin = w.shape[1] * conv.groups
+        self.own = (conv.kernel_size == (3, 3) and conv.padding == (1, 1) and conv.dilation == (1, 1) and conv.stride in ((1, 1), (2, 2))
+                    and conv.groups <= 8 and ops.conv3x3_supported(cin, conv.out_channels, conv.stride[0], dtype))
+        if self.own:
+            self.w = ops.pack_conv3x3_weight(w, dtype, groups=conv.groups).to(device)
+            self.cin = cin
+        else:
+            self.w = w.contiguous(memory_format=torch.channels_last)
 
-    def __call__(self, x, out=None, out_coff=0):
+    def __call__(self, x, out=None, out_coff=0, in_coff=0):
+        if self.own:
+            return ops.conv3x3_bias_act(x, self.w, self.b, act=self.act, stride=self.stride[0], in_coff=in_coff, cin=self.cin,
+                                        out=out, out_coff=out_coff)
+        if in_coff or x.shape[-1] != self.w.shape[1] * self.groups:
+            x = x[..., in_coff:in_coff + self.w.shape[1] * self.groups].contiguous()
         y = _nhwc(F.conv2d(_nchw_view(x), self.w, None, self.stride, self.padding, 1, self.groups))
         if out is None:
             return ops.bias_act_(y, self.b, self.act)
@@ -126,9 +140,14 @@ class FastDetector(torch.nn.Module):
             def elan(x):
                 cat = torch.empty(x.shape[:3] + (sum(widths),), dtype=x.dtype, device=x.device)
                 cv1(x, out=cat, out_coff=0)
-                y2 = cv2(cat[..., half:widths[0]].contiguous())
-                cat[..., widths[0]:widths[0] + widths[1]].copy_(y2)
-                cv3(y2, out=cat, out_coff=widths[0] + widths[1])
+                if isinstance(cv2, _ConvKxK) and isinstance(cv3, _ConvKxK):
+                    # the 3x3 convolutions read their input slice of the concatenation and write their own slice
+                    cv2(cat, in_coff=half, out=cat, out_coff=widths[0])
+                    cv3(cat, in_coff=widths[0], out=cat, out_coff=widths[0] + widths[1])
+                else:
+                    y2 = cv2(cat[..., half:widths[0]].contiguous())
+                    cat[..., widths[0]:widths[0] + widths[1]].copy_(y2)
+                    cv3(y2, out=cat, out_coff=widths[0] + widths[1])
                 return cv4(cat)
             return elan
         if isinstance(m, M.RepNCSPELAN4_KADC):

@@ -89,6 +89,9 @@ SIGNATURES = {
     'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
     'kad_gemm1x1_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p]),
+    'kad_conv3x3_tc_supported': (c_int, [c_int, c_int, c_int, c_int]),
+    'kad_conv3x3_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -332,6 +332,50 @@ def gemm1x1_bias_act_raw(src, shape, w, bias, act, k, out=None, out_coff=0):
     return out
 
 
+def conv3x3_supported(cin, cout, stride, dtype):
+    return dtype in (torch.float16, torch.bfloat16) and bool(_abi.load().kad_conv3x3_tc_supported(cin, cout, stride, _DT[dtype]))
+
+
+def pack_conv3x3_weight(weight, dtype, groups=1):
+    """Conv2d weight [Cout, Cin/groups, 3, 3] -> [Cout, 9, Cin] in `dtype` (tap-major, channels innermost). A grouped
+    convolution becomes the equivalent dense one (zeros outside each group's block)."""
+    cout, cg = weight.shape[:2]
+    w = weight.detach().float().permute(0, 2, 3, 1).reshape(cout, 9, cg)
+    if groups > 1:
+        dense = w.new_zeros((cout, 9, cg * groups))
+        og = cout // groups
+        for g in range(groups):
+            dense[g * og:(g + 1) * og, :, g * cg:(g + 1) * cg] = w[g * og:(g + 1) * og]
+        w = dense
+    return w.to(dtype).contiguous()
+
+
+def conv3x3_bias_act(x, w, bias=None, act=ACT_SILU, stride=1, in_coff=0, cin=None, out=None, out_coff=0):
+    """3x3 convolution, padding 1, on tensor cores. x [B,H,W,Cx] NHWC (channels [in_coff, in_coff+cin) are read),
+    w [Cout,9,cin] in x.dtype (pack_conv3x3_weight), bias float32 [Cout]. Writes out[..., out_coff:out_coff+Cout] when
+    `out` [B,Ho,Wo,Cy] is given."""
+    x = _cuda(x, 'x'); w = _cuda(w, 'w')
+    B, H, W, Cx = x.shape
+    N, _, K = w.shape
+    if cin is not None and cin != K:
+        raise ValueError(f'conv3x3_bias_act: weight has {K} input channels, cin = {cin}')
+    Ho, Wo = (H - 1) // stride + 1, (W - 1) // stride + 1
+    if out is None:
+        out = torch.empty((B, Ho, Wo, N), dtype=x.dtype, device=x.device)
+        dst, ldy = out, N
+    else:
+        if tuple(out.shape[:3]) != (B, Ho, Wo):
+            raise ValueError(f'conv3x3_bias_act: out has shape {tuple(out.shape)}, expected [{B},{Ho},{Wo},*]')
+        ldy = out.shape[-1]
+        dst = out.view(-1)[out_coff:]
+    src = x.view(-1)[in_coff:] if in_coff else x
+    bptr = _ptr(_f32(bias, 'bias')) if bias is not None else None
+    _abi.check(_abi.load().kad_conv3x3_bias_act(ctypes.c_void_p(src.data_ptr()), _ptr(w), bptr, ctypes.c_void_p(dst.data_ptr()),
+                                                B, H, W, K, N, stride, Cx, ldy, act, dtype_code(x), _ptr(status_word(x.device)), _stream()),
+               'kad_conv3x3_bias_act')
+    return out
+
+
 def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0):
     """pred [B,4+nc,A] (DDetect's y) -> (dets [B,max_det,6] float32, counts [B] int32), all on the device, one launch."""
     pred = _cuda(pred, 'pred')

@@ -183,6 +183,52 @@ def test_gemm1x1_slices_in_place():
     assert out[:, :16].abs().max().item() == 0 and out[:, 56:].abs().max().item() == 0
 
 
+@pytest.mark.parametrize('B,Cin,Cout,H,W,stride,dtype', [
+    (2, 64, 64, 25, 25, 1, torch.float16),        # one full-K chunk, 5x25 tiles
+    (3, 144, 144, 20, 30, 1, torch.float16),      # three chunks per tap, the last one 16 wide; H != W
+    (2, 40, 72, 26, 22, 2, torch.float16),        # stride 2, channel counts that are no multiple of 16
+    (2, 72, 144, 19, 23, 2, torch.bfloat16),      # stride 2 on odd sizes (AConv after its 2x2 stride-1 pool)
+    (1, 216, 288, 13, 9, 2, torch.float16),       # two output-channel tiles
+    (2, 32, 32, 7, 131, 1, torch.bfloat16),       # a row wider than a tile
+    (1, 8, 8, 1, 1, 1, torch.float16),            # smallest legal problem
+])
+def test_conv3x3_bias_silu(B, Cin, Cout, H, W, stride, dtype):
+    """3x3 convolution + bias + SiLU on tcgen05 against torch's fp32 conv2d on pre-rounded values (relative 1e-2)."""
+    from kadconv import ops
+    x = round_to(_rand((B, Cin, H, W), 60), dtype); w = round_to(_rand((Cout, Cin, 3, 3), 61, 1.0 / np.sqrt(9 * Cin)), dtype)
+    b = _rand((Cout,), 62, 0.1)
+    ref = F.silu(F.conv2d(x, w, b, stride, 1))
+    y = ops.conv3x3_bias_act(nhwc(x).cuda().to(dtype), ops.pack_conv3x3_weight(w, dtype).cuda(), b.cuda(), act=ops.ACT_SILU, stride=stride)
+    torch.cuda.synchronize()
+    ops.check_status(torch.device('cuda', 0))
+    assert tuple(y.shape) == (B, ref.shape[2], ref.shape[3], Cout)
+    assert rel_err(y.float().cpu().permute(0, 3, 1, 2), ref) <= 1e-2
+
+
+def test_conv3x3_slices_and_groups():
+    """Reads a channel slice, writes a channel slice (concat-free), and runs a grouped convolution as a dense one."""
+    from kadconv import ops
+    dtype = torch.float16
+    x = round_to(_rand((2, 96, 11, 14), 63), dtype); w = round_to(_rand((64, 16, 3, 3), 64, 0.1), dtype)
+    ref = F.conv2d(x[:, 32:96], w, None, 1, 1, 1, 4)
+    out = torch.zeros((2, 11, 14, 80), dtype=dtype, device='cuda')
+    ops.conv3x3_bias_act(nhwc(x).cuda().to(dtype), ops.pack_conv3x3_weight(w, dtype, groups=4).cuda(), None, act=ops.ACT_NONE,
+                         in_coff=32, cin=64, out=out, out_coff=8)
+    torch.cuda.synchronize()
+    ops.check_status(torch.device('cuda', 0))
+    assert rel_err(out[..., 8:72].float().cpu().permute(0, 3, 1, 2), ref) <= 1e-2
+    assert out[..., :8].abs().max().item() == 0 and out[..., 72:].abs().max().item() == 0
+
+
+def test_conv3x3_rejects_bad_arguments():
+    from kadconv import ops
+    x = torch.zeros((1, 4, 4, 12), dtype=torch.float16, device='cuda')
+    with pytest.raises(RuntimeError):
+        ops.conv3x3_bias_act(x, torch.zeros((8, 9, 12), dtype=torch.float16, device='cuda'))      # Cin % 8 != 0
+    with pytest.raises(RuntimeError):
+        ops.conv3x3_bias_act(x.float(), torch.zeros((8, 9, 12), dtype=torch.float32, device='cuda'))   # fp32 has no tensor path
+
+
 def test_avg_pool():
     from kadconv import ops
     for dtype in (torch.float32, torch.bfloat16):
