@@ -314,7 +314,7 @@ def run_c4(args, rank, world, local):
     device = torch.device('cuda', local)
     torch.cuda.set_device(device)
     host_group = torch.distributed.new_group(backend='gloo') if world > 1 else None
-    fast = kadcnet.load_model(None, 'optimized', str(device), randomize=True, seed=0, dtype=torch.float16)
+    fast = kadcnet.load_model(None, 'optimized', str(device), randomize=True, seed=0, dtype=torch.float16, conv3x3=args.conv3x3)
     # the job's images are sharded by batch: rank r owns images [r*64, (r+1)*64) of the step's 64 * world (its share is generated
     # from its own seed, which is what slicing one seeded global batch would amount to)
     a, b = shard_range(C4['images'] * world, rank, world)
@@ -564,6 +564,8 @@ def main():
                     help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
+    ap.add_argument('--conv3x3', default='library', choices=['library', 'tcgen05'],
+                    help="c4: 3x3 convolutions through the library (default, faster at this model's widths) or this package's tcgen05 kernel")
     ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
     args = ap.parse_args()
     # stdout carries exactly one JSON line: anything libraries print while they initialise (NCCL's version banner) goes to stderr

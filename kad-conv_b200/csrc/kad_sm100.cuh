@@ -30,6 +30,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test of a phase (mbarrier.try_wait may suspend the thread; this one never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 // Every wait in these kernels is bounded: after `limit` clock cycles without the phase completing,
 // or as soon as another thread has raised the CTA's abort flag, the wait gives up and returns false.
 // The caller then leaves its loop; nobody spins forever, so a protocol bug cannot hang the GPU.
@@ -124,6 +132,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
     d |= (uint64_t)1 << 46;                        // descriptor version for sm_100
     d |= (uint64_t)2 << 61;                        // layout type: 128-byte swizzle
     return d;
+}
+// The same descriptor as two 32-bit words, for issue loops that advance the start address with 32-bit adds:
+// the high word is a constant, the low word is (address >> 4) plus the fixed leading-offset field.
+__device__ __forceinline__ uint32_t smem_desc_sw128_hi() { return (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t saddr) { return ((saddr & 0x3FFFF) >> 4) | (1u << 16); }
+__device__ __forceinline__ void umma_f16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(desc_hi), "r"(accumulate) : "memory");
 }
 // Instruction descriptor for kind::f16: fp32 accumulator, both operands K-major, M = 128.
 // fmt: 0 = fp16, 1 = bf16.

@@ -53,13 +53,15 @@ class _Conv1x1:
 
 
 class _ConvKxK:
-    """3x3 convolution + bias + SiLU. Padding 1, stride 1 or 2, channel counts that are multiples of 8: the tcgen05
-    implicit GEMM of this package (grouped convolutions as the equivalent dense one), reading and writing channel
-    slices in place. Anything else (the first layer on a float image, other kernel sizes): the library convolution on a
-    channels_last view without bias, then one kadconv kernel for bias + SiLU. `cin_pad` zero-pads the input channels of
-    the weight (a float image is padded from 3 to 8 channels)."""
+    """3x3 convolution + bias + SiLU. Default: the library convolution on a channels_last view without bias, then one
+    kadconv kernel for bias + SiLU (it lands the result in a channel slice of a concatenation). With `own=True`
+    (FastDetector(conv3x3='tcgen05')) and padding 1, stride 1 or 2, channel counts that are multiples of 8: this
+    package's tcgen05 implicit GEMM (grouped convolutions as the equivalent dense one), which reads and writes channel
+    slices in place; it is bit-for-bit deterministic and parity-tested, but at the detector's narrow widths (32-288
+    channels) it is still slower than the library's kernels, so it is not the default. `cin_pad` zero-pads the input
+    channels of the weight (a float image is padded from 3 to 8 channels)."""
 
-    def __init__(self, conv_mod, dtype, device, cin_pad=None):
+    def __init__(self, conv_mod, dtype, device, cin_pad=None, own=False):
         conv = conv_mod.conv if hasattr(conv_mod, 'conv') else conv_mod
         w = conv.weight.detach().to(device, dtype)
         if cin_pad is not None and cin_pad > w.shape[1]:
@@ -68,7 +70,7 @@ class _ConvKxK:
         self.stride, self.padding, self.groups = conv.stride, conv.padding, conv.groups
         self.act = ops.ACT_SILU if (hasattr(conv_mod, 'act') and isinstance(conv_mod.act, torch.nn.SiLU)) else ops.ACT_NONE
         cin = w.shape[1] * conv.groups
-        self.own = (conv.kernel_size == (3, 3) and conv.padding == (1, 1) and conv.dilation == (1, 1) and conv.stride in ((1, 1), (2, 2))
+        self.own = (own and conv.kernel_size == (3, 3) and conv.padding == (1, 1) and conv.dilation == (1, 1) and conv.stride in ((1, 1), (2, 2))
                     and conv.groups <= 8 and ops.conv3x3_supported(cin, conv.out_channels, conv.stride[0], dtype))
         if self.own:
             self.w = ops.pack_conv3x3_weight(w, dtype, groups=conv.groups).to(device)
@@ -88,18 +90,23 @@ class _ConvKxK:
         return ops.bias_act_to(y, self.b, out, out_coff, self.act)    # lands in its slice of a concatenation
 
 
-def _conv(conv_mod, dtype, device):
+def _conv(conv_mod, dtype, device, own3x3=False):
     k = conv_mod.conv.kernel_size
     if k == (1, 1) and conv_mod.conv.groups == 1:
         return _Conv1x1(conv_mod, dtype, device)
-    return _ConvKxK(conv_mod, dtype, device)
+    return _ConvKxK(conv_mod, dtype, device, own=own3x3)
 
 
 class FastDetector(torch.nn.Module):
     """Callable with the model's signature: forward(x[B,3,H,W]) -> (y[B,4+nc,A], [raw P3,P4,P5] as NCHW views)."""
 
-    def __init__(self, model, dtype=torch.float16):
+    def __init__(self, model, dtype=torch.float16, conv3x3='library'):
+        """conv3x3: 'library' (cuDNN through torch, the faster choice at this model's widths) or 'tcgen05' (this
+        package's implicit-GEMM kernel for every 3x3 convolution with padding 1 and stride 1 or 2)."""
         super().__init__()
+        if conv3x3 not in ('library', 'tcgen05'):
+            raise ValueError("conv3x3 must be 'library' or 'tcgen05'")
+        self.own3x3 = conv3x3 == 'tcgen05'
         if any(hasattr(m, 'bn') for m in model.modules() if isinstance(m, M.Conv)):
             raise ValueError('call model.fuse() first: the engine runs the Conv+BN-folded model')
         if model.training:
@@ -126,13 +133,13 @@ class FastDetector(torch.nn.Module):
     def _compile(self, m):
         dt, dev = self.dtype, self.device
         if isinstance(m, M.Conv):
-            c = _ConvKxK(m, dt, dev, cin_pad=8) if (m.i == 0 and m.conv.in_channels < 8 and m.conv.kernel_size != (1, 1)) else _conv(m, dt, dev)
+            c = _ConvKxK(m, dt, dev, cin_pad=8) if (m.i == 0 and m.conv.in_channels < 8 and m.conv.kernel_size != (1, 1)) else _conv(m, dt, dev, self.own3x3)
             return lambda x: c(x)
         if isinstance(m, M.AConv):
-            c = _ConvKxK(m.cv1, dt, dev)
+            c = _ConvKxK(m.cv1, dt, dev, own=self.own3x3)
             return lambda x: c(ops.avg_pool2x2s1(x))
         if isinstance(m, M.ELAN1):
-            cv1, cv2, cv3, cv4 = (_conv(t, dt, dev) for t in (m.cv1, m.cv2, m.cv3, m.cv4))
+            cv1, cv2, cv3, cv4 = (_conv(t, dt, dev, self.own3x3) for t in (m.cv1, m.cv2, m.cv3, m.cv4))
             half = m.c
 
             widths = (m.cv1.conv.out_channels, m.cv2.conv.out_channels, m.cv3.conv.out_channels)
@@ -140,7 +147,7 @@ class FastDetector(torch.nn.Module):
             def elan(x):
                 cat = torch.empty(x.shape[:3] + (sum(widths),), dtype=x.dtype, device=x.device)
                 cv1(x, out=cat, out_coff=0)
-                if isinstance(cv2, _ConvKxK) and isinstance(cv3, _ConvKxK):
+                if isinstance(cv2, _ConvKxK) and isinstance(cv3, _ConvKxK) and cv2.own and cv3.own:
                     # the 3x3 convolutions read their input slice of the concatenation and write their own slice
                     cv2(cat, in_coff=half, out=cat, out_coff=widths[0])
                     cv3(cat, in_coff=widths[0], out=cat, out_coff=widths[0] + widths[1])
@@ -151,9 +158,9 @@ class FastDetector(torch.nn.Module):
                 return cv4(cat)
             return elan
         if isinstance(m, M.RepNCSPELAN4_KADC):
-            cv1, cv4 = _conv(m.cv1, dt, dev), _conv(m.cv4, dt, dev)
-            b2, c2 = self._csp(m.cv2[0]), _conv(m.cv2[1], dt, dev)
-            b3, c3 = self._csp(m.cv3[0]), _conv(m.cv3[1], dt, dev)
+            cv1, cv4 = _conv(m.cv1, dt, dev, self.own3x3), _conv(m.cv4, dt, dev, self.own3x3)
+            b2, c2 = self._csp(m.cv2[0]), _conv(m.cv2[1], dt, dev, self.own3x3)
+            b3, c3 = self._csp(m.cv3[0]), _conv(m.cv3[1], dt, dev, self.own3x3)
             half = m.c
 
             wt, w2, w3 = m.cv1.conv.out_channels, m.cv2[1].conv.out_channels, m.cv3[1].conv.out_channels
@@ -167,7 +174,7 @@ class FastDetector(torch.nn.Module):
                 return cv4(cat)
             return gelan
         if isinstance(m, M.SPPELAN):
-            cv1, cv5 = _conv(m.cv1, dt, dev), _conv(m.cv5, dt, dev)
+            cv1, cv5 = _conv(m.cv1, dt, dev, self.own3x3), _conv(m.cv5, dt, dev, self.own3x3)
 
             def spp(x):
                 ys = [cv1(x)]
@@ -197,7 +204,7 @@ class FastDetector(torch.nn.Module):
     def _csp(self, m):
         """RepNCSP_KADC: cv3(cat(KADConv x n (cv1(x)), cv2(x))); x is read as a channel slice in place."""
         dt, dev = self.dtype, self.device
-        cv1, cv2, cv3 = _conv(m.cv1, dt, dev), _conv(m.cv2, dt, dev), _conv(m.cv3, dt, dev)
+        cv1, cv2, cv3 = _conv(m.cv1, dt, dev, self.own3x3), _conv(m.cv2, dt, dev, self.own3x3), _conv(m.cv3, dt, dev, self.own3x3)
         layers = list(m.m)
 
         def csp(x, in_coff, cin):
@@ -216,8 +223,8 @@ class FastDetector(torch.nn.Module):
 
     def _head(self, m):
         dt, dev = self.dtype, self.device
-        box = [[_ConvKxK(s[0], dt, dev), _ConvKxK(s[1], dt, dev), _ConvKxK(s[2], dt, dev)] for s in m.cv2]
-        cls = [[_ConvKxK(s[0], dt, dev), _ConvKxK(s[1], dt, dev), _ConvKxK(s[2], dt, dev)] for s in m.cv3]
+        box = [[_ConvKxK(s[0], dt, dev, own=self.own3x3), _ConvKxK(s[1], dt, dev, own=self.own3x3), _ConvKxK(s[2], dt, dev, own=self.own3x3)] for s in m.cv2]
+        cls = [[_ConvKxK(s[0], dt, dev, own=self.own3x3), _ConvKxK(s[1], dt, dev, own=self.own3x3), _ConvKxK(s[2], dt, dev, own=self.own3x3)] for s in m.cv3]
         proj = torch.arange(m.reg_max, dtype=torch.float32, device=dev).to(dt).view(1, 1, m.reg_max, 1)
         cache = {}
 

@@ -76,7 +76,7 @@ def _state_dict_from(checkpoint, key):
 
 
 def load_model(weights=None, backend='raw', device='cuda:0', config=None, fuse=True, checkpoint_key='auto',
-               dtype=torch.float16, seed=0, state_dict=None, randomize=False):
+               dtype=torch.float16, seed=0, state_dict=None, randomize=False, conv3x3='library'):
     if backend not in {'raw', 'optimized', 'graph'}:
         raise ValueError(backend)
     numerical_protocol()
@@ -99,7 +99,7 @@ def load_model(weights=None, backend='raw', device='cuda:0', config=None, fuse=T
         raise ValueError('Acceleration requires CUDA')
     if not fuse:
         raise ValueError("the 'optimized' and 'graph' backends run the fused model")
-    fast = FastDetector(model, dtype=dtype)
+    fast = FastDetector(model, dtype=dtype, conv3x3=conv3x3)
     if backend == 'graph':
         fast.forward = graph_forward(fast.forward)
     return fast

@@ -76,6 +76,26 @@ def test_engine_fp16_relative(golden_dir, backend):
     assert rel_err(y[:, 4:].float().cpu(), ref[:, 4:]) <= 1e-2
 
 
+def test_engine_fp16_with_own_conv3x3(golden_dir):
+    """Every 3x3 convolution (stride 1 and 2, grouped head convolutions, ELAN slices) on the package's tcgen05
+    implicit GEMM instead of the library: same relative-1e-2 bar against the fp32 oracle, bit-equal reruns."""
+    import kadcnet
+    from kadconv import ops
+    g, sd = _sd(golden_dir)
+    sd16 = {k: round_to(v, torch.float16) for k, v in sd.items()}
+    img = seeding.seeded_input((2, 3, 160, 192), seed=5, kind='image')
+    x = round_to(img.float() / 255, torch.float16)
+    ref, _ = ko.detector(sd16, x)
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd16, dtype=torch.float16, conv3x3='tcgen05')
+    y, _ = fast(x.cuda().half())
+    y2, _ = fast(x.cuda().half())
+    torch.cuda.synchronize()
+    ops.check_status(torch.device('cuda', 0))
+    assert torch.equal(y, y2)
+    assert rel_err(y[:, :4].float().cpu(), ref[:, :4]) <= 1e-2
+    assert rel_err(y[:, 4:].float().cpu(), ref[:, 4:]) <= 1e-2
+
+
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
 def test_batched_nms_kernel_matches_oracle(golden_dir, dtype):
     """kad_nms_batched against the oracle's greedy NMS on the same prediction tensor (bit-equal boxes and order)."""
