@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the KAD-Conv inference hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel|conv3x3] [--impl ours|reference]
 
 Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloads (BASELINE.json configs):
   c4  (default) KAD-CNet-S detector, fp16, 64 uint8 3x800x800 synthetic images per step sharded over the ranks:
@@ -13,6 +13,7 @@ Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloa
       tcgen05 implicit GEMM). One step = one pass over the batch of 16 feature maps.
   c2  bf16 KADConv(128) at 200x200 + avg-pool + 1x1 GEMM+SiLU + SE, with a per-kernel-group table.
   c4-kernel  the detector's dominant kernel alone (small enough to profile).
+  conv3x3  the detector's 3x3 convolution shapes: this package's tcgen05 kernel next to the library path (table in the line).
 `--impl reference` times the plain PyTorch modules + torchvision (what the reference's raw backend executes) on the
 host cores on a bounded sample of the same workload.
 """
@@ -469,6 +470,58 @@ class OpTimer:
         return out
 
 
+# 3x3 convolutions of KAD-CNet-S at 800x800 (Cin, Cout, stride, input size); the model runs each at batch = mini-batch
+CONV3X3_SHAPES = [(144, 144, 1, 100), (64, 64, 1, 100), (96, 96, 1, 50), (40, 72, 2, 400), (72, 144, 2, 199), (144, 64, 1, 100), (32, 32, 1, 200),
+                  (216, 144, 1, 50), (144, 216, 2, 99), (144, 144, 1, 50), (128, 128, 1, 25), (144, 112, 2, 99), (216, 288, 2, 49), (216, 64, 1, 50),
+                  (288, 144, 1, 25), (216, 144, 2, 49), (144, 144, 1, 25), (288, 64, 1, 25)]
+
+
+def run_conv3x3(args, local):
+    """The detector's 3x3 convolution shapes (+ bias + SiLU, fp16, batch = --mini-batch): this package's tcgen05 kernel next to
+    the library path the engine uses by default (cuDNN convolution + kad_bias_act). --profile: the first shape only, own kernel only."""
+    import torch.nn.functional as F
+    from kadconv import ops
+    device = torch.device('cuda', local); torch.cuda.set_device(device)
+    B, dt = args.mini_batch, torch.float16
+    rows, tot = [], [0.0, 0.0]
+    g = torch.Generator(device='cpu').manual_seed(0)
+    for cin, cout, s, H in (CONV3X3_SHAPES[:1] if args.profile else CONV3X3_SHAPES):
+        x = torch.randn((B, H, H, cin), generator=g).to(device, dt)
+        w = (torch.randn((cout, cin, 3, 3), generator=g) / (9 * cin) ** 0.5).to(device, dt)
+        b = torch.randn((cout,), generator=g).to(device)
+        wp = ops.pack_conv3x3_weight(w, dt).to(device)
+        wl = w.contiguous(memory_format=torch.channels_last)
+
+        def own():
+            return ops.conv3x3_bias_act(x, wp, b, stride=s)
+
+        def lib():
+            return ops.bias_act_(F.conv2d(x.permute(0, 3, 1, 2), wl, None, s, 1).permute(0, 2, 3, 1), b, ops.ACT_SILU)
+        us = []
+        for fn in ((own,) if args.profile else (own, lib)):
+            for _ in range(max(3, args.warmup)):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = max(2, min(args.steps, 20))
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            us.append(1e3 * e0.elapsed_time(e1) / n)
+        Ho = (H - 1) // s + 1
+        flops = 2.0 * 9 * cin * cout * B * Ho * Ho
+        row = {'shape': f'{cin}->{cout} s{s} @{H}', 'own_us': round(us[0], 1), 'own_tflops': round(flops / us[0] / 1e6, 1)}
+        tot[0] += us[0]
+        if len(us) > 1:
+            row.update({'library_us': round(us[1], 1), 'library_tflops': round(flops / us[1] / 1e6, 1)})
+            tot[1] += us[1]
+        rows.append(row)
+    ops.check_status(device)
+    return {'metric': 'KAD-CNet-S 3x3 convolutions + bias + SiLU, us per launch', 'unit': 'us', 'batch': B, 'dtype': 'f16',
+            'total_own_us': round(tot[0], 1), 'total_library_us': round(tot[1], 1) if tot[1] else None, 'shapes': rows}
+
+
 def run_c2(args, rank, world, local):
     import kadconv
     import kadconv.fast as fast
@@ -560,7 +613,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel'],
+    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel', 'conv3x3'],
                     help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
@@ -628,6 +681,11 @@ def main():
         if rank == 0:
             emit(({'metric': 'dsc_mma_kernel us per launch', 'value': dom['us'], 'unit': 'us', 'shape': dom['shape'],
                               'algorithmic_bytes': dom['bytes'], 'gb_per_s': dom['gbs'], 'gpu_launches': max(3, min(args.steps, 20))}))
+        return
+    if args.workload == 'conv3x3':
+        res = run_conv3x3(args, local)
+        if rank == 0:
+            emit(res)
         return
     res = {'c1': run_c1, 'c2': run_c2, 'c4': run_c4}[args.workload](args, rank, world, local)
     if args.workload == 'c4' and not args.profile:
