@@ -270,6 +270,16 @@ int kad_nms_max_anchors(void);
 int kad_nms_batched(const void* pred, int B, int nc, int A, float conf_thres, float iou_thres, int max_det,
                     float max_wh, float* dets, int* counts, int dtype, void* stream);
 
+/* Head decode of one detection scale: distribution-focal-loss expectation, distances to box, sigmoid class scores.
+ * Replaces the inference branch of DDetect.forward (KAD-CNet/models/yolo.py:112-127) with DFL (models/common.py:232-243)
+ * and make_anchors / dist2bbox (utils/tal/anchor_generator.py:8-32); the reference's own fused version is
+ * kadc_head_decode.py:30-88.
+ *   raw NHWC [B][H][W][4*reg_max + nc] dtype (box logits side-major: channel = side*reg_max + bin; then class logits),
+ *   pred [B][4 + nc][A] dtype: this call writes anchors [a_offset, a_offset + H*W) in (y, x) order: centre x, centre y,
+ *   width, height in pixels (cell centre at +0.5, times `stride`), then nc sigmoid scores. fp32 arithmetic. */
+int kad_head_decode(const void* raw, void* pred, int B, int H, int W, int reg_max, int nc, float stride,
+                    int a_offset, int A, int dtype, void* stream);
+
 /* 1x1 convolution as a tcgen05 GEMM with bias and activation, TMA-fed operands:
  *   y[m, n] = act( sum_k x[m, k] * w[n, k] + bias[n] ),  m over B*H*W pixels.
  * Replaces Conv.forward_fuse for k = 1 (KAD-CNet/models/common.py:56-57 after fuse_conv_and_bn,

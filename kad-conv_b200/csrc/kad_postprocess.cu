@@ -132,6 +132,47 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
     if (tid == 0) counts[b] = s_nkept;
 }
 
+// Head decode of one detection scale: raw [B][H][W][4*reg_max + nc] (box distribution logits, then class logits) ->
+// columns [a_offset, a_offset + H*W) of pred [B][4 + nc][A]. One thread per (image, cell): the expectation of the
+// softmax over each side's reg_max bins gives the distances (left, top, right, bottom) from the cell centre
+// (x + 0.5, y + 0.5) in grid units; the box leaves as centre x, centre y, width, height in pixels (times the
+// stride), the classes as sigmoid scores. Arithmetic in fp32, one rounding at the store. A thread reads its cell's
+// contiguous channels, the stores of a warp are contiguous along the anchor axis.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_decode_kernel(const T* __restrict__ raw, T* __restrict__ pred, int B, int H, int W, int reg_max, int nc, float stride,
+                   int a_offset, int A) {
+    const long long cell = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int HW = H * W;
+    if (cell >= (long long)B * HW) return;
+    const int b = (int)(cell / HW), a = (int)(cell - (long long)b * HW);
+    const int y = a / W, x = a - y * W;
+    const int no = 4 * reg_max + nc;
+    const T* src = raw + cell * no;
+    float d[4];
+#pragma unroll
+    for (int side = 0; side < 4; ++side) {
+        const T* v = src + side * reg_max;
+        float m = -INFINITY;
+        for (int j = 0; j < reg_max; ++j) m = fmaxf(m, to_f<T>(v[j]));
+        float den = 0.f, num = 0.f;
+        for (int j = 0; j < reg_max; ++j) {
+            const float e = __expf(to_f<T>(v[j]) - m);
+            den += e; num = fmaf((float)j, e, num);
+        }
+        d[side] = num / den;
+    }
+    const float ax = (float)x + 0.5f, ay = (float)y + 0.5f;
+    const float x1 = ax - d[0], y1 = ay - d[1], x2 = ax + d[2], y2 = ay + d[3];
+    T* dst = pred + (size_t)b * (4 + nc) * A + a_offset + a;
+    dst[0] = from_f<T>(0.5f * (x1 + x2) * stride);
+    dst[(size_t)A] = from_f<T>(0.5f * (y1 + y2) * stride);
+    dst[(size_t)2 * A] = from_f<T>((x2 - x1) * stride);
+    dst[(size_t)3 * A] = from_f<T>((y2 - y1) * stride);
+    const T* cl = src + 4 * reg_max;
+    for (int c = 0; c < nc; ++c) dst[(size_t)(4 + c) * A] = from_f<T>(sigmoidf_(to_f<T>(cl[c])));
+}
+
 }  // namespace
 }  // namespace kad
 
@@ -157,5 +198,21 @@ extern "C" int kad_nms_batched(const void* pred, int B, int nc, int A, float con
         kern<<<B, NMS_THREADS, smem, (cudaStream_t)stream>>>((const T*)pred, nc, A, npow2, conf_thres, iou_thres, max_det, max_wh, dets, counts);
     });
     KAD_CHECK_LAUNCH("nms_kernel");
+    return KAD_OK;
+}
+
+extern "C" int kad_head_decode(const void* raw, void* pred, int B, int H, int W, int reg_max, int nc, float stride,
+                               int a_offset, int A, int dtype, void* stream) {
+    KAD_CHECK_ARG(raw && pred, "kad_head_decode: null pointer");
+    KAD_CHECK_ARG(B > 0 && H > 0 && W > 0 && reg_max > 0 && reg_max <= 64 && nc > 0, "kad_head_decode: bad shape");
+    KAD_CHECK_ARG(a_offset >= 0 && (long long)a_offset + (long long)H * W <= A, "kad_head_decode: anchors [%d, %d) outside [0, %d)",
+                  a_offset, a_offset + H * W, A);
+    const long long cells = (long long)B * H * W;
+    KAD_CHECK_ARG((cells + 127) / 128 < (1ll << 31), "kad_head_decode: too many cells");
+    KAD_DISPATCH_DTYPE(dtype, {
+        head_decode_kernel<T><<<(unsigned)((cells + 127) / 128), 128, 0, (cudaStream_t)stream>>>((const T*)raw, (T*)pred, B, H, W, reg_max, nc,
+                                                                                              stride, a_offset, A);
+    });
+    KAD_CHECK_LAUNCH("head_decode_kernel");
     return KAD_OK;
 }

@@ -9,7 +9,7 @@ contiguous [B,H,W,C] tensor:
     place (the ELAN / CSP `chunk` never copies)
   * 3x3 convolutions, pools, nearest upsampling -> library kernels on channels_last views (outside the
     KAD-Conv hot path; they are the next item to be replaced)
-  * head decode -> the reference's op sequence, so the fp16 rounding points are the same.
+  * head decode -> one kernel per scale (softmax expectation, box, sigmoid) in fp32 with one rounding at the store.
 There is no CPU path: the engine raises on a non-CUDA input.
 """
 import torch
@@ -225,8 +225,7 @@ class FastDetector(torch.nn.Module):
         dt, dev = self.dtype, self.device
         box = [[_ConvKxK(s[0], dt, dev, own=self.own3x3), _ConvKxK(s[1], dt, dev, own=self.own3x3), _ConvKxK(s[2], dt, dev, own=self.own3x3)] for s in m.cv2]
         cls = [[_ConvKxK(s[0], dt, dev, own=self.own3x3), _ConvKxK(s[1], dt, dev, own=self.own3x3), _ConvKxK(s[2], dt, dev, own=self.own3x3)] for s in m.cv3]
-        proj = torch.arange(m.reg_max, dtype=torch.float32, device=dev).to(dt).view(1, 1, m.reg_max, 1)
-        cache = {}
+        strides = [float(v) for v in m.stride]
 
         def head(feats):
             raw = []
@@ -234,22 +233,10 @@ class FastDetector(torch.nn.Module):
                 b = box[i][2](box[i][1](box[i][0](f)))
                 c = cls[i][2](cls[i][1](cls[i][0](f)))
                 raw.append(torch.cat((b, c), -1))                         # [B,H,W,no]
-            B = raw[0].shape[0]
-            key = tuple(tuple(r.shape[1:3]) for r in raw)
-            if key not in cache:
-                fake = [torch.empty((1, 1, h, w), dtype=dt, device=dev) for h, w in key]
-                cache[key] = tuple(t.transpose(0, 1) for t in M.make_anchors(fake, m.stride, 0.5))
-            anchors, strides = cache[key]
-            # the reference's sequence (KAD-CNet/models/yolo.py:112-127), on [B,no,A] with A in (y,x) order
-            allr = torch.cat([r.reshape(B, -1, m.no) for r in raw], 1).transpose(1, 2)
-            bx, cl = allr.split((4 * m.reg_max, m.nc), 1)
-            A = bx.shape[2]
-            d = (bx.reshape(B, 4, m.reg_max, A).softmax(2) * proj).sum(2)
-            lt, rb = d.split(2, 1)
-            a = anchors.unsqueeze(0)
-            x1y1, x2y2 = a - lt, a + rb
-            dbox = torch.cat(((x1y1 + x2y2) / 2, x2y2 - x1y1), 1) * strides
-            return torch.cat((dbox, cl.sigmoid()), 1), [_nchw_view(r) for r in raw]
+            # DFL expectation, dist2bbox and the class sigmoid of the reference's sequence (KAD-CNet/models/yolo.py:112-127)
+            # in one kernel per scale, anchors in (scale, y, x) order
+            y = ops.head_decode(raw, strides, m.reg_max, m.nc)
+            return y, [_nchw_view(r) for r in raw]
         return head
 
     # ---- forward -------------------------------------------------------------------------------

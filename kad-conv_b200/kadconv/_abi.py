@@ -86,6 +86,7 @@ SIGNATURES = {
     'kad_kadconv_forward': (c_int, [POINTER(KadLayerArgs), c_void_p]),
     'kad_nms_max_anchors': (c_int, []),
     'kad_nms_batched': (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]),
+    'kad_head_decode': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),
     'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
     'kad_gemm1x1_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p]),

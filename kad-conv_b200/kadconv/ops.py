@@ -387,6 +387,24 @@ def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0):
     return dets, counts
 
 
+def head_decode(raws, strides, reg_max, nc):
+    """DDetect's inference decode on the device: raws = per-scale [B,H,W,4*reg_max+nc] NHWC tensors, strides = their
+    pixel strides. Returns pred [B, 4+nc, A] (xywh in pixels + sigmoid scores), anchors in (scale, y, x) order."""
+    B = raws[0].shape[0]
+    A = sum(r.shape[1] * r.shape[2] for r in raws)
+    pred = torch.empty((B, 4 + nc, A), dtype=raws[0].dtype, device=raws[0].device)
+    off = 0
+    for r, s in zip(raws, strides):
+        r = _cuda(r, 'raw')
+        _, H, W, no = r.shape
+        if no != 4 * reg_max + nc:
+            raise ValueError(f'head_decode: {no} channels, expected {4 * reg_max + nc}')
+        _abi.check(_abi.load().kad_head_decode(_ptr(r), _ptr(pred), B, H, W, reg_max, nc, ctypes.c_float(float(s)), off, A, dtype_code(r), _stream()),
+                   'kad_head_decode')
+        off += H * W
+    return pred
+
+
 def avg_pool(x, pool):
     """NHWC average pool, kernel = stride = pool, floor mode."""
     x = _cuda(x, 'x')

@@ -229,6 +229,33 @@ def test_conv3x3_rejects_bad_arguments():
         ops.conv3x3_bias_act(x.float(), torch.zeros((8, 9, 12), dtype=torch.float32, device='cuda'))   # fp32 has no tensor path
 
 
+@pytest.mark.parametrize('dtype,tol', [(torch.float32, 1e-5), (torch.float16, 2e-3)])
+def test_head_decode(dtype, tol):
+    """DFL expectation + dist2bbox + sigmoid in one kernel per scale against the reference's op sequence in fp32
+    (KAD-CNet/models/yolo.py:112-127): three scales, non-square maps, anchors in (scale, y, x) order."""
+    from kadconv import ops
+    reg_max, nc, B = 16, 20, 3
+    sizes, strides = [(20, 24), (10, 12), (5, 6)], [8.0, 16.0, 32.0]
+    raws = [round_to(_rand((B, h, w, 4 * reg_max + nc), 70 + i, 2.0), dtype) for i, (h, w) in enumerate(sizes)]
+    # reference sequence on [B, no, A]
+    allr = torch.cat([r.reshape(B, -1, 4 * reg_max + nc) for r in raws], 1).transpose(1, 2)
+    bx, cl = allr.split((4 * reg_max, nc), 1)
+    A = bx.shape[2]
+    d = (bx.reshape(B, 4, reg_max, A).softmax(2) * torch.arange(reg_max, dtype=torch.float32).view(1, 1, reg_max, 1)).sum(2)
+    pts, st = [], []
+    for (h, w), s in zip(sizes, strides):
+        sy, sx = torch.meshgrid(torch.arange(h) + 0.5, torch.arange(w) + 0.5, indexing='ij')
+        pts.append(torch.stack((sx, sy), -1).view(-1, 2)); st.append(torch.full((h * w, 1), s))
+    anc, stv = torch.cat(pts).t().unsqueeze(0), torch.cat(st).t()
+    lt, rb = d.split(2, 1)
+    x1y1, x2y2 = anc - lt, anc + rb
+    ref = torch.cat((torch.cat(((x1y1 + x2y2) / 2, x2y2 - x1y1), 1) * stv, cl.sigmoid()), 1)
+    y = ops.head_decode([r.cuda().to(dtype) for r in raws], strides, reg_max, nc)
+    assert tuple(y.shape) == (B, 4 + nc, A)
+    assert rel_err(y[:, :4].float().cpu(), ref[:, :4]) <= tol
+    assert rel_err(y[:, 4:].float().cpu(), ref[:, 4:]) <= tol
+
+
 def test_avg_pool():
     from kadconv import ops
     for dtype in (torch.float32, torch.bfloat16):
