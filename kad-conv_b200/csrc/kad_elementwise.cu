@@ -257,6 +257,87 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[j]));
 }
 
+// The same mask for column strips: a thread owns LS_R vertically consecutive pixels of one column, so the ReLU'd
+// intermediate t(h) = relu(rowmean(h) * S + A) of the LS_R + 10 rows its 11x1 windows cover is evaluated once and shared
+// by the windows (2 * (LS_R + 10) instead of 22 * LS_R operations per channel), and the staged operands are read once
+// per strip instead of once per pixel. A block covers all W <= 128 columns of groups * LS_R rows of one image.
+constexpr int LS_R = 4;
+template <typename T>
+__global__ void __launch_bounds__(128)
+lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
+                       const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
+                       const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int groups, int mask_f32) {
+    extern __shared__ __align__(16) float sm[];
+    const int b = blockIdx.y, t = threadIdx.x;
+    const int RB = groups * LS_R, P = RB + 12;           // rows per block; row pitch of the staged means (rows h0-5 .. h0+RB+6)
+    const int h0 = blockIdx.x * RB;
+    float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
+    float* sw2 = sw3 + 12 * Cp;          // [Cp][12] 11x1 taps, slot 11 = bias b2
+    float* rm = sw2 + 12 * Cp;           // [Cp][P] row means (0 outside the image; those rows are masked below)
+    const float invW = 1.f / (float)W;
+    for (int e = t; e < 12 * Cp; e += 128) {
+        const int c = e / 12, k = e - c * 12;
+        sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f;
+        sw2[e] = c < C ? (k < 11 ? w2[c * 11 + k] : b2[c]) : 0.f;
+    }
+    for (int e = t; e < Cp * P; e += 128) {
+        const int j = e / Cp, c = e - j * Cp, hh = h0 - 5 + j;       // consecutive threads read consecutive channels
+        rm[c * P + j] = (hh >= 0 && hh < H && c < C) ? rowsum[((size_t)b * H + hh) * C + c] * invW : 0.f;
+    }
+    __syncthreads();
+    const int g = t / W, w = t - g * W;
+    if (g >= groups) return;
+    const int r0 = h0 + g * LS_R;                        // first row of this thread's strip
+    if (r0 >= H) return;
+    uint32_t valid = 0;                                  // bit j: row r0 - 5 + j lies inside the image
+#pragma unroll
+    for (int j = 0; j < LS_R + 10; ++j) valid |= (uint32_t)(r0 - 5 + j >= 0 && r0 - 5 + j < H) << j;
+    float logit[LS_R][9];
+#pragma unroll
+    for (int r = 0; r < LS_R; ++r)
+#pragma unroll
+        for (int j = 0; j < 9; ++j) logit[r][j] = b3[j];
+    const float4* A4 = reinterpret_cast<const float4*>(A + ((size_t)b * W + w) * Cp);
+    const float4* S4 = reinterpret_cast<const float4*>(Sm + (size_t)w * Cp);
+    const float4* w24 = reinterpret_cast<const float4*>(sw2);
+    const float4* w34 = reinterpret_cast<const float4*>(sw3);
+#pragma unroll 1
+    for (int c4 = 0; c4 < (Cp >> 2); ++c4) {
+        const float4 av = __ldg(A4 + c4), sv = __ldg(S4 + c4);
+        const float aa[4] = {av.x, av.y, av.z, av.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            const int c = 4 * c4 + j4;
+            const float a = aa[j4], s = ss[j4];
+            const float4* rm4 = reinterpret_cast<const float4*>(rm + c * P + g * LS_R);
+            float tv[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float4 v4 = rm4[q]; tv[4 * q] = v4.x; tv[4 * q + 1] = v4.y; tv[4 * q + 2] = v4.z; tv[4 * q + 3] = v4.w; }
+#pragma unroll
+            for (int j = 0; j < LS_R + 10; ++j) tv[j] = ((valid >> j) & 1u) ? fmaxf(fmaf(tv[j], s, a), 0.f) : 0.f;
+            const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
+            const float uk[11] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w, u2.x, u2.y, u2.z};
+            const float4 q0 = w34[3 * c], q1 = w34[3 * c + 1], q2 = w34[3 * c + 2];
+#pragma unroll
+            for (int r = 0; r < LS_R; ++r) {
+                float v = u2.w;       // bias of the 11x1 convolution (0 for a padding channel, whose weights are 0 as well)
+#pragma unroll
+                for (int k = 0; k < 11; ++k) v = fmaf(uk[k], tv[r + k], v);
+                logit[r][0] = fmaf(q0.x, v, logit[r][0]); logit[r][1] = fmaf(q0.y, v, logit[r][1]); logit[r][2] = fmaf(q0.z, v, logit[r][2]);
+                logit[r][3] = fmaf(q0.w, v, logit[r][3]); logit[r][4] = fmaf(q1.x, v, logit[r][4]); logit[r][5] = fmaf(q1.y, v, logit[r][5]);
+                logit[r][6] = fmaf(q1.z, v, logit[r][6]); logit[r][7] = fmaf(q1.w, v, logit[r][7]); logit[r][8] = fmaf(q2.x, v, logit[r][8]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < LS_R; ++r) {
+        if (r0 + r >= H) break;
+        const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
+#pragma unroll
+        for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[r][j]));
+    }
+}
+
 // ------------------------------------------------------------------------------ SE
 // Channel means from per-tile sums, by all 256 threads of a block and in a fixed order: K tiles are summed side by side
 // (thread = (tile residue, channel), coalesced), then the K partial sums of a channel are added in order.
@@ -842,6 +923,19 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
     float* Sm = scratch + (size_t)B * W * Cp;
     lcsa_prep_partials_kernel<<<dim3((W + PREP_COLS - 1) / PREP_COLS, B), 256, sizeof(float) * (size_t)(PREP_COLS + 10) * C, st>>>(
         rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C, Cp);
+    // column strips when the map is wide enough in rows and blocks to fill the GPU twice over; else one pixel per thread
+    if (W <= 128) {
+        const int groups = 128 / W, RB = groups * LS_R;
+        const int row_blocks = (H + RB - 1) / RB;
+        const size_t smem_strip = sizeof(float) * (size_t)Cp * (24 + RB + 12);
+        if ((long long)row_blocks * B >= 296 && smem_strip <= 48 * 1024) {
+            KAD_DISPATCH_DTYPE(dtype, {
+                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32);
+            });
+            KAD_CHECK_LAUNCH("lcsa_mask_from_partials (strips)");
+            return KAD_OK;
+        }
+    }
     const int nrows = (127 / W + 2) < H ? (127 / W + 2) : H;
     const size_t smem = sizeof(float) * (size_t)(2 * nrows + 1) * 12 * Cp;
     KAD_DISPATCH_DTYPE(dtype, {

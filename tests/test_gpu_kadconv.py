@@ -73,6 +73,20 @@ def test_16bit_relative(dtype):
     assert rel_err(y, ref) <= 1e-2
 
 
+def test_16bit_many_images_column_strip_mask():
+    """A batch large enough that the LCSA mask of the full-resolution branch runs as column strips (4 rows per
+    thread, shared 11x1 window terms); H != W, the last strip of a column is ragged (52 = 6 * 8 + 4)."""
+    import kadconv
+    dtype = torch.float16
+    layer, sd = _layer(32, 23, dtype=dtype)
+    x = round_to(seeding.seeded_input((48, 32, 52, 50), seed=23), dtype)
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda().to(dtype)).float().cpu()
+    assert rel_err(y, ref) <= 1e-2
+
+
 def test_wide_layer_uses_tensor_path_fp16():
     """KADConv(96): all three branches are 32 channels wide -> the DSCs run on tcgen05."""
     import kadconv
