@@ -415,7 +415,8 @@ def run_c4(args, rank, world, local):
         'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 64 uint8 3x800x800 images per GPU and step '
                                '(the batch is sharded over the ranks, no collective, host gather of the detections), backbone + neck + head + decode + NMS (conf 0.001, IoU 0.65, max_det 300)',
                    'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
-                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)'},
+                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)',
+                   'conv3x3': 'library (cuDNN through torch) + kad_bias_act' if args.conv3x3 == 'library' else 'kad_conv3x3_bias_act (tcgen05)'},
         'roofline': {'bound': 'hbm', 'achieved': dom['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s', 'frac': dom['gbs'] / pk['hbm_gbs'],
                      'traffic': NCU_TRAFFIC['c4_dsc_mma'], 'peak_source': pk['_source'],
                      'kernel': 'dsc_mma_kernel (fused offset convolution + deformable convolution of a KAD-Conv branch), the largest share of the '
