@@ -35,6 +35,7 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
     float2* cmeta = reinterpret_cast<float2*>(craw + NMS_CHUNK);                         // [64] (conf, class)
     unsigned long long* cmask = reinterpret_cast<unsigned long long*>(cmeta + NMS_CHUNK);   // [64] intra-chunk suppression
     unsigned int* csupp = reinterpret_cast<unsigned int*>(cmask + NMS_CHUNK);            // [64] suppressed by a kept box
+    unsigned char* scls = reinterpret_cast<unsigned char*>(csupp + NMS_CHUNK);          // [npow2] best class of every anchor
     __shared__ int s_ncand, s_nkept;
 
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -49,8 +50,10 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
     for (int a = tid; a < npow2; a += NMS_THREADS) {
         unsigned long long key = 0ull;
         if (a < A) {
-            float best = to_f<T>(pb[(size_t)4 * A + a]);
-            for (int c = 1; c < nc; ++c) best = fmaxf(best, to_f<T>(pb[(size_t)(4 + c) * A + a]));
+            // the first maximum wins, as in the reference's argmax over the class scores
+            float best = to_f<T>(pb[(size_t)4 * A + a]); int cls = 0;
+            for (int c = 1; c < nc; ++c) { const float v = to_f<T>(pb[(size_t)(4 + c) * A + a]); if (v > best) { best = v; cls = c; } }
+            scls[a] = (unsigned char)cls;
             if (best > conf_thres) {
                 unsigned int u = __float_as_uint(best);
                 u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -88,15 +91,18 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
             cmask[tid] = 0ull;
             csupp[tid] = tid < nch ? 0u : 1u;
             if (tid < nch) {
-                const int a = (int)(0xFFFFFFFFu - (unsigned int)(keys[c0 + tid] & 0xFFFFFFFFull));
+                const unsigned long long key = keys[c0 + tid];
+                const int a = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
                 // box corners are formed in the storage type, as the reference does before it widens to float32
                 const float cx = to_f<T>(pb[a]), cy = to_f<T>(pb[(size_t)A + a]);
                 const float hw = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)2 * A + a]) * 0.5f)), hh = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)3 * A + a]) * 0.5f));
                 float4 r;
                 r.x = to_f<T>(from_f<T>(cx - hw)); r.y = to_f<T>(from_f<T>(cy - hh));
                 r.z = to_f<T>(from_f<T>(cx + hw)); r.w = to_f<T>(from_f<T>(cy + hh));
-                float best = to_f<T>(pb[(size_t)4 * A + a]); int cls = 0;
-                for (int c = 1; c < nc; ++c) { const float v = to_f<T>(pb[(size_t)(4 + c) * A + a]); if (v > best) { best = v; cls = c; } }
+                // score and class come from the sort key and the per-anchor table of step 1: no second pass over the class scores
+                const unsigned int u = (unsigned int)(key >> 32);
+                const float best = __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+                const int cls = scls[a];
                 const float sh = (float)cls * max_wh;
                 craw[tid] = r;
                 cbox[tid] = make_float4(r.x + sh, r.y + sh, r.z + sh, r.w + sh);
@@ -190,7 +196,8 @@ extern "C" int kad_nms_batched(const void* pred, int B, int nc, int A, float con
         return fail(KAD_ERR_UNSUPPORTED, "kad_nms_batched: %d anchors exceed the %d the in-shared-memory sort holds", A, NMS_MAX_ANCHORS);
     int npow2 = 64;
     while (npow2 < A) npow2 <<= 1;
-    size_t smem = (size_t)npow2 * 8 + (size_t)max_det * 16 + NMS_CHUNK * (16 + 16 + 8 + 8 + 4) + 64;
+    KAD_CHECK_ARG(nc <= 256, "kad_nms_batched: at most 256 classes (the per-anchor class table holds bytes)");
+    size_t smem = (size_t)npow2 * 8 + (size_t)max_det * 16 + NMS_CHUNK * (16 + 16 + 8 + 8 + 4) + (size_t)npow2 + 64;
     KAD_DISPATCH_DTYPE(dtype, {
         auto kern = nms_kernel<T>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
