@@ -580,7 +580,7 @@ def run_c2(args, rank, world, local):
     pk = peaks()
     px = B * H * W
     widths = [C - (C // 3) * 2, C // 3, C // 3]
-    alg = {   # algorithmic bytes per step of each kernel group (formulas: DESIGN.md section 3)
+    alg = {   # algorithmic bytes per step of each kernel group: inputs read once + outputs written once, s bytes per element
         'pool_project': sum(s * (px * C + (px >> (2 * i)) * c) for i, c in enumerate(widths)),
         'avg_pool': s * (px * C + (px // 4) * C), 'gemm1x1_bias_act': s * ((px // 4) * (C + Co) + C * Co),
         'lcsa_mask': sum((px >> (2 * i)) * (s * c + 4 * 9) for i, c in enumerate(widths)),

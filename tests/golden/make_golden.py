@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by running the REFERENCE modules on CPU.
 
-Run in a container that has the reference checkout (default /root/reference, override with
-KAD_REFERENCE_ROOT); the GPU test box does not have it and only reads the committed .npz files.
+Run where the reference checkout is available: set KAD_REFERENCE_ROOT to its path (default: `reference`
+beside this repository). The tests never need it: they only read the committed .npz files.
 
     python tests/golden/make_golden.py
 
@@ -24,7 +24,7 @@ import torchvision
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(os.environ.get('KAD_REFERENCE_ROOT', '/root/reference'))
+REF = Path(os.environ.get('KAD_REFERENCE_ROOT', str(ROOT.parent / 'reference')))
 sys.path.insert(0, str(ROOT))
 from oracle import seeding  # noqa: E402
 
