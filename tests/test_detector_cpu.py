@@ -46,3 +46,20 @@ def test_optimized_backend_refuses_cpu():
     import kadcnet
     with pytest.raises(ValueError):
         kadcnet.load_model(None, 'optimized', 'cpu')
+
+
+def test_conv3x3_weight_packing_host_logic():
+    """pack_conv3x3_weight is host-side layout work: [Cout, Cin/g, 3, 3] -> [Cout, 9, Cin] tap-major; a grouped
+    convolution becomes the dense one with zeros outside each group's block (checked through torch's conv2d on CPU)."""
+    import torch.nn.functional as F
+    from kadconv import ops
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((1, 16, 7, 9), generator=g)
+    w = torch.randn((8, 4, 3, 3), generator=g)
+    packed = ops.pack_conv3x3_weight(w, torch.float32, groups=4)
+    assert tuple(packed.shape) == (8, 9, 16)
+    dense = packed.reshape(8, 3, 3, 16).permute(0, 3, 1, 2).contiguous()        # back to [Cout, Cin, 3, 3]
+    assert torch.allclose(F.conv2d(x, dense, None, 1, 1), F.conv2d(x, w, None, 1, 1, 1, 4), atol=1e-6)
+    plain = ops.pack_conv3x3_weight(w, torch.float16)
+    assert plain.dtype == torch.float16 and tuple(plain.shape) == (8, 9, 4)
+    assert torch.equal(plain[3, 5].float(), w[3, :, 1, 2].half().float())        # tap 5 = (ky 1, kx 2)
