@@ -166,6 +166,25 @@ def test_engine_at_the_full_benchmark_size(golden_dir):
         assert abs(d.shape[0] - r.shape[0]) <= 2 and match_fraction(d.cpu(), r.cpu().float()) >= 0.97
 
 
+def test_own_conv3x3_at_the_full_benchmark_size(golden_dir):
+    """800x800: the engine with every 3x3 convolution on the package's tcgen05 kernel (maps 400x400 ... 25x25, odd
+    199 / 99 / 49 inputs of the stride-2 layers) against the plain fp32 modules on the GPU, same bars as the default engine."""
+    import kadcnet
+    from kadconv import ops
+    g, sd = _sd(golden_dir)
+    img = seeding.seeded_input((2, 3, 800, 800), seed=21, kind='image').cuda()
+    raw = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
+    with torch.no_grad():
+        ref = raw(img.float() / 255)[0].float()
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16, conv3x3='tcgen05')
+    y, _ = fast(img)
+    y2, _ = fast(img)
+    torch.cuda.synchronize(); ops.check_status(img.device)
+    assert torch.equal(y, y2)
+    assert rel_err(y[:, :4].float(), ref[:, :4]) <= 1e-2
+    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 2e-2
+
+
 def test_streaming_pipeline_matches_direct_calls(golden_dir):
     """DetectionPipeline (copies overlapped with the forward graph, padded detections + counts) returns, batch by batch and
     in order, what the direct call + non_max_suppression_device returns."""
