@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the KAD-Conv inference hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel|conv3x3] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel|conv3x3|gemm1x1] [--impl ours|reference]
 
 Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloads (BASELINE.json configs):
   c4  (default) KAD-CNet-S detector, fp16, 64 uint8 3x800x800 synthetic images per step sharded over the ranks:
@@ -13,6 +13,7 @@ Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloa
       tcgen05 implicit GEMM). One step = one pass over the batch of 16 feature maps.
   c2  bf16 KADConv(128) at 200x200 + avg-pool + 1x1 GEMM+SiLU + SE, with a per-kernel-group table.
   c4-kernel  the detector's dominant kernel alone (small enough to profile).
+  gemm1x1  the detector's 1x1 GEMM + bias + SiLU shapes on the tcgen05 GEMM kernel, GB/s against the measured HBM peak.
   conv3x3  the detector's 3x3 convolution shapes: this package's tcgen05 kernel next to the library path (table in the line).
 `--impl reference` times the plain PyTorch modules + torchvision (what the reference's raw backend executes) on the
 host cores on a bounded sample of the same workload.
@@ -523,6 +524,46 @@ def run_conv3x3(args, local):
             'total_own_us': round(tot[0], 1), 'total_library_us': round(tot[1], 1) if tot[1] else None, 'shapes': rows}
 
 
+# fused 1x1 convolutions (Conv k=1 + folded BN + SiLU) of KAD-CNet-S at 800x800: (Cin, Cout, map size)
+GEMM1X1_SHAPES = [(72, 64, 200), (128, 72, 200), (144, 128, 100), (64, 32, 100), (64, 64, 100), (256, 144, 100), (360, 128, 100), (216, 192, 50),
+                  (96, 48, 50), (96, 96, 50), (384, 216, 50), (504, 192, 50), (328, 192, 50), (288, 256, 25), (128, 64, 25), (128, 128, 25),
+                  (512, 288, 25), (288, 128, 25), (432, 256, 25)]
+
+
+def run_gemm1x1(args, local):
+    """The detector's 1x1 GEMM + bias + SiLU shapes (fp16, batch = --mini-batch) on gemm1x1_tc_kernel: microseconds and achieved
+    GB/s of the algorithmic bytes 2*M*(K+N) + 2*K*N against the measured HBM peak. --profile: the (256, 144, 100) shape only."""
+    from kadconv import ops
+    device = torch.device('cuda', local); torch.cuda.set_device(device)
+    B, dt = args.mini_batch, torch.float16
+    peak = peaks(); src = peak['_source']
+    rows, tot, tot_floor = [], 0.0, 0.0
+    g = torch.Generator(device='cpu').manual_seed(0)
+    for K, N, H in ([(256, 144, 100)] if args.profile else GEMM1X1_SHAPES):
+        x = torch.randn((B, H, H, K), generator=g).to(device, dt)
+        w = (torch.randn((N, K), generator=g) / K ** 0.5).to(device, dt)
+        b = torch.randn((N,), generator=g).to(device)
+        for _ in range(max(3, args.warmup)):
+            ops.gemm1x1_bias_act(x, w, b, act=ops.ACT_SILU)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(2, min(args.steps, 20))
+        e0.record()
+        for _ in range(n):
+            ops.gemm1x1_bias_act(x, w, b, act=ops.ACT_SILU)
+        e1.record(); torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / n
+        M = B * H * H
+        nbytes = 2.0 * M * (K + N) + 2.0 * K * N
+        gbs = nbytes / us / 1e3
+        rows.append({'shape': f'{K}->{N} @{H}', 'us': round(us, 1), 'gb_per_s': round(gbs), 'hbm_frac': round(gbs / peak['hbm_gbs'], 3),
+                     'tflops': round(2.0 * M * K * N / us / 1e6, 1)})
+        tot += us; tot_floor += nbytes / peak['hbm_gbs'] / 1e3
+    ops.check_status(device)
+    return {'metric': 'KAD-CNet-S 1x1 GEMM + bias + SiLU, us per launch', 'unit': 'us', 'batch': B, 'dtype': 'f16', 'total_us': round(tot, 1),
+            'hbm_floor_us': round(tot_floor, 1), 'peak_gb_per_s': peak['hbm_gbs'], 'peak_source': src, 'shapes': rows}
+
+
 def run_c2(args, rank, world, local):
     import kadconv
     import kadconv.fast as fast
@@ -614,7 +655,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel', 'conv3x3'],
+    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel', 'conv3x3', 'gemm1x1'],
                     help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
@@ -683,8 +724,8 @@ def main():
             emit(({'metric': 'dsc_mma_kernel us per launch', 'value': dom['us'], 'unit': 'us', 'shape': dom['shape'],
                               'algorithmic_bytes': dom['bytes'], 'gb_per_s': dom['gbs'], 'gpu_launches': max(3, min(args.steps, 20))}))
         return
-    if args.workload == 'conv3x3':
-        res = run_conv3x3(args, local)
+    if args.workload in ('conv3x3', 'gemm1x1'):
+        res = run_conv3x3(args, local) if args.workload == 'conv3x3' else run_gemm1x1(args, local)
         if rank == 0:
             emit(res)
         return

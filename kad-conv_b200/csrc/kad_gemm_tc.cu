@@ -8,7 +8,8 @@
 //   warps 0-7 epilogue (TMEM -> bias/activation -> NHWC store; warps w and w+4 share a TMEM lane quadrant and split
 //   the columns), warp 8 MMA issuer, warp 9 TMA.
 // The op is HBM-bound at the detector's shapes (K <= 512): the design goal is to keep enough bytes
-// in flight, which a ring of 4 to 10 stages (as many as fit beside the weight tile) and the double-buffered accumulator do.
+// in flight, which a ring of 4 to 10 stages (as many as fit beside the weight tile) and the double-buffered accumulator do;
+// the weight tile is loaded once per CTA and stays in shared memory when it fits (it is the same for every M tile).
 #include "kad_common.cuh"
 #include "kad_sm100.cuh"
 
@@ -30,11 +31,13 @@ struct GemmParams {
     int n_tiles, m_tiles, ksteps;
     int b_stage_bytes;
     int stages;
+    int resident;      // 1: all K slices of the weight tile stay in shared memory for the whole kernel (one output-channel tile)
 };
 
 struct GemmBars {
     uint64_t full[GMAX_STAGES], empty[GMAX_STAGES];
     uint64_t acc_full[2], acc_empty[2];
+    uint64_t w_full;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -51,7 +54,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     unsigned char* sa = smem;
     const int GSTAGES = p.stages;
     unsigned char* sb = smem + GSTAGES * G_A_BYTES;
-    GemmBars* bars = reinterpret_cast<GemmBars*>(sb + GSTAGES * p.b_stage_bytes);
+    GemmBars* bars = reinterpret_cast<GemmBars*>(sb + (p.resident ? p.ksteps : GSTAGES) * p.b_stage_bytes);
     volatile int* abort_flag = &bars->abort_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long ntiles = (long long)p.m_tiles * p.n_tiles;
@@ -59,6 +62,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (tid == 0) {
         for (int i = 0; i < GSTAGES; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], G_EPI_WARPS * 32); }
+        mbar_init(&bars->w_full, 1);
         bars->abort_flag = 0;
         mbar_fence_init();
     }
@@ -135,6 +139,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         int it = 0;
         int slot = 0; uint32_t phase = 0;          // ring position (wrap counters: no division in this loop)
         bool ok = true;
+        if (p.resident && !mbar_wait(&bars->w_full, 0, abort_flag)) { greport(p.status, 5, 0); ok = false; }
         for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) { greport(p.status, 2, it); break; }
@@ -143,7 +148,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (int s = 0; s < p.ksteps; ++s) {
                 if (!mbar_wait(&bars->full[slot], phase, abort_flag)) { greport(p.status, 3, s); ok = false; break; }
                 if (lane == 0) {
-                    const uint32_t aaddr = a_base + slot * G_A_BYTES, baddr = b_base + slot * p.b_stage_bytes;
+                    const uint32_t aaddr = a_base + slot * G_A_BYTES, baddr = b_base + (p.resident ? s : slot) * p.b_stage_bytes;
                     // K beyond the tensor extent is zero-filled in both operands, so a full stage is always safe
                     const int kleft = p.K - s * 64;
                     const int nk = kleft >= 64 ? 4 : (kleft + 15) / 16;
@@ -163,7 +168,13 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             long long is = 0;
             int slot = 0; uint32_t phase = 0;
             bool ok = true;
-            const uint32_t tx = (uint32_t)(G_A_BYTES + p.nt * 128);
+            // resident weights: every K slice of the (only) output-channel tile once, on a barrier of its own; the MMA warp
+            // waits for them before its first instruction, so they have landed long before the block can exit
+            if (p.resident) {
+                mbar_arrive_expect_tx(&bars->w_full, (uint32_t)(p.ksteps * p.nt * 128));
+                for (int s = 0; s < p.ksteps; ++s) tma_load_2d(sb + s * p.b_stage_bytes, &map_b, s * 64, 0, &bars->w_full);
+            }
+            const uint32_t tx = (uint32_t)(G_A_BYTES + (p.resident ? 0 : p.nt * 128));
             for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 const long long mt = tile / p.n_tiles;
                 const int n0 = (int)(tile - mt * p.n_tiles) * p.nt;
@@ -171,7 +182,7 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (!mbar_wait(&bars->empty[slot], phase ^ 1u, abort_flag)) { greport(p.status, 4, s); ok = false; break; }
                     mbar_arrive_expect_tx(&bars->full[slot], tx);
                     tma_load_2d(sa + slot * G_A_BYTES, &map_a, s * 64, (int)(mt * GBM), &bars->full[slot]);
-                    tma_load_2d(sb + slot * p.b_stage_bytes, &map_b, s * 64, n0, &bars->full[slot]);
+                    if (!p.resident) tma_load_2d(sb + slot * p.b_stage_bytes, &map_b, s * 64, n0, &bars->full[slot]);
                     if (++slot == GSTAGES) { slot = 0; phase ^= 1u; }
                 }
             }
@@ -243,10 +254,16 @@ extern "C" int kad_gemm1x1_bias_act(const void* x, const void* w, const float* b
     }
     // as many stages as fit in ~200 KB (4 for 256 output channels, 10 for 32): HBM-bound shapes need the bytes in flight
     const size_t fixed = sizeof(GemmBars) + (size_t)n_tiles * nt * 4 + 1024 + 128;
-    int stages = (int)((200 * 1024 - fixed) / (size_t)(G_A_BYTES + p.b_stage_bytes));
+    // Every M tile needs the same weights: when all K slices of the (single) output-channel tile fit beside a ring of at least
+    // four x stages they are loaded once per CTA and stay resident, which halves the L2 -> SM traffic of the typical layer
+    // (the ring then carries x only, and gets deeper); otherwise weights stream through the ring with x.
+    const size_t w_all = (size_t)p.ksteps * p.b_stage_bytes;
+    p.resident = (n_tiles == 1 && w_all + 4 * (size_t)G_A_BYTES + fixed <= 200 * 1024) ? 1 : 0;
+    int stages = p.resident ? (int)((200 * 1024 - fixed - w_all) / (size_t)G_A_BYTES)
+                            : (int)((200 * 1024 - fixed) / (size_t)(G_A_BYTES + p.b_stage_bytes));
     stages = stages < 2 ? 2 : (stages > GMAX_STAGES ? GMAX_STAGES : stages);
     p.stages = stages;
-    size_t smem = (size_t)stages * (G_A_BYTES + p.b_stage_bytes) + fixed;
+    size_t smem = p.resident ? (size_t)stages * G_A_BYTES + w_all + fixed : (size_t)stages * (G_A_BYTES + p.b_stage_bytes) + fixed;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
