@@ -258,8 +258,9 @@ extern "C" int kad_gemm1x1_bias_act(const void* x, const void* w, const float* b
     // four x stages they are loaded once per CTA and stay resident, which halves the L2 -> SM traffic of the typical layer
     // (the ring then carries x only, and gets deeper); otherwise weights stream through the ring with x.
     const size_t w_all = (size_t)p.ksteps * p.b_stage_bytes;
-    p.resident = (n_tiles == 1 && w_all + 4 * (size_t)G_A_BYTES + fixed <= 200 * 1024) ? 1 : 0;
-    int stages = p.resident ? (int)((200 * 1024 - fixed - w_all) / (size_t)G_A_BYTES)
+    const size_t budget = 224 * 1024;      // of the 227 KB a block may have
+    p.resident = (n_tiles == 1 && w_all + 4 * (size_t)G_A_BYTES + fixed <= budget) ? 1 : 0;
+    int stages = p.resident ? (int)((budget - fixed - w_all) / (size_t)G_A_BYTES)
                             : (int)((200 * 1024 - fixed) / (size_t)(G_A_BYTES + p.b_stage_bytes));
     stages = stages < 2 ? 2 : (stages > GMAX_STAGES ? GMAX_STAGES : stages);
     p.stages = stages;
