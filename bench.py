@@ -146,20 +146,49 @@ def c1_inputs(device, seed, dtype=torch.float16):
     return x, off, msk, w, b
 
 
-def c1_cpu_sample(seconds_target=12.0, max_images=16):
-    """torchvision.ops.deform_conv2d (what DSC.forward calls in the reference) in fp32 on all host cores."""
+def c1_cpu_step(x, off, msk, w, b, i):
+    """One feature map of the c1 batch through torchvision.ops.deform_conv2d (what DSC.forward calls in the reference), fp32, all host cores."""
     import torchvision
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        torchvision.ops.deform_conv2d(x[i:i + 1], off[i:i + 1], w, b, stride=1, padding=1, mask=msk[i:i + 1])
+    return time.perf_counter() - t0
+
+
+def c1_cpu_inputs():
     torch.set_num_threads(os.cpu_count() or 1)
     x, off, msk, w, b = c1_inputs('cpu', 0)
-    x, off, msk, w = x.float(), off.float(), msk.float(), w.float()
-    with torch.no_grad():
-        torchvision.ops.deform_conv2d(x[:1], off[:1], w, b, stride=1, padding=1, mask=msk[:1])   # warm-up
-        t0 = time.perf_counter(); n = 0
-        while n < max_images and (time.perf_counter() - t0) < seconds_target:
-            torchvision.ops.deform_conv2d(x[n:n + 1], off[n:n + 1], w, b, stride=1, padding=1, mask=msk[n:n + 1])
-            n += 1
-        dt = time.perf_counter() - t0
-    return n / dt, n, dt
+    return x.float(), off.float(), msk.float(), w.float(), b
+
+
+def c1_cpu_sample(n_maps=5, warmup=1):
+    """Median over `n_maps` single-map steps; returns (feature maps/s, n, seconds)."""
+    t = c1_cpu_inputs()
+    for i in range(warmup):
+        c1_cpu_step(*t, i)
+    ts = [c1_cpu_step(*t, (warmup + i) % C1['B']) for i in range(n_maps)]
+    return 1.0 / statistics.median(ts), n_maps, sum(ts)
+
+
+def c1_torch_gpu_sample(device, iters=5):
+    """torchvision.ops.deform_conv2d on the same GPU in fp16 (NCHW, the library's im2col + GEMM): the call the reference makes."""
+    import torchvision
+    x, off, msk, w, b = (t.to(device) for t in c1_inputs(device, 0))
+    b = b.half()
+
+    def once():
+        with torch.no_grad():
+            return torchvision.ops.deform_conv2d(x, off, w, b, stride=1, padding=1, mask=msk)
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        once()
+    e1.record(); torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / iters * 1e3
+    return {'us_per_op': us, 'tflops': C1_FLOPS / us / 1e6, 'dtype': 'f16', 'what': 'torchvision.ops.deform_conv2d on the same GPU (library kernels)'}
 
 
 def run_c1(args, rank, world, local):
@@ -231,9 +260,8 @@ def run_c1(args, rank, world, local):
         'unit': 'images/s', 'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3),
         'ms_per_step': ms_total / args.steps, 'us_per_op': kern_ms * 1e3, 'higher_is_better': True, 'scaling': 'weak',
         'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
-        'config': {'workload': 'c1: DSC 256->256, x[16,256,100,100] fp16, offsets N(0,2) px, mask sigmoid(N(0,1)), W U(+-1/48)',
-                   'per_gpu_batch': C1['B'], 'l2': 'two 174 MB input sets alternated (each larger than the 126 MB L2)',
-                   'layout': 'NHWC in HBM'},
+        'config': {'workload': C1_WORKLOAD},
+        'run': {'per_gpu_batch': C1['B'], 'l2': 'two 174 MB input sets alternated (each larger than the 126 MB L2)', 'layout': 'NHWC in HBM'},
         'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': pk['bf16_tflops'], 'unit': 'TFLOP/s',
                      'frac': achieved / pk['bf16_tflops'], 'traffic': NCU_TRAFFIC['c1'], 'peak_source': pk['_source'] + ' (burst)',
                      'kernel': 'dsc_tc_kernel', 'flops_per_launch': C1_FLOPS, 'algorithmic_bytes': C1_BYTES,
@@ -251,6 +279,12 @@ def run_c1(args, rank, world, local):
 C4 = dict(images=64, H=800, W=800, mb=8, conf=0.001, iou=0.65, max_det=300)
 C4_GFLOP_PER_IMAGE = 38.9          # 2*MAC of the fused model at 800x800 (72 % 3x3 conv, 22 % 1x1 conv, 1.9 % DSC GEMM)
 C4_MIN_BYTES_PER_IMAGE = 0.35e9    # sum of conv inputs + outputs in fp16: the activation traffic floor
+
+
+C4_WORKLOAD = ('c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), batches of uint8 3x800x800 images, 64 per GPU and step, '
+               'sharded by batch over the ranks (no collective, host gather of the detections): backbone + neck + head + decode + NMS '
+               '(conf 0.001, IoU 0.65, max_det 300)')
+C1_WORKLOAD = 'c1: DSC 256->256, x[16,256,100,100] fp16, offsets N(0,2) px, mask sigmoid(N(0,1)), W U(+-1/48)'
 
 
 def c4_images(n, seed=0):
@@ -291,20 +325,53 @@ def c4_dominant_kernel(device, mb, stream, n=20):
     return {'us': us, 'bytes': nbytes, 'gbs': nbytes / (us * 1e-6) / 1e9, 'shape': [B, H, W, c]}
 
 
-def c4_cpu_sample(n_images=2):
-    """The plain PyTorch modules (what the reference's raw backend executes) + NMS, fp32, all host cores."""
+def c4_cpu_model():
+    import kadcnet
+    torch.set_num_threads(os.cpu_count() or 1)
+    return kadcnet.load_model(None, 'raw', 'cpu', randomize=True, seed=0)
+
+
+def c4_cpu_step(model, img):
+    """One image through the plain PyTorch modules (what the reference's raw backend executes) + NMS, fp32, all host cores."""
+    from kadcnet.postprocess import non_max_suppression
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        non_max_suppression(model(img.float() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])
+    return time.perf_counter() - t0
+
+
+def c4_cpu_sample(n_images=5, warmup=2):
+    """Median over `n_images` single-image steps after `warmup` untimed ones; returns (images/s, n, seconds)."""
+    model = c4_cpu_model()
+    imgs = c4_images(n_images + warmup)
+    for i in range(warmup):
+        c4_cpu_step(model, imgs[i:i + 1])
+    ts = [c4_cpu_step(model, imgs[warmup + i:warmup + i + 1]) for i in range(n_images)]
+    return 1.0 / statistics.median(ts), n_images, sum(ts)
+
+
+def c4_torch_gpu_sample(device, mb=8, iters=3):
+    """The same plain PyTorch modules in fp16 on the GPU (library kernels: cuDNN, torchvision deform_conv2d and nms), eager, the
+    way the reference's 'raw' backend runs on a GPU. A secondary yardstick next to the CPU arm; not this package's code path."""
     import kadcnet
     from kadcnet.postprocess import non_max_suppression
-    torch.set_num_threads(os.cpu_count() or 1)
-    model = kadcnet.load_model(None, 'raw', 'cpu', randomize=True, seed=0)
-    imgs = c4_images(n_images + 1)
-    with torch.no_grad():
-        non_max_suppression(model(imgs[:1].float() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])   # warm-up
-        t0 = time.perf_counter()
-        for i in range(1, n_images + 1):
-            non_max_suppression(model(imgs[i:i + 1].float() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])
-        dt = time.perf_counter() - t0
-    return n_images / dt, n_images, dt
+    model = kadcnet.load_model(None, 'raw', str(device), randomize=True, seed=0).half()
+    imgs = c4_images(mb, seed=7).to(device)
+
+    def once():
+        with torch.no_grad():
+            return non_max_suppression(model(imgs.half() / 255), C4['conf'], C4['iou'], max_det=C4['max_det'])
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        once()
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {'value': mb / (ms * 1e-3), 'unit': 'images/s', 'ms_per_mini_batch': ms, 'mini_batch': mb, 'dtype': 'f16',
+            'what': 'plain PyTorch modules + torchvision deform_conv2d + reference-order NMS on the same GPU, eager (library kernels only)'}
 
 
 def run_c4(args, rank, world, local):
@@ -384,6 +451,48 @@ def run_c4(args, rank, world, local):
     g1.record(stream); torch.cuda.synchronize()
     fwd_ms = g0.elapsed_time(g1) / 5
 
+    # strong-scaling point of the same sweep: ONE batch of 64 images in total, sharded by batch over the ranks
+    # (64 / 32 / 16 / 8 images per GPU at 1 / 2 / 4 / 8 GPUs), same forward graph + NMS per rank, no collective
+    sa, sb = shard_range(C4['images'], rank, world)
+    n_strong = sb - sa
+    if world == 1:
+        strong_ms = ms_total / args.steps
+    else:
+        for _ in range(3):
+            run_mb(dev[:n_strong])
+        barrier(world); torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(args.steps):
+            run_mb(dev[:n_strong])
+        s1.record(stream)
+        torch.cuda.synchronize(); barrier(world)
+        strong_ms = max_over_ranks(s0.elapsed_time(s1), world, device) / args.steps
+    strong = {'scaling': 'strong', 'images_total': C4['images'], 'images_per_rank': n_strong, 'value': C4['images'] / (strong_ms * 1e-3),
+              'unit': 'images/s', 'ms_per_step': strong_ms}
+
+    # latency of one image (BASELINE configs[3]: batch 1, 800x800): forward graph + NMS, and the same from a pinned host image
+    # to detections on the host
+    c3 = None
+    if rank == 0:
+        one = dev[:1]
+        for _ in range(3):
+            run_mb(one)
+        torch.cuda.synchronize()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_lat = 30
+        l0.record(stream)
+        for _ in range(n_lat):
+            run_mb(one)
+        l1.record(stream); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n_lat):
+            d = run_mb(host[:1].to(device, non_blocking=True))
+            d = [t.cpu() for t in d]
+        host_ms = (time.perf_counter() - t0) / n_lat * 1e3
+        c3 = {'workload': 'c3: one uint8 3x800x800 image, fp16, forward graph + NMS (conf 0.001, IoU 0.65)', 'ms_per_image': l0.elapsed_time(l1) / n_lat,
+              'e2e_ms_per_image': host_ms, 'detections': int(d[0].shape[0]), 'launches_per_image': kernels_per_mb + 1}
+
     # end to end through the streaming API (kadcnet.pipeline.DetectionPipeline): pinned host images in, detections on the host
     # out; per step the H2D copy of the step's images and the D2H copy of its detections are inside the timed region (the copy of
     # the next mini-batch overlaps the forward of the current one)
@@ -413,11 +522,11 @@ def run_c4(args, rank, world, local):
         'metric': 'KAD-CNet-S 800x800 images/s', 'value': C4['images'] * world * args.steps / (ms_total * 1e-3), 'unit': 'images/s',
         'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_total / args.steps,
         'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
-        'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 64 uint8 3x800x800 images per GPU and step '
-                               '(the batch is sharded over the ranks, no collective, host gather of the detections), backbone + neck + head + decode + NMS (conf 0.001, IoU 0.65, max_det 300)',
-                   'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
-                   'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)',
-                   'conv3x3': 'library (cuDNN through torch) + kad_bias_act' if args.conv3x3 == 'library' else 'kad_conv3x3_bias_act (tcgen05)'},
+        'config': {'workload': C4_WORKLOAD},
+        'run': {'images_per_rank': n_local, 'mini_batch': mb, 'l2': f'activations of a mini-batch of {mb} images exceed the 126 MB L2',
+                'detections_per_step_rank0': n_det, 'detections_gathered': n_total, 'forward': 'CUDA graph per mini-batch shape', 'nms': 'one batched CUDA kernel per mini-batch (kad_nms_batched)',
+                'conv3x3': 'library (cuDNN through torch) + kad_bias_act' if args.conv3x3 == 'library' else 'kad_conv3x3_bias_act (tcgen05)'},
+        'strong_scaling': strong, 'c3_latency': c3,
         'roofline': {'bound': 'hbm', 'achieved': dom['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s', 'frac': dom['gbs'] / pk['hbm_gbs'],
                      'traffic': NCU_TRAFFIC['c4_dsc_mma'], 'peak_source': pk['_source'],
                      'kernel': 'dsc_mma_kernel (fused offset convolution + deformable convolution of a KAD-Conv branch), the largest share of the '
@@ -674,45 +783,47 @@ def main():
         print(json.dumps(obj), flush=True)
         os.dup2(2, 1)
 
-    rank, world, local = dist_setup(args.gpus)
-
-    if args.impl == 'reference' and args.workload == 'c4':
-        if rank == 0:
-            model, cores = cpu_info()
-            vals = []
-            for _ in range(max(1, min(args.steps, 3))):
-                ips, n, dt = c4_cpu_sample()
-                vals.append(ips)
-            v = statistics.median(vals)
-            emit(({
-                'impl': 'reference', 'metric': 'KAD-CNet-S 800x800 images/s', 'value': v, 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
-                'warmup': args.warmup, 'ms_per_step': 1e3 * C4['images'] * world / v, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-                'dtype': 'f32', 'data': 'synthetic',
-                'config': {'workload': 'c4: KAD-CNet-S (dior_s_base graph, 20 classes, seeded synthetic weights), 3x800x800 images, backbone + neck + '
-                                       'head + decode + NMS (conf 0.001, IoU 0.65, max_det 300); plain PyTorch modules on the host cores'},
-                'cpu_baseline': {'value': v, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
-                                 'sample': f'{n} images 3x800x800 per step, fp32 plain PyTorch modules + torchvision deform_conv2d + NMS',
-                                 'cpu': model, 'os_cpu_count': cores},
-                'e2e': {'value': v, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
-        return
     if args.impl == 'reference':
-        if rank == 0:
-            model, cores = cpu_info()
-            vals = []
-            for _ in range(max(1, min(args.steps, 3))):
-                ips, n, dt = c1_cpu_sample(seconds_target=8.0, max_images=4)
-                vals.append(ips)
-            v = statistics.median(vals)
-            sample = f'{n} feature maps [1,256,100,100] of the c1 batch per step, fp32, torchvision.ops.deform_conv2d'
-            emit(({
-                'impl': 'reference', 'metric': 'KAD-Conv op (DSC 256->256 @100x100 fp16) feature maps/s', 'value': v, 'unit': 'images/s',
-                'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * C1['B'] / v, 'higher_is_better': True,
-                'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-                'config': {'workload': 'c1: DSC 256->256, x[16,256,100,100], offsets N(0,2) px (CPU oracle port, fp32)'},
-                'cpu_baseline': {'value': v, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port', 'sample': sample,
-                                 'cpu': model, 'os_cpu_count': cores},
-                'e2e': {'value': v, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+        # the reference's plain PyTorch path on the host cores. No process group is created: under torchrun rank 0 alone
+        # works, the other ranks leave at once. One step = one unit of the workload (one image / one feature map); the
+        # line reports the steps it really ran and the measured time of one step.
+        rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+        if rank != 0:
+            return
+        model_name, cores = cpu_info()
+        steps, warm = max(1, args.steps), max(0, args.warmup)
+        if args.workload == 'c4':
+            model = c4_cpu_model()
+            imgs = c4_images(min(steps + warm, 16))
+            for i in range(warm):
+                c4_cpu_step(model, imgs[i % len(imgs):i % len(imgs) + 1])
+            t0 = time.perf_counter()
+            ts = [c4_cpu_step(model, imgs[(warm + i) % len(imgs):(warm + i) % len(imgs) + 1]) for i in range(steps)]
+            total = time.perf_counter() - t0
+            metric, workload, unit_name = 'KAD-CNet-S 800x800 images/s', C4_WORKLOAD, 'image 3x800x800'
+            what = 'fp32 plain PyTorch modules (the op sequence of the reference\'s raw backend) + torchvision deform_conv2d + NMS'
+        else:
+            t = c1_cpu_inputs()
+            for i in range(warm):
+                c1_cpu_step(*t, i % C1['B'])
+            t0 = time.perf_counter()
+            ts = [c1_cpu_step(*t, (warm + i) % C1['B']) for i in range(steps)]
+            total = time.perf_counter() - t0
+            metric, workload, unit_name = 'KAD-Conv op (DSC 256->256 @100x100 fp16) feature maps/s', C1_WORKLOAD, 'feature map [1,256,100,100]'
+            what = 'fp32 torchvision.ops.deform_conv2d (the call DSC.forward makes)'
+        v = steps / total
+        emit({
+            'impl': 'reference', 'metric': metric, 'value': v, 'unit': 'images/s', 'n_gpus': world, 'steps': steps, 'warmup': warm,
+            'ms_per_step': 1e3 * total / steps, 'ms_per_step_median': 1e3 * statistics.median(ts), 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': {'workload': workload},
+            'run': {'step': f'one {unit_name} of the workload per step (a bounded sample: the host cores need about {64 * total / steps:.0f} s for '
+                            'the 64 images of one GPU step)' if args.workload == 'c4' else f'one {unit_name} of the batch of 16 per step'},
+            'cpu_baseline': {'value': v, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                             'sample': f'{steps} steps of one {unit_name} after {warm} warm-up steps, {what}', 'cpu': model_name, 'os_cpu_count': cores},
+            'e2e': {'value': v, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}})
         return
+
+    rank, world, local = dist_setup(args.gpus)
 
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline')
@@ -738,21 +849,25 @@ def main():
         res['kadconv_op'] = {'workload': op['config']['workload'], 'us_per_op': op['us_per_op'], 'feature_maps_per_s': op['value'],
                              'roofline': op['roofline']}
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline and not args.profile:
+        if world == 1 and not args.no_cpu_baseline and not args.profile and args.workload in ('c1', 'c4'):
             model, cores = cpu_info()
-            if args.workload == 'c2':
-                emit(res)
-                return
+            device = torch.device('cuda', local)
             if args.workload == 'c4':
                 ips, n, dt = c4_cpu_sample()
-                res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
-                                       'sample': f'{n} images 3x800x800 in {dt:.1f} s, fp32 plain PyTorch modules + torchvision deform_conv2d + NMS',
-                                       'cpu': model, 'os_cpu_count': cores}
-                emit(res)
-                return
-            ips, n, dt = c1_cpu_sample()
-            res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port',
-                                   'sample': f'{n} of the 16 c1 feature maps in {dt:.1f} s, fp32, torchvision.ops.deform_conv2d (the call DSC.forward makes)',
+                sample = f'median of {n} single-image steps ({dt:.1f} s), fp32 plain PyTorch modules + torchvision deform_conv2d + NMS'
+                try:
+                    res['torch_gpu_reference'] = c4_torch_gpu_sample(device)
+                    res['kadconv_op']['torch_gpu_reference'] = c1_torch_gpu_sample(device)
+                except Exception as e:      # the library op may be missing for this GPU: say so instead of failing the line
+                    res['torch_gpu_reference'] = {'unavailable': f'{type(e).__name__}: {e}'[:300]}
+            else:
+                ips, n, dt = c1_cpu_sample()
+                sample = f'median of {n} single-map steps of the 16 c1 feature maps ({dt:.1f} s), fp32, torchvision.ops.deform_conv2d (the call DSC.forward makes)'
+                try:
+                    res['torch_gpu_reference'] = c1_torch_gpu_sample(device)
+                except Exception as e:
+                    res['torch_gpu_reference'] = {'unavailable': f'{type(e).__name__}: {e}'[:300]}
+            res['cpu_baseline'] = {'value': ips, 'unit': 'images/s', 'cores': torch.get_num_threads(), 'kind': 'port', 'sample': sample,
                                    'cpu': model, 'os_cpu_count': cores}
         emit(res)
     if world > 1:

@@ -41,6 +41,19 @@ __device__ __forceinline__ void store_mixed(void* p, size_t i, int f32, float v)
 }
 
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+// SiLU for the 16-bit epilogues: v / (1 + 2^(-v * log2 e)) with the hardware exponential and reciprocal (two
+// special-function instructions, about 2 ulp of float32: far below the rounding of the 16-bit store that follows).
+// Building with -DKAD_SILU_TANH selects v * (0.5 * tanh.approx(v / 2) + 0.5) instead: one special-function
+// instruction, but about 5e-4 relative error, the size of a half-precision rounding step, on every activation.
+__device__ __forceinline__ float silu_fast(float v) {
+#ifdef KAD_SILU_TANH
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * v));
+    return v * fmaf(0.5f, th, 0.5f);
+#else
+    return __fdividef(v, 1.0f + __expf(-v));
+#endif
+}
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == KAD_ACT_SILU) return v * sigmoidf_(v);
     if (act == KAD_ACT_RELU) return fmaxf(v, 0.0f);

@@ -146,13 +146,8 @@ conv3x3_tc_kernel(const __grid_constant__ ConvMaps maps, const ConvParams p) {
                                 uint4 w;
                                 T* h = reinterpret_cast<T*>(&w);
                                 if (p.act == KAD_ACT_SILU) {
-                                    // x * sigmoid(x) = x * (0.5 * tanh(x / 2) + 0.5): one special-function instruction per element
 #pragma unroll
-                                    for (int e = 0; e < 8; ++e) {
-                                        float th;
-                                        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * a[e]));
-                                        h[e] = from_f<T>(a[e] * fmaf(0.5f, th, 0.5f));
-                                    }
+                                    for (int e = 0; e < 8; ++e) h[e] = from_f<T>(silu_fast(a[e]));
                                 } else if (p.act == KAD_ACT_RELU) {
 #pragma unroll
                                     for (int e = 0; e < 8; ++e) h[e] = from_f<T>(fmaxf(a[e], 0.f));

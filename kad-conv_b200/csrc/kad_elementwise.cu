@@ -1240,11 +1240,7 @@ __global__ void avg_pool2x2s1_kernel(const T* __restrict__ x, T* __restrict__ y,
     }
 }
 
-__device__ __forceinline__ float silu_tanh(float v) {      // v * sigmoid(v) with one special-function instruction
-    float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * v));
-    return v * fmaf(0.5f, th, 0.5f);
-}
+__device__ __forceinline__ float silu_tanh(float v) { return silu_fast(v); }
 
 // out[m][0..C) = act(y[m][0..C) + bias), 8 channels per thread; out rows are out_ld8 vectors apart (out may be y itself,
 // or a channel slice of a wider tensor). Two vectors per thread are in flight.

@@ -109,15 +109,8 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             uint4 w;
                             T* h = reinterpret_cast<T*>(&w);
                             if (p.act == KAD_ACT_SILU) {
-                                // x * sigmoid(x) = x * (0.5 * tanh(x / 2) + 0.5): one special-function instruction per element (the
-                                // exponential + division form needs two, and this epilogue would then be bound by that unit);
-                                // tanh.approx is good to about 5e-4 relative, the result is rounded to 16 bits anyway
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    float th;
-                                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * a[e]));
-                                    h[e] = from_f<T>(a[e] * fmaf(0.5f, th, 0.5f));
-                                }
+                                for (int e = 0; e < 8; ++e) h[e] = from_f<T>(silu_fast(a[e]));
                             } else if (p.act == KAD_ACT_RELU) {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) h[e] = from_f<T>(fmaxf(a[e], 0.f));

@@ -4,7 +4,7 @@
 // The layer is memory-bound (3 bytes in, 2*Cout bytes out per output pixel, 27*Cout MACs), but on CUDA cores the MACs
 // and the SiLU would take longer than the traffic. So the contraction runs on the warp-level tensor-core instruction
 // (mma.sync m16n8k16): K = Cin*9 <= 48 padded to 16-chunks, pixel values enter as exact fp16 integers 0..255 and the
-// 1/255 is applied to the fp32 accumulator; SiLU uses one tanh.approx per element. A block owns 8 x 32 output pixels;
+// 1/255 is applied to the fp32 accumulator; SiLU uses the hardware exponential and reciprocal. A block owns 8 x 32 output pixels;
 // its (17 x 65 x Cin)-byte input patch goes through shared memory, and each warp's 32 output pixels leave as one
 // contiguous run of 16-byte vectors.
 #include "kad_common.cuh"
@@ -32,11 +32,7 @@ template <> __device__ __forceinline__ void st_mma<__nv_bfloat16>(float (&c)[4],
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
 
-__device__ __forceinline__ float fast_silu(float v) {
-    float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * v));
-    return v * fmaf(0.5f, th, 0.5f);
-}
+__device__ __forceinline__ float fast_silu(float v) { return silu_fast(v); }
 
 // K index of the contraction: k = ci*9 + ky*3 + kx (the flattening of an [Cout][Cin][3][3] weight). Lane t of a 16-chunk
 // owns k = chunk*16 + {2t, 2t+1, 2t+8, 2t+9} (the operand layout of mma.sync, no permutation needed here).

@@ -11,6 +11,11 @@ contiguous [B,H,W,C] tensor:
     KAD-Conv hot path; they are the next item to be replaced)
   * head decode -> one kernel per scale (softmax expectation, box, sigmoid) in fp32 with one rounding at the store.
 There is no CPU path: the engine raises on a non-CUDA input.
+
+Error reporting: the tcgen05 kernels bound every wait; one that gives up records that in a device status word and its
+results are not valid. FastDetector.forward and StaticGraph.__call__ look at that word without synchronising (a snapshot
+taken after each call is examined at the next one), non_max_suppression_device and DetectionPipeline read it together with
+their results, and kadconv.ops.check_status(device) checks it at once (it synchronises).
 """
 import torch
 import torch.nn.functional as F
@@ -246,6 +251,9 @@ class FastDetector(torch.nn.Module):
         normalised by 1/255 on the way in (the `/255` of the reference's inference scripts)."""
         if not x.is_cuda:
             raise RuntimeError('FastDetector has no CPU path: move the input to the GPU')
+        capturing = torch.cuda.is_current_stream_capturing()
+        if not capturing:
+            ops.status_poll(x.device)
         first = self.model.model[0]
         pad8 = isinstance(first, M.Conv) and first.conv.in_channels < 8 and first.conv.kernel_size != (1, 1)
         skip_first = False
@@ -266,4 +274,6 @@ class FastDetector(torch.nn.Module):
             if not (skip_first and m.i == 0):
                 x = fn(x)
             ys.append(x if m.i in save else None)
+        if not capturing:
+            ops.status_snapshot(x.device)
         return x

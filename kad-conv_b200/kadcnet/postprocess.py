@@ -59,5 +59,8 @@ def non_max_suppression_device(prediction, conf_thres=0.25, iou_thres=0.45, max_
     if isinstance(prediction, (list, tuple)):
         prediction = prediction[0]
     dets, counts = ops.nms_batched(prediction.contiguous(), conf_thres, iou_thres, max_det)
-    counts = counts.tolist()
-    return [dets[i, :n] for i, n in enumerate(counts)]
+    # one device-to-host read for the counts and the kernels' status word: a forward whose tensor-core kernel gave up on a
+    # wait must not hand out detections
+    host = torch.cat((counts, ops.status_word(prediction.device))).tolist()
+    ops.raise_if_aborted(host[-4:], ops.status_word(prediction.device).zero_)
+    return [dets[i, :n] for i, n in enumerate(host[:-4])]

@@ -47,8 +47,11 @@ class StaticGraph:
         torch.cuda.synchronize()
 
     def __call__(self, value, clone=True):
+        from kadconv import ops
+        ops.status_poll(self.input.device)          # an earlier replay whose kernel gave up on a wait raises here
         self.input.copy_(value)
         self.graph.replay()
+        ops.status_snapshot(self.input.device)
         return clone_output(self.output) if clone else self.output
 
 

@@ -67,10 +67,20 @@ class _BranchParams:
         return ops.PATH_SIMT, self.w_dsc_simt
 
 
+def parameter_fingerprint(layer):
+    """Changes whenever a parameter or buffer of the layer is replaced (load_state_dict on a meta/cast module, .half(),
+    .to()) or updated in place (optimizer step, load_state_dict's copy_, manual edits): storage address and version
+    counter of every tensor of the layer."""
+    return tuple((t.data_ptr(), t._version) for t in list(layer.parameters()) + list(layer.buffers()))
+
+
 def _prepare(layer, device):
+    """Folded / packed parameters of the layer on `device`, rebuilt when the layer's tensors have changed since they
+    were derived (the plain forward reads live parameters, so the fast one must not run on stale copies)."""
     st = getattr(layer, _FAST_ATTR, None)
-    if st is None or st['device'] != device:
-        st = {'device': device,
+    fp = parameter_fingerprint(layer)
+    if st is None or st['device'] != device or st['fingerprint'] != fp:
+        st = {'device': device, 'fingerprint': fp,
               'branches': [_BranchParams(layer.convs[i], layer.fc[i], layer.weight[i], device) for i in range(layer.n)]}
         object.__setattr__(layer, _FAST_ATTR, st)
     return st
@@ -184,7 +194,12 @@ def _fast_forward(layer, x):
     if x.dim() != 4:
         raise ValueError('KADConv expects a [B,C,H,W] tensor')
     channels_last = x.permute(0, 2, 3, 1).is_contiguous()
+    capturing = torch.cuda.is_current_stream_capturing()
+    if not capturing:
+        ops.status_poll(x.device)        # a tensor-core kernel of an earlier call that gave up on a wait raises here
     out = kadconv_forward_nhwc(layer, ops.to_nhwc(x))
+    if not capturing:
+        ops.status_snapshot(x.device)
     if channels_last:
         return out.permute(0, 3, 1, 2)      # same logical shape, channels_last memory like the input
     return ops.to_nchw(out)

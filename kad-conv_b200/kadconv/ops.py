@@ -108,12 +108,48 @@ def status_word(device):
     return _status[key]
 
 
+def raise_if_aborted(words, clear=None):
+    """`words`: the four status integers as host values. Raises RuntimeError when a kernel recorded a wait that gave up
+    (its results are then not valid); `clear()` is called first so that one failure is reported once."""
+    if int(words[0]) != 0:
+        if clear is not None:
+            clear()
+        raise RuntimeError(f'kadconv tensor-core kernel aborted: role {int(words[0])}, detail {int(words[1])}, block {int(words[2])}')
+
+
 def check_status(device):
     """Synchronises and raises if a tensor-core kernel gave up on a wait since the last check."""
-    st = status_word(device).cpu()
-    if int(st[0]) != 0:
-        status_word(device).zero_()
-        raise RuntimeError(f'kadconv tensor-core kernel aborted: role {int(st[0])}, detail {int(st[1])}, block {int(st[2])}')
+    raise_if_aborted(status_word(device).cpu().tolist(), status_word(device).zero_)
+
+
+_monitor = {}
+
+
+def status_poll(device):
+    """Non-blocking: raises if a status snapshot taken by an earlier status_snapshot() has arrived on the host and shows an
+    aborted kernel. The public entry points (FastDetector.forward, StaticGraph.__call__, the fast KADConv forward) call this on
+    entry and status_snapshot() on exit, so a kernel that gave up surfaces as an exception on the next call at the latest,
+    without a host synchronisation on the inference path; callers that synchronise anyway use check_status()."""
+    m = _monitor.get((device.type, device.index))
+    if m is not None and m['pending'] and m['event'].query():
+        m['pending'] = False
+        raise_if_aborted(m['host'].tolist(), status_word(device).zero_)
+
+
+def status_snapshot(device):
+    """Enqueues an asynchronous copy of the device status word into pinned host memory (skipped while a stream capture is
+    in progress, and while the previous snapshot is still in flight)."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    key = (device.type, device.index)
+    m = _monitor.get(key)
+    if m is None:
+        m = _monitor[key] = {'host': torch.zeros(4, dtype=torch.int32).pin_memory(), 'event': torch.cuda.Event(), 'pending': False}
+    if m['pending'] and not m['event'].query():
+        return
+    m['host'].copy_(status_word(device), non_blocking=True)
+    m['event'].record(torch.cuda.current_stream(device))
+    m['pending'] = True
 
 
 def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=None, act=ACT_NONE,

@@ -9,7 +9,15 @@ from helpers import rel_err, round_to
 from oracle import kad_oracle as ko
 from oracle import seeding
 
+import nms_explain as ne
+
 pytestmark = pytest.mark.gpu
+
+# Half-precision tolerances of the configs[3] acceptance test: scores agree to 1e-2 (the stated relative bar; scores lie in
+# [0,1]); a corner stored in half precision at 400-800 px moves in steps of 0.25-0.5 px, which shifts the IoU of the small
+# boxes this model emits by several percent.
+C3_EPS_SCORE = 1e-2
+C3_EPS_IOU = 0.1
 
 
 def match_fraction(det, ref, tol=0.05):
@@ -33,7 +41,7 @@ def _sd(golden_dir, dtype=None):
 
 def test_engine_fp32_matches_fixture(golden_dir):
     import kadcnet
-    from kadcnet.postprocess import non_max_suppression
+    from kadcnet.postprocess import non_max_suppression_device
     g, sd = _sd(golden_dir)
     fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float32)
     img = seeding.seeded_input((1, 3, 160, 192), seed=int(g['seed']), kind='image')
@@ -42,17 +50,64 @@ def test_engine_fp32_matches_fixture(golden_dir):
     assert y.shape == ref.shape
     assert rel_err(y.cpu(), ref) <= 1e-5
     assert (raw[0].cpu().float() - torch.from_numpy(g['raw0'])).abs().max().item() <= 1e-3
-    # NMS of the reference's own y, run on the GPU, reproduces the fixture's detections (the CPU and CUDA
-    # library NMS may order exact score ties differently, hence a match fraction and not bit equality) ...
+    # absolute per-box bound, each scale on its own (a wrong anchor order or offset on one scale cannot hide behind a global maximum)
+    for lo, hi in ((0, 480), (480, 600), (600, 630)):
+        assert (y[:, :4, lo:hi].cpu() - ref[:, :4, lo:hi]).abs().max().item() <= 1e-3          # pixels
+        assert (y[:, 4:, lo:hi].cpu() - ref[:, 4:, lo:hi]).abs().max().item() <= 1e-5          # scores
+    # Detections. The batched NMS kernel on the reference's own y reproduces the reference-made detections bit for bit ...
     gd = torch.from_numpy(g['det'])
-    det_ref = non_max_suppression(ref.cuda(), 0.001, 0.65, max_det=300)[0].cpu()
-    assert match_fraction(det_ref, gd) >= 0.97 and abs(det_ref.shape[0] - gd.shape[0]) <= 2
-    # ... and NMS of the engine's y keeps the same boxes except where a 1e-5 relative difference flips an IoU
-    # comparison that sits on the 0.65 threshold; greedy NMS then cascades (a random-init model emits many nearly
-    # coincident boxes), so the bar is a match fraction, with the highest-scoring detections required to agree
-    det = non_max_suppression(y, 0.001, 0.65, max_det=300)[0].cpu()
-    assert match_fraction(det, gd) >= 0.75 and abs(det.shape[0] - gd.shape[0]) <= 6
-    assert match_fraction(det[:10], gd[:10]) >= 0.9
+    assert torch.equal(non_max_suppression_device(ref.cuda(), 0.001, 0.65, max_det=300)[0].cpu(), gd)
+    # ... and on the engine's y it equals exact greedy NMS of that y; where that result differs from the reference-made one,
+    # every difference is a decision that sits on a threshold: the kept set is a valid NMS solution of the REFERENCE's boxes and
+    # scores once IoU comparisons get 1e-3 and score comparisons 1e-5 of slack, and each differing box is traced to an IoU within
+    # that slack of 0.65, to a score tie (this random-init model emits exact ties), or to a box that differs for such a reason.
+    det = non_max_suppression_device(y, 0.001, 0.65, max_det=300)[0].cpu()
+    ca, cb = ne.candidates(y[0].cpu(), 0.001), ne.candidates(ref[0], 0.001)
+    ka, kb = ne.greedy_keep(ca, 0.65), ne.greedy_keep(cb, 0.65)
+    assert torch.equal(det, torch.cat((ca['box'][ka], ca['conf'][ka, None], ca['cls'][ka, None].float()), 1)[:300])
+    rep = ne.check_explained(ka, ca, cb, 0.001, 0.65, eps_iou=1e-3, eps_score=1e-5)
+    assert rep['ok'], rep
+    reasons = ne.trace_differences(ka, kb, cb, 0.65, 1e-3, 1e-5, 0.001)
+    assert all(r[0] is not None for r in reasons.values()), reasons
+    print(f'fp32 fixture: {len(kb)} reference detections, {len(set(ka) ^ set(kb))} differing boxes, reasons '
+          f'{sorted((r[0] for r in reasons.values()))}')
+
+
+def test_c3_config_detections_against_same_dtype_reference(golden_dir):
+    """BASELINE configs[3] as written: fp16, one uint8 3x800x800 image, conf 0.001, IoU 0.65, max_det 300, through
+    load_model(..., 'optimized') + the batched NMS kernel, against the plain modules run in fp16 on the same GPU (the
+    reference's own half-precision path: library kernels, decode in half) + the reference-order NMS.
+    Bit-identical detections cannot be expected between two half-precision evaluation orders (this engine decodes in fp32 and
+    rounds once, the modules decode in half; the class scores carry up to 1e-2 of relative error on both sides), so the
+    criterion is the one that can be stated exactly: the engine's kept set must be a valid greedy-NMS solution of the
+    REFERENCE's boxes and scores within the half-precision tolerances below, and every differing box must trace to a decision
+    inside them. The kernel itself is exact on its own input."""
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression, non_max_suppression_device
+    from kadconv import ops
+    g, sd = _sd(golden_dir)
+    img = seeding.seeded_input((1, 3, 800, 800), seed=3, kind='image').cuda()
+    raw16 = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd).half()
+    with torch.no_grad():
+        yb = raw16(img.half() / 255)[0]
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    ya = fast(img)[0]
+    torch.cuda.synchronize(); ops.check_status(img.device)
+    assert ya.dtype == yb.dtype == torch.float16 and ya.shape == yb.shape == (1, 24, 13125)
+    det = non_max_suppression_device(ya, 0.001, 0.65, max_det=300)[0].cpu()
+    det_ref = non_max_suppression(yb, 0.001, 0.65, max_det=300)[0].cpu().float()
+    ca, cb = ne.candidates(ya[0].cpu(), 0.001), ne.candidates(yb[0].cpu(), 0.001)
+    ka, kb = ne.greedy_keep(ca, 0.65), ne.greedy_keep(cb, 0.65)
+    rows = lambda c, k: torch.cat((c['box'][k], c['conf'][k, None], c['cls'][k, None].float()), 1)[:300]
+    assert torch.equal(det, rows(ca, ka))                       # the kernel is exact greedy NMS of its input
+    assert det_ref.shape[0] == min(300, len(kb))
+    rep = ne.check_explained(ka, ca, cb, 0.001, 0.65, eps_iou=C3_EPS_IOU, eps_score=C3_EPS_SCORE)
+    assert rep['ok'], {k: (v[:5] if isinstance(v, list) else v) for k, v in rep.items()}
+    reasons = ne.trace_differences(ka, kb, cb, 0.65, C3_EPS_IOU, C3_EPS_SCORE, 0.001)
+    assert all(r[0] is not None for r in reasons.values())
+    from collections import Counter
+    print(f'c3 fp16: candidates {int(ca["cand"].sum())} / {int(cb["cand"].sum())}, kept {len(ka)} / {len(kb)}, differing '
+          f'{len(set(ka) ^ set(kb))} (top 300: {len(set(ka[:300]) ^ set(kb[:300]))}), reasons {dict(Counter(r[0] for r in reasons.values()))}')
 
 
 @pytest.mark.parametrize('backend', ['optimized', 'graph'])

@@ -102,6 +102,26 @@ def test_wide_layer_uses_tensor_path_fp16():
     assert rel_err(y, ref) <= 1e-2
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_c2_width_layer_16bit(dtype):
+    """KADConv(128), the layer of configs[2] (bf16 there), with N(0,1) branch scales: branch widths 44 / 42 / 42, i.e. the
+    warp-MMA deformable convolution with six 8-column accumulator tiles per warp and the pyramid kernel at the same width
+    (the kernels the c2 benchmark times), against the fp32 oracle on values rounded to the storage type. H != W."""
+    import kadconv
+    from kadconv import ops
+    layer, sd = _layer(128, 41, dtype=dtype, scale_mode='normal')
+    x = round_to(seeding.seeded_input((2, 128, 40, 36), seed=41), dtype)
+    ref = ko.kadconv(sd, '', x)
+    kadconv.enable_fast_inference(layer.cuda())
+    with torch.no_grad():
+        y = layer(x.cuda().to(dtype))
+        y2 = layer(x.cuda().to(dtype))
+    ops.check_status(torch.device('cuda', 0))
+    assert ops.dsc_mma_supported(44, 44, dtype, 40, 36) and ops.pyramid_project_supported(128, [44, 42, 42], dtype, 40, 36)
+    assert torch.equal(y, y2)
+    assert rel_err(y.float().cpu(), ref) <= 1e-2
+
+
 def test_fast_mode_refuses_cpu_and_training():
     import kadconv
     layer, _ = _layer(24, 1)
