@@ -76,6 +76,16 @@ typedef struct KadDscArgs {
        the kernel computes the offsets of its own pixels itself (kad_conv.py:64 fused into :66-67): the offset
        tensor is never written to memory. */
     const float* offset_weight; const float* offset_bias;
+    /* path 3 with offset_weight only, optional: the modulation mask of LCSA.forward + sigmoid (kad_conv.py:24-39,:65) evaluated
+       inside the kernel, per pixel, so that the mask tensor is never written to memory. When lcsa_rowsum is set, `mask` is
+       ignored. With C = Cin and Cp = C rounded up to a multiple of 4:
+         lcsa_rowsum float32 [B][H][C]  sums of x over the row (pool_h * W)
+         lcsa_A      float32 [B][W][Cp] and lcsa_Sm float32 [W][Cp]: the separable 1x11 + BatchNorm stage per column, as
+                     kad_pyramid_project_lcsa / kad_lcsa_mask_from_partials compute them (16-byte aligned)
+         lcsa_w2 [C][11], lcsa_b2 [C] (11x1 depthwise), lcsa_w3 [9][C], lcsa_b3 [9] (1x1)
+       kad_dsc_mma_inline_mask_supported() says whether the operands fit shared memory for this shape. */
+    const float* lcsa_rowsum; const float* lcsa_A; const float* lcsa_Sm;
+    const float* lcsa_w2; const float* lcsa_b2; const float* lcsa_w3; const float* lcsa_b3;
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);
 int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path);
@@ -85,6 +95,7 @@ int kad_dsc_tc_supported(int Cin, int Cout, int dtype);
  * pixels touches (W * Cin * 2 bytes each) fit in shared memory beside the kernel's tables. x must be 16-byte aligned.
  * Path 3 writes its channel sums per group of 256 pixels: kad_dsc_gap_tiles(..., 3) = ceil(H*W / 256). */
 int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
+int kad_dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W);
 /* Packs W[Cout][Cin][3][3] (float32, the layout of DSC.weight) into the tensor path's K-major
  * operand: dst is dtype [9*Cin/64 (rounded up)][Cout][64]; K index = (ci/32)*288 + tap*32 + ci%32. */
 int kad_dsc_pack_weight_tc(const float* w_oihw, void* dst, int Cin, int Cout, int dtype, void* stream);
@@ -120,6 +131,24 @@ int kad_pyramid_partial_dims(int B, int H, int W, int dim, int c0, int c1, int c
 int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
                         int B, int H, int W, int dim, const int* c, int dtype,
                         float* const* rowpart, float* const* colpart, void* stream);
+/* kad_pyramid_project that also finishes the first, separable stage of the three LCSAs (kad_conv.py:27-31: pool_h + pool_w,
+ * the 1x11 depthwise convolution, BatchNorm) in the tail of the same kernel: the block that finishes an image last reduces
+ * that image's partial sums (fixed order, so the result does not depend on which block it is) and writes, per branch i,
+ *   lcsa_rowsum[i] float32 [B][h_i][c_i], lcsa_A[i] float32 [B][w_i][Cp_i], lcsa_Sm[i] float32 [w_i][Cp_i]  (Cp = c rounded up to 4)
+ * which kad_dsc_forward (path 3, lcsa_* fields) consumes; the same values kad_lcsa_mask_from_partials derives in a kernel of
+ * its own. lcsa_w1[i] [c_i][11], lcsa_b1[i] [c_i]: the 1x11 depthwise convolution; lcsa_bn_scale / lcsa_bn_shift [c_i]: folded BatchNorm.
+ * counters: device int[B], zero before the first call; every call leaves them zero again (calls that share them must not overlap).
+ * kad_pyramid_lcsa_supported: kad_pyramid_project_supported and the widest column-sum table (W * c0 floats) fits the block's shared memory. */
+typedef struct KadPyramidArgs {
+    const void* x; const float* w[3]; const float* bias[3]; void* t[3];
+    int B, H, W, dim, c[3], dtype;
+    float* rowpart[3]; float* colpart[3];
+    int* counters;
+    const float* lcsa_w1[3]; const float* lcsa_b1[3]; const float* lcsa_bn_scale[3]; const float* lcsa_bn_shift[3];
+    float* lcsa_rowsum[3]; float* lcsa_A[3]; float* lcsa_Sm[3];
+} KadPyramidArgs;
+int kad_pyramid_lcsa_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W);
+int kad_pyramid_project_lcsa(const KadPyramidArgs* args, void* stream);
 
 /* Average pool, kernel = stride = pool, floor mode, NHWC: F.avg_pool2d as used for the branch pyramid
  * (KAD-Conv/kadconv/kad_conv.py:115) when the pooled tensor feeds the tensor-core 1x1 GEMM. */
@@ -255,8 +284,14 @@ typedef struct KadLayerArgs {
     int B, H, W, dim, dtype;
     KadBranchParams br[3];
     int out_cstride;     /* elements per pixel of `out` (0 = dim): the layer can write into a channel slice of a wider tensor */
+    int* counters;       /* NULL, or device int[B], zero before the first call and left zero by every call: lets the pyramid kernel
+                            finish the LCSA's first stage in its tail and the deformable convolutions evaluate the mask in-kernel
+                            (five launches per layer instead of eleven) when the shape qualifies */
 } KadLayerArgs;
 size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches);
+/* 1 if kad_kadconv_forward runs this shape as five launches when `counters` is given (kad_pyramid_project_lcsa, three
+ * kad_dsc_forward with the in-kernel LCSA mask, merge): all three branches on path 3 and the LCSA operands fit shared memory. */
+int kad_kadconv_uses_inline_mask(int B, int H, int W, int dim, int dtype, int tc_branches);
 int kad_kadconv_forward(const KadLayerArgs* args, void* stream);
 
 /* Batched detection post-processing, one launch for the whole batch. Replaces non_max_suppression

@@ -27,6 +27,7 @@ int dsc_tc_tiles(int H, int W);
 int launch_dsc_tc(const KadDscArgs& a, cudaStream_t st);
 int dsc_mma_tiles(int H, int W);
 bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
+bool dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W);
 int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st);
 
 }  // namespace kad
@@ -44,6 +45,7 @@ extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {
 }
 
 extern "C" int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) { return dsc_mma_supported(Cin, Cout, dtype, H, W) ? 1 : 0; }
+extern "C" int kad_dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W) { return dsc_mma_inline_mask_supported(Cin, Cout, dtype, H, W) ? 1 : 0; }
 
 extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
     KAD_CHECK_ARG(a != nullptr, "kad_dsc_forward: null args");

@@ -23,6 +23,9 @@
 //         deform  offsets and modulation mask read from global memory
 //         fused   the offset convolution runs first on the same pixels and its 18 outputs go through shared memory
 //                 straight into the sampling geometry: the offset tensor never exists in global memory.
+//         inline  fused, and the LCSA modulation mask (kad_conv.py:24-39,:65) is evaluated by the lane that owns the pixel
+//                 from the row means and the per-column terms of the separable 1x11 stage (a few KB per image, prepared
+//                 by the pyramid kernel): the mask tensor (36 bytes per pixel, written and read back) never exists either.
 #include "kad_mma.cuh"
 
 namespace kad {
@@ -42,6 +45,10 @@ struct MmaParams {
     int H, W, Cin, Cout, KC, align;
     int offset_f32, mask_f32, y_f32, act;
     int B, win_margin;                  // win_margin: rows staged above / below the 3x3 halo for the learned offsets
+    // inline mode: LCSA operands. rowsum [B][H][Cin] (sums over x), A [B][W][Cp], Sm [W][Cp] (Cp = Cin rounded up to 4),
+    // w2 [Cin][11], b2 [Cin], w3 [9][Cin], b3 [9]
+    const float* l_rowsum; const float* l_A; const float* l_Sm; const float* l_w2; const float* l_b2; const float* l_w3; const float* l_b3;
+    int Cp, rm_rows;                    // rm_rows: image rows a group of 256 pixels can span, + 10 for the 11x1 window
 };
 
 constexpr int SCRATCH_PER_WARP = 4224;  // sampling table (3 taps x 32 pixels x 32 bytes), later the warp's output tile (+ 16 bytes of shift)
@@ -137,20 +144,68 @@ __device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned c
     }
 }
 
-template <typename T, int NT, int MODE, int ALIGN, int KCT>      // MODE 0 plain, 1 deform, 2 fused
+// LCSA modulation mask of one pixel (column x of image row h), the arithmetic of lcsa_mask_flat_kernel in the same order:
+//   h1(r, c) = relu(rowmean[r][c] * Sm[x][c] + A[x][c])        (1x11 depthwise + BatchNorm + ReLU, separated)
+//   v(c)     = b2[c] + sum_k w2[c][k] * h1(h + k - 5, c)       (11x1 depthwise, zero padding: rows outside contribute 0)
+//   mask[j]  = sigmoid(b3[j] + sum_c w3[j][c] * v(c))
+// rm: staged row means, row (h - 5) first, Cp floats per row; sw2 / sw3: [Cp][12] (slot 11 of sw2 = b2); valid: bit k set
+// when row h + k - 5 lies inside the image (BORDER = false: the caller knows all 11 rows do).
+template <bool BORDER>
+__device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* __restrict__ A, const float* __restrict__ Sm, const float* rm,
+                                                const float* sw2, const float* sw3, const float* __restrict__ b3, int Cp, uint32_t valid) {
+    float logit[9];
+#pragma unroll
+    for (int j = 0; j < 9; ++j) logit[j] = __ldg(b3 + j);
+    const float4* A4 = reinterpret_cast<const float4*>(A);
+    const float4* S4 = reinterpret_cast<const float4*>(Sm);
+    const float4* w24 = reinterpret_cast<const float4*>(sw2);
+    const float4* w34 = reinterpret_cast<const float4*>(sw3);
+#pragma unroll 1
+    for (int c4 = 0; c4 < (Cp >> 2); ++c4) {
+        const float4 av = __ldg(A4 + c4), sv = __ldg(S4 + c4);
+        const float aa[4] = {av.x, av.y, av.z, av.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            const int c = 4 * c4 + j4;
+            const float a = aa[j4], s = ss[j4];
+            const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
+            const float uk[11] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w, u2.x, u2.y, u2.z};
+            float v = u2.w;           // bias of the 11x1 convolution (0 for a padding channel, whose weights are 0 as well)
+            const float* r = rm + c;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                float tv = fmaxf(fmaf(r[k * Cp], s, a), 0.f);
+                if (BORDER && !((valid >> k) & 1u)) tv = 0.f;
+                v = fmaf(uk[k], tv, v);
+            }
+            const float4 q0 = w34[3 * c], q1 = w34[3 * c + 1], q2 = w34[3 * c + 2];
+            logit[0] = fmaf(q0.x, v, logit[0]); logit[1] = fmaf(q0.y, v, logit[1]); logit[2] = fmaf(q0.z, v, logit[2]);
+            logit[3] = fmaf(q0.w, v, logit[3]); logit[4] = fmaf(q1.x, v, logit[4]); logit[5] = fmaf(q1.y, v, logit[5]);
+            logit[6] = fmaf(q1.z, v, logit[6]); logit[7] = fmaf(q1.w, v, logit[7]); logit[8] = fmaf(q2.x, v, logit[8]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 9; ++j) mk[j] = sigmoidf_(logit[j]);
+}
+
+template <typename T, int NT, int MODE, int ALIGN, int KCT>      // MODE 0 plain, 1 deform, 2 fused, 3 fused + inline LCSA mask
 __global__ void __launch_bounds__(MMA_THREADS, NT <= 4 ? 2 : 1)
 dsc_mma_kernel(const MmaParams p) {
     constexpr int COP = NT * 8;
     extern __shared__ __align__(16) unsigned char smem_mma[];
     const int KC = KCT ? KCT : p.KC;
     uint2* Bs = reinterpret_cast<uint2*>(smem_mma);                                   // [9][KC][NT][32]
+    constexpr bool FUSED = MODE >= 2, INLINE = MODE == 3;
     uint2* Bo = Bs + 9 * KC * NT * 32;                                                // [9][KC][3][32]   (fused)
-    unsigned char* cur = reinterpret_cast<unsigned char*>(Bo + (MODE == 2 ? 9 * KC * NT_OFF * 32 : 0));
+    unsigned char* cur = reinterpret_cast<unsigned char*>(Bo + (FUSED ? 9 * KC * NT_OFF * 32 : 0));
     unsigned char* scratch = cur; cur += MMA_WARPS * SCRATCH_PER_WARP;
     float* ep = reinterpret_cast<float*>(cur); cur += 3 * COP * 4;                    // scale | shift | post
     float* red = reinterpret_cast<float*>(cur); cur += MMA_WARPS * COP * 4;
-    float* offs = reinterpret_cast<float*>(cur); cur += (MODE == 2 ? MMA_WARPS * 32 * OFF_PITCH * 4 : 0);
-    float* boffs = reinterpret_cast<float*>(cur); cur += (MODE == 2 ? 32 * 4 : 0);    // [24] (fused)
+    float* offs = reinterpret_cast<float*>(cur); cur += (FUSED ? MMA_WARPS * 32 * OFF_PITCH * 4 : 0);
+    float* boffs = reinterpret_cast<float*>(cur); cur += (FUSED ? 32 * 4 : 0);        // [24] (fused)
+    float* sw2 = reinterpret_cast<float*>(cur); cur += (INLINE ? p.Cp * 48 : 0);      // [Cp][12] 11x1 taps, slot 11 = bias (inline)
+    float* sw3 = reinterpret_cast<float*>(cur); cur += (INLINE ? p.Cp * 48 : 0);      // [Cp][12] 1x1 weights of the 9 mask outputs
+    float* rms = reinterpret_cast<float*>(cur); cur += (INLINE ? p.rm_rows * p.Cp * 4 : 0);   // [rm_rows][Cp] row means of the group's rows
     const uint32_t zoff = static_cast<uint32_t>(cur - smem_mma); cur += ZERO_BYTES;   // the block of zeros
     const uint32_t wdata = static_cast<uint32_t>(cur - smem_mma) + 16;                // staged rows start here (16 bytes of slack in front)
 
@@ -186,9 +241,16 @@ dsc_mma_kernel(const MmaParams p) {
         const int sel0 = static_cast<int>(wdata) - static_cast<int>(static_cast<ptrdiff_t>(a16) - static_cast<ptrdiff_t>(reinterpret_cast<uintptr_t>(gimg)));
         if (first) {
             stage_weights<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
-            if (MODE == 2) {
+            if (FUSED) {
                 stage_weights<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
                 if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
+            }
+            if (INLINE) {
+                for (int e = tid; e < 12 * p.Cp; e += MMA_THREADS) {
+                    const int c = e / 12, k = e - c * 12;
+                    sw3[e] = (k < 9 && c < Cin) ? p.l_w3[k * Cin + c] : 0.f;
+                    sw2[e] = c < Cin ? (k < 11 ? p.l_w2[c * 11 + k] : p.l_b2[c]) : 0.f;
+                }
             }
             for (int e = tid; e < COP; e += MMA_THREADS) {
                 const bool on = e < Cout;
@@ -206,8 +268,35 @@ dsc_mma_kernel(const MmaParams p) {
         const int mpy = mypix / W, mpx = mypix - mpy * W;
         const size_t gp = (size_t)b * HW + mypix;
         float mk[9];
+        if (INLINE) {
+            // row means of the rows this group's 11x1 windows reach (0 outside the image), then every lane evaluates its pixel's mask
+            const int r_lo = base / W, nrm = last / W - r_lo + 11;
+            const float invW = 1.f / (float)W;
+            for (int e = tid; e < nrm * p.Cp; e += MMA_THREADS) {
+                const int j = e / p.Cp, c = e - j * p.Cp, hh = r_lo - 5 + j;
+                rms[e] = (hh >= 0 && hh < H && c < Cin) ? p.l_rowsum[((size_t)b * H + hh) * Cin + c] * invW : 0.f;
+            }
+            __syncthreads();
 #pragma unroll
-        for (int k = 0; k < 9; ++k) mk[k] = (MODE != 0 && mylive && p.mask) ? load_mixed<T>(p.mask, gp * 9 + k, p.mask_f32) : 1.f;
+            for (int k = 0; k < 9; ++k) mk[k] = 1.f;
+            uint32_t valid = 0x7ffu;
+            if (mylive) {
+                valid = 0;
+#pragma unroll
+                for (int k = 0; k < 11; ++k) valid |= (uint32_t)(mpy + k - 5 >= 0 && mpy + k - 5 < H) << k;
+            }
+            const bool border = __any_sync(0xffffffffu, valid != 0x7ffu);
+            if (mylive) {
+                const float* Ap = p.l_A + ((size_t)b * W + mpx) * p.Cp;
+                const float* Sp = p.l_Sm + (size_t)mpx * p.Cp;
+                const float* rmp = rms + (mpy - r_lo) * p.Cp;
+                if (border) lcsa_mask_pixel<true>(mk, Ap, Sp, rmp, sw2, sw3, p.l_b3, p.Cp, valid);
+                else lcsa_mask_pixel<false>(mk, Ap, Sp, rmp, sw2, sw3, p.l_b3, p.Cp, valid);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 9; ++k) mk[k] = (MODE != 0 && mylive && p.mask) ? load_mixed<T>(p.mask, gp * 9 + k, p.mask_f32) : 1.f;
+        }
         uint32_t myvm = 0;                                     // which 3x3 neighbours of my pixel are inside the image
         if (mylive) {
 #pragma unroll
@@ -242,7 +331,7 @@ dsc_mma_kernel(const MmaParams p) {
             if (MODE == 0) {
                 plain_pass<T, NT, ALIGN, KCT>(acc, smem_mma, so, vm, zoff, Bs, KC, Cin, W, lane);
             } else {
-                if (MODE == 2) {
+                if (FUSED) {
                     // offset convolution of the warp's 32 pixels -> shared memory [32][18]
                     float oacc[2][NT_OFF][4];
 #pragma unroll
@@ -274,7 +363,7 @@ dsc_mma_kernel(const MmaParams p) {
                         bool out = false;
                         if (mylive) {
                             float dy, dx;
-                            if (MODE == 2) { dy = my_offs[lane * OFF_PITCH + 2 * k]; dx = my_offs[lane * OFF_PITCH + 2 * k + 1]; }
+                            if (FUSED) { dy = my_offs[lane * OFF_PITCH + 2 * k]; dx = my_offs[lane * OFF_PITCH + 2 * k + 1]; }
                             else { dy = load_mixed<T>(p.offset, gp * 18 + 2 * k, p.offset_f32); dx = load_mixed<T>(p.offset, gp * 18 + 2 * k + 1, p.offset_f32); }
                             const float m = r == 0 ? mk[kk] : (r == 1 ? mk[3 + kk] : mk[6 + kk]);
                             const float sy = (float)(mpy + r - 1) + dy, sx = (float)(mpx + kk - 1) + dx;
@@ -407,8 +496,19 @@ inline int pick_nt(int Cout) {
 // Shared memory of one block without the staged rows.
 inline size_t fixed_smem(int KC, int nt, int mode) {
     size_t s = (size_t)9 * KC * nt * 32 * 8 + (size_t)MMA_WARPS * SCRATCH_PER_WARP + (size_t)3 * nt * 8 * 4 + (size_t)MMA_WARPS * nt * 8 * 4 + ZERO_BYTES;
-    if (mode == 2) s += (size_t)9 * KC * NT_OFF * 32 * 8 + (size_t)MMA_WARPS * 32 * OFF_PITCH * 4 + 32 * 4;
+    if (mode >= 2) s += (size_t)9 * KC * NT_OFF * 32 * 8 + (size_t)MMA_WARPS * 32 * OFF_PITCH * 4 + 32 * 4;
     return s;
+}
+// Image rows a group of 256 consecutive pixels can span, + 10 for the reach of the LCSA's 11x1 window.
+inline int lcsa_rm_rows(int H, int W) {
+    int rows = (W + MMA_THREADS - 2) / W + 1;
+    if (rows > H) rows = H;
+    return rows + 10;
+}
+// Extra shared memory of the inline-mask mode: 11x1 taps and 1x1 weights ([Cp][12] each) and the staged row means.
+inline size_t lcsa_smem(int Cin, int H, int W) {
+    const int Cp = (Cin + 3) & ~3;
+    return (size_t)2 * Cp * 48 + (size_t)lcsa_rm_rows(H, W) * Cp * 4;
 }
 // Bytes for the staged rows with `margin` rows for the learned offsets (incl. alignment slack on both sides).
 inline size_t window_smem(int H, int W, int Cin, int margin) {
@@ -436,6 +536,11 @@ template <typename T, int NT>
 int launch_mma_mode(const MmaParams& p, int mode, dim3 grid, size_t smem, cudaStream_t st) {
     if (mode == 0) return launch_mma_align<T, NT, 0, 0>(p, grid, smem, st);
     if (mode == 1) return launch_mma_align<T, NT, 1, 0>(p, grid, smem, st);
+    if (mode == 3) {
+        if (NT == 2 && p.KC == 1) return launch_mma_align<T, NT, 3, (NT == 2 ? 1 : 0)>(p, grid, smem, st);
+        if (NT == 3 && p.KC == 2) return launch_mma_align<T, NT, 3, (NT == 3 ? 2 : 0)>(p, grid, smem, st);
+        return launch_mma_align<T, NT, 3, 0>(p, grid, smem, st);
+    }
     // the fused kernel at the detector's widths (<= 16 channels: NT 2, one chunk; 17-24 channels: NT 3, two chunks) is
     // compiled with the chunk count as a constant: index arithmetic folds and the chunk loops unroll
     if (NT == 2 && p.KC == 1) return launch_mma_align<T, NT, 2, (NT == 2 ? 1 : 0)>(p, grid, smem, st);
@@ -479,21 +584,36 @@ bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) {
     return fixed_smem((Cin + 15) / 16, nt, 2) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
 }
 
+// Inline-mask mode: the fused mode's footprint plus the LCSA operands must fit with at least the 3x3 halo staged.
+bool dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W) {
+    if (!dsc_mma_supported(Cin, Cout, dtype, H, W)) return false;
+    return fixed_smem((Cin + 15) / 16, pick_nt(Cout), 3) + lcsa_smem(Cin, H, W) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
+}
+
 int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
     const bool fused = a.offset_weight != nullptr;
-    const int mode = fused ? 2 : (a.offset ? 1 : 0);
+    const bool inline_mask = a.lcsa_rowsum != nullptr;
+    KAD_CHECK_ARG(!inline_mask || fused, "kad_dsc_forward: the in-kernel LCSA mask needs the fused offset convolution (offset_weight)");
+    KAD_CHECK_ARG(!inline_mask || (a.lcsa_A && a.lcsa_Sm && a.lcsa_w2 && a.lcsa_b2 && a.lcsa_w3 && a.lcsa_b3), "kad_dsc_forward: LCSA operand missing");
+    KAD_CHECK_ARG(!inline_mask || ((uintptr_t)a.lcsa_A % 16 == 0 && (uintptr_t)a.lcsa_Sm % 16 == 0), "kad_dsc_forward: lcsa_A / lcsa_Sm must be 16-byte aligned");
+    if (inline_mask && !dsc_mma_inline_mask_supported(a.Cin, a.Cout, a.dtype, a.H, a.W))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_dsc_forward: the in-kernel LCSA mask does not fit shared memory for Cin=%d H=%d W=%d", a.Cin, a.H, a.W);
+    const int mode = inline_mask ? 3 : (fused ? 2 : (a.offset ? 1 : 0));
     KAD_CHECK_ARG(mode != 0 || a.mask == nullptr, "kad_dsc_forward: the warp-MMA path takes a mask only together with offsets");
     KAD_CHECK_ARG((uintptr_t)a.x % 16 == 0, "kad_dsc_forward: the warp-MMA path needs x aligned to 16 bytes");
     KAD_CHECK_ARG((uintptr_t)a.y % 4 == 0, "kad_dsc_forward: the warp-MMA path needs y aligned to 4 bytes");
     MmaParams p{};
     p.x = a.x; p.offset = fused ? nullptr : a.offset; p.mask = a.mask; p.Wt = (const float*)a.weight;
     p.Woff = a.offset_weight; p.boff = a.offset_bias;
+    if (inline_mask) p.mask = nullptr;
     p.scale = a.scale; p.shift = a.shift; p.post = a.post; p.y = a.y; p.gap_partial = a.gap_partial;
     p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KC = (a.Cin + 15) / 16; p.B = a.B;
     p.align = a.Cin % 4 == 0 ? 8 : (a.Cin % 2 == 0 ? 4 : 2);
     p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
+    p.l_rowsum = a.lcsa_rowsum; p.l_A = a.lcsa_A; p.l_Sm = a.lcsa_Sm; p.l_w2 = a.lcsa_w2; p.l_b2 = a.lcsa_b2; p.l_w3 = a.lcsa_w3; p.l_b3 = a.lcsa_b3;
+    p.Cp = (a.Cin + 3) & ~3; p.rm_rows = lcsa_rm_rows(a.H, a.W);
     const int nt = pick_nt(a.Cout);
-    size_t smem = fixed_smem(p.KC, nt, mode);
+    size_t smem = fixed_smem(p.KC, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W) : 0);
     // rows of margin for the learned offsets: as many as fit, at most 2 (none for the plain convolution); the narrow
     // variants (128 registers) keep two blocks per SM when the halo alone allows it
     const size_t soft = (nt <= 4 && smem + window_smem(a.H, a.W, a.Cin, 0) <= SMEM_TWO_BLOCKS) ? SMEM_TWO_BLOCKS : SMEM_ONE_BLOCK;

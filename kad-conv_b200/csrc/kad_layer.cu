@@ -72,6 +72,7 @@ struct LayerPlan {
     BranchWs ws[3];
     int path[3], tiles[3];
     bool pyramid, partials;      // one kernel for the three projections; LCSA sums taken from that kernel's partial sums
+    bool inline_mask;            // LCSA first stage in the pyramid kernel's tail, mask evaluated inside the deformable convolutions
     int nct, nrg;
     size_t bytes;
 };
@@ -94,6 +95,9 @@ LayerPlan plan_layer(int B, int H, int W, int dim, int dtype, int tc_mask) {
         o = L.ws[i].end;
     }
     L.bytes = o;
+    L.inline_mask = L.partials && kad_pyramid_lcsa_supported(dim, widths[0], widths[1], widths[2], dtype, H, W) != 0;
+    for (int i = 0; i < 3; ++i)
+        L.inline_mask = L.inline_mask && L.path[i] == 3 && kad_dsc_mma_inline_mask_supported(widths[i], widths[i], dtype, H >> i, W >> i) != 0;
     return L;
 }
 
@@ -105,6 +109,11 @@ using namespace kad;
 extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches) {
     if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
     return plan_layer(B, H, W, dim, dtype, tc_branches).bytes;
+}
+
+extern "C" int kad_kadconv_uses_inline_mask(int B, int H, int W, int dim, int dtype, int tc_branches) {
+    if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
+    return plan_layer(B, H, W, dim, dtype, tc_branches).inline_mask ? 1 : 0;
 }
 
 extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
@@ -134,7 +143,22 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     // the three pooled projections read the same x: one kernel on the caller's stream, before the branches fork
     const bool pyramid = L.pyramid && (uintptr_t)a->x % 16 == 0;
     const bool partials = pyramid && L.partials;
-    if (pyramid) {
+    const bool inline_mask = partials && L.inline_mask && a->counters != nullptr;
+    if (inline_mask) {
+        KadPyramidArgs q{};
+        q.x = a->x; q.B = a->B; q.H = a->H; q.W = a->W; q.dim = a->dim; q.dtype = a->dtype; q.counters = a->counters;
+        for (int i = 0; i < 3; ++i) {
+            const KadBranchParams& br = a->br[i];
+            const int Cp = (br.c + 3) & ~3, w = a->W >> i;
+            q.w[i] = br.w_proj; q.bias[i] = br.b_proj; q.t[i] = ws + L.ws[i].t; q.c[i] = br.c;
+            q.rowpart[i] = (float*)(ws + L.ws[i].rowpart); q.colpart[i] = (float*)(ws + L.ws[i].colpart);
+            q.lcsa_w1[i] = br.lcsa_w1; q.lcsa_b1[i] = br.lcsa_b1; q.lcsa_bn_scale[i] = br.lcsa_bn_scale; q.lcsa_bn_shift[i] = br.lcsa_bn_shift;
+            q.lcsa_rowsum[i] = (float*)(ws + L.ws[i].rows);
+            q.lcsa_A[i] = (float*)(ws + L.ws[i].scratch); q.lcsa_Sm[i] = (float*)(ws + L.ws[i].scratch) + (size_t)a->B * w * Cp;
+        }
+        rc = kad_pyramid_project_lcsa(&q, stream);
+        if (rc) return rc;
+    } else if (pyramid) {
         const float* w3[3] = {a->br[0].w_proj, a->br[1].w_proj, a->br[2].w_proj};
         const float* b3[3] = {a->br[0].b_proj, a->br[1].b_proj, a->br[2].b_proj};
         void* t3[3] = {ws + L.ws[0].t, ws + L.ws[1].t, ws + L.ws[2].t};
@@ -162,7 +186,9 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
             rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
             if (rc) break;
         }
-        if (partials) {
+        if (inline_mask) {
+            // nothing to launch: the pyramid kernel has left the LCSA operands, the deformable convolution evaluates the mask
+        } else if (partials) {
             rc = kad_lcsa_mask_from_partials((const float*)(ws + p.rowpart), L.nct, (const float*)(ws + p.colpart), L.nrg,
                                              br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift, br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3,
                                              (float*)(ws + p.scratch), (float*)(ws + p.rows), ws + p.mask, a->B, h, w, c, 1, a->dtype, s);
@@ -186,7 +212,15 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
             if (rc) break;
             q.offset = ws + p.offset; q.offset_f32 = 1;
         }
-        q.x = ws + p.t; q.mask = ws + p.mask; q.mask_f32 = 1;
+        q.x = ws + p.t;
+        if (inline_mask) {
+            const int Cp = (c + 3) & ~3;
+            q.lcsa_rowsum = (const float*)(ws + p.rows);
+            q.lcsa_A = (const float*)(ws + p.scratch); q.lcsa_Sm = (const float*)(ws + p.scratch) + (size_t)a->B * w * Cp;
+            q.lcsa_w2 = br.lcsa_w2; q.lcsa_b2 = br.lcsa_b2; q.lcsa_w3 = br.lcsa_w3; q.lcsa_b3 = br.lcsa_b3;
+        } else {
+            q.mask = ws + p.mask; q.mask_f32 = 1;
+        }
         q.weight = path == 1 ? br.w_dsc_tc : (const void*)br.w_dsc_simt;
         q.scale = br.ep_scale; q.shift = br.ep_shift; q.post = br.ep_post; q.y = ws + p.y; q.gap_partial = (float*)(ws + p.gap);
         q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;

@@ -20,7 +20,59 @@ struct PyramidParams {
     // sum over the rows this block covers (RT consecutive 4-row tiles); sums of the values as stored (rounded to T)
     float* rowpart[3]; float* colpart[3];
     int RT;
+    // optional LCSA preparation in the tail (set counters): see lcsa_prepare_image
+    int* counters;
+    const float* lw1[3]; const float* lb1[3]; const float* lbn_m[3]; const float* lbn_a[3];
+    float* l_rowsum[3]; float* l_A[3]; float* l_Sm[3];
 };
+
+// First, separable stage of one branch's LCSA for image b, from the partial sums every block of the image has written:
+// row sums (over the column tiles), column sums (over the row groups), then per column w and channel c
+//   A[b][w][c] = (sum_k w1[c][k] * colmean[w + k - 5][c] + b1[c]) * bn_m[c] + bn_a[c],   Sm[w][c] = (sum of the taps inside the row) * bn_m[c]
+// (the 1x11 convolution of rowmean[h] + colmean[w] separates into rowmean[h] * S[w] + conv(colmean)[w]; zero padding makes S
+// depend on w). Same arithmetic and summation order as lcsa_prep_partials_kernel, which does this in a launch of its own.
+// One block, all threads; partial sums are read past L1 (other blocks wrote them). colsum_s: W*C floats of shared memory.
+__device__ void lcsa_prepare_image(const float* rowpart, int nct, const float* colpart, int nrg,
+                                   const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ bn_m, const float* __restrict__ bn_a,
+                                   float* __restrict__ A, float* __restrict__ Sm, float* __restrict__ rowsum,
+                                   int b, int H, int W, int C, float* colsum_s, int tid) {
+    const int Cp = (C + 3) & ~3;
+    const float* cp = colpart + (size_t)b * nrg * W * C;
+    for (int e = tid; e < W * C; e += MMA_THREADS) {
+        float s = 0.f;
+        for (int g = 0; g < nrg; ++g) s += __ldcg(cp + (size_t)g * W * C + e);
+        colsum_s[e] = s;
+    }
+    for (int e = tid; e < H * C; e += MMA_THREADS) {
+        const int h = e / C, c = e - h * C;
+        float s = 0.f;
+        for (int k = 0; k < nct; ++k) s += __ldcg(rowpart + (((size_t)b * H + h) * nct + k) * C + c);
+        rowsum[((size_t)b * H + h) * C + c] = s;
+    }
+    __syncthreads();
+    const float invH = 1.f / (float)H;
+    for (int e = tid; e < W * Cp; e += MMA_THREADS) {
+        const int w = e / Cp, c = e - w * Cp;
+        float av = 0.f, sv = 0.f;
+        if (c < C) {
+            float conv = 0.f, S = 0.f;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const int ww = w + k - 5;
+                if (ww >= 0 && ww < W) {
+                    const float wk = w1[c * 11 + k];
+                    conv = fmaf(wk, colsum_s[ww * C + c] * invH, conv);
+                    S += wk;
+                }
+            }
+            const float m = bn_m[c];
+            av = (conv + b1[c]) * m + bn_a[c]; sv = S * m;
+        }
+        A[((size_t)b * W + w) * Cp + c] = av;
+        if (b == 0) Sm[(size_t)w * Cp + c] = sv;
+    }
+    __syncthreads();
+}
 
 // Weight fragments of a 1x1 convolution w[Cout][Cin] (see stage_weights of the deformable kernel for the slot layout).
 template <typename T>
@@ -239,6 +291,24 @@ pyramid_project_kernel(const PyramidParams p) {
             cabase += tw * ci;
         }
     }
+
+    // ---- LCSA preparation by whichever block finishes this image last ----------------------------------------------------
+    if (p.counters) {
+        __shared__ int s_last;
+        __threadfence();                                      // this block's partial sums are visible device-wide ...
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(p.counters + b, 1) == (int)(gridDim.x * gridDim.y) - 1;     // ... before it is counted
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            float* colsum_s = reinterpret_cast<float*>(sm);   // everything staged in shared memory is dead by now
+#pragma unroll 1
+            for (int i = 0; i < 3; ++i)
+                lcsa_prepare_image(p.rowpart[i], gridDim.x, p.colpart[i], gridDim.y, p.lw1[i], p.lb1[i], p.lbn_m[i], p.lbn_a[i],
+                                   p.l_A[i], p.l_Sm[i], p.l_rowsum[i], b, p.H >> i, p.W >> i, p.c[i], colsum_s, tid);
+            if (tid == 0) p.counters[b] = 0;                  // ready for the next launch
+        }
+    }
 }
 
 inline int pyr_nt(int c) {
@@ -313,6 +383,35 @@ extern "C" int kad_pyramid_partial_dims(int B, int H, int W, int dim, int c0, in
     return KAD_OK;
 }
 
+namespace kad {
+namespace {
+int launch_pyramid(PyramidParams& p, int dtype, cudaStream_t st) {
+    const int* c = p.c;
+    const size_t smem = pyramid_plan(p.W, p.dim, c, &p);
+    const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
+    const int nct = (p.W + p.TW - 1) / p.TW;
+    p.RT = pyramid_row_tiles_per_block(p.B, p.H, nct);
+    dim3 grid(nct, ((p.H + 3) / 4 + p.RT - 1) / p.RT, p.B);
+    KAD_CHECK_ARG(grid.y <= 65535, "kad_pyramid_project: image too tall");
+#define KAD_PYR(TT, N)                                                                                                \
+    {                                                                                                                 \
+        auto kern = pyramid_project_kernel<TT, N>;                                                                    \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "pyramid smem attribute: %s", cudaGetErrorString(e));         \
+        kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
+    }
+#define KAD_PYR_NT(TT)                                                                                                \
+    switch (nt) { case 2: KAD_PYR(TT, 2) break; case 3: KAD_PYR(TT, 3) break; case 4: KAD_PYR(TT, 4) break;          \
+                  case 6: KAD_PYR(TT, 6) break; default: KAD_PYR(TT, 8) break; }
+    if (dtype == KAD_F16) { KAD_PYR_NT(__half) } else { KAD_PYR_NT(__nv_bfloat16) }
+#undef KAD_PYR_NT
+#undef KAD_PYR
+    KAD_CHECK_LAUNCH("pyramid_project_kernel");
+    return KAD_OK;
+}
+}  // namespace
+}  // namespace kad
+
 extern "C" int kad_pyramid_project(const void* x, const float* const* w, const float* const* bias, void* const* t,
                                    int B, int H, int W, int dim, const int* c, int dtype,
                                    float* const* rowpart, float* const* colpart, void* stream) {
@@ -334,26 +433,36 @@ extern "C" int kad_pyramid_project(const void* x, const float* const* w, const f
         }
     }
     KAD_CHECK_ARG((uintptr_t)x % 16 == 0, "kad_pyramid_project: x must be 16-byte aligned");
-    const size_t smem = pyramid_plan(W, dim, c, &p);
-    const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
-    const int nct = (W + p.TW - 1) / p.TW;
-    p.RT = pyramid_row_tiles_per_block(B, H, nct);
-    dim3 grid(nct, ((H + 3) / 4 + p.RT - 1) / p.RT, B);
-    KAD_CHECK_ARG(grid.y <= 65535, "kad_pyramid_project: image too tall");
-    cudaStream_t st = (cudaStream_t)stream;
-#define KAD_PYR(TT, N)                                                                                                \
-    {                                                                                                                 \
-        auto kern = pyramid_project_kernel<TT, N>;                                                                    \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
-        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "pyramid smem attribute: %s", cudaGetErrorString(e));         \
-        kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
+    return launch_pyramid(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int kad_pyramid_lcsa_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W) {
+    if (!kad_pyramid_project_supported(dim, c0, c1, c2, dtype, H, W)) return 0;
+    const int c[3] = {c0, c1, c2};
+    const size_t smem = pyramid_plan(W, dim, c, nullptr);
+    size_t need = (size_t)W * c0 * 4;                        // the widest column-sum table (branch 0)
+    if ((size_t)(W >> 1) * c1 * 4 > need) need = (size_t)(W >> 1) * c1 * 4;
+    if ((size_t)(W >> 2) * c2 * 4 > need) need = (size_t)(W >> 2) * c2 * 4;
+    return need <= smem ? 1 : 0;
+}
+
+extern "C" int kad_pyramid_project_lcsa(const KadPyramidArgs* a, void* stream) {
+    KAD_CHECK_ARG(a && a->x && a->counters, "kad_pyramid_project_lcsa: null pointer");
+    KAD_CHECK_ARG(a->B > 0 && a->B <= 65535, "kad_pyramid_project_lcsa: bad batch %d", a->B);
+    if (!kad_pyramid_lcsa_supported(a->dim, a->c[0], a->c[1], a->c[2], a->dtype, a->H, a->W))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_pyramid_project_lcsa: shape not supported (dim=%d c=%d,%d,%d H=%d W=%d dtype=%d)",
+                    a->dim, a->c[0], a->c[1], a->c[2], a->H, a->W, a->dtype);
+    PyramidParams p{};
+    p.x = a->x; p.B = a->B; p.H = a->H; p.W = a->W; p.dim = a->dim; p.counters = a->counters;
+    for (int i = 0; i < 3; ++i) {
+        KAD_CHECK_ARG(a->w[i] && a->t[i] && a->rowpart[i] && a->colpart[i] && a->lcsa_w1[i] && a->lcsa_b1[i] && a->lcsa_bn_scale[i] && a->lcsa_bn_shift[i] &&
+                      a->lcsa_rowsum[i] && a->lcsa_A[i] && a->lcsa_Sm[i], "kad_pyramid_project_lcsa: null pointer for branch %d", i);
+        KAD_CHECK_ARG((uintptr_t)a->t[i] % 4 == 0, "kad_pyramid_project_lcsa: t[%d] must be 4-byte aligned", i);
+        p.w[i] = a->w[i]; p.b[i] = a->bias[i]; p.t[i] = a->t[i]; p.c[i] = a->c[i];
+        p.rowpart[i] = a->rowpart[i]; p.colpart[i] = a->colpart[i];
+        p.lw1[i] = a->lcsa_w1[i]; p.lb1[i] = a->lcsa_b1[i]; p.lbn_m[i] = a->lcsa_bn_scale[i]; p.lbn_a[i] = a->lcsa_bn_shift[i];
+        p.l_rowsum[i] = a->lcsa_rowsum[i]; p.l_A[i] = a->lcsa_A[i]; p.l_Sm[i] = a->lcsa_Sm[i];
     }
-#define KAD_PYR_NT(TT)                                                                                                \
-    switch (nt) { case 2: KAD_PYR(TT, 2) break; case 3: KAD_PYR(TT, 3) break; case 4: KAD_PYR(TT, 4) break;          \
-                  case 6: KAD_PYR(TT, 6) break; default: KAD_PYR(TT, 8) break; }
-    if (dtype == KAD_F16) { KAD_PYR_NT(__half) } else { KAD_PYR_NT(__nv_bfloat16) }
-#undef KAD_PYR_NT
-#undef KAD_PYR
-    KAD_CHECK_LAUNCH("pyramid_project_kernel");
-    return KAD_OK;
+    KAD_CHECK_ARG((uintptr_t)a->x % 16 == 0, "kad_pyramid_project_lcsa: x must be 16-byte aligned");
+    return launch_pyramid(p, a->dtype, (cudaStream_t)stream);
 }

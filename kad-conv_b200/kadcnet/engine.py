@@ -275,5 +275,5 @@ class FastDetector(torch.nn.Module):
                 x = fn(x)
             ys.append(x if m.i in save else None)
         if not capturing:
-            ops.status_snapshot(x.device)
+            ops.status_snapshot(self.device)
         return x

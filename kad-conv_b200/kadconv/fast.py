@@ -118,6 +118,7 @@ def _layer_args(layer, st, dtype, H, W):
             if all(ops.lcsa_mask_from_partials_supported(H >> i, W >> i, br.c) for i, br in enumerate(st['branches'])):
                 launches -= 6      # row/column sums come out of the pyramid kernel
         st[key] = (a, tc_mask, keep, launches)
+        a.counters = ops.layer_counters(st['device']).data_ptr()
     return st[key]
 
 
@@ -148,6 +149,8 @@ def kadconv_forward_nhwc(layer, x, out=None, out_coff=0):
     a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out_ptr, ws.data_ptr(), nbytes
     a.status = ops.status_word(x.device).data_ptr()
     a.B, a.H, a.W, a.dim = B, H, W, C
+    if lib.kad_kadconv_uses_inline_mask(B, H, W, C, a.dtype, tc_mask):
+        launches -= 6              # LCSA first stage in the pyramid kernel's tail, mask inside the deformable convolutions
     _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward', launches)
     return out
 

@@ -153,13 +153,15 @@ def status_snapshot(device):
 
 
 def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=None, act=ACT_NONE,
-                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None, offset_weight=None, offset_bias=None):
+                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None, offset_weight=None, offset_bias=None, lcsa_inline=None):
     """Deformable 3x3 convolution with fused epilogue on NHWC tensors.
 
     x [B,H,W,Cin]; offset [B,H,W,18] (float32 or x.dtype) or None; mask [B,H,W,9] or None;
     weight: pack_dsc_weight_simt(...) for PATH_SIMT / PATH_MMA or pack_dsc_weight_tc(...) for PATH_TC.
     PATH_MMA only: offset_weight (pack_dsc_weight_simt of the offset convolution's weight, [9,Cin,18]) and
-    offset_bias ([18]) make the kernel compute the offsets itself instead of reading `offset`.
+    offset_bias ([18]) make the kernel compute the offsets itself instead of reading `offset`; with them, lcsa_inline =
+    dict(rowsum [B,H,Cin], A [B,W,Cp], Sm [W,Cp] from pyramid_project_lcsa, and the LCSA's w2 [Cin,11], b2, w3 [9,Cin], b3) makes
+    the kernel evaluate the modulation mask itself instead of reading `mask`.
     Returns y [B,H,W,Cout] (and the per-tile channel sums [B,tiles,Cout] when want_gap).
     """
     lib = _abi.load()
@@ -199,6 +201,16 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
             if _f32(offset_bias, 'offset_bias').numel() != 18:
                 raise ValueError('offset_bias must have 18 elements')
             a.offset_bias = offset_bias.data_ptr()
+    if lcsa_inline is not None:
+        if offset_weight is None:
+            raise ValueError('lcsa_inline goes with offset_weight (PATH_MMA)')
+        Cp = (Cin + 3) & ~3
+        want = {'rowsum': (B, H, Cin), 'A': (B, W, Cp), 'Sm': (W, Cp), 'w2': (Cin, 11), 'b2': (Cin,), 'w3': (9, Cin), 'b3': (9,)}
+        for name, shape in want.items():
+            t = _f32(lcsa_inline[name], 'lcsa_inline.' + name)
+            if tuple(t.shape) != shape:
+                raise ValueError(f'lcsa_inline[{name!r}] must be {shape}, got {tuple(t.shape)}')
+            setattr(a, 'lcsa_' + name, t.data_ptr())
     for name, t in (('scale', scale), ('shift', shift), ('post', post)):
         if t is not None:
             if _f32(t, name).numel() != Cout:
@@ -525,6 +537,59 @@ def stem_conv_u8(img_u8, w, bias, dtype, act=ACT_SILU, scale=1.0 / 255.0):
 
 def pyramid_project_supported(dim, cs, dtype, H, W):
     return dtype in _DT and bool(_abi.load().kad_pyramid_project_supported(dim, cs[0], cs[1], cs[2], _DT[dtype], H, W))
+
+
+_counters = {}
+
+
+def layer_counters(device):
+    """Per-device int32[65536] of zeros for the kernels that count finished blocks per image (every such kernel leaves
+    them zero again). Created on first use; create it outside any stream capture."""
+    key = (device.type, device.index)
+    if key not in _counters:
+        _counters[key] = torch.zeros(65536, dtype=torch.int32, device=device)
+    return _counters[key]
+
+
+def pyramid_lcsa_supported(dim, cs, dtype, H, W):
+    return dtype in _DT and bool(_abi.load().kad_pyramid_lcsa_supported(dim, cs[0], cs[1], cs[2], _DT[dtype], H, W))
+
+
+def dsc_mma_inline_mask_supported(Cin, Cout, dtype, H, W):
+    return dtype in _DT and bool(_abi.load().kad_dsc_mma_inline_mask_supported(Cin, Cout, _DT[dtype], H, W))
+
+
+def pyramid_project_lcsa(x, ws, bs, lcsas):
+    """pyramid_project that also finishes the first stage of the three LCSAs in the kernel's tail. lcsas[i]: dict with
+    w1 [c_i,11], b1, bn_m, bn_a (folded BatchNorm). Returns (ts, ops) where ops[i] = dict(rowsum [B,h_i,c_i], A [B,w_i,Cp_i],
+    Sm [w_i,Cp_i]) is what dsc_forward(..., lcsa_inline=...) consumes."""
+    x = _cuda(x, 'x')
+    B, H, W, dim = x.shape
+    cs = [int(w.shape[0]) for w in ws]
+    lib = _abi.load()
+    nct, nrg = ctypes.c_int(0), ctypes.c_int(0)
+    _abi.check(lib.kad_pyramid_partial_dims(B, H, W, dim, cs[0], cs[1], cs[2], dtype_code(x), ctypes.byref(nct), ctypes.byref(nrg)), 'kad_pyramid_partial_dims', 0)
+    a = _abi.KadPyramidArgs()
+    a.x = x.data_ptr(); a.B, a.H, a.W, a.dim, a.dtype = B, H, W, dim, dtype_code(x)
+    a.counters = layer_counters(x.device).data_ptr()
+    ts, outs, keep = [], [], []
+    for i in range(3):
+        h, w, c = H >> i, W >> i, cs[i]
+        Cp = (c + 3) & ~3
+        t = torch.empty((B, h, w, c), dtype=x.dtype, device=x.device)
+        rp = torch.empty((B, h, nct.value, c), dtype=torch.float32, device=x.device)
+        cp = torch.empty((B, nrg.value, w, c), dtype=torch.float32, device=x.device)
+        o = {'rowsum': torch.empty((B, h, c), dtype=torch.float32, device=x.device),
+             'A': torch.empty((B, w, Cp), dtype=torch.float32, device=x.device), 'Sm': torch.empty((w, Cp), dtype=torch.float32, device=x.device)}
+        a.w[i] = _f32(ws[i], 'w').data_ptr(); a.bias[i] = _f32(bs[i], 'bias').data_ptr() if bs[i] is not None else None
+        a.t[i] = t.data_ptr(); a.c[i] = c; a.rowpart[i] = rp.data_ptr(); a.colpart[i] = cp.data_ptr()
+        l = lcsas[i]
+        a.lcsa_w1[i] = _f32(l['w1'], 'w1').data_ptr(); a.lcsa_b1[i] = _f32(l['b1'], 'b1').data_ptr()
+        a.lcsa_bn_scale[i] = _f32(l['bn_m'], 'bn_m').data_ptr(); a.lcsa_bn_shift[i] = _f32(l['bn_a'], 'bn_a').data_ptr()
+        a.lcsa_rowsum[i] = o['rowsum'].data_ptr(); a.lcsa_A[i] = o['A'].data_ptr(); a.lcsa_Sm[i] = o['Sm'].data_ptr()
+        ts.append(t); outs.append(o); keep += [rp, cp]
+    _abi.check(lib.kad_pyramid_project_lcsa(ctypes.byref(a), _stream()), 'kad_pyramid_project_lcsa')
+    return ts, outs
 
 
 def pyramid_project(x, ws, bs, want_partials=False):

@@ -21,12 +21,17 @@ def _rng(seed, key):
     return np.random.default_rng([int(seed), zlib.crc32(key.encode())])
 
 
-def seeded_state_dict(shapes, seed=0, offset_std=0.5, scale_mode='uniform', cls_bias=-3.0):
+def seeded_state_dict(shapes, seed=0, offset_std=0.5, scale_mode='uniform', cls_bias=-3.0, weight_gain=1.0, cls_gain=60.0):
     """``shapes``: mapping key -> shape (e.g. from ``module.state_dict()``). Returns float32 tensors.
 
     offset_std: target standard deviation, in pixels, of the DSC offsets for unit-variance input.
     scale_mode: 'uniform' draws branch scales from U(0.5,1.5); 'normal' from N(0,1).
     cls_bias: mean of the detector's class-logit biases (stock init is about -10, which leaves NMS no candidates).
+    weight_gain: factor on every convolution / linear weight except the offset convolutions, the LCSA, the DFL and the class
+        logits. With 1.0 (the bound 1/sqrt(fan_in) of the reference's initialisers) the signal fades from layer to layer and a
+        60-layer detector computes nearly the same scores for every image and position; about 2.6 keeps it alive, so that
+        scores and boxes vary over the image (the acceptance test of the detector uses that).
+    cls_gain: factor on the class-logit weights of the detector head.
     """
     bn = {k[:-len('.running_mean')] for k in shapes if k.endswith('.running_mean')}
     out = {}
@@ -60,7 +65,9 @@ def seeded_state_dict(shapes, seed=0, offset_std=0.5, scale_mode='uniform', cls_
             fan_in = int(np.prod(shape[1:])) if len(shape) > 1 else shape[0]
             bound = 1.0 / math.sqrt(max(fan_in, 1))
             if '.cv3.' in key and key.endswith('.2.weight'):
-                bound *= 60.0   # detector class logits: spread the scores so that NMS is not a field of ties
+                bound *= cls_gain   # detector class logits: spread the scores so that NMS is not a field of ties
+            elif 'RCA_mask' not in key:
+                bound *= weight_gain
             v = g.uniform(-bound, bound, shape)
         else:  # plain conv / linear bias
             v = g.normal(0.0, 0.1, shape)

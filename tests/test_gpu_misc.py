@@ -374,3 +374,44 @@ def test_lcsa_mask_from_pyramid_partial_sums(shape, dtype):
         m1 = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], prm, dtype, mask_f32=True)
         m0 = ops.lcsa_mask(t, prm, mask_f32=True)
         assert (m1 - m0).abs().max().item() <= 2e-5
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((3, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
+                                         ((5, 48, 9, 30), torch.float16)])
+def test_inline_lcsa_mask_equals_mask_tensor(shape, dtype):
+    """The five-launch form of a KAD-Conv branch (LCSA first stage finished in the pyramid kernel's tail by the last block of each
+    image, mask evaluated inside the deformable convolution by the lane that owns the pixel) against the step-by-step form
+    (partial sums -> preparation kernel -> mask kernel -> mask tensor -> deformable convolution): same arithmetic in the same
+    order, so outputs and channel sums are bit-identical; also on the second call (the block counters reset themselves),
+    on image borders (rows nearer than 5 to the edge) and on maps where a group of 256 pixels spans many rows."""
+    from kadconv import ops
+    B, dim, H, W = shape
+    cs = (dim - 2 * (dim // 3), dim // 3, dim // 3)
+    f = lambda a: a.cuda()
+    x = nhwc(round_to(_rand((B, dim, H, W), 210), dtype)).cuda().to(dtype)
+    ws = [f(_rand((c, dim), 211 + i, 1.0 / np.sqrt(dim))) for i, c in enumerate(cs)]
+    bs = [f(_rand((c,), 215 + i, 0.1)) for i, c in enumerate(cs)]
+    prms = [dict(w1=f(_rand((c, 11), 220 + i, 0.3)), b1=f(_rand((c,), 223 + i, 0.1)), bn_m=f(1.0 + _rand((c,), 226 + i, 0.1)), bn_a=f(_rand((c,), 229 + i, 0.1)),
+                 w2=f(_rand((c, 11), 232 + i, 0.3)), b2=f(_rand((c,), 235 + i, 0.1)), w3=f(_rand((9, c), 238 + i, 0.3)), b3=f(_rand((9,), 241 + i, 0.1)))
+            for i, c in enumerate(cs)]
+    assert ops.pyramid_lcsa_supported(dim, cs, dtype, H, W)
+    ts0, parts = ops.pyramid_project(x, ws, bs, want_partials=True)
+    for rep in range(2):
+        ts1, lops = ops.pyramid_project_lcsa(x, ws, bs, prms)
+        for i, c in enumerate(cs):
+            h, w = H >> i, W >> i
+            assert torch.equal(ts1[i], ts0[i])
+            assert rel_err(lops[i]['rowsum'].cpu(), ts0[i].float().sum(2).cpu()) <= 1e-5
+            if not ops.dsc_mma_inline_mask_supported(c, c, dtype, h, w):
+                continue
+            wd = ops.pack_dsc_weight_simt(f(_rand((c, c, 3, 3), 250 + i, 1.0 / np.sqrt(9 * c))))
+            wo = ops.pack_dsc_weight_simt(f(_rand((18, c, 3, 3), 260 + i, 0.6 / np.sqrt(9 * c))))
+            bo = f(_rand((18,), 270 + i, 0.2))
+            mask = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], prms[i], dtype, mask_f32=True)
+            y0, g0 = ops.dsc_forward(ts0[i], wd, None, mask, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo)
+            inl = dict(lops[i], w2=prms[i]['w2'], b2=prms[i]['b2'], w3=prms[i]['w3'], b3=prms[i]['b3'])
+            y1, g1 = ops.dsc_forward(ts1[i], wd, None, None, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo,
+                                     lcsa_inline=inl)
+            torch.cuda.synchronize()
+            assert torch.equal(y1, y0) and torch.equal(g1, g0)
+    assert int(ops.layer_counters(x.device).abs().sum()) == 0
