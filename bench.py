@@ -293,12 +293,12 @@ def c4_images(n, seed=0):
     return torch.randint(0, 256, (n, 3, C4['H'], C4['W']), dtype=torch.uint8, generator=g)
 
 
-def c4_dominant_kernel(device, mb, stream, n=20, variant='inline'):
+def c4_dominant_kernel(device, mb, stream, n=20, variant='tensor'):
     """The kernel with the largest share of the detector forward, timed alone with CUDA events: the deformable convolution of a
-    KAD-Conv branch (offset convolution fused in, LCSA modulation mask evaluated in-kernel: the form the layer call launches) at
-    the detector's largest KAD-Conv shape (stride 8: 100x100, 12 channels). variant='tensor' times the earlier form that reads a
-    float32 mask tensor. Two input sets are alternated; at mini-batch 64 one set (x and y: 30.7 MB, + 23 MB of mask for 'tensor')
-    does not stay in the L2 between launches because the sets alternate."""
+    KAD-Conv branch with the offset convolution fused in, at the detector's largest KAD-Conv shape (stride 8: 100x100, 12
+    channels). variant='tensor' (what the layer call launches by default) reads the float32 LCSA mask tensor; variant='inline'
+    evaluates the mask in-kernel (KadLayerArgs.scheme = 3). Two input sets are alternated.
+    """
     from kadconv import ops
     B, H, W, c = mb, 100, 100, 12
     Cp = (c + 3) & ~3
@@ -309,7 +309,7 @@ def c4_dominant_kernel(device, mb, stream, n=20, variant='inline'):
         x = r(B, H, W, c).half()
         if variant == 'inline':
             xf = x.float()
-            extra = dict(rowsum=xf.sum(2).contiguous(), A=r(B, W, Cp, s=0.3), Sm=r(W, Cp, s=0.3), w2=r(c, 11, s=0.3), b2=r(c, s=0.1), w3=r(9, c, s=0.3), b3=r(9, s=0.1))
+            extra = dict(rowmean=xf.mean(2).contiguous(), A=r(B, W, Cp, s=0.3), Sm=r(W, Cp, s=0.3), w2=r(c, 11, s=0.3), b2=r(c, s=0.1), w3=r(9, c, s=0.3), b3=r(9, s=0.1))
         else:
             extra = torch.sigmoid(r(B, H, W, 9))
         sets.append((x, extra))
@@ -541,11 +541,11 @@ def run_c4(args, rank, world, local):
         'strong_scaling': strong, 'c3_latency': c3,
         'roofline': {'bound': 'hbm', 'achieved': dom['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s', 'frac': dom['gbs'] / pk['hbm_gbs'],
                      'traffic': NCU_TRAFFIC['c4_dsc_mma'], 'peak_source': pk['_source'],
-                     'kernel': 'dsc_mma_kernel (offset convolution + in-kernel LCSA mask + deformable convolution of a KAD-Conv branch), the largest '
+                     'kernel': 'dsc_mma_kernel (offset convolution + deformable convolution of a KAD-Conv branch), the largest '
                                'share of the forward; timed alone on its largest detector shape', 'shape': dom['shape'],
                      'us_per_launch': dom['us'], 'algorithmic_bytes': dom['bytes'],
                      'limiter': 'instruction issue', 'issue_slot_frac': NCU_ISSUE['c4_dsc_mma'],
-                     'note': 'HBM is not what limits this kernel (12-channel maps: 48 bytes per pixel against about 4000 warp instructions per 32 pixels '
+                     'note': 'HBM is not what limits this kernel (12-channel maps: 84 bytes per pixel against about 4000 warp instructions per 32 pixels '
                              'of gather geometry): `frac` relates it to the HBM roofline as the contract asks, `issue_slot_frac` is the fraction '
                              'of issue slots it keeps busy in the committed ncu summary (profiles/dsc_mma_kernel_c4.md)'},
         'roofline_forward_graph': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
@@ -846,11 +846,11 @@ def main():
         # the detector's dominant kernel alone (what the `roofline` object of the c4 line is measured on); small enough for ncu
         device = torch.device('cuda', local); torch.cuda.set_device(device)
         dom = c4_dominant_kernel(device, args.mini_batch, torch.cuda.current_stream(), n=max(3, min(args.steps, 20)))
-        old = None if args.profile else c4_dominant_kernel(device, args.mini_batch, torch.cuda.current_stream(), n=max(3, min(args.steps, 20)), variant='tensor')
+        old = None if args.profile else c4_dominant_kernel(device, args.mini_batch, torch.cuda.current_stream(), n=max(3, min(args.steps, 20)), variant='inline')
         if rank == 0:
             emit(({'metric': 'dsc_mma_kernel us per launch', 'value': dom['us'], 'unit': 'us', 'shape': dom['shape'],
                    'algorithmic_bytes': dom['bytes'], 'gb_per_s': dom['gbs'], 'gpu_launches': max(3, min(args.steps, 20)),
-                   'mask_tensor_variant_us': old['us'] if old else None}))
+                   'inline_mask_variant_us': old['us'] if old else None}))
         return
     if args.workload in ('conv3x3', 'gemm1x1'):
         res = run_conv3x3(args, local) if args.workload == 'conv3x3' else run_gemm1x1(args, local)

@@ -77,14 +77,14 @@ typedef struct KadDscArgs {
        tensor is never written to memory. */
     const float* offset_weight; const float* offset_bias;
     /* path 3 with offset_weight only, optional: the modulation mask of LCSA.forward + sigmoid (kad_conv.py:24-39,:65) evaluated
-       inside the kernel, per pixel, so that the mask tensor is never written to memory. When lcsa_rowsum is set, `mask` is
+       inside the kernel, per pixel, so that the mask tensor is never written to memory. When lcsa_rowmean is set, `mask` is
        ignored. With C = Cin and Cp = C rounded up to a multiple of 4:
-         lcsa_rowsum float32 [B][H][C]  sums of x over the row (pool_h * W)
+         lcsa_rowmean float32 [B][H][C] means of x over the row (pool_h)
          lcsa_A      float32 [B][W][Cp] and lcsa_Sm float32 [W][Cp]: the separable 1x11 + BatchNorm stage per column, as
                      kad_pyramid_project_lcsa / kad_lcsa_mask_from_partials compute them (16-byte aligned)
          lcsa_w2 [C][11], lcsa_b2 [C] (11x1 depthwise), lcsa_w3 [9][C], lcsa_b3 [9] (1x1)
        kad_dsc_mma_inline_mask_supported() says whether the operands fit shared memory for this shape. */
-    const float* lcsa_rowsum; const float* lcsa_A; const float* lcsa_Sm;
+    const float* lcsa_rowmean; const float* lcsa_A; const float* lcsa_Sm;
     const float* lcsa_w2; const float* lcsa_b2; const float* lcsa_w3; const float* lcsa_b3;
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);
@@ -134,7 +134,7 @@ int kad_pyramid_project(const void* x, const float* const* w, const float* const
 /* kad_pyramid_project that also finishes the first, separable stage of the three LCSAs (kad_conv.py:27-31: pool_h + pool_w,
  * the 1x11 depthwise convolution, BatchNorm) in the tail of the same kernel: the block that finishes an image last reduces
  * that image's partial sums (fixed order, so the result does not depend on which block it is) and writes, per branch i,
- *   lcsa_rowsum[i] float32 [B][h_i][c_i], lcsa_A[i] float32 [B][w_i][Cp_i], lcsa_Sm[i] float32 [w_i][Cp_i]  (Cp = c rounded up to 4)
+ *   lcsa_rowmean[i] float32 [B][h_i][c_i] (means over the row), lcsa_A[i] float32 [B][w_i][Cp_i], lcsa_Sm[i] float32 [w_i][Cp_i]  (Cp = c rounded up to 4)
  * which kad_dsc_forward (path 3, lcsa_* fields) consumes; the same values kad_lcsa_mask_from_partials derives in a kernel of
  * its own. lcsa_w1[i] [c_i][11], lcsa_b1[i] [c_i]: the 1x11 depthwise convolution; lcsa_bn_scale / lcsa_bn_shift [c_i]: folded BatchNorm.
  * counters: device int[B], zero before the first call; every call leaves them zero again (calls that share them must not overlap).
@@ -145,7 +145,7 @@ typedef struct KadPyramidArgs {
     float* rowpart[3]; float* colpart[3];
     int* counters;
     const float* lcsa_w1[3]; const float* lcsa_b1[3]; const float* lcsa_bn_scale[3]; const float* lcsa_bn_shift[3];
-    float* lcsa_rowsum[3]; float* lcsa_A[3]; float* lcsa_Sm[3];
+    float* lcsa_rowmean[3]; float* lcsa_A[3]; float* lcsa_Sm[3];
 } KadPyramidArgs;
 int kad_pyramid_lcsa_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W);
 int kad_pyramid_project_lcsa(const KadPyramidArgs* args, void* stream);
@@ -285,13 +285,17 @@ typedef struct KadLayerArgs {
     KadBranchParams br[3];
     int out_cstride;     /* elements per pixel of `out` (0 = dim): the layer can write into a channel slice of a wider tensor */
     int* counters;       /* NULL, or device int[B], zero before the first call and left zero by every call: lets the pyramid kernel
-                            finish the LCSA's first stage in its tail and the deformable convolutions evaluate the mask in-kernel
-                            (five launches per layer instead of eleven) when the shape qualifies */
+                            finish the LCSA's first stage in its tail (kad_pyramid_project_lcsa) when the shape qualifies */
+    int scheme;          /* how the LCSA masks are produced when `counters` is given and the shape qualifies:
+                            0 = the library's choice (the fastest measured form: 1);
+                            1 = separate preparation + mask kernels (eleven launches per layer: what runs without `counters`);
+                            2 = first stage in the pyramid kernel's tail, one mask kernel per branch (eight launches);
+                            3 = first stage in the tail, masks evaluated inside the deformable convolutions (five launches).
+                            All forms compute bit-identical results. */
 } KadLayerArgs;
 size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches);
-/* 1 if kad_kadconv_forward runs this shape as five launches when `counters` is given (kad_pyramid_project_lcsa, three
- * kad_dsc_forward with the in-kernel LCSA mask, merge): all three branches on path 3 and the LCSA operands fit shared memory. */
-int kad_kadconv_uses_inline_mask(int B, int H, int W, int dim, int dtype, int tc_branches);
+/* Launches kad_kadconv_forward issues for this shape under `scheme` (as in KadLayerArgs; 0 with_counters = scheme 1). */
+int kad_kadconv_launch_count(int B, int H, int W, int dim, int dtype, int tc_branches, int with_counters, int scheme);
 int kad_kadconv_forward(const KadLayerArgs* args, void* stream);
 
 /* Batched detection post-processing, one launch for the whole batch. Replaces non_max_suppression

@@ -62,6 +62,12 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 inline size_t dtype_size(int dtype) { return dtype == KAD_F32 ? 4 : 2; }
 
+// kad_elementwise.cu: second stage of the LCSA from prepared operands (used by the layer call when the pyramid kernel has
+// finished the first stage in its tail)
+int lcsa_mask_from_prepared(const float* rows, int rows_are_means, const float* A, const float* Sm,
+                            const float* w2, const float* b2, const float* w3, const float* b3,
+                            void* mask, int B, int H, int W, int C, int mask_f32, int dtype, cudaStream_t st);
+
 // Dispatch a templated launcher on the storage type.
 #define KAD_DISPATCH_DTYPE(dtype, ...)                                                   \
     switch (dtype) {                                                                     \

@@ -45,10 +45,11 @@ struct MmaParams {
     int H, W, Cin, Cout, KC, align;
     int offset_f32, mask_f32, y_f32, act;
     int B, win_margin;                  // win_margin: rows staged above / below the 3x3 halo for the learned offsets
-    // inline mode: LCSA operands. rowsum [B][H][Cin] (sums over x), A [B][W][Cp], Sm [W][Cp] (Cp = Cin rounded up to 4),
+    // inline mode: LCSA operands. rowmean [B][H][Cin] (means over x), A [B][W][Cp], Sm [W][Cp] (Cp = Cin rounded up to 4),
     // w2 [Cin][11], b2 [Cin], w3 [9][Cin], b3 [9]
-    const float* l_rowsum; const float* l_A; const float* l_Sm; const float* l_w2; const float* l_b2; const float* l_w3; const float* l_b3;
+    const float* l_rowmean; const float* l_A; const float* l_Sm; const float* l_w2; const float* l_b2; const float* l_w3; const float* l_b3;
     int Cp, rm_rows;                    // rm_rows: image rows a group of 256 pixels can span, + 10 for the 11x1 window
+    int stage_cols;                     // 1: the image's A rows and Sm are staged in shared memory (they fit); 0: read through L2
 };
 
 constexpr int SCRATCH_PER_WARP = 4224;  // sampling table (3 taps x 32 pixels x 32 bytes), later the warp's output tile (+ 16 bytes of shift)
@@ -151,7 +152,7 @@ __device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned c
 // rm: staged row means, row (h - 5) first, Cp floats per row; sw2 / sw3: [Cp][12] (slot 11 of sw2 = b2); valid: bit k set
 // when row h + k - 5 lies inside the image (BORDER = false: the caller knows all 11 rows do).
 template <bool BORDER>
-__device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* __restrict__ A, const float* __restrict__ Sm, const float* rm,
+__device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* A, const float* Sm, const float* rm,
                                                 const float* sw2, const float* sw3, const float* __restrict__ b3, int Cp, uint32_t valid) {
     float logit[9];
 #pragma unroll
@@ -162,7 +163,7 @@ __device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* __r
     const float4* w34 = reinterpret_cast<const float4*>(sw3);
 #pragma unroll 1
     for (int c4 = 0; c4 < (Cp >> 2); ++c4) {
-        const float4 av = __ldg(A4 + c4), sv = __ldg(S4 + c4);
+        const float4 av = A4[c4], sv = S4[c4];
         const float aa[4] = {av.x, av.y, av.z, av.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
         for (int j4 = 0; j4 < 4; ++j4) {
@@ -206,6 +207,8 @@ dsc_mma_kernel(const MmaParams p) {
     float* sw2 = reinterpret_cast<float*>(cur); cur += (INLINE ? p.Cp * 48 : 0);      // [Cp][12] 11x1 taps, slot 11 = bias (inline)
     float* sw3 = reinterpret_cast<float*>(cur); cur += (INLINE ? p.Cp * 48 : 0);      // [Cp][12] 1x1 weights of the 9 mask outputs
     float* rms = reinterpret_cast<float*>(cur); cur += (INLINE ? p.rm_rows * p.Cp * 4 : 0);   // [rm_rows][Cp] row means of the group's rows
+    float* As = reinterpret_cast<float*>(cur); cur += ((INLINE && p.stage_cols) ? p.W * p.Cp * 4 : 0);     // [W][Cp] column terms of the current image
+    float* Sms = reinterpret_cast<float*>(cur); cur += ((INLINE && p.stage_cols) ? p.W * p.Cp * 4 : 0);    // [W][Cp] (the same for every image)
     const uint32_t zoff = static_cast<uint32_t>(cur - smem_mma); cur += ZERO_BYTES;   // the block of zeros
     const uint32_t wdata = static_cast<uint32_t>(cur - smem_mma) + 16;                // staged rows start here (16 bytes of slack in front)
 
@@ -230,12 +233,27 @@ dsc_mma_kernel(const MmaParams p) {
         const int e_lo = wy0 * W * Cin, e_hi = (wy1 + 1) * W * Cin;                  // staged image elements [e_lo, e_hi)
         const uintptr_t a_lo = reinterpret_cast<uintptr_t>(gimg) + 2 * (size_t)e_lo, a16 = a_lo & ~uintptr_t(15);
         const uintptr_t a_hi = reinterpret_cast<uintptr_t>(gimg) + 2 * (size_t)e_hi;
+        if (INLINE) {
+            // first copy group: row means of the rows this group's 11x1 windows reach (0 outside the image) and the image's column terms
+            const int r_lo = base / W, nrm = last / W - r_lo + 11;
+            for (int e = tid; e < nrm * p.Cp; e += MMA_THREADS) {
+                const int j = e / p.Cp, c = e - j * p.Cp, hh = r_lo - 5 + j;
+                if (hh >= 0 && hh < H && c < Cin) cp_async4(rms + e, p.l_rowmean + ((size_t)b * H + hh) * Cin + c);
+                else rms[e] = 0.f;
+            }
+            if (p.stage_cols) {
+                const float* Ag = p.l_A + (size_t)b * W * p.Cp;
+                for (int i = tid; i < (W * p.Cp) >> 2; i += MMA_THREADS) cp_async16(As + 4 * i, Ag + 4 * i);
+            }
+            cp_async_commit();
+        }
         {
             const int nbytes = static_cast<int>(a_hi - a16), nvec = nbytes >> 4, ntail = (nbytes & 15) >> 1;
             unsigned char* dst = smem_mma + wdata;
             for (int i = tid; i < nvec; i += MMA_THREADS) cp_async16(dst + 16 * i, reinterpret_cast<const void*>(a16 + 16 * (size_t)i));
             if (tid < ntail)
                 *reinterpret_cast<uint16_t*>(dst + 16 * nvec + 2 * tid) = *reinterpret_cast<const uint16_t*>(a16 + 16 * (size_t)nvec + 2 * tid);
+            if (INLINE) cp_async_commit();                     // second copy group: the image rows
         }
         // shared-memory address of image element e: sel0 + 2*e
         const int sel0 = static_cast<int>(wdata) - static_cast<int>(static_cast<ptrdiff_t>(a16) - static_cast<ptrdiff_t>(reinterpret_cast<uintptr_t>(gimg)));
@@ -251,6 +269,7 @@ dsc_mma_kernel(const MmaParams p) {
                     sw3[e] = (k < 9 && c < Cin) ? p.l_w3[k * Cin + c] : 0.f;
                     sw2[e] = c < Cin ? (k < 11 ? p.l_w2[c * 11 + k] : p.l_b2[c]) : 0.f;
                 }
+                if (p.stage_cols) for (int e = tid; e < W * p.Cp; e += MMA_THREADS) Sms[e] = p.l_Sm[e];
             }
             for (int e = tid; e < COP; e += MMA_THREADS) {
                 const bool on = e < Cout;
@@ -269,13 +288,9 @@ dsc_mma_kernel(const MmaParams p) {
         const size_t gp = (size_t)b * HW + mypix;
         float mk[9];
         if (INLINE) {
-            // row means of the rows this group's 11x1 windows reach (0 outside the image), then every lane evaluates its pixel's mask
-            const int r_lo = base / W, nrm = last / W - r_lo + 11;
-            const float invW = 1.f / (float)W;
-            for (int e = tid; e < nrm * p.Cp; e += MMA_THREADS) {
-                const int j = e / p.Cp, c = e - j * p.Cp, hh = r_lo - 5 + j;
-                rms[e] = (hh >= 0 && hh < H && c < Cin) ? p.l_rowsum[((size_t)b * H + hh) * Cin + c] * invW : 0.f;
-            }
+            // the LCSA operands have landed (the image rows may still be in flight): every lane evaluates its pixel's mask
+            const int r_lo = base / W;
+            cp_async_wait_but_one();
             __syncthreads();
 #pragma unroll
             for (int k = 0; k < 9; ++k) mk[k] = 1.f;
@@ -287,8 +302,8 @@ dsc_mma_kernel(const MmaParams p) {
             }
             const bool border = __any_sync(0xffffffffu, valid != 0x7ffu);
             if (mylive) {
-                const float* Ap = p.l_A + ((size_t)b * W + mpx) * p.Cp;
-                const float* Sp = p.l_Sm + (size_t)mpx * p.Cp;
+                const float* Ap = p.stage_cols ? As + mpx * p.Cp : p.l_A + ((size_t)b * W + mpx) * p.Cp;
+                const float* Sp = p.stage_cols ? Sms + mpx * p.Cp : p.l_Sm + (size_t)mpx * p.Cp;
                 const float* rmp = rms + (mpy - r_lo) * p.Cp;
                 if (border) lcsa_mask_pixel<true>(mk, Ap, Sp, rmp, sw2, sw3, p.l_b3, p.Cp, valid);
                 else lcsa_mask_pixel<false>(mk, Ap, Sp, rmp, sw2, sw3, p.l_b3, p.Cp, valid);
@@ -505,11 +520,14 @@ inline int lcsa_rm_rows(int H, int W) {
     if (rows > H) rows = H;
     return rows + 10;
 }
-// Extra shared memory of the inline-mask mode: 11x1 taps and 1x1 weights ([Cp][12] each) and the staged row means.
-inline size_t lcsa_smem(int Cin, int H, int W) {
+// Extra shared memory of the inline-mask mode: 11x1 taps and 1x1 weights ([Cp][12] each), the staged row means and, when
+// `cols`, the column terms A (current image) and Sm ([W][Cp] each).
+inline size_t lcsa_smem(int Cin, int H, int W, bool cols) {
     const int Cp = (Cin + 3) & ~3;
-    return (size_t)2 * Cp * 48 + (size_t)lcsa_rm_rows(H, W) * Cp * 4;
+    return (size_t)2 * Cp * 48 + (size_t)lcsa_rm_rows(H, W) * Cp * 4 + (cols ? (size_t)2 * W * Cp * 4 : 0);
 }
+// The column terms are staged when that costs at most 24 KB (narrow maps, few channels: the detector's shapes).
+inline bool lcsa_stage_cols(int Cin, int W) { return (size_t)2 * W * ((Cin + 3) & ~3) * 4 <= 24 * 1024; }
 // Bytes for the staged rows with `margin` rows for the learned offsets (incl. alignment slack on both sides).
 inline size_t window_smem(int H, int W, int Cin, int margin) {
     int rows = (W + MMA_THREADS - 2) / W + 1 + 2 + 2 * margin;      // rows 256 consecutive pixels span + halo + margin
@@ -587,12 +605,12 @@ bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) {
 // Inline-mask mode: the fused mode's footprint plus the LCSA operands must fit with at least the 3x3 halo staged.
 bool dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W) {
     if (!dsc_mma_supported(Cin, Cout, dtype, H, W)) return false;
-    return fixed_smem((Cin + 15) / 16, pick_nt(Cout), 3) + lcsa_smem(Cin, H, W) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
+    return fixed_smem((Cin + 15) / 16, pick_nt(Cout), 3) + lcsa_smem(Cin, H, W, lcsa_stage_cols(Cin, W)) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
 }
 
 int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
     const bool fused = a.offset_weight != nullptr;
-    const bool inline_mask = a.lcsa_rowsum != nullptr;
+    const bool inline_mask = a.lcsa_rowmean != nullptr;
     KAD_CHECK_ARG(!inline_mask || fused, "kad_dsc_forward: the in-kernel LCSA mask needs the fused offset convolution (offset_weight)");
     KAD_CHECK_ARG(!inline_mask || (a.lcsa_A && a.lcsa_Sm && a.lcsa_w2 && a.lcsa_b2 && a.lcsa_w3 && a.lcsa_b3), "kad_dsc_forward: LCSA operand missing");
     KAD_CHECK_ARG(!inline_mask || ((uintptr_t)a.lcsa_A % 16 == 0 && (uintptr_t)a.lcsa_Sm % 16 == 0), "kad_dsc_forward: lcsa_A / lcsa_Sm must be 16-byte aligned");
@@ -610,10 +628,10 @@ int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
     p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KC = (a.Cin + 15) / 16; p.B = a.B;
     p.align = a.Cin % 4 == 0 ? 8 : (a.Cin % 2 == 0 ? 4 : 2);
     p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
-    p.l_rowsum = a.lcsa_rowsum; p.l_A = a.lcsa_A; p.l_Sm = a.lcsa_Sm; p.l_w2 = a.lcsa_w2; p.l_b2 = a.lcsa_b2; p.l_w3 = a.lcsa_w3; p.l_b3 = a.lcsa_b3;
-    p.Cp = (a.Cin + 3) & ~3; p.rm_rows = lcsa_rm_rows(a.H, a.W);
+    p.l_rowmean = a.lcsa_rowmean; p.l_A = a.lcsa_A; p.l_Sm = a.lcsa_Sm; p.l_w2 = a.lcsa_w2; p.l_b2 = a.lcsa_b2; p.l_w3 = a.lcsa_w3; p.l_b3 = a.lcsa_b3;
+    p.Cp = (a.Cin + 3) & ~3; p.rm_rows = lcsa_rm_rows(a.H, a.W); p.stage_cols = (inline_mask && lcsa_stage_cols(a.Cin, a.W)) ? 1 : 0;
     const int nt = pick_nt(a.Cout);
-    size_t smem = fixed_smem(p.KC, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W) : 0);
+    size_t smem = fixed_smem(p.KC, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W, p.stage_cols != 0) : 0);
     // rows of margin for the learned offsets: as many as fit, at most 2 (none for the plain convolution); the narrow
     // variants (128 registers) keep two blocks per SM when the halo alone allows it
     const size_t soft = (nt <= 4 && smem + window_smem(a.H, a.W, a.Cin, 0) <= SMEM_TWO_BLOCKS) ? SMEM_TWO_BLOCKS : SMEM_ONE_BLOCK;

@@ -200,7 +200,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                       const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
-                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int mask_f32) {
+                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int mask_f32, int rows_are_means) {
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.y, t = threadIdx.x, HW = H * W;
     const int p0 = blockIdx.x * 128, p1 = min(HW, p0 + 128);
@@ -208,7 +208,7 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
     float* rm = sw3 + 12 * Cp;           // [nrows][Cp][12] row means of rows h-5..h+5 (0 outside the image), pad 0
     float* sw2 = rm + nrows * 12 * Cp;   // [nrows][Cp][12] 11x1 taps (0 for rows outside the image), slot 11 = bias b2
-    const float invW = 1.f / (float)W;
+    const float invW = rows_are_means ? 1.f : 1.f / (float)W;      // `rowsum` holds row means already
     for (int e = t; e < 12 * Cp; e += 128) { const int c = e / 12, k = e - c * 12; sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f; }
     for (int e = t; e < nrows * 12 * Cp; e += 128) {
         const int r = e / (12 * Cp), rem = e - r * 12 * Cp, c = rem / 12, k = rem - c * 12, hh = r_lo + r + k - 5;
@@ -266,7 +266,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                        const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
-                       const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int groups, int mask_f32) {
+                       const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int groups, int mask_f32, int rows_are_means) {
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.y, t = threadIdx.x;
     const int RB = groups * LS_R, P = RB + 12;           // rows per block; row pitch of the staged means (rows h0-5 .. h0+RB+6)
@@ -274,7 +274,7 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
     float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
     float* sw2 = sw3 + 12 * Cp;          // [Cp][12] 11x1 taps, slot 11 = bias b2
     float* rm = sw2 + 12 * Cp;           // [Cp][P] row means (0 outside the image; those rows are masked below)
-    const float invW = 1.f / (float)W;
+    const float invW = rows_are_means ? 1.f : 1.f / (float)W;
     for (int e = t; e < 12 * Cp; e += 128) {
         const int c = e / 12, k = e - c * 12;
         sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f;
@@ -923,6 +923,15 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
     float* Sm = scratch + (size_t)B * W * Cp;
     lcsa_prep_partials_kernel<<<dim3((W + PREP_COLS - 1) / PREP_COLS, B), 256, sizeof(float) * (size_t)(PREP_COLS + 10) * C, st>>>(
         rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C, Cp);
+    return kad::lcsa_mask_from_prepared(rowsum, 0, A, Sm, w2, b2, w3, b3, mask, B, H, W, C, mask_f32, dtype, st);
+}
+
+// The second stage of the LCSA (11x1 depthwise, 1x1, sigmoid) from prepared first-stage operands: rows float32 [B][H][C] (row sums,
+// or row means when rows_are_means), A [B][W][Cp], Sm [W][Cp]. One launch.
+int kad::lcsa_mask_from_prepared(const float* rowsum, int rows_are_means, const float* A, const float* Sm,
+                                 const float* w2, const float* b2, const float* w3, const float* b3,
+                                 void* mask, int B, int H, int W, int C, int mask_f32, int dtype, cudaStream_t st) {
+    const int Cp = (C + 3) & ~3;
     // column strips when the map is wide enough in rows and blocks to fill the GPU twice over; else one pixel per thread
     if (W <= 128) {
         const int groups = 128 / W, RB = groups * LS_R;
@@ -930,7 +939,7 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
         const size_t smem_strip = sizeof(float) * (size_t)Cp * (24 + RB + 12);
         if ((long long)row_blocks * B >= 296 && smem_strip <= 48 * 1024) {
             KAD_DISPATCH_DTYPE(dtype, {
-                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32);
+                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32, rows_are_means);
             });
             KAD_CHECK_LAUNCH("lcsa_mask_from_partials (strips)");
             return KAD_OK;
@@ -944,7 +953,7 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "lcsa_mask smem attribute: %s", cudaGetErrorString(e));
         }
-        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32);
+        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means);
     });
     KAD_CHECK_LAUNCH("lcsa_mask_from_partials");
     return KAD_OK;

@@ -72,7 +72,8 @@ struct LayerPlan {
     BranchWs ws[3];
     int path[3], tiles[3];
     bool pyramid, partials;      // one kernel for the three projections; LCSA sums taken from that kernel's partial sums
-    bool inline_mask;            // LCSA first stage in the pyramid kernel's tail, mask evaluated inside the deformable convolutions
+    bool tail_prep;              // LCSA first stage can be finished in the pyramid kernel's tail
+    bool inline_mask;            // ... and the masks can be evaluated inside the deformable convolutions
     int nct, nrg;
     size_t bytes;
 };
@@ -95,7 +96,8 @@ LayerPlan plan_layer(int B, int H, int W, int dim, int dtype, int tc_mask) {
         o = L.ws[i].end;
     }
     L.bytes = o;
-    L.inline_mask = L.partials && kad_pyramid_lcsa_supported(dim, widths[0], widths[1], widths[2], dtype, H, W) != 0;
+    L.tail_prep = L.partials && kad_pyramid_lcsa_supported(dim, widths[0], widths[1], widths[2], dtype, H, W) != 0;
+    L.inline_mask = L.tail_prep;
     for (int i = 0; i < 3; ++i)
         L.inline_mask = L.inline_mask && L.path[i] == 3 && kad_dsc_mma_inline_mask_supported(widths[i], widths[i], dtype, H >> i, W >> i) != 0;
     return L;
@@ -111,9 +113,28 @@ extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int 
     return plan_layer(B, H, W, dim, dtype, tc_branches).bytes;
 }
 
-extern "C" int kad_kadconv_uses_inline_mask(int B, int H, int W, int dim, int dtype, int tc_branches) {
+// 1 = separate kernels, 2 = first stage in the pyramid tail + mask kernels, 3 = tail + masks inside the deformable convolutions
+// Default (scheme 0) = 1: measured on the detector forward (CUDA-graph replay, 64 / 8 / 1 images) the eleven-launch form is the
+// fastest (16.6 / 4.8 / 3.2 ms against 17.4 / 6.2 / 4.3 ms for 2 and 17.3 / 5.9 / 4.2 ms for 3): inside a graph the extra launches
+// cost little and run on three streams, whereas the tail of the pyramid kernel is one block per image on the critical path and the
+// in-kernel mask cannot share work between vertically adjacent pixels the way the column-strip mask kernel does.
+static int resolve_scheme(const LayerPlan& L, bool pyramid_ok, bool counters, int scheme) {
+    if (!counters || !pyramid_ok || !L.tail_prep || scheme <= 1) return 1;
+    if (scheme == 3) return L.inline_mask ? 3 : 2;
+    return 2;
+}
+
+extern "C" int kad_kadconv_launch_count(int B, int H, int W, int dim, int dtype, int tc_branches, int with_counters, int scheme) {
     if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
-    return plan_layer(B, H, W, dim, dtype, tc_branches).inline_mask ? 1 : 0;
+    const LayerPlan L = plan_layer(B, H, W, dim, dtype, tc_branches);
+    const int sc = resolve_scheme(L, L.pyramid, with_counters != 0, scheme);
+    int n = L.pyramid ? 1 : 3;
+    for (int i = 0; i < 3; ++i) {
+        n += sc == 3 ? 0 : (sc == 2 ? 1 : (L.partials ? 2 : 4));       // LCSA
+        n += L.path[i] == 3 ? 1 : 2;                                    // deformable convolution (+ offset convolution unless fused)
+    }
+    const bool merge_has_se = dtype != KAD_F32 && dim % 8 == 0;
+    return n + 1 + (merge_has_se ? 0 : 3);
 }
 
 extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
@@ -143,8 +164,9 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     // the three pooled projections read the same x: one kernel on the caller's stream, before the branches fork
     const bool pyramid = L.pyramid && (uintptr_t)a->x % 16 == 0;
     const bool partials = pyramid && L.partials;
-    const bool inline_mask = partials && L.inline_mask && a->counters != nullptr;
-    if (inline_mask) {
+    const int scheme = resolve_scheme(L, partials, a->counters != nullptr, a->scheme);
+    const bool inline_mask = scheme == 3;
+    if (scheme >= 2) {
         KadPyramidArgs q{};
         q.x = a->x; q.B = a->B; q.H = a->H; q.W = a->W; q.dim = a->dim; q.dtype = a->dtype; q.counters = a->counters;
         for (int i = 0; i < 3; ++i) {
@@ -153,7 +175,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
             q.w[i] = br.w_proj; q.bias[i] = br.b_proj; q.t[i] = ws + L.ws[i].t; q.c[i] = br.c;
             q.rowpart[i] = (float*)(ws + L.ws[i].rowpart); q.colpart[i] = (float*)(ws + L.ws[i].colpart);
             q.lcsa_w1[i] = br.lcsa_w1; q.lcsa_b1[i] = br.lcsa_b1; q.lcsa_bn_scale[i] = br.lcsa_bn_scale; q.lcsa_bn_shift[i] = br.lcsa_bn_shift;
-            q.lcsa_rowsum[i] = (float*)(ws + L.ws[i].rows);
+            q.lcsa_rowmean[i] = (float*)(ws + L.ws[i].rows);
             q.lcsa_A[i] = (float*)(ws + L.ws[i].scratch); q.lcsa_Sm[i] = (float*)(ws + L.ws[i].scratch) + (size_t)a->B * w * Cp;
         }
         rc = kad_pyramid_project_lcsa(&q, stream);
@@ -188,6 +210,11 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         }
         if (inline_mask) {
             // nothing to launch: the pyramid kernel has left the LCSA operands, the deformable convolution evaluates the mask
+        } else if (scheme == 2) {
+            const int Cp = (c + 3) & ~3;
+            rc = lcsa_mask_from_prepared((const float*)(ws + p.rows), 1, (const float*)(ws + p.scratch), (const float*)(ws + p.scratch) + (size_t)a->B * w * Cp,
+                                         br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3, ws + p.mask, a->B, h, w, c, 1, a->dtype, st[i]);
+            if (rc) break;
         } else if (partials) {
             rc = kad_lcsa_mask_from_partials((const float*)(ws + p.rowpart), L.nct, (const float*)(ws + p.colpart), L.nrg,
                                              br.lcsa_w1, br.lcsa_b1, br.lcsa_bn_scale, br.lcsa_bn_shift, br.lcsa_w2, br.lcsa_b2, br.lcsa_w3, br.lcsa_b3,
@@ -215,7 +242,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         q.x = ws + p.t;
         if (inline_mask) {
             const int Cp = (c + 3) & ~3;
-            q.lcsa_rowsum = (const float*)(ws + p.rows);
+            q.lcsa_rowmean = (const float*)(ws + p.rows);
             q.lcsa_A = (const float*)(ws + p.scratch); q.lcsa_Sm = (const float*)(ws + p.scratch) + (size_t)a->B * w * Cp;
             q.lcsa_w2 = br.lcsa_w2; q.lcsa_b2 = br.lcsa_b2; q.lcsa_w3 = br.lcsa_w3; q.lcsa_b3 = br.lcsa_b3;
         } else {

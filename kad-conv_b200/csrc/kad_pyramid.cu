@@ -23,20 +23,21 @@ struct PyramidParams {
     // optional LCSA preparation in the tail (set counters): see lcsa_prepare_image
     int* counters;
     const float* lw1[3]; const float* lb1[3]; const float* lbn_m[3]; const float* lbn_a[3];
-    float* l_rowsum[3]; float* l_A[3]; float* l_Sm[3];
+    float* l_rowmean[3]; float* l_A[3]; float* l_Sm[3];
 };
 
 // First, separable stage of one branch's LCSA for image b, from the partial sums every block of the image has written:
-// row sums (over the column tiles), column sums (over the row groups), then per column w and channel c
+// row means (sums over the column tiles, / W), column sums (over the row groups), then per column w and channel c
 //   A[b][w][c] = (sum_k w1[c][k] * colmean[w + k - 5][c] + b1[c]) * bn_m[c] + bn_a[c],   Sm[w][c] = (sum of the taps inside the row) * bn_m[c]
 // (the 1x11 convolution of rowmean[h] + colmean[w] separates into rowmean[h] * S[w] + conv(colmean)[w]; zero padding makes S
 // depend on w). Same arithmetic and summation order as lcsa_prep_partials_kernel, which does this in a launch of its own.
 // One block, all threads; partial sums are read past L1 (other blocks wrote them). colsum_s: W*C floats of shared memory.
 __device__ void lcsa_prepare_image(const float* rowpart, int nct, const float* colpart, int nrg,
                                    const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ bn_m, const float* __restrict__ bn_a,
-                                   float* __restrict__ A, float* __restrict__ Sm, float* __restrict__ rowsum,
+                                   float* __restrict__ A, float* __restrict__ Sm, float* __restrict__ rowmean,
                                    int b, int H, int W, int C, float* colsum_s, int tid) {
     const int Cp = (C + 3) & ~3;
+    const float invW = 1.f / (float)W;
     const float* cp = colpart + (size_t)b * nrg * W * C;
     for (int e = tid; e < W * C; e += MMA_THREADS) {
         float s = 0.f;
@@ -47,7 +48,7 @@ __device__ void lcsa_prepare_image(const float* rowpart, int nct, const float* c
         const int h = e / C, c = e - h * C;
         float s = 0.f;
         for (int k = 0; k < nct; ++k) s += __ldcg(rowpart + (((size_t)b * H + h) * nct + k) * C + c);
-        rowsum[((size_t)b * H + h) * C + c] = s;
+        rowmean[((size_t)b * H + h) * C + c] = s * invW;
     }
     __syncthreads();
     const float invH = 1.f / (float)H;
@@ -305,7 +306,7 @@ pyramid_project_kernel(const PyramidParams p) {
 #pragma unroll 1
             for (int i = 0; i < 3; ++i)
                 lcsa_prepare_image(p.rowpart[i], gridDim.x, p.colpart[i], gridDim.y, p.lw1[i], p.lb1[i], p.lbn_m[i], p.lbn_a[i],
-                                   p.l_A[i], p.l_Sm[i], p.l_rowsum[i], b, p.H >> i, p.W >> i, p.c[i], colsum_s, tid);
+                                   p.l_A[i], p.l_Sm[i], p.l_rowmean[i], b, p.H >> i, p.W >> i, p.c[i], colsum_s, tid);
             if (tid == 0) p.counters[b] = 0;                  // ready for the next launch
         }
     }
@@ -456,12 +457,12 @@ extern "C" int kad_pyramid_project_lcsa(const KadPyramidArgs* a, void* stream) {
     p.x = a->x; p.B = a->B; p.H = a->H; p.W = a->W; p.dim = a->dim; p.counters = a->counters;
     for (int i = 0; i < 3; ++i) {
         KAD_CHECK_ARG(a->w[i] && a->t[i] && a->rowpart[i] && a->colpart[i] && a->lcsa_w1[i] && a->lcsa_b1[i] && a->lcsa_bn_scale[i] && a->lcsa_bn_shift[i] &&
-                      a->lcsa_rowsum[i] && a->lcsa_A[i] && a->lcsa_Sm[i], "kad_pyramid_project_lcsa: null pointer for branch %d", i);
+                      a->lcsa_rowmean[i] && a->lcsa_A[i] && a->lcsa_Sm[i], "kad_pyramid_project_lcsa: null pointer for branch %d", i);
         KAD_CHECK_ARG((uintptr_t)a->t[i] % 4 == 0, "kad_pyramid_project_lcsa: t[%d] must be 4-byte aligned", i);
         p.w[i] = a->w[i]; p.b[i] = a->bias[i]; p.t[i] = a->t[i]; p.c[i] = a->c[i];
         p.rowpart[i] = a->rowpart[i]; p.colpart[i] = a->colpart[i];
         p.lw1[i] = a->lcsa_w1[i]; p.lb1[i] = a->lcsa_b1[i]; p.lbn_m[i] = a->lcsa_bn_scale[i]; p.lbn_a[i] = a->lcsa_bn_shift[i];
-        p.l_rowsum[i] = a->lcsa_rowsum[i]; p.l_A[i] = a->lcsa_A[i]; p.l_Sm[i] = a->lcsa_Sm[i];
+        p.l_rowmean[i] = a->lcsa_rowmean[i]; p.l_A[i] = a->lcsa_A[i]; p.l_Sm[i] = a->lcsa_Sm[i];
     }
     KAD_CHECK_ARG((uintptr_t)a->x % 16 == 0, "kad_pyramid_project_lcsa: x must be 16-byte aligned");
     return launch_pyramid(p, a->dtype, (cudaStream_t)stream);

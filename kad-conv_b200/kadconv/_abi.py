@@ -22,7 +22,7 @@ class KadDscArgs(Structure):
                 ('dtype', c_int), ('offset_f32', c_int), ('mask_f32', c_int), ('y_f32', c_int), ('act', c_int),
                 ('path', c_int), ('status', c_void_p),
                 ('offset_weight', c_void_p), ('offset_bias', c_void_p),
-                ('lcsa_rowsum', c_void_p), ('lcsa_A', c_void_p), ('lcsa_Sm', c_void_p),
+                ('lcsa_rowmean', c_void_p), ('lcsa_A', c_void_p), ('lcsa_Sm', c_void_p),
                 ('lcsa_w2', c_void_p), ('lcsa_b2', c_void_p), ('lcsa_w3', c_void_p), ('lcsa_b3', c_void_p)]
 
 
@@ -31,7 +31,7 @@ class KadPyramidArgs(Structure):
                 ('B', c_int), ('H', c_int), ('W', c_int), ('dim', c_int), ('c', c_int * 3), ('dtype', c_int),
                 ('rowpart', c_void_p * 3), ('colpart', c_void_p * 3), ('counters', c_void_p),
                 ('lcsa_w1', c_void_p * 3), ('lcsa_b1', c_void_p * 3), ('lcsa_bn_scale', c_void_p * 3), ('lcsa_bn_shift', c_void_p * 3),
-                ('lcsa_rowsum', c_void_p * 3), ('lcsa_A', c_void_p * 3), ('lcsa_Sm', c_void_p * 3)]
+                ('lcsa_rowmean', c_void_p * 3), ('lcsa_A', c_void_p * 3), ('lcsa_Sm', c_void_p * 3)]
 
 
 class KadMergeArgs(Structure):
@@ -51,7 +51,7 @@ class KadBranchParams(Structure):
 class KadLayerArgs(Structure):
     _fields_ = [('x', c_void_p), ('out', c_void_p), ('workspace', c_void_p), ('workspace_bytes', c_size_t), ('status', c_void_p),
                 ('B', c_int), ('H', c_int), ('W', c_int), ('dim', c_int), ('dtype', c_int), ('br', KadBranchParams * 3),
-                ('out_cstride', c_int), ('counters', c_void_p)]
+                ('out_cstride', c_int), ('counters', c_void_p), ('scheme', c_int)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/kadconv_b200.h
@@ -68,7 +68,7 @@ SIGNATURES = {
     'kad_pyramid_lcsa_supported': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     'kad_pyramid_project_lcsa': (c_int, [POINTER(KadPyramidArgs), c_void_p]),
     'kad_dsc_mma_inline_mask_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
-    'kad_kadconv_uses_inline_mask': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    'kad_kadconv_launch_count': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     'kad_pyramid_partial_dims': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     'kad_lcsa_mask_from_partials_supported': (c_int, [c_int, c_int, c_int]),
     'kad_lcsa_mask_from_partials': (c_int, [c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 8 + [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -20,6 +20,10 @@ from . import ops
 
 _LAYER_TYPES = {'KADConv', 'KADC4', 'KADC4_m'}
 _FAST_ATTR = '_kad_b200'
+# How kad_kadconv_forward produces the LCSA masks (KadLayerArgs.scheme): 0 = the library's choice, 1 = separate kernels,
+# 2 = first stage in the pyramid kernel's tail + one mask kernel per branch, 3 = masks inside the deformable convolutions.
+# All forms are bit-identical; tests and benchmarks switch this to compare them.
+LAYER_SCHEME = 0
 
 
 def _bn_fold(bn):
@@ -149,8 +153,8 @@ def kadconv_forward_nhwc(layer, x, out=None, out_coff=0):
     a.x, a.out, a.workspace, a.workspace_bytes = x.data_ptr(), out_ptr, ws.data_ptr(), nbytes
     a.status = ops.status_word(x.device).data_ptr()
     a.B, a.H, a.W, a.dim = B, H, W, C
-    if lib.kad_kadconv_uses_inline_mask(B, H, W, C, a.dtype, tc_mask):
-        launches -= 6              # LCSA first stage in the pyramid kernel's tail, mask inside the deformable convolutions
+    a.scheme = LAYER_SCHEME
+    launches = lib.kad_kadconv_launch_count(B, H, W, C, a.dtype, tc_mask, 1, a.scheme)
     _abi.check(lib.kad_kadconv_forward(ctypes.byref(a), ops._stream()), 'kad_kadconv_forward', launches)
     return out
 

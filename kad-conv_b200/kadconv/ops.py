@@ -160,7 +160,7 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
     weight: pack_dsc_weight_simt(...) for PATH_SIMT / PATH_MMA or pack_dsc_weight_tc(...) for PATH_TC.
     PATH_MMA only: offset_weight (pack_dsc_weight_simt of the offset convolution's weight, [9,Cin,18]) and
     offset_bias ([18]) make the kernel compute the offsets itself instead of reading `offset`; with them, lcsa_inline =
-    dict(rowsum [B,H,Cin], A [B,W,Cp], Sm [W,Cp] from pyramid_project_lcsa, and the LCSA's w2 [Cin,11], b2, w3 [9,Cin], b3) makes
+    dict(rowmean [B,H,Cin], A [B,W,Cp], Sm [W,Cp] from pyramid_project_lcsa, and the LCSA's w2 [Cin,11], b2, w3 [9,Cin], b3) makes
     the kernel evaluate the modulation mask itself instead of reading `mask`.
     Returns y [B,H,W,Cout] (and the per-tile channel sums [B,tiles,Cout] when want_gap).
     """
@@ -205,7 +205,7 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
         if offset_weight is None:
             raise ValueError('lcsa_inline goes with offset_weight (PATH_MMA)')
         Cp = (Cin + 3) & ~3
-        want = {'rowsum': (B, H, Cin), 'A': (B, W, Cp), 'Sm': (W, Cp), 'w2': (Cin, 11), 'b2': (Cin,), 'w3': (9, Cin), 'b3': (9,)}
+        want = {'rowmean': (B, H, Cin), 'A': (B, W, Cp), 'Sm': (W, Cp), 'w2': (Cin, 11), 'b2': (Cin,), 'w3': (9, Cin), 'b3': (9,)}
         for name, shape in want.items():
             t = _f32(lcsa_inline[name], 'lcsa_inline.' + name)
             if tuple(t.shape) != shape:
@@ -561,7 +561,7 @@ def dsc_mma_inline_mask_supported(Cin, Cout, dtype, H, W):
 
 def pyramid_project_lcsa(x, ws, bs, lcsas):
     """pyramid_project that also finishes the first stage of the three LCSAs in the kernel's tail. lcsas[i]: dict with
-    w1 [c_i,11], b1, bn_m, bn_a (folded BatchNorm). Returns (ts, ops) where ops[i] = dict(rowsum [B,h_i,c_i], A [B,w_i,Cp_i],
+    w1 [c_i,11], b1, bn_m, bn_a (folded BatchNorm). Returns (ts, ops) where ops[i] = dict(rowmean [B,h_i,c_i], A [B,w_i,Cp_i],
     Sm [w_i,Cp_i]) is what dsc_forward(..., lcsa_inline=...) consumes."""
     x = _cuda(x, 'x')
     B, H, W, dim = x.shape
@@ -579,14 +579,14 @@ def pyramid_project_lcsa(x, ws, bs, lcsas):
         t = torch.empty((B, h, w, c), dtype=x.dtype, device=x.device)
         rp = torch.empty((B, h, nct.value, c), dtype=torch.float32, device=x.device)
         cp = torch.empty((B, nrg.value, w, c), dtype=torch.float32, device=x.device)
-        o = {'rowsum': torch.empty((B, h, c), dtype=torch.float32, device=x.device),
+        o = {'rowmean': torch.empty((B, h, c), dtype=torch.float32, device=x.device),
              'A': torch.empty((B, w, Cp), dtype=torch.float32, device=x.device), 'Sm': torch.empty((w, Cp), dtype=torch.float32, device=x.device)}
         a.w[i] = _f32(ws[i], 'w').data_ptr(); a.bias[i] = _f32(bs[i], 'bias').data_ptr() if bs[i] is not None else None
         a.t[i] = t.data_ptr(); a.c[i] = c; a.rowpart[i] = rp.data_ptr(); a.colpart[i] = cp.data_ptr()
         l = lcsas[i]
         a.lcsa_w1[i] = _f32(l['w1'], 'w1').data_ptr(); a.lcsa_b1[i] = _f32(l['b1'], 'b1').data_ptr()
         a.lcsa_bn_scale[i] = _f32(l['bn_m'], 'bn_m').data_ptr(); a.lcsa_bn_shift[i] = _f32(l['bn_a'], 'bn_a').data_ptr()
-        a.lcsa_rowsum[i] = o['rowsum'].data_ptr(); a.lcsa_A[i] = o['A'].data_ptr(); a.lcsa_Sm[i] = o['Sm'].data_ptr()
+        a.lcsa_rowmean[i] = o['rowmean'].data_ptr(); a.lcsa_A[i] = o['A'].data_ptr(); a.lcsa_Sm[i] = o['Sm'].data_ptr()
         ts.append(t); outs.append(o); keep += [rp, cp]
     _abi.check(lib.kad_pyramid_project_lcsa(ctypes.byref(a), _stream()), 'kad_pyramid_project_lcsa')
     return ts, outs

@@ -99,26 +99,31 @@ def check_explained(keep_a, ca, cb, conf_thres, iou_thres, eps_iou, eps_score):
     return out
 
 
-def trace_differences(keep_a, keep_b, cb, iou_thres, eps_iou, eps_score, conf_thres):
+def trace_differences(keep_a, keep_b, ca, cb, iou_thres, eps_iou, eps_score, conf_thres):
     """For every anchor kept by exactly one of the two runs, the reason, judged on B's data:
     'threshold'  its confidence is within eps_score of the confidence threshold;
+    'class'      its best class (or that of the box that suppresses it) differs between A and B: a tie of the two best class
+                 scores within eps_score (check_explained verifies the margin);
     'iou'        its IoU with a kept box of the other run lies within eps_iou of the IoU threshold (a direct flip);
     'order'      it overlaps a kept box of the other run whose score is within eps_score of its own (order flip);
-    'cascade'    the box that suppresses it in the other run is itself a differing box (linked by `parent`);
+    'cascade'    the box that suppresses it in the other run is itself a differing box (second entry: that box);
     None         unexplained."""
     sa, sb = set(keep_a), set(keep_b)
     box, conf, cls = cb['box'], cb['conf'], cb['cls']
+    flip = ca['cls'] != cb['cls']
     res = {}
     for d, other, own in [(d, sb, sa) for d in sa - sb] + [(d, sa, sb) for d in sb - sa]:
         # d is kept in `own` and dropped in `other`: look at the kept boxes of `other` that could have suppressed it there
         if abs(float(conf[d]) - conf_thres) <= eps_score:
             res[d] = ('threshold', None); continue
+        if bool(flip[d]):
+            res[d] = ('class', None); continue
         ks = torch.tensor(sorted(other), dtype=torch.long)
         if ks.numel() == 0:
             res[d] = (None, None); continue
         iou = pair_iou(box[d:d + 1], box[ks])[0]
-        same = cls[ks] == cls[d]
-        close = same & (iou >= iou_thres - eps_iou)
+        near = iou >= iou_thres - eps_iou
+        close = near & (cls[ks] == cls[d])
         reason = None
         for k, v in zip(ks[close].tolist(), iou[close].tolist()):
             if abs(v - iou_thres) <= eps_iou:
@@ -130,5 +135,9 @@ def trace_differences(keep_a, keep_b, cb, iou_thres, eps_iou, eps_score, conf_th
             for k in ks[close].tolist():
                 if k not in own:
                     reason = ('cascade', k); break
+        if reason is None:
+            # an overlapping box whose class differs between the two predictions suppresses d in one of them only
+            for k in ks[near & flip[ks]].tolist():
+                reason = ('class', k); break
         res[d] = reason if reason is not None else (None, None)
     return res

@@ -13,11 +13,12 @@ import nms_explain as ne
 
 pytestmark = pytest.mark.gpu
 
-# Half-precision tolerances of the configs[3] acceptance test: scores agree to 1e-2 (the stated relative bar; scores lie in
-# [0,1]); a corner stored in half precision at 400-800 px moves in steps of 0.25-0.5 px, which shifts the IoU of the small
-# boxes this model emits by several percent.
-C3_EPS_SCORE = 1e-2
-C3_EPS_IOU = 0.1
+# Half-precision tolerances of the configs[3] acceptance test. Measured on a B200 (two image seeds): against the fp32 modules the
+# engine's scores differ by at most 2.3e-3 and its box coordinates by at most 0.26 px (the modules' own fp16 path: 5.1e-3 and
+# 0.75 px), and every NMS difference is explained once IoU comparisons get 0.02 and score comparisons 2e-3 of slack. The
+# constants leave a 1.5x margin over that.
+C3_EPS_SCORE = 3e-3
+C3_EPS_IOU = 0.03
 
 
 def match_fraction(det, ref, tol=0.05):
@@ -76,7 +77,7 @@ def test_engine_fp32_matches_fixture(golden_dir):
     assert torch.equal(det, torch.cat((ca['box'][ka], ca['conf'][ka, None], ca['cls'][ka, None].float()), 1)[:300])
     rep = ne.check_explained(ka, ca, cb, 0.001, 0.65, eps_iou=1e-3, eps_score=1e-5)
     assert rep['ok'], rep
-    reasons = ne.trace_differences(ka, kb, cb, 0.65, 1e-3, 1e-5, 0.001)
+    reasons = ne.trace_differences(ka, kb, ca, cb, 0.65, 1e-3, 1e-5, 0.001)
     assert all(r[0] is not None for r in reasons.values()), reasons
     print(f'fp32 fixture: {len(kb)} reference detections, {len(set(ka) ^ set(kb))} differing boxes, reasons '
           f'{sorted((r[0] for r in reasons.values()))}')
@@ -112,11 +113,30 @@ def test_c3_config_detections_against_same_dtype_reference(golden_dir):
     assert det_ref.shape[0] == min(300, len(kb))
     rep = ne.check_explained(ka, ca, cb, 0.001, 0.65, eps_iou=C3_EPS_IOU, eps_score=C3_EPS_SCORE)
     assert rep['ok'], {k: (v[:5] if isinstance(v, list) else v) for k, v in rep.items()}
-    reasons = ne.trace_differences(ka, kb, cb, 0.65, C3_EPS_IOU, C3_EPS_SCORE, 0.001)
+    reasons = ne.trace_differences(ka, kb, ca, cb, 0.65, C3_EPS_IOU, C3_EPS_SCORE, 0.001)
     assert all(r[0] is not None for r in reasons.values())
     from collections import Counter
-    print(f'c3 fp16: candidates {int(ca["cand"].sum())} / {int(cb["cand"].sum())}, kept {len(ka)} / {len(kb)}, differing '
+    print(f'c3 fp16 vs the fp16 modules: candidates {int(ca["cand"].sum())} / {int(cb["cand"].sum())}, kept {len(ka)} / {len(kb)}, differing '
           f'{len(set(ka) ^ set(kb))} (top 300: {len(set(ka[:300]) ^ set(kb[:300]))}), reasons {dict(Counter(r[0] for r in reasons.values()))}')
+    # the same against the fp32 modules, and how the two half-precision paths compare with fp32: the engine (fp32 accumulation
+    # and decode, one rounding per stored tensor) must be at least as close to the fp32 result as the modules' own fp16 path is
+    raw32 = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
+    with torch.no_grad():
+        y32 = raw32(img.float() / 255)[0]
+    c32 = ne.candidates(y32[0].cpu(), 0.001)
+    k32 = ne.greedy_keep(c32, 0.65)
+    rep32 = ne.check_explained(ka, ca, c32, 0.001, 0.65, eps_iou=C3_EPS_IOU, eps_score=C3_EPS_SCORE)
+    assert rep32['ok'], {k: (v[:5] if isinstance(v, list) else v) for k, v in rep32.items()}
+    assert all(r[0] is not None for r in ne.trace_differences(ka, k32, ca, c32, 0.65, C3_EPS_IOU, C3_EPS_SCORE, 0.001).values())
+    e_box, e_cls = rel_err(ya[:, :4].float(), y32[:, :4]), rel_err(ya[:, 4:].float(), y32[:, 4:])
+    r_box, r_cls = rel_err(yb[:, :4].float(), y32[:, :4]), rel_err(yb[:, 4:].float(), y32[:, 4:])
+    print(f'c3 vs the fp32 modules: engine box {e_box:.2e} cls {e_cls:.2e}; fp16 modules box {r_box:.2e} cls {r_cls:.2e}; '
+          f'differing boxes engine {len(set(ka) ^ set(k32))}, fp16 modules {len(set(kb) ^ set(k32))}')
+    assert e_box <= 1e-2 and e_cls <= 1e-2                      # the stated fp16 bar (relative 1e-2), boxes and scores separately
+    assert e_box <= r_box and e_cls <= r_cls
+    for lo, hi in ((0, 10000), (10000, 12500), (12500, 13125)):  # per scale: <= 1 px and <= 1e-2 in score, absolutely
+        assert (ya[:, :4, lo:hi].float() - y32[:, :4, lo:hi]).abs().max().item() <= 1.0
+        assert (ya[:, 4:, lo:hi].float() - y32[:, 4:, lo:hi]).abs().max().item() <= 1e-2
 
 
 @pytest.mark.parametrize('backend', ['optimized', 'graph'])
@@ -199,7 +219,7 @@ def test_engine_uint8_input_equals_float_input(golden_dir):
     raw = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
     with torch.no_grad():
         yr = raw(img.float() / 255)[0]
-    assert rel_err(y8.float(), yr.float()) <= 2e-2 and rel_err(yf.float(), yr.float()) <= 2e-2
+    assert rel_err(y8.float(), yr.float()) <= 1e-2 and rel_err(yf.float(), yr.float()) <= 1e-2
 
 
 def test_engine_at_the_full_benchmark_size(golden_dir):
@@ -209,7 +229,7 @@ def test_engine_at_the_full_benchmark_size(golden_dir):
     import kadcnet
     from kadcnet.postprocess import non_max_suppression, non_max_suppression_device
     from kadconv import ops
-    g, sd = _sd(golden_dir)
+    sd = _sd_alive(golden_dir)
     img = seeding.seeded_input((2, 3, 800, 800), seed=21, kind='image').cuda()
     raw = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
     with torch.no_grad():
@@ -219,15 +239,18 @@ def test_engine_at_the_full_benchmark_size(golden_dir):
     torch.cuda.synchronize(); ops.check_status(img.device)
     assert y.shape == ref.shape == (2, 24, 13125)
     assert rel_err(y[:, :4].float(), ref[:, :4]) <= 1e-2          # boxes (pixels)
-    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 2e-2          # class scores
+    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 1e-2          # class scores
+    for lo, hi in ((0, 10000), (10000, 12500), (12500, 13125)):   # each scale on its own, absolutely: <= 1 px (2 half-precision steps at 800)
+        assert (y[:, :4, lo:hi].float() - ref[:, :4, lo:hi]).abs().max().item() <= 1.0
     graph = kadcnet.load_model(None, 'graph', 'cuda:0', state_dict=sd, dtype=torch.float16)
     yg, _ = graph(img)
     yg2, _ = graph(img)
     assert torch.equal(yg, yg2) and rel_err(yg.float(), y.float()) <= 1e-3
-    dets = non_max_suppression_device(y, 0.25, 0.65, max_det=300)
-    dets_ref = non_max_suppression(y, 0.25, 0.65, max_det=300)
+    # the batched NMS kernel at the configuration's thresholds: exactly the boxes, scores, classes and order of the reference-order NMS
+    dets = non_max_suppression_device(y, 0.001, 0.65, max_det=300)
+    dets_ref = non_max_suppression(y, 0.001, 0.65, max_det=300)
     for d, r in zip(dets, dets_ref):
-        assert abs(d.shape[0] - r.shape[0]) <= 2 and match_fraction(d.cpu(), r.cpu().float()) >= 0.97
+        assert d.shape == r.shape and torch.equal(d.cpu(), r.cpu().float())
 
 
 def test_own_conv3x3_at_the_full_benchmark_size(golden_dir):
@@ -235,7 +258,7 @@ def test_own_conv3x3_at_the_full_benchmark_size(golden_dir):
     199 / 99 / 49 inputs of the stride-2 layers) against the plain fp32 modules on the GPU, same bars as the default engine."""
     import kadcnet
     from kadconv import ops
-    g, sd = _sd(golden_dir)
+    sd = _sd_alive(golden_dir)
     img = seeding.seeded_input((2, 3, 800, 800), seed=21, kind='image').cuda()
     raw = kadcnet.load_model(None, 'raw', 'cuda:0', state_dict=sd)
     with torch.no_grad():
@@ -246,7 +269,7 @@ def test_own_conv3x3_at_the_full_benchmark_size(golden_dir):
     torch.cuda.synchronize(); ops.check_status(img.device)
     assert torch.equal(y, y2)
     assert rel_err(y[:, :4].float(), ref[:, :4]) <= 1e-2
-    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 2e-2
+    assert rel_err(y[:, 4:].float(), ref[:, 4:]) <= 1e-2
 
 
 def test_streaming_pipeline_matches_direct_calls(golden_dir):

@@ -150,6 +150,15 @@ def test_layer_call_matches_stepwise_kernels(dtype):
     b = fast.kadconv_forward_nhwc(layer, x)
     torch.cuda.synchronize()
     assert torch.equal(a, ref) and torch.equal(b, ref)
+    # the three ways the layer call can produce the LCSA masks (separate kernels; first stage finished in the pyramid kernel's
+    # tail; masks evaluated inside the deformable convolutions) give the same bits
+    try:
+        for scheme in (1, 2, 3):
+            fast.LAYER_SCHEME = scheme
+            assert torch.equal(fast.kadconv_forward_nhwc(layer, x), ref), scheme
+            assert torch.equal(fast.kadconv_forward_nhwc(layer, x), ref), scheme
+    finally:
+        fast.LAYER_SCHEME = 0
     g = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())

@@ -401,7 +401,7 @@ def test_inline_lcsa_mask_equals_mask_tensor(shape, dtype):
         for i, c in enumerate(cs):
             h, w = H >> i, W >> i
             assert torch.equal(ts1[i], ts0[i])
-            assert rel_err(lops[i]['rowsum'].cpu(), ts0[i].float().sum(2).cpu()) <= 1e-5
+            assert rel_err(lops[i]['rowmean'].cpu(), ts0[i].float().mean(2).cpu()) <= 1e-5
             if not ops.dsc_mma_inline_mask_supported(c, c, dtype, h, w):
                 continue
             wd = ops.pack_dsc_weight_simt(f(_rand((c, c, 3, 3), 250 + i, 1.0 / np.sqrt(9 * c))))

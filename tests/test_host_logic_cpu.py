@@ -98,11 +98,11 @@ def test_nms_differences_are_explained_or_flagged(golden_dir):
         ka = ne.greedy_keep(ca, 0.65)
         rep = ne.check_explained(ka, ca, cb, 0.001, 0.65, eps_iou=20 * rel, eps_score=4 * rel)
         assert rep['ok'], rep
-        reasons = ne.trace_differences(ka, kb, cb, 0.65, 20 * rel, 4 * rel, 0.001)
+        reasons = ne.trace_differences(ka, kb, ca, cb, 0.65, 20 * rel, 4 * rel, 0.001)
         assert set(reasons) == set(ka) ^ set(kb)
-        assert all(r[0] in ('iou', 'order', 'cascade', 'threshold') for r in reasons.values()), reasons
+        assert all(r[0] in ('iou', 'order', 'cascade', 'threshold', 'class') for r in reasons.values()), reasons
     # identical predictions: identical result, nothing to explain
-    assert ne.check_explained(kb, cb, cb, 0.001, 0.65, 0.0, 0.0)['ok'] and not ne.trace_differences(kb, kb, cb, 0.65, 0.0, 0.0, 0.001)
+    assert ne.check_explained(kb, cb, cb, 0.001, 0.65, 0.0, 0.0)['ok'] and not ne.trace_differences(kb, kb, cb, cb, 0.65, 0.0, 0.0, 0.001)
     # a localisation error is not a threshold effect: move the best box of the result by 40 pixels
     yb = y.clone()
     yb[0, kb[0]] += 40.0
