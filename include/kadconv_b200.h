@@ -344,6 +344,34 @@ int kad_conv3x3_bias_act(const void* x, const void* w, const float* bias, void* 
                          int B, int H, int W, int Cin, int Cout, int stride, int ldx, int ldy, int act, int dtype,
                          int* status, void* stream);
 
+/* The pooling chain of SPPELAN.forward (KAD-CNet/models/common.py:590-598 with SP, :187-193): three chained 5x5 max-pools
+ * (stride 1, padding 2) and the torch.cat of the four tensors, in one kernel and in place:
+ *   cat NHWC [B][H][W][4*C] dtype; channels [0, C) hold y1 (written there by the 1x1 convolution cv1); the call fills
+ *   [C, 2C) = maxpool(y1), [2C, 3C) = maxpool of that, [3C, 4C) = maxpool of that. The reference's own fused version:
+ *   sppelin_split_projection (KAD-CNet/inference/acceleration/kadc_fused_nsmall.py:421-443).
+ * kad_spp_pool3_supported: dtype f16/bf16, C % 8 == 0 and H*W*32 bytes of shared memory (two planes of 16-byte vectors). */
+int kad_spp_pool3_supported(int H, int W, int C, int dtype);
+int kad_spp_pool3(void* cat, int B, int H, int W, int C, int dtype, void* stream);
+
+/* Preprocessing of the inference script on the device: letterbox() of KAD-CNet/utils/augmentations.py:106-136 (cv2.resize with
+ * INTER_LINEAR to the unpadded size, then a constant border) followed by the BGR->RGB flip and the HWC->CHW transpose of
+ * KAD-CNet/inference/infer_dior.py:39-46, for one 8-bit image; the `/255` happens in the detector's first layer
+ * (kad_stem_conv_u8). The result equals the OpenCV path bit for bit: same 11-bit fixed-point coefficients and integer passes.
+ *   src  uint8 [H0][W0][3] BGR (what cv2.imread returns), dst uint8 [3][Hn][Wn] RGB planes;
+ *   the image is resized to new_h x new_w and placed at (top, left); everything else is pad_value (114 in the reference);
+ *   xofs int32 [new_w] / xalpha int16 [new_w][2], yofs int32 [new_h] / ybeta int16 [new_h][2]: OpenCV's per-column and per-row
+ *   source offsets and coefficients (kadcnet.preprocess.resize_tables computes them on the host as cv::resize does);
+ *   area2x = 1 for a shrink by exactly 2 in both directions, which OpenCV computes as the rounded mean of 2x2 blocks (tables unused). */
+int kad_letterbox_u8(const void* src_bgr_hwc, void* dst_rgb_chw, int H0, int W0, int Hn, int Wn,
+                     int new_h, int new_w, int top, int left, int area2x,
+                     const int* xofs, const short* xalpha, const int* yofs, const short* ybeta,
+                     int pad_value, void* stream);
+/* scale_boxes + clip_boxes + round of the inference script (KAD-CNet/utils/general.py:824-868, infer_dior.py:56) on the padded
+ * output of kad_nms_batched: x = clamp((x - pad_x) / gain, 0, width0), y likewise, then round-half-even when do_round.
+ *   dets float32 [B][max_det][6] (columns 0-3 are modified in place for the first counts[b] rows of image b), counts int32 [B],
+ *   geom float32 [B][5] = gain, pad_x, pad_y, width0, height0 of each image. */
+int kad_scale_boxes(float* dets, const int* counts, const float* geom, int B, int max_det, int do_round, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

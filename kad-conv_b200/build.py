@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / 'csrc'
 OUT_DIR = HERE / 'kadconv' / '_lib'
 LIB = OUT_DIR / 'libkadconv_b200.so'
-SOURCES = ['kad_api.cu', 'kad_simt.cu', 'kad_px.cu', 'kad_elementwise.cu', 'kad_dsc_tc.cu', 'kad_dsc_mma.cu', 'kad_stem.cu', 'kad_pyramid.cu', 'kad_gemm_tc.cu', 'kad_conv3x3_tc.cu', 'kad_postprocess.cu', 'kad_layer.cu']
+SOURCES = ['kad_api.cu', 'kad_simt.cu', 'kad_px.cu', 'kad_elementwise.cu', 'kad_dsc_tc.cu', 'kad_dsc_mma.cu', 'kad_stem.cu', 'kad_pyramid.cu', 'kad_gemm_tc.cu', 'kad_conv3x3_tc.cu', 'kad_postprocess.cu', 'kad_preprocess.cu', 'kad_layer.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17', '-Xcompiler', '-fPIC']
 
 

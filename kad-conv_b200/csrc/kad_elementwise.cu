@@ -1396,3 +1396,85 @@ extern "C" int kad_image_to_nhwc(const void* img_u8, void* y, int B, int C, int 
     KAD_CHECK_LAUNCH("image_to_nhwc_kernel");
     return KAD_OK;
 }
+
+
+// ---- SPPELAN pooling chain ------------------------------------------------------------------------------------------------
+// y2 = maxpool5(y1), y3 = maxpool5(y2), y4 = maxpool5(y3) (kernel 5, stride 1, padding 2: SP of KAD-CNet/models/common.py:187-193
+// as chained by SPPELAN.forward, :590-598) in one kernel that reads slice 0 of the concatenation [y1 | y2 | y3 | y4] and writes
+// slices 1-3 in place, so neither the three pooled tensors nor the torch.cat exist as separate passes over memory.
+// A block owns one image and 8 channels: the H x W plane of 16-byte vectors sits in shared memory and each pooling is a
+// horizontal then a vertical running maximum over 5 (padding = the window simply stops at the border, as -inf padding does).
+namespace kad {
+namespace {
+template <typename T> struct Vec2;
+template <> struct Vec2<__half> { using type = __half2; };
+template <> struct Vec2<__nv_bfloat16> { using type = __nv_bfloat162; };
+
+template <typename T>
+__device__ __forceinline__ uint4 max8(uint4 a, uint4 b) {
+    using V = typename Vec2<T>::type;
+    uint4 r;
+    V* pr = reinterpret_cast<V*>(&r); const V* pa = reinterpret_cast<const V*>(&a); const V* pb = reinterpret_cast<const V*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = __hmax2_nan(pa[i], pb[i]);      // NaN propagates, as in the library's max pooling
+    return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) spp_pool3_kernel(uint4* __restrict__ cat, int H, int W, int ld8, int c8) {
+    extern __shared__ __align__(16) uint4 spp_sm[];
+    uint4* a = spp_sm;                // current plane
+    uint4* h = spp_sm + H * W;        // horizontally pooled plane
+    const int b = blockIdx.y, ch = blockIdx.x, HW = H * W;
+    uint4* base = cat + (size_t)b * HW * ld8 + ch;
+    for (int e = threadIdx.x; e < HW; e += 256) a[e] = base[(size_t)e * ld8];
+    __syncthreads();
+    for (int pass = 1; pass <= 3; ++pass) {
+        for (int e = threadIdx.x; e < HW; e += 256) {
+            const int y = e / W, x = e - y * W;
+            uint4 m = a[e];
+#pragma unroll
+            for (int d = -2; d <= 2; ++d) if (d != 0 && x + d >= 0 && x + d < W) m = max8<T>(m, a[e + d]);
+            h[e] = m;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < HW; e += 256) {
+            const int y = e / W;
+            uint4 m = h[e];
+#pragma unroll
+            for (int d = -2; d <= 2; ++d) if (d != 0 && y + d >= 0 && y + d < H) m = max8<T>(m, h[e + d * W]);
+            a[e] = m;
+            base[(size_t)e * ld8 + (size_t)pass * c8] = m;
+        }
+        __syncthreads();
+    }
+}
+}  // namespace
+}  // namespace kad
+
+extern "C" int kad_spp_pool3_supported(int H, int W, int C, int dtype) {
+    return (dtype == KAD_F16 || dtype == KAD_BF16) && C > 0 && C % 8 == 0 && H > 0 && W > 0 && (size_t)H * W * 32 <= 200 * 1024;
+}
+
+extern "C" int kad_spp_pool3(void* cat, int B, int H, int W, int C, int dtype, void* stream) {
+    KAD_CHECK_ARG(cat && B > 0 && B <= 65535, "kad_spp_pool3: bad argument");
+    if (!kad_spp_pool3_supported(H, W, C, dtype))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_spp_pool3: needs f16/bf16, C %% 8 == 0 and a plane of H*W*32 bytes in shared memory (got H=%d W=%d C=%d)", H, W, C);
+    KAD_CHECK_ARG((uintptr_t)cat % 16 == 0, "kad_spp_pool3: the tensor must be 16-byte aligned");
+    const size_t smem = (size_t)H * W * 32;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(C / 8, B);
+    if (dtype == KAD_F16) {
+        auto kern = spp_pool3_kernel<__half>;
+        if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "spp_pool3 smem attribute: %s", cudaGetErrorString(e)); }
+        kern<<<grid, 256, smem, st>>>((uint4*)cat, H, W, 4 * C / 8, C / 8);
+    } else {
+        auto kern = spp_pool3_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "spp_pool3 smem attribute: %s", cudaGetErrorString(e)); }
+        kern<<<grid, 256, smem, st>>>((uint4*)cat, H, W, 4 * C / 8, C / 8);
+    }
+    KAD_CHECK_LAUNCH("spp_pool3_kernel");
+    return KAD_OK;
+}

@@ -85,6 +85,10 @@ class _ConvKxK:
 
     def __call__(self, x, out=None, out_coff=0, in_coff=0):
         if self.own:
+            if out is not None and (out.shape[-1] % 8 or out_coff % 8):       # the kernel stores 16-byte vectors: rows must stay aligned
+                y = ops.conv3x3_bias_act(x, self.w, self.b, act=self.act, stride=self.stride[0], in_coff=in_coff, cin=self.cin)
+                out[..., out_coff:out_coff + y.shape[-1]].copy_(y)
+                return out
             return ops.conv3x3_bias_act(x, self.w, self.b, act=self.act, stride=self.stride[0], in_coff=in_coff, cin=self.cin,
                                         out=out, out_coff=out_coff)
         if in_coff or x.shape[-1] != self.w.shape[1] * self.groups:
@@ -181,10 +185,19 @@ class FastDetector(torch.nn.Module):
         if isinstance(m, M.SPPELAN):
             cv1, cv5 = _conv(m.cv1, dt, dev, self.own3x3), _conv(m.cv5, dt, dev, self.own3x3)
 
+            c3 = m.cv1.conv.out_channels
+            five = all(getattr(sp.m, 'kernel_size', None) == 5 and sp.m.stride == 1 and sp.m.padding == 2 for sp in (m.cv2, m.cv3, m.cv4))
+
             def spp(x):
+                B, H, W, _ = x.shape
+                if five and ops.spp_pool3_supported(H, W, c3, x.dtype):
+                    # cv1 lands in the first quarter of the concatenation, one kernel fills the other three with the pooling chain
+                    cat = torch.empty((B, H, W, 4 * c3), dtype=x.dtype, device=x.device)
+                    cv1(x, out=cat, out_coff=0)
+                    return cv5(ops.spp_pool3_(cat, c3))
                 ys = [cv1(x)]
-                for _ in range(3):
-                    ys.append(_nhwc(F.max_pool2d(_nchw_view(ys[-1]), 5, 1, 2)))
+                for sp in (m.cv2, m.cv3, m.cv4):
+                    ys.append(_nhwc(sp.m(_nchw_view(ys[-1]))))
                 return cv5(torch.cat(ys, -1))
             return spp
         if isinstance(m, torch.nn.Upsample):
@@ -234,10 +247,13 @@ class FastDetector(torch.nn.Module):
 
         def head(feats):
             raw = []
+            nb = 4 * m.reg_max
             for i, f in enumerate(feats):
-                b = box[i][2](box[i][1](box[i][0](f)))
-                c = cls[i][2](cls[i][1](cls[i][0](f)))
-                raw.append(torch.cat((b, c), -1))                         # [B,H,W,no]
+                # the last convolution of each branch writes its slice of the raw map [B,H,W,no]: no concatenation pass
+                r = torch.empty(f.shape[:3] + (nb + m.nc,), dtype=f.dtype, device=f.device)
+                box[i][2](box[i][1](box[i][0](f)), out=r, out_coff=0)
+                cls[i][2](cls[i][1](cls[i][0](f)), out=r, out_coff=nb)
+                raw.append(r)
             # DFL expectation, dist2bbox and the class sigmoid of the reference's sequence (KAD-CNet/models/yolo.py:112-127)
             # in one kernel per scale, anchors in (scale, y, x) order
             y = ops.head_decode(raw, strides, m.reg_max, m.nc)

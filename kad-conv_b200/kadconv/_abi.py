@@ -104,6 +104,10 @@ SIGNATURES = {
     'kad_gemm1x1_tc_supported': (c_int, [c_int, c_int, c_int]),
     'kad_gemm1x1_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p]),
+    'kad_spp_pool3_supported': (c_int, [c_int, c_int, c_int, c_int]),
+    'kad_spp_pool3': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_letterbox_u8': (c_int, [c_void_p, c_void_p] + [c_int] * 9 + [c_void_p] * 4 + [c_int, c_void_p]),
+    'kad_scale_boxes': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     'kad_conv3x3_tc_supported': (c_int, [c_int, c_int, c_int, c_int]),
     'kad_conv3x3_bias_act': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_void_p, c_void_p]),

@@ -637,3 +637,18 @@ def lcsa_mask_from_partials(rowpart, colpart, prm, dtype, mask_f32=False):
         _ptr(prm['w2']), _ptr(prm['b2']), _ptr(prm['w3']), _ptr(prm['b3']), _ptr(scratch), _ptr(rowsum), _ptr(mask),
         B, H, W, C, int(mask_f32), _DT[dtype], _stream()), 'kad_lcsa_mask_from_partials', 2)
     return mask
+
+
+def spp_pool3_supported(H, W, C, dtype):
+    return dtype in _DT and bool(_abi.load().kad_spp_pool3_supported(H, W, C, _DT[dtype]))
+
+
+def spp_pool3_(cat, C):
+    """cat [B,H,W,4*C] NHWC with y1 in channels [0, C): fills the other three quarters with the chained 5x5 max-pools
+    (stride 1, padding 2) of SPPELAN, in place. Returns cat."""
+    cat = _cuda(cat, 'cat')
+    B, H, W, C4 = cat.shape
+    if C4 != 4 * C:
+        raise ValueError('cat must have 4*C channels')
+    _abi.check(_abi.load().kad_spp_pool3(_ptr(cat), B, H, W, C, dtype_code(cat), _stream()), 'kad_spp_pool3')
+    return cat

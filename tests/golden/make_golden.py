@@ -11,6 +11,7 @@ Fixtures (all float32, weights are NOT stored: they are regenerated from oracle/
   dcn_op.npz        torchvision.ops.deform_conv2d on [2,16,9,12] -> 24 channels, offsets N(0,2)
   detector_s.npz    KAD-CNet-S (dior_s_base graph) on [1,3,160,192]: y[1,24,A], NMS detections and the
                     model's state_dict key -> shape table (so the weights can be regenerated)
+  preprocess.npz    letterbox() (cv2) + BGR->RGB + CHW on eight small images, and scale_boxes(...).round() of seeded boxes
 """
 import json
 import os
@@ -102,7 +103,29 @@ def golden_detector():
     print('detector', tuple(y.shape), 'detections', tuple(det.shape), 'max score', float(y[:, 4:].max()))
 
 
+def golden_preprocess():
+    """letterbox() of the reference (on the real cv2) + the BGR->RGB / CHW step of its inference script, and scale_boxes(...).round(),
+    on small seeded images: up- and down-scaling, an exact 2x shrink (OpenCV's area path), no resize at all, odd sizes."""
+    import_reference_detector()
+    from utils.augmentations import letterbox
+    from utils.general import scale_boxes
+    cases = [((60, 80), 64), ((96, 72), 64), ((48, 64), 96), ((128, 128), 64), ((64, 64), 64), ((37, 91), 96), ((75, 50), 64), ((33, 200), 128)]
+    out = {'n': len(cases)}
+    for i, (shape, size) in enumerate(cases):
+        g = np.random.default_rng([77, i])
+        img = g.integers(0, 256, shape + (3,), dtype=np.uint8)
+        proc, ratio, pad = letterbox(img, new_shape=(size, size), auto=False, stride=32)
+        x = np.ascontiguousarray(proc[:, :, ::-1].transpose(2, 0, 1))
+        boxes = g.uniform(-4, size + 4, (40, 4)).astype(np.float32)
+        boxes[:, 2:] = boxes[:, :2] + np.abs(boxes[:, 2:] - boxes[:, :2])
+        scaled = scale_boxes(x.shape[1:], torch.from_numpy(boxes.copy()), img.shape).round().numpy()
+        out.update({f'img{i}': img, f'x{i}': x, f'size{i}': size, f'ratio{i}': np.array(ratio), f'pad{i}': np.array(pad), f'boxes{i}': boxes, f'scaled{i}': scaled})
+    np.savez_compressed(HERE / 'preprocess.npz', **out)
+    print('preprocess', len(cases), 'cases')
+
+
 if __name__ == '__main__':
     golden_kadconv()
     golden_dcn()
     golden_detector()
+    golden_preprocess()

@@ -415,3 +415,23 @@ def test_inline_lcsa_mask_equals_mask_tensor(shape, dtype):
             torch.cuda.synchronize()
             assert torch.equal(y1, y0) and torch.equal(g1, g0)
     assert int(ops.layer_counters(x.device).abs().sum()) == 0
+
+
+@pytest.mark.parametrize('shape,dtype', [((3, 25, 25, 144), torch.float16), ((2, 7, 5, 16), torch.bfloat16), ((1, 50, 40, 8), torch.float16), ((2, 3, 9, 24), torch.float16)])
+def test_spp_pooling_chain_in_place(shape, dtype):
+    """kad_spp_pool3: the three chained 5x5 max-pools of SPPELAN written into the channel quarters of the concatenation, against
+    torch's max_pool2d + cat (exact: a maximum has no rounding), on maps smaller than the window too."""
+    import torch.nn.functional as F
+    from kadconv import ops
+    B, H, W, C = shape
+    y1 = _rand((B, C, H, W), 300).to(dtype)
+    ys = [y1]
+    for _ in range(3):
+        ys.append(F.max_pool2d(ys[-1].float(), 5, 1, 2).to(dtype))
+    ref = torch.cat([nhwc(t) for t in ys], -1)
+    assert ops.spp_pool3_supported(H, W, C, dtype)
+    cat = torch.full((B, H, W, 4 * C), float('nan'), dtype=dtype).cuda()
+    cat[..., :C] = nhwc(y1).cuda()
+    out = ops.spp_pool3_(cat, C)
+    assert torch.equal(out.cpu(), ref)
+    assert not ops.spp_pool3_supported(100, 100, 144, dtype) and not ops.spp_pool3_supported(25, 25, 12, dtype)
