@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the KAD-Conv inference hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c4-kernel|conv3x3|gemm1x1] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c0|c1|c2|c4-kernel|conv3x3|gemm1x1] [--impl ours|reference]
 
 Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloads (BASELINE.json configs):
   c4  (default) KAD-CNet-S detector, fp16, 64 uint8 3x800x800 synthetic images per step sharded over the ranks:
@@ -9,6 +9,7 @@ Prints ONE JSON line on stdout (rank 0; everything else goes to stderr). Workloa
       through the public Python API from pinned host images, detections read back, both copies inside the timed
       region; `roofline` = the kernel with the largest share of the forward timed alone; `kadconv_op` = the c1
       measurement below, taken in the same run (the second half of the metric: op microseconds + % of roofline).
+  c0  KADConv(64) on x[2,64,80,80] fp32 through the module API: microseconds per forward next to the plain module on the GPU and the CPU.
   c1  KAD-Conv operator alone: DSC 256->256, [16,256,100,100] fp16, offsets N(0,2) px, mask given (gather +
       tcgen05 implicit GEMM). One step = one pass over the batch of 16 feature maps.
   c2  bf16 KADConv(128) at 200x200 + avg-pool + 1x1 GEMM+SiLU + SE, with a per-kernel-group table.
@@ -772,6 +773,63 @@ def run_c2(args, rank, world, local):
         'stages': stages, 'e2e': None, 'gpu_launches': launches, 'clocks': clocks,
     }
 
+# ------------------------------------------------------------------------------------------- C0
+def run_c0(args, local):
+    """BASELINE configs[0]: KADConv(64) on x[2,64,80,80] fp32 (the reference's CPU-runnable case). Microseconds per forward of the
+    module with the B200 pipeline enabled (NCHW in, NCHW out, eager launches), of the plain PyTorch module on the same GPU, and of
+    the plain module on the host cores."""
+    import kadconv
+    device = torch.device('cuda', local); torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    layer = kadconv.KADConv(64).eval()
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        for name, m in layer.named_modules():
+            if name.endswith('conv_offset'):      # the reference zero-initialises it: give the offsets a spread of about 0.5 px
+                m.weight.normal_(0, 0.5 / m.weight[0].numel() ** 0.5, generator=g); m.bias.normal_(0, 0.05, generator=g)
+    x = torch.randn((2, 64, 80, 80), generator=g)
+
+    def timed(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    n = max(10, args.steps)
+    xd = x.to(device)
+    plain = layer.to(device)
+    with torch.no_grad():
+        ref = plain(xd)
+        us_torch = timed(lambda: plain(xd), n)
+        kadconv.enable_fast_inference(plain)
+        y = plain(xd)
+        us_ours = timed(lambda: plain(xd), n)
+    err = (y - ref).abs().max().item()
+    kadconv.disable_fast_inference(plain)
+    cpu = plain.cpu()
+    torch.set_num_threads(os.cpu_count() or 1)
+    with torch.no_grad():
+        cpu(x)
+        t0 = time.perf_counter()
+        for _ in range(5):
+            cpu(x)
+        us_cpu = (time.perf_counter() - t0) / 5 * 1e6
+    model, cores = cpu_info()
+    return {'metric': 'KAD-Conv op (KADConv(64), x[2,64,80,80] fp32) forwards/s', 'value': 1e6 / us_ours, 'unit': 'forwards/s', 'n_gpus': 1,
+            'steps': n, 'warmup': 5, 'ms_per_step': us_ours / 1e3, 'us_per_forward': us_ours, 'higher_is_better': True, 'vs_baseline': None,
+            'dtype': 'f32', 'data': 'synthetic', 'config': {'workload': 'c0: KADConv(64), x[2,64,80,80] fp32, module API (NCHW in / out), eager'},
+            'max_abs_vs_plain_module_on_gpu': err,
+            'torch_gpu_reference': {'us_per_forward': us_torch, 'what': 'the plain PyTorch module on the same GPU (torchvision deform_conv2d)'},
+            'cpu_baseline': {'value': 1e6 / us_cpu, 'unit': 'forwards/s', 'us_per_forward': us_cpu, 'cores': torch.get_num_threads(), 'kind': 'port',
+                             'sample': '5 forwards of the plain module, fp32', 'cpu': model, 'os_cpu_count': cores},
+            'e2e': None, 'gpu_launches': n * 27}
+
+
 # ------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -779,7 +837,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c4', choices=['c1', 'c2', 'c4', 'c4-kernel', 'conv3x3', 'gemm1x1'],
+    ap.add_argument('--workload', default='c4', choices=['c0', 'c1', 'c2', 'c4', 'c4-kernel', 'conv3x3', 'gemm1x1'],
                     help='c4 (default): KAD-CNet-S images/s, with the KAD-Conv op of c1 timed in the same run; c1 / c2: the operator configurations alone')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mini-batch', type=int, default=64, help='c4: images per forward graph')
@@ -852,8 +910,8 @@ def main():
                    'algorithmic_bytes': dom['bytes'], 'gb_per_s': dom['gbs'], 'gpu_launches': max(3, min(args.steps, 20)),
                    'inline_mask_variant_us': old['us'] if old else None}))
         return
-    if args.workload in ('conv3x3', 'gemm1x1'):
-        res = run_conv3x3(args, local) if args.workload == 'conv3x3' else run_gemm1x1(args, local)
+    if args.workload in ('conv3x3', 'gemm1x1', 'c0'):
+        res = run_conv3x3(args, local) if args.workload == 'conv3x3' else (run_gemm1x1(args, local) if args.workload == 'gemm1x1' else run_c0(args, local))
         if rank == 0:
             emit(res)
         return

@@ -2,22 +2,25 @@
 // tensor-core instruction (mma.sync m16n8k16, fp16/bf16 operands, fp32 accumulators), NHWC.
 //
 // Why not the tcgen05 implicit GEMM: with K = 9 taps x 10..44 channels and N <= 64 the contraction is tiny; what costs
-// is the bilinear gather. So the A operand is never staged as a matrix: the four lanes that share an accumulator row
-// gather four channels each (one 8-byte load per corner) straight into the A-fragment registers. The bilinear
-// interpolation itself is folded into the contraction: a sample is sum_corner w_corner * x[corner], so every corner
-// contributes one MMA with A = w_corner * x[corner] (one packed multiply per register) against the same weight
-// fragment; products are rounded to the storage type, the sum over corners, taps and channels is fp32.
+// is the bilinear gather and its geometry, i.e. instruction issue. So the kernel keeps the instruction count per pixel low:
+// lane l of a warp OWNS pixel l of the warp's 32 pixels. It computes the pixel's sampling geometry in registers (no table),
+// gathers the four corners of a tap for all channels with 8-byte shared-memory loads, interpolates them with packed
+// half-precision FMAs (fp32 for bf16) and stores the interpolated samples as one row of a per-warp A tile
+// [32 pixels][taps of the chunk x channels] in shared memory; after a chunk of taps (one kernel row) the warp reads the
+// tile back as MMA fragments with ldmatrix and contracts it against the weight fragments. A gather instruction therefore
+// serves 32 pixels (the earlier form of this kernel, where the four lanes of an accumulator row gathered straight into the
+// fragments, served 8) and the bilinear blend costs one operation per two channels and corner.
 //
 // Blocks are persistent (two per SM for the narrow variants) and walk over (image, group of 256 consecutive pixels);
 // a warp owns 32 pixels of the group (two 16-row MMA tiles). The image rows a group can reach (its own rows, one row of
 // 3x3 halo, a margin for the learned offsets) are one CONTIGUOUS range of the NHWC tensor; it is copied to shared
 // memory with 16-byte cp.async, so HBM sees one coalesced pass over x and the gathers are shared-memory loads with
-// 32-bit addresses. Lane l computes the sampling geometry of pixel l, one kernel row (3 taps) at a time, into a
-// warp-private table: per corner the shared-memory address of the pixel (the address of a block of zeros when the
-// corner leaves the image) and the mask-scaled weight. The gathering lanes then run straight-line code: address +
-// channel offset, one load, multiply, MMA. A tap in which some lane's sample leaves the staged rows (a warp vote)
-// takes a slower variant of the same code that reads those corners from global memory.
-// Results leave through shared memory as well, so that a warp writes its 32 pixels as one contiguous run.
+// 32-bit addresses. A corner outside the image points at a block of zeros; a corner outside the staged rows (a large
+// learned offset) is read from global memory by that lane. Results leave through shared memory as well, so that a warp
+// writes its 32 pixels as one contiguous run.
+//
+// K layout of a tap: channels in groups of four (one 8-byte load); when Cin is no multiple of four the last group re-reads the
+// last four channels of the pixel and the weight fragments carry zeros for the slots that would count a channel twice.
 //
 // Modes:  plain   offset == NULL: ordinary zero-padded 3x3 convolution (the offset convolution, c -> 18)
 //         deform  offsets and modulation mask read from global memory
@@ -42,7 +45,9 @@ struct MmaParams {
     const float* boff;                  // [18] (fused mode)
     const float* scale; const float* shift; const float* post;
     void* y; float* gap_partial;
-    int H, W, Cin, Cout, KC, align;
+    int H, W, Cin, Cout, align;
+    int G, KT, TPC, KS, pitchA, scratch;   // channel groups per tap, K slots per tap (4G), taps per chunk, 16-wide k-steps per chunk,
+                                          // bytes per A-tile row, bytes of per-warp scratch (A tile, later the output tile)
     int offset_f32, mask_f32, y_f32, act;
     int B, win_margin;                  // win_margin: rows staged above / below the 3x3 halo for the learned offsets
     // inline mode: LCSA operands. rowmean [B][H][Cin] (means over x), A [B][W][Cp], Sm [W][Cp] (Cp = Cin rounded up to 4),
@@ -52,15 +57,114 @@ struct MmaParams {
     int stage_cols;                     // 1: the image's A rows and Sm are staged in shared memory (they fit); 0: read through L2
 };
 
-constexpr int SCRATCH_PER_WARP = 4224;  // sampling table (3 taps x 32 pixels x 32 bytes), later the warp's output tile (+ 16 bytes of shift)
 constexpr int ZERO_BYTES = 160;         // block of zeros in shared memory that out-of-image corners point at
-constexpr uint32_t OUTSIDE = 0x80000000u;   // table address flag: the corner is not staged; low bits = image element offset
 
-// Weight fragments for mma.sync: lane (g = lane / 4, t = lane % 4) of n-tile nt holds output channel nt*8 + g and four
-// input channels (the K order inside a 16-chunk is permuted so that a lane's four A values are four CONSECUTIVE
-// channels: logical k = 2t, 2t+1, 2t+8, 2t+9  <->  slot 0..3 = channel first + 0..3, first = lane_first_channel()).
+// First channel of channel group j of a pixel (see the K layout above).
+__device__ __forceinline__ int group_first(int j, int Cin) {
+    const int ch = 4 * j, nv = Cin - ch;
+    return nv >= 4 ? ch : Cin - 4;
+}
+
+// Weight fragments for mma.sync, per chunk of TPC taps: dst [9 / TPC][KS][NT][32 lanes]. Lane (g = lane / 4, t = lane % 4) of
+// n-tile nt holds output channel nt*8 + g and the K slots ks*16 + {2t, 2t+1, 2t+8, 2t+9} of the chunk; slot = tap_in_chunk * KT +
+// 4*group + i stands for channel group_first(group) + i of that tap, and is zero when the slot is padding or repeats a channel.
 template <typename T>
-__device__ __forceinline__ void stage_weights(uint2* dst, const float* __restrict__ Wt, int Cin, int Cout, int KC, int NT, int tid) {
+__device__ __forceinline__ void stage_weights(uint2* dst, const float* __restrict__ Wt, int Cin, int Cout, int KT, int TPC, int KS, int NT, int tid) {
+    const int total = (9 / TPC) * KS * NT * 32;
+    for (int e = tid; e < total; e += MMA_THREADS) {
+        const int lane = e & 31, f = e >> 5, nt = f % NT, ks = (f / NT) % KS, ch = f / (NT * KS);
+        const int n = nt * 8 + (lane >> 2), t = lane & 3;
+        const int kk[4] = {ks * 16 + 2 * t, ks * 16 + 2 * t + 1, ks * 16 + 2 * t + 8, ks * 16 + 2 * t + 9};
+        float w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tl = kk[i] / KT, slot = kk[i] - tl * KT, j = slot >> 2, c = group_first(j, Cin) + (slot & 3);
+            const bool ok = tl < TPC && n < Cout && c >= 4 * j;
+            w[i] = ok ? Wt[((size_t)(ch * TPC + tl) * Cin + c) * Cout + n] : 0.f;
+        }
+        dst[e] = make_uint2(pack2<T>(w[0], w[1]), pack2<T>(w[2], w[3]));
+    }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// acc += A tile (32 rows x KS*16, rows pitchA bytes apart, at shared-memory address `tile`) x the chunk's weight fragments.
+template <typename T, int NTP>
+__device__ __forceinline__ void mma_chunk(float (&acc)[2][NTP][4], uint32_t tile, int pitchA, const uint2* __restrict__ Bc, int KS, int lane) {
+    // ldmatrix x4 of a 16 x 16 block: lanes 0-15 address rows 0-15 at k 0-7, lanes 16-31 the same rows at k 8-15
+    const uint32_t a0 = tile + (uint32_t)((lane & 15) * pitchA + (lane >> 4) * 16);
+#pragma unroll 1
+    for (int ks = 0; ks < KS; ++ks) {
+        uint2 bf[NTP];
+#pragma unroll
+        for (int nt = 0; nt < NTP; ++nt) bf[nt] = Bc[(ks * NTP + nt) * 32 + lane];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            uint32_t r0, r1, r2, r3;
+            ldmatrix_x4(a0 + (uint32_t)(mt * 16 * pitchA + ks * 32), r0, r1, r2, r3);
+#pragma unroll
+            for (int nt = 0; nt < NTP; ++nt) mma16816<T>(acc[mt][nt], r0, r1, r2, r3, bf[nt]);
+        }
+    }
+}
+
+// Bilinear blend of four corners, four channels at a time; weights are the mask-scaled corner weights.
+template <typename T> struct CornerWeights;
+template <> struct CornerWeights<__half> {
+    uint32_t w[4];
+    __device__ __forceinline__ void set(float a, float b, float c, float d) {
+        w[0] = pack2<__half>(a, a); w[1] = pack2<__half>(b, b); w[2] = pack2<__half>(c, c); w[3] = pack2<__half>(d, d);
+    }
+    __device__ __forceinline__ uint32_t blend(uint32_t a, uint32_t b, uint32_t c, uint32_t d) const {
+        const __half2* pw = reinterpret_cast<const __half2*>(w);
+        __half2 r = __hmul2(pw[0], *reinterpret_cast<__half2*>(&a));
+        r = __hfma2(pw[1], *reinterpret_cast<__half2*>(&b), r);
+        r = __hfma2(pw[2], *reinterpret_cast<__half2*>(&c), r);
+        r = __hfma2(pw[3], *reinterpret_cast<__half2*>(&d), r);
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+};
+template <> struct CornerWeights<__nv_bfloat16> {      // bf16 has 8 bits of mantissa: blend in float32, round once
+    float w[4];
+    __device__ __forceinline__ void set(float a, float b, float c, float d) { w[0] = a; w[1] = b; w[2] = c; w[3] = d; }
+    __device__ __forceinline__ uint32_t blend(uint32_t a, uint32_t b, uint32_t c, uint32_t d) const {
+        const float2 fa = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&a)), fb = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&b));
+        const float2 fc = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&c)), fd = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&d));
+        return pack2<__nv_bfloat16>(fmaf(w[3], fd.x, fmaf(w[2], fc.x, fmaf(w[1], fb.x, w[0] * fa.x))),
+                                    fmaf(w[3], fd.y, fmaf(w[2], fc.y, fmaf(w[1], fb.y, w[0] * fa.y))));
+    }
+};
+
+// One tap of one pixel: gather the four corners group by group, blend, store at `dst` (the tap's slots of the pixel's A-tile row).
+// aq: shared-memory byte offsets of the four corners (always inside the staged rows). SLOW (some lane of the warp has a corner in
+// an image row that is not staged): such a corner, marked in `far` (bit cr), is read from global memory at element offset ge[cr].
+template <typename T, int ALIGN, bool SLOW, int GT>
+__device__ __forceinline__ void gather_tap(unsigned char* dst, const unsigned char* smem, const unsigned char* gimg, const uint32_t (&aq)[4],
+                                           uint32_t far, const int (&ge)[4], const CornerWeights<T>& cw, int Gr, int Cin) {
+    const int G = GT ? GT : Gr;
+#pragma unroll (GT ? GT : 1)
+    for (int j = 0; j < G; ++j) {
+        // with GT known, Cin lies in (4*(GT-1), 4*GT]: every group but the last starts at channel 4*j (a constant offset)
+        const uint32_t coff = (GT && j < GT - 1) ? 8u * (uint32_t)j : 2u * (uint32_t)group_first(j, Cin);
+        uint2 v[4];
+#pragma unroll
+        for (int cr = 0; cr < 4; ++cr) {
+            if (SLOW && ((far >> cr) & 1u)) v[cr] = ldg8<ALIGN>(gimg + 2 * (size_t)ge[cr] + coff);
+            else v[cr] = lds8<ALIGN>(smem, aq[cr] + coff);
+        }
+        *reinterpret_cast<uint2*>(dst + 8 * j) = make_uint2(cw.blend(v[0].x, v[1].x, v[2].x, v[3].x), cw.blend(v[0].y, v[1].y, v[2].y, v[3].y));
+    }
+}
+
+// Ordinary zero-padded 3x3 convolution (the offset convolution; the whole kernel in plain mode). No A tile here: without
+// deformation the four lanes that share an accumulator row load four channels each straight into the A fragment registers, and
+// a 3x3 convolution has no geometry to compute, so that form has the fewest instructions. Its weight fragments use a K order
+// permuted to match: lane t of a 16-channel chunk holds four CONSECUTIVE channels (logical k = 2t, 2t+1, 2t+8, 2t+9 <-> channel
+// lane_first_channel() + 0..3), layout [9 taps][KC chunks][NT][32 lanes].
+template <typename T>
+__device__ __forceinline__ void stage_weights_rows(uint2* dst, const float* __restrict__ Wt, int Cin, int Cout, int KC, int NT, int tid) {
     const int total = 9 * KC * NT * 32;
     for (int e = tid; e < total; e += MMA_THREADS) {
         const int lane = e & 31, f = e >> 5, nt = f % NT, kc = (f / NT) % KC, k = f / (NT * KC);
@@ -76,12 +180,11 @@ __device__ __forceinline__ void stage_weights(uint2* dst, const float* __restric
     }
 }
 
-// Ordinary 3x3 convolution of this lane's four accumulator rows over all taps and chunks, out of the staged rows.
-// so[j] = shared-memory address of row j's pixel, vm[j] = which of its 9 neighbours lie inside the image.
-// KCT: the number of 16-channel chunks when it is known at compile time (1 or 2: the detector's widths), 0 = use KCr.
+// so[j] = shared-memory address of the pixel of this lane's accumulator row j, vm[j] = which of its 9 neighbours lie inside the image.
+// KCT: the number of 16-channel chunks when it is known at compile time, 0 = use KCr.
 template <typename T, int NTP, int ALIGN, int KCT>
 __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsigned char* smem, const uint32_t (&so)[4], const uint32_t (&vm)[4],
-                                           uint32_t zoff, const uint2* __restrict__ Bs, int KCr, int Cin, int W, int lane) {
+                                           uint32_t zoff, const uint2* __restrict__ Bw, int KCr, int Cin, int W, int lane) {
     const int KC = KCT ? KCT : KCr;
     const int t = lane & 3;
 #pragma unroll 3
@@ -95,7 +198,7 @@ __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsign
             const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
             uint2 bf[NTP];
 #pragma unroll
-            for (int nt = 0; nt < NTP; ++nt) bf[nt] = Bs[((k * KC + kc) * NTP + nt) * 32 + lane];
+            for (int nt = 0; nt < NTP; ++nt) bf[nt] = Bw[((k * KC + kc) * NTP + nt) * 32 + lane];
             uint2 v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = lds8<ALIGN>(smem, q[j] + coff);
@@ -103,44 +206,6 @@ __device__ __forceinline__ void plain_pass(float (&acc)[2][NTP][4], const unsign
             for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                 for (int nt = 0; nt < NTP; ++nt) mma16816<T>(acc[mt][nt], v[2 * mt].x, v[2 * mt + 1].x, v[2 * mt].y, v[2 * mt + 1].y, bf[nt]);
-        }
-    }
-}
-
-// One tap of the deformable pass for one 16-row tile: A = corner weight * gathered channels, four corners, all chunks.
-// SLOW: some address in the warp carries the OUTSIDE flag and is read from global memory instead.
-template <typename T, int NT, int ALIGN, bool SLOW, int KCT>
-__device__ __forceinline__ void deform_tap(float (&acc)[NT][4], const unsigned char* smem, const unsigned char* gimg, const uint4* tw, const uint4* ta,
-                                           int row0, const uint2* __restrict__ Bs, int k, int KCr, int Cin, int lane) {
-    const int KC = KCT ? KCT : KCr;
-    const int t = lane & 3;
-    uint32_t w[2][4], a[2][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint4 wq = tw[row0 + 8 * h], aq = ta[row0 + 8 * h];
-        w[h][0] = wq.x; w[h][1] = wq.y; w[h][2] = wq.z; w[h][3] = wq.w;
-        a[h][0] = aq.x; a[h][1] = aq.y; a[h][2] = aq.z; a[h][3] = aq.w;
-    }
-#pragma unroll (KCT ? KCT : 1)
-    for (int kc = 0; kc < KC; ++kc) {
-        const uint32_t coff = 2 * lane_first_channel(kc, t, Cin);
-        uint2 bf[NT];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) bf[nt] = Bs[((k * KC + kc) * NT + nt) * 32 + lane];
-        uint2 v[2][4];
-#pragma unroll
-        for (int cr = 0; cr < 4; ++cr)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (SLOW && (a[h][cr] & OUTSIDE)) v[h][cr] = ldg8<ALIGN>(gimg + 2 * (size_t)(a[h][cr] & ~OUTSIDE) + coff);
-                else v[h][cr] = lds8<ALIGN>(smem, a[h][cr] + coff);
-            }
-#pragma unroll
-        for (int cr = 0; cr < 4; ++cr) {
-            const uint32_t a0 = mul2<T>(v[0][cr].x, w[0][cr]), a2 = mul2<T>(v[0][cr].y, w[0][cr]);
-            const uint32_t a1 = mul2<T>(v[1][cr].x, w[1][cr]), a3 = mul2<T>(v[1][cr].y, w[1][cr]);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma16816<T>(acc[nt], a0, a1, a2, a3, bf[nt]);
         }
     }
 }
@@ -189,17 +254,18 @@ __device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* A, 
     for (int j = 0; j < 9; ++j) mk[j] = sigmoidf_(logit[j]);
 }
 
-template <typename T, int NT, int MODE, int ALIGN, int KCT>      // MODE 0 plain, 1 deform, 2 fused, 3 fused + inline LCSA mask
+template <typename T, int NT, int MODE, int ALIGN, int GT>       // MODE 0 plain, 1 deform, 2 fused, 3 fused + inline LCSA mask; GT: channel groups per tap when known at compile time
 __global__ void __launch_bounds__(MMA_THREADS, NT <= 4 ? 2 : 1)
 dsc_mma_kernel(const MmaParams p) {
     constexpr int COP = NT * 8;
     extern __shared__ __align__(16) unsigned char smem_mma[];
-    const int KC = KCT ? KCT : p.KC;
-    uint2* Bs = reinterpret_cast<uint2*>(smem_mma);                                   // [9][KC][NT][32]
     constexpr bool FUSED = MODE >= 2, INLINE = MODE == 3;
-    uint2* Bo = Bs + 9 * KC * NT * 32;                                                // [9][KC][3][32]   (fused)
+    constexpr int KCT = GT ? (GT + 3) / 4 : 0;                                        // 16-channel chunks of the plain passes, if known
+    const int nch = 9 / p.TPC, KS = p.KS, KC = KCT ? KCT : (p.Cin + 15) / 16;
+    uint2* Bs = reinterpret_cast<uint2*>(smem_mma);                                   // deform: [nch][KS][NT][32]; plain mode: [9][KC][NT][32]
+    uint2* Bo = Bs + (MODE == 0 ? 9 * KC : nch * KS) * NT * 32;                       // [9][KC][3][32]   (fused: the offset convolution)
     unsigned char* cur = reinterpret_cast<unsigned char*>(Bo + (FUSED ? 9 * KC * NT_OFF * 32 : 0));
-    unsigned char* scratch = cur; cur += MMA_WARPS * SCRATCH_PER_WARP;
+    unsigned char* scratch = cur; cur += MMA_WARPS * p.scratch;
     float* ep = reinterpret_cast<float*>(cur); cur += 3 * COP * 4;                    // scale | shift | post
     float* red = reinterpret_cast<float*>(cur); cur += MMA_WARPS * COP * 4;
     float* offs = reinterpret_cast<float*>(cur); cur += (FUSED ? MMA_WARPS * 32 * OFF_PITCH * 4 : 0);
@@ -216,9 +282,9 @@ dsc_mma_kernel(const MmaParams p) {
     const int H = p.H, W = p.W, HW = H * W, Cin = p.Cin, Cout = p.Cout;
     const int gpi = (HW + MMA_THREADS - 1) / MMA_THREADS, total = gpi * p.B;      // groups per image, groups in all
 
-    uint4* my_w = reinterpret_cast<uint4*>(scratch + warp * SCRATCH_PER_WARP);    // [3][32] corner weights, each a duplicated pair
-    uint4* my_a = my_w + 96;                                                          // [3][32] corner addresses
-    unsigned char* my_tile = scratch + warp * SCRATCH_PER_WARP;                       // output tile (after the taps are done)
+    unsigned char* my_tile = scratch + warp * p.scratch;                              // the warp's A tile; after the taps its output tile
+    unsigned char* my_row = my_tile + lane * p.pitchA;                                // this lane's pixel's row of the A tile
+    const uint32_t my_tile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(my_tile));
     float* my_offs = offs + warp * 32 * OFF_PITCH;
     const float relu_floor = p.act == KAD_ACT_RELU ? 0.f : -INFINITY;
 
@@ -258,9 +324,10 @@ dsc_mma_kernel(const MmaParams p) {
         // shared-memory address of image element e: sel0 + 2*e
         const int sel0 = static_cast<int>(wdata) - static_cast<int>(static_cast<ptrdiff_t>(a16) - static_cast<ptrdiff_t>(reinterpret_cast<uintptr_t>(gimg)));
         if (first) {
-            stage_weights<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
+            if (MODE == 0) stage_weights_rows<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
+            else stage_weights<T>(Bs, p.Wt, Cin, Cout, p.KT, p.TPC, KS, NT, tid);
             if (FUSED) {
-                stage_weights<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
+                stage_weights_rows<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
                 if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
             }
             if (INLINE) {
@@ -327,14 +394,6 @@ dsc_mma_kernel(const MmaParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) psum[nt][0] = psum[nt][1] = 0.f;
         if (wbase < HW) {
-            // the four accumulator rows of this lane: j = mt*2 + half -> pixel wbase + mt*16 + g + 8*half
-            uint32_t so[4], vm[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int r = (j >> 1) * 16 + g + 8 * (j & 1);
-                vm[j] = __shfl_sync(0xffffffffu, myvm, r);
-                so[j] = static_cast<uint32_t>(sel0 + 2 * (wbase + r) * Cin);
-            }
             float acc[2][NT][4];
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
@@ -343,10 +402,18 @@ dsc_mma_kernel(const MmaParams p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
-            if (MODE == 0) {
-                plain_pass<T, NT, ALIGN, KCT>(acc, smem_mma, so, vm, zoff, Bs, KC, Cin, W, lane);
-            } else {
-                if (FUSED) {
+            if (MODE == 0 || FUSED) {
+                // plain passes work on accumulator rows: j = mt*2 + half -> pixel wbase + mt*16 + g + 8*half
+                uint32_t so4[4], vm4[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int rr = (j >> 1) * 16 + g + 8 * (j & 1);
+                    vm4[j] = __shfl_sync(0xffffffffu, myvm, rr);
+                    so4[j] = static_cast<uint32_t>(sel0 + 2 * (wbase + rr) * Cin);
+                }
+                if (MODE == 0) {
+                    plain_pass<T, NT, ALIGN, KCT>(acc, smem_mma, so4, vm4, zoff, Bs, KC, Cin, W, lane);
+                } else {
                     // offset convolution of the warp's 32 pixels -> shared memory [32][18]
                     float oacc[2][NT_OFF][4];
 #pragma unroll
@@ -355,7 +422,7 @@ dsc_mma_kernel(const MmaParams p) {
                         for (int nt = 0; nt < NT_OFF; ++nt)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) oacc[mt][nt][i] = 0.f;
-                    plain_pass<T, NT_OFF, ALIGN, KCT>(oacc, smem_mma, so, vm, zoff, Bo, KC, Cin, W, lane);
+                    plain_pass<T, NT_OFF, ALIGN, KCT>(oacc, smem_mma, so4, vm4, zoff, Bo, KC, Cin, W, lane);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -367,64 +434,72 @@ dsc_mma_kernel(const MmaParams p) {
                             }
                         }
                 }
-#pragma unroll (KCT ? 3 : 1)
-                for (int r = 0; r < 3; ++r) {
-                    __syncwarp();                              // readers of the previous row's table are done; offsets are visible
-                    uint32_t slow = 0;                         // bit kk: some lane's sample of tap kk leaves the staged rows
+            }
+            if (MODE != 0) {
+                // K slots of this lane's A-tile row beyond the chunk's taps are never written by the gather; their weights are zero, but
+                // what the previous group's output tile left there may not be a finite number: clear them
+                for (int o = p.TPC * p.KT * 2; o < KS * 32; o += 8) *reinterpret_cast<uint2*>(my_row + o) = make_uint2(0u, 0u);
+                // Sampling geometry of this lane's pixel, per tap, in registers. A corner outside the image gets weight 0 and its
+                // coordinates are clamped, so every address is valid; rows are clamped to the STAGED rows [ys0, ys1], and a corner
+                // that lies in the image but in a row that is not staged (a large offset) is flagged and read from global memory.
+                const int ys0 = e_lo / (W * Cin), ys1 = e_hi / (W * Cin) - 1;
+                const uint32_t row_bytes = 2u * (uint32_t)(W * Cin), px_bytes = 2u * (uint32_t)Cin;
+                const uint32_t s00 = static_cast<uint32_t>(sel0);
+                const float fy0 = (float)(mpy - 1), fx0 = (float)(mpx - 1);
+                auto tap = [&](int k, int tl) {
+                    const int r = k / 3, kk = k - 3 * r;
+                    float dy, dx;
+                    if (FUSED) { dy = my_offs[lane * OFF_PITCH + 2 * k]; dx = my_offs[lane * OFF_PITCH + 2 * k + 1]; }
+                    else { dy = load_mixed<T>(p.offset, gp * 18 + 2 * k, p.offset_f32); dx = load_mixed<T>(p.offset, gp * 18 + 2 * k + 1, p.offset_f32); }
+                    float m = mk[0];
 #pragma unroll
-                    for (int kk = 0; kk < 3; ++kk) {
-                        const int k = 3 * r + kk;
-                        uint4 wq = make_uint4(0u, 0u, 0u, 0u), aq = make_uint4(zoff, zoff, zoff, zoff);
-                        bool out = false;
-                        if (mylive) {
-                            float dy, dx;
-                            if (FUSED) { dy = my_offs[lane * OFF_PITCH + 2 * k]; dx = my_offs[lane * OFF_PITCH + 2 * k + 1]; }
-                            else { dy = load_mixed<T>(p.offset, gp * 18 + 2 * k, p.offset_f32); dx = load_mixed<T>(p.offset, gp * 18 + 2 * k + 1, p.offset_f32); }
-                            const float m = r == 0 ? mk[kk] : (r == 1 ? mk[3 + kk] : mk[6 + kk]);
-                            const float sy = (float)(mpy + r - 1) + dy, sx = (float)(mpx + kk - 1) + dx;
-                            if (sy > -1.f && sy < (float)H && sx > -1.f && sx < (float)W) {
-                                const float fy = floorf(sy), fx = floorf(sx);
-                                const int y0 = (int)fy, x0 = (int)fx;
-                                const float ly = sy - fy, lx = sx - fx, hy = 1.f - ly, hx = 1.f - lx;
-                                const bool yl = y0 >= 0, yh = y0 + 1 < H, xl = x0 >= 0, xh = x0 + 1 < W;
-                                const int o00 = (y0 * W + x0) * Cin, o10 = o00 + W * Cin;
-                                // rows y0 and y0+1 are staged as a whole or not at all
-                                const bool in0 = o00 - x0 * Cin >= e_lo && o00 - x0 * Cin < e_hi, in1 = o10 - x0 * Cin >= e_lo && o10 - x0 * Cin < e_hi;
-                                if (yl && xl) aq.x = in0 ? static_cast<uint32_t>(sel0 + 2 * o00) : (OUTSIDE | static_cast<uint32_t>(o00));
-                                if (yl && xh) aq.y = in0 ? static_cast<uint32_t>(sel0 + 2 * (o00 + Cin)) : (OUTSIDE | static_cast<uint32_t>(o00 + Cin));
-                                if (yh && xl) aq.z = in1 ? static_cast<uint32_t>(sel0 + 2 * o10) : (OUTSIDE | static_cast<uint32_t>(o10));
-                                if (yh && xh) aq.w = in1 ? static_cast<uint32_t>(sel0 + 2 * (o10 + Cin)) : (OUTSIDE | static_cast<uint32_t>(o10 + Cin));
-                                out = (yl && !in0) || (yh && !in1);
-                                const float w00 = hy * hx * m, w01 = hy * lx * m, w10 = ly * hx * m, w11 = ly * lx * m;
-                                wq = make_uint4(pack2<T>(w00, w00), pack2<T>(w01, w01), pack2<T>(w10, w10), pack2<T>(w11, w11));
-                            }
-                        }
-                        my_w[kk * 32 + lane] = wq;
-                        my_a[kk * 32 + lane] = aq;
-                        if (__any_sync(0xffffffffu, out)) slow |= 1u << kk;
-                    }
-                    __syncwarp();
-                    if (slow == 0) {
-                        // the common case, unrolled over the three taps so that the loads of one tap overlap the MMAs of the previous
-#pragma unroll
-                        for (int kk = 0; kk < 3; ++kk)
-#pragma unroll
-                            for (int mt = 0; mt < 2; ++mt)
-                                deform_tap<T, NT, ALIGN, false, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, 3 * r + kk, KC, Cin, lane);
+                    for (int q = 1; q < 9; ++q) m = (k == q) ? mk[q] : m;         // folds when the tap loops are unrolled
+                    const float sy = (fy0 + (float)r) + dy, sx = (fx0 + (float)kk) + dx;
+                    const float fy = floorf(sy), fx = floorf(sx);
+                    const float ly = sy - fy, lx = sx - fx;
+                    // saturating conversions: a sample far outside the image ends with all four corners invalid
+                    const int y0 = __float2int_rd(fminf(fmaxf(sy, -4.f), (float)H + 2.f)), x0 = __float2int_rd(fminf(fmaxf(sx, -4.f), (float)W + 2.f));
+                    const bool yl = (unsigned)y0 < (unsigned)H, yh = (unsigned)(y0 + 1) < (unsigned)H;
+                    const bool xl = (unsigned)x0 < (unsigned)W, xh = (unsigned)(x0 + 1) < (unsigned)W;
+                    const float wy0 = (yl && mylive) ? (1.f - ly) * m : 0.f, wy1 = (yh && mylive) ? ly * m : 0.f;
+                    const float wx0 = xl ? 1.f - lx : 0.f, wx1 = xh ? lx : 0.f;
+                    CornerWeights<T> cw;
+                    cw.set(wy0 * wx0, wy0 * wx1, wy1 * wx0, wy1 * wx1);
+                    const int r0 = min(max(y0, ys0), ys1), r1 = min(max(y0 + 1, ys0), ys1);
+                    const int c0 = min(max(x0, 0), W - 1), c1 = min(max(x0 + 1, 0), W - 1);
+                    const uint32_t a0 = s00 + (uint32_t)r0 * row_bytes, a1 = s00 + (uint32_t)r1 * row_bytes;
+                    const uint32_t b0 = (uint32_t)c0 * px_bytes, b1 = (uint32_t)c1 * px_bytes;
+                    const uint32_t aq[4] = {a0 + b0, a0 + b1, a1 + b0, a1 + b1};
+                    // corners with weight in an image row outside the staged ones
+                    const bool far0 = mylive && yl && r0 != y0, far1 = mylive && yh && r1 != y0 + 1;
+                    unsigned char* dst = my_row + tl * p.KT * 2;
+                    if (!__any_sync(0xffffffffu, far0 || far1)) {
+                        const int ge[4] = {0, 0, 0, 0};
+                        gather_tap<T, ALIGN, false, GT>(dst, smem_mma, gimg, aq, 0u, ge, cw, p.G, Cin);
                     } else {
+                        const uint32_t far = (far0 ? 3u : 0u) | (far1 ? 12u : 0u);
+                        const int g0 = (min(max(y0, 0), H - 1) * W) * Cin, g1 = (min(max(y0 + 1, 0), H - 1) * W) * Cin;
+                        const int ge[4] = {g0 + c0 * Cin, g0 + c1 * Cin, g1 + c0 * Cin, g1 + c1 * Cin};
+                        gather_tap<T, ALIGN, true, GT>(dst, smem_mma, gimg, aq, far, ge, cw, p.G, Cin);
+                    }
+                };
+                if (GT) {          // three taps per chunk (GT <= 6 groups), everything unrolled
+#pragma unroll
+                    for (int ch = 0; ch < 3; ++ch) {
+                        __syncwarp();                          // the previous chunk's fragments have been read; the offsets are visible
+#pragma unroll
+                        for (int tl = 0; tl < 3; ++tl) tap(3 * ch + tl, tl);
+                        __syncwarp();
+                        mma_chunk<T, NT>(acc, my_tile_addr, p.pitchA, Bs + (size_t)ch * KS * NT * 32, KS, lane);
+                    }
+                } else {
 #pragma unroll 1
-                        for (int kk = 0; kk < 3; ++kk) {
-                            const int k = 3 * r + kk;
-                            if ((slow >> kk) & 1u) {
-#pragma unroll
-                                for (int mt = 0; mt < 2; ++mt)
-                                    deform_tap<T, NT, ALIGN, true, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
-                            } else {
-#pragma unroll
-                                for (int mt = 0; mt < 2; ++mt)
-                                    deform_tap<T, NT, ALIGN, false, KCT>(acc[mt], smem_mma, gimg, my_w + kk * 32, my_a + kk * 32, mt * 16 + g, Bs, k, KC, Cin, lane);
-                            }
-                        }
+                    for (int ch = 0; ch < nch; ++ch) {
+                        __syncwarp();
+#pragma unroll 1
+                        for (int tl = 0; tl < p.TPC; ++tl) tap(ch * p.TPC + tl, tl);
+                        __syncwarp();
+                        mma_chunk<T, NT>(acc, my_tile_addr, p.pitchA, Bs + (size_t)ch * KS * NT * 32, KS, lane);
                     }
                 }
             }
@@ -432,7 +507,7 @@ dsc_mma_kernel(const MmaParams p) {
             // ---- epilogue: affine, activation, post scale; the warp's 32 pixels leave as one contiguous run --------
             const int es = p.y_f32 ? 4 : 2;
             const int npx = min(32, HW - wbase);
-            const bool tiled = 32 * Cout * es + 16 <= SCRATCH_PER_WARP;
+            const bool tiled = 32 * Cout * es + 16 <= p.scratch;
             unsigned char* ydst = reinterpret_cast<unsigned char*>(p.y) + ((size_t)b * HW + wbase) * Cout * es;
             // the tile sits in shared memory at the same offset from a 16-byte boundary as its destination
             const int mis = static_cast<int>(reinterpret_cast<uintptr_t>(ydst) & 15);
@@ -508,10 +583,27 @@ inline int pick_nt(int Cout) {
     return n <= 2 ? 2 : n <= 3 ? 3 : n <= 4 ? 4 : n <= 6 ? 6 : 8;
 }
 
+// K structure of the A tile for Cin channels: groups of four channels per tap, taps per chunk (a kernel row of three taps while
+// its K stays <= 80, i.e. up to 24 channels, else single taps), 16-wide k-steps per chunk, row pitch (an odd number of 16-byte units, so that the eight
+// rows of an ldmatrix phase hit different banks) and the per-warp scratch (A tile or output tile, whichever is larger).
+struct KPlan { int G, KT, TPC, KS, pitchA, scratch; };
+inline KPlan k_plan(int Cin, int Cout) {
+    KPlan k;
+    k.G = (Cin + 3) / 4; k.KT = 4 * k.G;
+    k.TPC = 3 * k.KT <= 80 ? 3 : 1;
+    k.KS = (k.TPC * k.KT + 15) / 16;
+    k.pitchA = k.KS * 32 + 16;
+    const int tile = 32 * k.pitchA, outt = 32 * Cout * 4 + 16;
+    k.scratch = ((tile > outt ? tile : outt) + 15) & ~15;
+    return k;
+}
 // Shared memory of one block without the staged rows.
-inline size_t fixed_smem(int KC, int nt, int mode) {
-    size_t s = (size_t)9 * KC * nt * 32 * 8 + (size_t)MMA_WARPS * SCRATCH_PER_WARP + (size_t)3 * nt * 8 * 4 + (size_t)MMA_WARPS * nt * 8 * 4 + ZERO_BYTES;
-    if (mode >= 2) s += (size_t)9 * KC * NT_OFF * 32 * 8 + (size_t)MMA_WARPS * 32 * OFF_PITCH * 4 + 32 * 4;
+inline size_t fixed_smem(int Cin, int Cout, int nt, int mode) {
+    const KPlan k = k_plan(Cin, Cout);
+    const size_t frag = (size_t)(9 / k.TPC) * k.KS * 32 * 8;          // bytes of weight fragments per n-tile, deformable passes
+    const size_t frag_rows = (size_t)9 * ((Cin + 15) / 16) * 32 * 8;  // the same for the plain passes
+    size_t s = (mode == 0 ? frag_rows : frag) * nt + (size_t)MMA_WARPS * k.scratch + (size_t)3 * nt * 8 * 4 + (size_t)MMA_WARPS * nt * 8 * 4 + ZERO_BYTES;
+    if (mode >= 2) s += frag_rows * NT_OFF + (size_t)MMA_WARPS * 32 * OFF_PITCH * 4 + 32 * 4;
     return s;
 }
 // Image rows a group of 256 consecutive pixels can span, + 10 for the reach of the LCSA's 11x1 window.
@@ -536,11 +628,11 @@ inline size_t window_smem(int H, int W, int Cin, int margin) {
 }
 constexpr size_t SMEM_ONE_BLOCK = 224 * 1024, SMEM_TWO_BLOCKS = 112 * 1024;
 
-template <typename T, int NT, int MODE, int KCT>
+template <typename T, int NT, int MODE, int GT>
 int launch_mma_align(const MmaParams& p, dim3 grid, size_t smem, cudaStream_t st) {
 #define KAD_MMA_LAUNCH(A)                                                                                             \
     {                                                                                                                 \
-        auto kern = dsc_mma_kernel<T, NT, MODE, A, KCT>;                                                              \
+        auto kern = dsc_mma_kernel<T, NT, MODE, A, GT>;                                                              \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_mma smem attribute: %s", cudaGetErrorString(e));         \
         kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
@@ -554,15 +646,17 @@ template <typename T, int NT>
 int launch_mma_mode(const MmaParams& p, int mode, dim3 grid, size_t smem, cudaStream_t st) {
     if (mode == 0) return launch_mma_align<T, NT, 0, 0>(p, grid, smem, st);
     if (mode == 1) return launch_mma_align<T, NT, 1, 0>(p, grid, smem, st);
+    // the fused kernels at the detector's widths (9-12 and 13-16 channels: NT 2, three / four channel groups; 21-24 channels: NT 3,
+    // six groups) are compiled with the group count as a constant: the gather loops unroll and their addresses fold
     if (mode == 3) {
-        if (NT == 2 && p.KC == 1) return launch_mma_align<T, NT, 3, (NT == 2 ? 1 : 0)>(p, grid, smem, st);
-        if (NT == 3 && p.KC == 2) return launch_mma_align<T, NT, 3, (NT == 3 ? 2 : 0)>(p, grid, smem, st);
+        if (NT == 2 && p.G == 3) return launch_mma_align<T, NT, 3, (NT == 2 ? 3 : 0)>(p, grid, smem, st);
+        if (NT == 2 && p.G == 4) return launch_mma_align<T, NT, 3, (NT == 2 ? 4 : 0)>(p, grid, smem, st);
+        if (NT == 3 && p.G == 6) return launch_mma_align<T, NT, 3, (NT == 3 ? 6 : 0)>(p, grid, smem, st);
         return launch_mma_align<T, NT, 3, 0>(p, grid, smem, st);
     }
-    // the fused kernel at the detector's widths (<= 16 channels: NT 2, one chunk; 17-24 channels: NT 3, two chunks) is
-    // compiled with the chunk count as a constant: index arithmetic folds and the chunk loops unroll
-    if (NT == 2 && p.KC == 1) return launch_mma_align<T, NT, 2, (NT == 2 ? 1 : 0)>(p, grid, smem, st);
-    if (NT == 3 && p.KC == 2) return launch_mma_align<T, NT, 2, (NT == 3 ? 2 : 0)>(p, grid, smem, st);
+    if (NT == 2 && p.G == 3) return launch_mma_align<T, NT, 2, (NT == 2 ? 3 : 0)>(p, grid, smem, st);
+    if (NT == 2 && p.G == 4) return launch_mma_align<T, NT, 2, (NT == 2 ? 4 : 0)>(p, grid, smem, st);
+    if (NT == 3 && p.G == 6) return launch_mma_align<T, NT, 2, (NT == 3 ? 6 : 0)>(p, grid, smem, st);
     return launch_mma_align<T, NT, 2, 0>(p, grid, smem, st);
 }
 
@@ -599,13 +693,13 @@ bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) {
     if (!((dtype == KAD_F16 || dtype == KAD_BF16) && Cin >= 4 && Cin <= 64 && Cout >= 1 && Cout <= 64 && H >= 1 && W >= 1)) return false;
     if ((long long)H * W * Cin >= (1ll << 30)) return false;
     const int nt = pick_nt(Cout);
-    return fixed_smem((Cin + 15) / 16, nt, 2) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
+    return fixed_smem(Cin, Cout, nt, 2) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
 }
 
 // Inline-mask mode: the fused mode's footprint plus the LCSA operands must fit with at least the 3x3 halo staged.
 bool dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W) {
     if (!dsc_mma_supported(Cin, Cout, dtype, H, W)) return false;
-    return fixed_smem((Cin + 15) / 16, pick_nt(Cout), 3) + lcsa_smem(Cin, H, W, lcsa_stage_cols(Cin, W)) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
+    return fixed_smem(Cin, Cout, pick_nt(Cout), 3) + lcsa_smem(Cin, H, W, lcsa_stage_cols(Cin, W)) + window_smem(H, W, Cin, 0) <= SMEM_ONE_BLOCK;
 }
 
 int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
@@ -625,13 +719,14 @@ int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
     p.Woff = a.offset_weight; p.boff = a.offset_bias;
     if (inline_mask) p.mask = nullptr;
     p.scale = a.scale; p.shift = a.shift; p.post = a.post; p.y = a.y; p.gap_partial = a.gap_partial;
-    p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KC = (a.Cin + 15) / 16; p.B = a.B;
+    p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.B = a.B;
+    { const KPlan k = k_plan(a.Cin, a.Cout); p.G = k.G; p.KT = k.KT; p.TPC = k.TPC; p.KS = k.KS; p.pitchA = k.pitchA; p.scratch = k.scratch; }
     p.align = a.Cin % 4 == 0 ? 8 : (a.Cin % 2 == 0 ? 4 : 2);
     p.offset_f32 = a.offset_f32; p.mask_f32 = a.mask_f32; p.y_f32 = a.y_f32; p.act = a.act;
     p.l_rowmean = a.lcsa_rowmean; p.l_A = a.lcsa_A; p.l_Sm = a.lcsa_Sm; p.l_w2 = a.lcsa_w2; p.l_b2 = a.lcsa_b2; p.l_w3 = a.lcsa_w3; p.l_b3 = a.lcsa_b3;
     p.Cp = (a.Cin + 3) & ~3; p.rm_rows = lcsa_rm_rows(a.H, a.W); p.stage_cols = (inline_mask && lcsa_stage_cols(a.Cin, a.W)) ? 1 : 0;
     const int nt = pick_nt(a.Cout);
-    size_t smem = fixed_smem(p.KC, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W, p.stage_cols != 0) : 0);
+    size_t smem = fixed_smem(a.Cin, a.Cout, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W, p.stage_cols != 0) : 0);
     // rows of margin for the learned offsets: as many as fit, at most 2 (none for the plain convolution); the narrow
     // variants (128 registers) keep two blocks per SM when the halo alone allows it
     const size_t soft = (nt <= 4 && smem + window_smem(a.H, a.W, a.Cin, 0) <= SMEM_TWO_BLOCKS) ? SMEM_TWO_BLOCKS : SMEM_ONE_BLOCK;
