@@ -39,7 +39,7 @@ template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4
 // it away (the staged window has slack on both sides for exactly this).
 template <int ALIGN>
 __device__ __forceinline__ uint2 lds8(const unsigned char* smem, uint32_t off) {
-    if (ALIGN == 8) return *reinterpret_cast<const uint2*>(smem + off);
+    if (ALIGN >= 8) return *reinterpret_cast<const uint2*>(smem + off);
     if (ALIGN == 4) { const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + off); return make_uint2(q[0], q[1]); }
     const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + (off & ~3u));
     const uint32_t sh = (off & 2u) * 8u;
@@ -48,7 +48,7 @@ __device__ __forceinline__ uint2 lds8(const unsigned char* smem, uint32_t off) {
 // The same through a global pointer; here the word after the span is only read when the span ends inside it.
 template <int ALIGN>
 __device__ __forceinline__ uint2 ldg8(const unsigned char* p) {
-    if (ALIGN == 8) return __ldg(reinterpret_cast<const uint2*>(p));
+    if (ALIGN >= 8) return __ldg(reinterpret_cast<const uint2*>(p));
     if (ALIGN == 4) { const uint32_t* q = reinterpret_cast<const uint32_t*>(p); return make_uint2(__ldg(q), __ldg(q + 1)); }
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
     const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
