@@ -2,7 +2,7 @@
 // squeeze / excite / rescale, and the upsample + concat + residual tail. All NHWC, fp32 arithmetic.
 #include <mutex>
 
-#include "kad_common.cuh"
+#include "kad_mma.cuh"
 
 namespace kad {
 namespace {
@@ -738,6 +738,82 @@ __device__ __forceinline__ void merge_branch(const T* __restrict__ ysrc, T* __re
     }
 }
 
+// The tail for 16-bit tensors without shared memory: a thread OWNS a group of four consecutive channels of ONE branch (so its
+// source tensor, its attention scalars and, for a pooled branch, the horizontal interpolation of its column are fixed) and one
+// column x of a strip of the image, and walks down the rows of the block. Groups never straddle a branch: branch i has
+// ceil(c_i / 4) groups, and when c_i is no multiple of four its last group is the LAST four channels of the branch (it
+// overlaps its neighbour and stores only the channels that neighbour does not cover), so every thread runs the same
+// vector code. Consecutive threads hold consecutive groups of the same pixel and then the next pixel: x and out are read and
+// written as (nearly) contiguous 8-byte pieces; the branch values come through L1 / L2 (a pooled branch is read four or
+// sixteen times, by neighbouring threads and rows). Attention values are read from memory (att[i][b][c]).
+// ALIGN: guaranteed alignment in bytes of every group's address in x, out and the branch tensors (8, 4 or 2).
+template <typename T, int ALIGN>
+__global__ void __launch_bounds__(256)
+merge_col_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int G, int PL, int R, int out_ld) {
+    const int tid = threadIdx.x;
+    if (tid >= G * PL) return;
+    const int g = tid % G, pl = tid / G, b = blockIdx.z;
+    const int xw = blockIdx.x * PL + pl;
+    if (xw >= p.W) return;
+    const int row0 = blockIdx.y * R, row1 = min(p.H, row0 + R);
+    const int HW = p.H * p.W;
+    const int c0 = p.c[0], c1 = p.c[1], g0 = (c0 + 3) >> 2, g1 = (c1 + 3) >> 2;
+    const int i = g < g0 ? 0 : (g < g0 + g1 ? 1 : 2);
+    const int ci = i == 0 ? c0 : (i == 1 ? c1 : p.c[2]), hi = i == 0 ? p.h[0] : (i == 1 ? p.h[1] : p.h[2]);
+    const int wi = i == 0 ? p.w[0] : (i == 1 ? p.w[1] : p.w[2]);
+    const int lg = g - (i == 0 ? 0 : (i == 1 ? g0 : g0 + g1));
+    const int lc = min(4 * lg, ci - 4), skip = 4 * lg - lc;             // first channel of the group inside the branch; channels to leave alone
+    const int ch0 = (i == 0 ? 0 : (i == 1 ? c0 : c0 + c1)) + lc;
+    const float sy = i == 0 ? p.sy[0] : (i == 1 ? p.sy[1] : p.sy[2]), sx = i == 0 ? p.sx[0] : (i == 1 ? p.sx[1] : p.sx[2]);
+    const unsigned char* yb = reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(i == 0 ? p.y[0] : (i == 1 ? p.y[1] : p.y[2])) + (size_t)b * hi * wi * ci + lc);
+    const float* ai = (i == 0 ? p.att[0] : (i == 1 ? p.att[1] : p.att[2])) + (size_t)b * ci + lc;
+    const float a0 = ai[0], a1 = ai[1], a2 = ai[2], a3 = ai[3];
+    const bool same = hi == p.H && wi == p.W;
+    int x0 = xw, x1 = xw; float lx = 0.f;
+    if (!same) src_index(xw, sx, wi, x0, x1, lx);
+    const float hx = 1.f - lx;
+    const unsigned char* xp = reinterpret_cast<const unsigned char*>(x + ((size_t)b * HW + (size_t)row0 * p.W + xw) * p.C + ch0);
+    T* op = out + ((size_t)b * HW + (size_t)row0 * p.W + xw) * out_ld + ch0;
+    const size_t xstep = 2 * (size_t)p.W * p.C, ostep = (size_t)p.W * out_ld;
+    for (int yh = row0; yh < row1; ++yh, xp += xstep, op += ostep) {
+        const uint2 xin = ldg8<ALIGN>(xp);
+        const float2 xa = unpack2<T>(xin.x), xb = unpack2<T>(xin.y);
+        float v0, v1, v2, v3;
+        if (same) {
+            const uint2 v = ldg8<ALIGN>(yb + 2 * ((size_t)yh * wi + xw) * ci);
+            const float2 va = unpack2<T>(v.x), vb = unpack2<T>(v.y);
+            v0 = va.x; v1 = va.y; v2 = vb.x; v3 = vb.y;
+        } else {
+            int y0, y1; float ly;
+            src_index(yh, sy, hi, y0, y1, ly);
+            const float hy = 1.f - ly;
+            const unsigned char* r0 = yb + 2 * (size_t)y0 * wi * ci;
+            const unsigned char* r1 = yb + 2 * (size_t)y1 * wi * ci;
+            const uint2 q00 = ldg8<ALIGN>(r0 + 2 * x0 * ci), q01 = ldg8<ALIGN>(r0 + 2 * x1 * ci);
+            const uint2 q10 = ldg8<ALIGN>(r1 + 2 * x0 * ci), q11 = ldg8<ALIGN>(r1 + 2 * x1 * ci);
+            const float2 a00 = unpack2<T>(q00.x), b00 = unpack2<T>(q00.y), a01 = unpack2<T>(q01.x), b01 = unpack2<T>(q01.y);
+            const float2 a10 = unpack2<T>(q10.x), b10 = unpack2<T>(q10.y), a11 = unpack2<T>(q11.x), b11 = unpack2<T>(q11.y);
+            v0 = hy * (hx * a00.x + lx * a01.x) + ly * (hx * a10.x + lx * a11.x);
+            v1 = hy * (hx * a00.y + lx * a01.y) + ly * (hx * a10.y + lx * a11.y);
+            v2 = hy * (hx * b00.x + lx * b01.x) + ly * (hx * b10.x + lx * b11.x);
+            v3 = hy * (hx * b00.y + lx * b01.y) + ly * (hx * b10.y + lx * b11.y);
+        }
+        const uint32_t lo = pack2f<T>(fmaf(v0, a0, xa.x), fmaf(v1, a1, xa.y)), hi2 = pack2f<T>(fmaf(v2, a2, xb.x), fmaf(v3, a3, xb.y));
+        if (skip == 0) {
+            if (ALIGN == 8) *reinterpret_cast<uint2*>(op) = make_uint2(lo, hi2);
+            else if (ALIGN == 4) { reinterpret_cast<uint32_t*>(op)[0] = lo; reinterpret_cast<uint32_t*>(op)[1] = hi2; }
+            else { uint16_t* o16 = reinterpret_cast<uint16_t*>(op); o16[0] = (uint16_t)lo; o16[1] = (uint16_t)(lo >> 16); o16[2] = (uint16_t)hi2; o16[3] = (uint16_t)(hi2 >> 16); }
+        } else if (skip == 2 && ALIGN >= 4) {
+            reinterpret_cast<uint32_t*>(op)[1] = hi2;
+        } else {
+            uint16_t* o16 = reinterpret_cast<uint16_t*>(op);
+            if (skip <= 1) o16[1] = (uint16_t)(lo >> 16);
+            if (skip <= 2) o16[2] = (uint16_t)hi2;
+            o16[3] = (uint16_t)(hi2 >> 16);
+        }
+    }
+}
+
 template <typename T, bool PAIRS>
 __global__ void __launch_bounds__(256)
 merge_tile_kernel(const T* __restrict__ x, uint4* __restrict__ out, MergeParams p, MergeSe se, MergeStage stg, int use_se, int R, int out_ld8,
@@ -1034,6 +1110,40 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
     const size_t se_smem = sizeof(float) * (size_t)(2 * a->C + 3 * hmax + 768);
     const bool vec8 = a->dtype != KAD_F32 && a->C % 8 == 0 && a->C <= 2048 && out_ld % 8 == 0 && (uintptr_t)a->x % 16 == 0 &&
                       (uintptr_t)a->out % 16 == 0 && se_smem <= 48 * 1024 && a->c[0] <= 256 && a->c[1] <= 256 && a->c[2] <= 256;
+    // 16-bit tensors with C % 4 == 0: the column-walking kernel (no shared memory, attention read from att[])
+    const bool col = a->dtype != KAD_F32 && a->C <= 1024 && a->c[0] >= 4 && a->c[1] >= 4 && a->c[2] >= 4 && (uintptr_t)a->x % 2 == 0 && (uintptr_t)a->out % 2 == 0;
+    if (col) {
+        if (use_se) {      // the attention takes its own small launches into att[] (callers that overlap them with other work pass gap = NULL)
+            for (int i = 0; i < 3; ++i) {
+                const int rc = kad_se_excite(a->gap[i], a->gap_tiles[i], se.inv[i], a->fc_w1[i], a->fc_b1[i], a->fc_w2[i], a->fc_b2[i],
+                                             const_cast<float*>(a->att[i]), a->B, a->c[i], a->hidden[i], stream);
+                if (rc) return rc;
+            }
+        }
+        // alignment every channel group is guaranteed to have in x, out and its branch tensor
+        int align = 8;
+        while (align > 2 && ((uintptr_t)a->x % align || (uintptr_t)a->out % align || (a->C * 2) % align || (out_ld * 2) % align)) align >>= 1;
+        int cbase = 0;
+        for (int i = 0; i < 3; ++i) {
+            while (align > 2 && ((uintptr_t)a->y[i] % align || (a->c[i] * 2) % align || (cbase * 2) % align)) align >>= 1;
+            cbase += a->c[i];
+        }
+        const int C4 = (a->c[0] + 3) / 4 + (a->c[1] + 3) / 4 + (a->c[2] + 3) / 4;          // channel groups per pixel
+        int PL = 256 / C4; if (PL > a->W) PL = a->W; if (PL < 1) PL = 1;
+        const int xstrips = (a->W + PL - 1) / PL;
+        // rows per block: long enough columns to amortise the per-thread set-up, enough blocks for a few waves
+        int R = (int)(((long long)xstrips * a->H * a->B) / (148 * 8));
+        R = R < 4 ? 4 : (R > 32 ? 32 : R);
+        if (R > a->H) R = a->H;
+        dim3 grid(xstrips, (a->H + R - 1) / R, a->B);
+        KAD_CHECK_ARG(grid.y <= 65535, "kad_merge_upsample_residual: image too tall");
+#define KAD_MERGE_COL(TT, AL) merge_col_kernel<TT, AL><<<grid, 256, 0, st>>>((const TT*)a->x, (TT*)a->out, p, C4, PL, R, out_ld)
+        if (a->dtype == KAD_F16) { if (align == 8) KAD_MERGE_COL(__half, 8); else if (align == 4) KAD_MERGE_COL(__half, 4); else KAD_MERGE_COL(__half, 2); }
+        else { if (align == 8) KAD_MERGE_COL(__nv_bfloat16, 8); else if (align == 4) KAD_MERGE_COL(__nv_bfloat16, 4); else KAD_MERGE_COL(__nv_bfloat16, 2); }
+#undef KAD_MERGE_COL
+        KAD_CHECK_LAUNCH("merge_col_kernel");
+        return KAD_OK;
+    }
     if (vec8) {
         const int G = a->C / 8, PL = 256 / G;
         const int se_floats = ((2 * a->C + 3 * hmax + 768 + 3) / 4) * 4;

@@ -133,8 +133,8 @@ extern "C" int kad_kadconv_launch_count(int B, int H, int W, int dim, int dtype,
         n += sc == 3 ? 0 : (sc == 2 ? 1 : (L.partials ? 2 : 4));       // LCSA
         n += L.path[i] == 3 ? 1 : 2;                                    // deformable convolution (+ offset convolution unless fused)
     }
-    const bool merge_has_se = dtype != KAD_F32 && dim % 8 == 0;
-    return n + 1 + (merge_has_se ? 0 : 3);
+    (void)dtype;
+    return n + 1 + 3;      // merge + the three squeeze-excite launches
 }
 
 extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
@@ -253,10 +253,12 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;
         rc = kad_dsc_forward(&q, s);
         if (rc) break;
-        // the channel attention is evaluated by the merge kernel from the sums the DSC kernel wrote
+        // the channel attention of the branch (squeeze-excite MLP on the sums the DSC kernel wrote) on the branch's own stream:
+        // a few microseconds that overlap the other branches; the merge kernel then reads B x c attention values
+        rc = kad_se_excite((const float*)(ws + p.gap), tiles, 1.0f / (float)(h * w), br.fc_w1, br.fc_b1, br.fc_w2, br.fc_b2,
+                           (float*)(ws + p.att), a->B, c, br.hidden, s);
+        if (rc) break;
         m.y[i] = ws + p.y; m.att[i] = (const float*)(ws + p.att); m.c[i] = c; m.h[i] = h; m.w[i] = w;
-        m.gap[i] = (const float*)(ws + p.gap); m.gap_tiles[i] = tiles; m.hidden[i] = br.hidden;
-        m.fc_w1[i] = br.fc_w1; m.fc_b1[i] = br.fc_b1; m.fc_w2[i] = br.fc_w2; m.fc_b2[i] = br.fc_b2;
     }
     // join (always, so that a capture in progress is left well-formed even after an argument error)
     for (int i = 1; i < 3; ++i) {
