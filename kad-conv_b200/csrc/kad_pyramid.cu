@@ -14,6 +14,7 @@ struct PyramidParams {
     const void* x; const float* w[3]; const float* b[3]; void* t[3];
     int B, H, W, dim, c[3];
     int TW, KC, xpitch;           // tile width (a multiple of 4), 16-channel chunks, bytes per staged pixel (dim*2 + 16)
+    unsigned vpp_magic;           // ceil(2^32 / (dim / 8)): n / (dim / 8) == __umulhi(n, vpp_magic) for the index ranges used here
     int off_p1, off_p2, off_B, off_bias, off_out, off_colacc, off_part;   // shared-memory byte offsets
     // optional by-products for the LCSA that follows (kad_conv.py:27-28: means over rows and over columns of every t_i):
     // rowpart[i] [B][h_i][gridDim.x][c_i]: sum over the columns of this block's tile; colpart[i] [B][gridDim.y][w_i][c_i]:
@@ -146,9 +147,13 @@ pyramid_project_kernel(const PyramidParams p) {
     if (r0 >= p.H) break;
     const int rows = min(4, p.H - r0);
     // ---- stage x (asynchronous), weights and bias meanwhile ----------------------------------------------------------
-    for (int v = tid; v < rows * cols * vpp; v += MMA_THREADS) {
-        const int px = v / vpp, k = v - px * vpp, r = px / cols, c = px - r * cols;
-        cp_async16(xt + (size_t)(r * TW + c) * xp + 16 * k, xb + ((size_t)(r0 + r) * p.W + c0 + c) * dim * 2 + 16 * k);
+    for (int r = 0; r < rows; ++r) {          // a tile row is one contiguous run of cols * dim * 2 bytes in x
+        const unsigned char* src = xb + ((size_t)(r0 + r) * p.W + c0) * dim * 2;
+        unsigned char* dst = xt + (size_t)r * TW * xp;
+        for (int v = tid; v < cols * vpp; v += MMA_THREADS) {
+            const int c = (int)__umulhi((unsigned)v, p.vpp_magic), k = v - c * vpp;
+            cp_async16(dst + (size_t)c * xp + 16 * k, src + 16 * (size_t)v);
+        }
     }
     if (rt == 0) {
 #pragma unroll
@@ -164,13 +169,13 @@ pyramid_project_kernel(const PyramidParams p) {
     const int h1 = p.H >> 1, w1 = p.W >> 1, h2 = p.H >> 2, w2 = p.W >> 2;
     const int TW1 = TW >> 1, TW2 = TW >> 2;
     for (int v = tid; v < 2 * TW1 * vpp; v += MMA_THREADS) {
-        const int px = v / vpp, k = v - px * vpp, r = px / TW1, c = px - r * TW1;
+        const int px = (int)__umulhi((unsigned)v, p.vpp_magic), k = v - px * vpp, r = px >= TW1 ? 1 : 0, c = px - r * TW1;
         if ((r0 >> 1) + r < h1 && (c0 >> 1) + c < w1) {
             *reinterpret_cast<uint4*>(p1 + (size_t)px * xp + 16 * k) = mean_block<T, 2>(xt + (size_t)((2 * r) * TW + 2 * c) * xp + 16 * k, xp, (size_t)TW * xp);
         }
     }
     for (int v = tid; v < TW2 * vpp; v += MMA_THREADS) {
-        const int c = v / vpp, k = v - c * vpp;
+        const int c = (int)__umulhi((unsigned)v, p.vpp_magic), k = v - c * vpp;
         if ((r0 >> 2) < h2 && (c0 >> 2) + c < w2)
             *reinterpret_cast<uint4*>(p2 + (size_t)c * xp + 16 * k) = mean_block<T, 4>(xt + (size_t)(4 * c) * xp + 16 * k, xp, (size_t)TW * xp);
     }
@@ -227,17 +232,15 @@ pyramid_project_kernel(const PyramidParams p) {
         const T* ot = reinterpret_cast<const T*>(outs + obase[i]);
         T* dst = reinterpret_cast<T*>(p.t[i]) + (((size_t)b * hi_ + rr0) * wi + cc0) * ci;
         const int seg = ncols * ci;                           // elements per row segment
-        if (!(ci & 1)) {
-            const int segw = seg >> 1;
-            for (int e = tid; e < nrows * segw; e += MMA_THREADS) {
-                const int r = e / segw, k = e - r * segw;
-                reinterpret_cast<uint32_t*>(dst + (size_t)r * wi * ci)[k] = reinterpret_cast<const uint32_t*>(ot + (size_t)r * tw * ci)[k];
-            }
-        } else {
-            for (int e = tid; e < nrows * seg; e += MMA_THREADS) {
-                const int r = e / seg, k = e - r * seg;
-                dst[(size_t)r * wi * ci + k] = ot[(size_t)r * tw * ci + k];
-            }
+        // widest access that every row segment's length, its source in shared memory and its destination allow
+        const uintptr_t al = reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(ot) | (uintptr_t)(2 * seg) | (uintptr_t)(2 * wi * ci) | (uintptr_t)(2 * tw * ci);
+        for (int r = 0; r < nrows; ++r) {
+            const T* srow = ot + (size_t)r * tw * ci;
+            T* drow = dst + (size_t)r * wi * ci;
+            if (!(al & 15)) { for (int k = tid; k < (seg >> 3); k += MMA_THREADS) reinterpret_cast<uint4*>(drow)[k] = reinterpret_cast<const uint4*>(srow)[k]; }
+            else if (!(al & 7)) { for (int k = tid; k < (seg >> 2); k += MMA_THREADS) reinterpret_cast<uint2*>(drow)[k] = reinterpret_cast<const uint2*>(srow)[k]; }
+            else if (!(al & 3)) { for (int k = tid; k < (seg >> 1); k += MMA_THREADS) reinterpret_cast<uint32_t*>(drow)[k] = reinterpret_cast<const uint32_t*>(srow)[k]; }
+            else { for (int k = tid; k < seg; k += MMA_THREADS) drow[k] = srow[k]; }
         }
     }
 
@@ -343,6 +346,7 @@ size_t pyramid_plan(int W, int dim, const int c[3], PyramidParams* p) {
         if (o > 112 * 1024) continue;
         if (p) {
             p->TW = TW; p->KC = KC; p->xpitch = xpitch;
+            p->vpp_magic = (unsigned)((0x100000000ull + (unsigned)(dim / 8) - 1) / (unsigned)(dim / 8));
             p->off_p1 = (int)off_p1; p->off_p2 = (int)off_p2; p->off_B = (int)off_B; p->off_bias = (int)off_bias; p->off_out = (int)off_out;
             p->off_colacc = (int)off_colacc; p->off_part = (int)off_part;
         }

@@ -40,15 +40,32 @@ def _both(B, H, W, C, seed):
     _abi.check(lib.kad_lcsa_mask(*args, _p(scratch), _p(ref), B, H, W, C, 1, _abi.KAD_F32, stream), 'kad_lcsa_mask')
     _abi.check(lib.kad_lcsa_mask_noalloc(*args, _p(out), B, H, W, C, 1, _abi.KAD_F32, stream), 'kad_lcsa_mask_noalloc')
     torch.cuda.synchronize()
-    return ref, out
+    return ref, out, x, prm
+
+
+def _oracle_mask(x_nhwc, prm):
+    """sigmoid(LCSA(x)) by the CPU oracle (oracle/kad_oracle.py:lcsa), from the folded parameters the entry points take: the
+    folded BatchNorm (scale m, shift a) is handed to the oracle as weight = m, bias = a with zero mean and unit variance."""
+    from oracle import kad_oracle as ko
+    C = x_nhwc.shape[3]
+    c = lambda t: t.detach().cpu()
+    e = 'l.excite'
+    sd = {e + '.0.weight': c(prm['w1']).view(C, 1, 1, 11), e + '.0.bias': c(prm['b1']),
+          e + '.1.weight': c(prm['bn_m']) * (1.0 + ko.BN_EPS) ** 0.5, e + '.1.bias': c(prm['bn_a']),
+          e + '.1.running_mean': torch.zeros(C), e + '.1.running_var': torch.ones(C),
+          e + '.3.weight': c(prm['w2']).view(C, 1, 11, 1), e + '.3.bias': c(prm['b2']),
+          e + '.4.weight': c(prm['w3']).view(9, C, 1, 1), e + '.4.bias': c(prm['b3'])}
+    return torch.sigmoid(ko.lcsa(sd, 'l', c(x_nhwc).permute(0, 3, 1, 2))).permute(0, 2, 3, 1)
 
 
 def test_noalloc_matches_regular_entry_point_twice():
     # second call is smaller than the first: whatever the first left in the shared array must not matter
     for (B, H, W, C), seed in (((3, 20, 31, 44), 1), ((2, 9, 14, 21), 2)):
-        ref, out = _both(B, H, W, C, seed)
+        ref, out, x, prm = _both(B, H, W, C, seed)
         assert (out - ref).abs().max().item() <= 1e-5
         assert 0.0 < float(out.min()) and float(out.max()) < 1.0
+        # ... and both agree with the CPU oracle's LCSA on the same input (the entry point itself, not only its sibling)
+        assert (out.cpu() - _oracle_mask(x, prm)).abs().max().item() <= 1e-5
 
 
 def test_noalloc_rejects_oversize():
