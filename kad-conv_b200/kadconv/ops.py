@@ -424,12 +424,19 @@ def conv3x3_bias_act(x, w, bias=None, act=ACT_SILU, stride=1, in_coff=0, cin=Non
     return out
 
 
-def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0):
-    """pred [B,4+nc,A] (DDetect's y) -> (dets [B,max_det,6] float32, counts [B] int32), all on the device, one launch."""
+def nms_batched(pred, conf_thres, iou_thres, max_det=300, max_wh=7680.0, out=None):
+    """pred [B,4+nc,A] (DDetect's y) -> (dets [B,max_det,6] float32, counts [B] int32), all on the device, one launch.
+    `out` = (dets, counts) reuses existing buffers (they are cleared first)."""
     pred = _cuda(pred, 'pred')
     B, no, A = pred.shape
-    dets = torch.zeros((B, max_det, 6), dtype=torch.float32, device=pred.device)
-    counts = torch.zeros(B, dtype=torch.int32, device=pred.device)
+    if out is None:
+        dets = torch.zeros((B, max_det, 6), dtype=torch.float32, device=pred.device)
+        counts = torch.zeros(B, dtype=torch.int32, device=pred.device)
+    else:
+        dets, counts = out
+        if tuple(dets.shape) != (B, max_det, 6) or dets.dtype != torch.float32 or tuple(counts.shape) != (B,) or counts.dtype != torch.int32:
+            raise ValueError('out must be (float32 [B,max_det,6], int32 [B])')
+        _cuda(dets, 'dets').zero_(); _cuda(counts, 'counts').zero_()
     _abi.check(_abi.load().kad_nms_batched(_ptr(pred), B, no - 4, A, ctypes.c_float(conf_thres), ctypes.c_float(iou_thres), max_det,
                                            ctypes.c_float(max_wh), _ptr(dets), _ptr(counts), dtype_code(pred), _stream()), 'kad_nms_batched')
     return dets, counts
