@@ -204,6 +204,17 @@ int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles, const flo
                                 const float* w2, const float* b2, const float* w3, const float* b3,
                                 float* scratch, float* rowsum, void* mask, int B, int H, int W, int C, int mask_f32, int dtype, void* stream);
 
+/* The LCSA masks of the three branches of a KAD-Conv layer in ONE launch, from the partial sums of kad_pyramid_project: what three
+ * calls of kad_lcsa_mask_from_partials compute (bit-identical), with the first stage recomputed per block in shared memory
+ * instead of passing through a preparation kernel and a scratch buffer. Arrays of three (branch i works at (H >> i) x (W >> i)
+ * with c[i] channels); rowpart / colpart and their tile counts as kad_pyramid_project wrote them; mask[i] [B][H>>i][W>>i][9].
+ * kad_lcsa_masks3_supported: W <= 128 (a block spans all columns of its rows) and the per-image operands fit shared memory. */
+int kad_lcsa_masks3_supported(int H, int W, int c0, int c1, int c2);
+int kad_lcsa_masks3_from_partials(const float* const* rowpart, const float* const* colpart, int n_col_tiles, int n_row_groups,
+                                  const float* const* w1, const float* const* b1, const float* const* bn_scale, const float* const* bn_shift,
+                                  const float* const* w2, const float* const* b2, const float* const* w3, const float* const* b3,
+                                  void* const* mask, int B, int H, int W, const int* c, int mask_f32, int dtype, void* stream);
+
 /* LCSA step 2 without a scratch argument and without any allocation. No counterpart in the reference project: it
  * exists for hosts that cannot create device memory where they call this library (a server whose own pool took all
  * of HBM at start-up, or a frame loop that must avoid the device-wide synchronisation of cudaMalloc / cudaFree).
@@ -286,11 +297,12 @@ typedef struct KadLayerArgs {
     int out_cstride;     /* elements per pixel of `out` (0 = dim): the layer can write into a channel slice of a wider tensor */
     int* counters;       /* NULL, or device int[B], zero before the first call and left zero by every call: lets the pyramid kernel
                             finish the LCSA's first stage in its tail (kad_pyramid_project_lcsa) when the shape qualifies */
-    int scheme;          /* how the LCSA masks are produced when `counters` is given and the shape qualifies:
+    int scheme;          /* how the LCSA masks are produced (launches per layer include three squeeze-excite launches and the merge):
                             0 = the library's choice (the fastest measured form: 1);
-                            1 = separate preparation + mask kernels (eleven launches per layer: what runs without `counters`);
-                            2 = first stage in the pyramid kernel's tail, one mask kernel per branch (eight launches);
-                            3 = first stage in the tail, masks evaluated inside the deformable convolutions (five launches).
+                            1 = a preparation and a mask kernel per branch, on the branch streams (14 launches per layer);
+                            2 = first stage in the pyramid kernel's tail, one mask kernel per branch (11; needs `counters`);
+                            3 = first stage in the tail, masks evaluated inside the deformable convolutions (8; needs `counters`);
+                            4 = one launch for the three branches' LCSAs, first stage recomputed per block (9).
                             All forms compute bit-identical results. */
 } KadLayerArgs;
 size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int dtype, int tc_branches);

@@ -338,6 +338,139 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
     }
 }
 
+// ---- the three LCSA masks of a KAD-Conv layer in ONE launch, straight from the pyramid kernel's partial sums -------------------
+// What lcsa_prep_partials_kernel + lcsa_mask_strip_kernel / lcsa_mask_flat_kernel do in two launches per branch (six per layer):
+// a block first finishes, in shared memory, the first stage of ITS branch and image for the columns and rows it needs (column sums
+// over the row groups, the separable 1x11 convolution + BatchNorm -> A and Sm for every column; row means of its rows and the five
+// above and below), then evaluates the masks of its rows as column strips of LS_R rows per thread (lcsa_mask_strip_kernel's
+// arithmetic, in the same order: the results are bit-identical to the two-launch path). The first stage is recomputed by every
+// block of an image (a few thousand L2 loads and FMAs against ~100 k FMAs of mask work per block); in exchange the layer's
+// LCSAs are one graph node in front of the fork instead of six on the branch streams.
+struct LcsaBranch {
+    const float* rowpart; const float* colpart;
+    const float* w1; const float* b1; const float* bn_m; const float* bn_a; const float* w2; const float* b2; const float* w3; const float* b3;
+    void* mask;
+    int H, W, C, Cp, groups, row_blocks, first_block;
+};
+struct LcsaFusedParams { LcsaBranch br[3]; int nct, nrg, mask_f32; };
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+lcsa_fused_kernel(const LcsaFusedParams p) {
+    extern __shared__ __align__(16) float sm[];
+    const int t = threadIdx.x, b = blockIdx.y;
+    const int i = (int)blockIdx.x >= p.br[2].first_block ? 2 : ((int)blockIdx.x >= p.br[1].first_block ? 1 : 0);
+    const LcsaBranch& q = i == 0 ? p.br[0] : (i == 1 ? p.br[1] : p.br[2]);
+    const int H = q.H, W = q.W, C = q.C, Cp = q.Cp, groups = q.groups;
+    const int RB = groups * LS_R, P = RB + 12;           // rows per block; row pitch of the staged means (rows h0-5 .. h0+RB+6)
+    const int h0 = ((int)blockIdx.x - q.first_block) * RB;
+    float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
+    float* sw2 = sw3 + 12 * Cp;          // [Cp][12] 11x1 taps, slot 11 = bias b2
+    float* rm = sw2 + 12 * Cp;           // [Cp][P] row means (0 outside the image; those rows are masked below)
+    float* As = rm + Cp * P;             // [W][Cp]
+    float* Sms = As + W * Cp;            // [W][Cp]
+    float* colsum_s = Sms + W * Cp;      // [W][C]
+    // ---- first stage ------------------------------------------------------------------------------------------------------
+    const float* cp = q.colpart + (size_t)b * p.nrg * W * C;
+    for (int e = t; e < W * C; e += 128) {
+        float s = 0.f;
+#pragma unroll 4
+        for (int g = 0; g < p.nrg; ++g) s += cp[(size_t)g * W * C + e];
+        colsum_s[e] = s;
+    }
+    for (int e = t; e < 12 * Cp; e += 128) {
+        const int c = e / 12, k = e - c * 12;
+        sw3[e] = (k < 9 && c < C) ? q.w3[k * C + c] : 0.f;
+        sw2[e] = c < C ? (k < 11 ? q.w2[c * 11 + k] : q.b2[c]) : 0.f;
+    }
+    const float invW = 1.f / (float)W;
+    for (int e = t; e < Cp * P; e += 128) {
+        const int j = e / Cp, c = e - j * Cp, hh = h0 - 5 + j;       // consecutive threads read consecutive channels
+        float v = 0.f;
+        if (hh >= 0 && hh < H && c < C) {
+            float s = 0.f;
+#pragma unroll 4
+            for (int k = 0; k < p.nct; ++k) s += q.rowpart[(((size_t)b * H + hh) * p.nct + k) * C + c];
+            v = s * invW;
+        }
+        rm[c * P + j] = v;
+    }
+    __syncthreads();
+    const float invH = 1.f / (float)H;
+    for (int e = t; e < W * Cp; e += 128) {
+        const int w = e / Cp, c = e - w * Cp;
+        float av = 0.f, sv = 0.f;
+        if (c < C) {
+            float conv = 0.f, S = 0.f;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const int ww = w + k - 5;
+                if (ww >= 0 && ww < W) {
+                    const float wk = q.w1[c * 11 + k];
+                    conv = fmaf(wk, colsum_s[ww * C + c] * invH, conv);
+                    S += wk;
+                }
+            }
+            const float m = q.bn_m[c];
+            av = (conv + q.b1[c]) * m + q.bn_a[c]; sv = S * m;
+        }
+        As[e] = av; Sms[e] = sv;
+    }
+    __syncthreads();
+    // ---- masks of this block's rows, a thread owns LS_R vertically consecutive pixels of one column ---------------------------
+    const int g = t / W, w = t - g * W;
+    if (g >= groups) return;
+    const int r0 = h0 + g * LS_R;                        // first row of this thread's strip
+    if (r0 >= H) return;
+    uint32_t valid = 0;                                  // bit j: row r0 - 5 + j lies inside the image
+#pragma unroll
+    for (int j = 0; j < LS_R + 10; ++j) valid |= (uint32_t)(r0 - 5 + j >= 0 && r0 - 5 + j < H) << j;
+    float logit[LS_R][9];
+#pragma unroll
+    for (int r = 0; r < LS_R; ++r)
+#pragma unroll
+        for (int j = 0; j < 9; ++j) logit[r][j] = q.b3[j];
+    const float4* A4 = reinterpret_cast<const float4*>(As + w * Cp);
+    const float4* S4 = reinterpret_cast<const float4*>(Sms + w * Cp);
+    const float4* w24 = reinterpret_cast<const float4*>(sw2);
+    const float4* w34 = reinterpret_cast<const float4*>(sw3);
+#pragma unroll 1
+    for (int c4 = 0; c4 < (Cp >> 2); ++c4) {
+        const float4 av = A4[c4], sv = S4[c4];
+        const float aa[4] = {av.x, av.y, av.z, av.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            const int c = 4 * c4 + j4;
+            const float a = aa[j4], s = ss[j4];
+            const float4* rm4 = reinterpret_cast<const float4*>(rm + c * P + g * LS_R);
+            float tv[16];
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) { const float4 v4 = rm4[qq]; tv[4 * qq] = v4.x; tv[4 * qq + 1] = v4.y; tv[4 * qq + 2] = v4.z; tv[4 * qq + 3] = v4.w; }
+#pragma unroll
+            for (int j = 0; j < LS_R + 10; ++j) tv[j] = ((valid >> j) & 1u) ? fmaxf(fmaf(tv[j], s, a), 0.f) : 0.f;
+            const float4 u0 = w24[3 * c], u1 = w24[3 * c + 1], u2 = w24[3 * c + 2];
+            const float uk[11] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w, u2.x, u2.y, u2.z};
+            const float4 q0 = w34[3 * c], q1 = w34[3 * c + 1], q2 = w34[3 * c + 2];
+#pragma unroll
+            for (int r = 0; r < LS_R; ++r) {
+                float v = u2.w;       // bias of the 11x1 convolution (0 for a padding channel, whose weights are 0 as well)
+#pragma unroll
+                for (int k = 0; k < 11; ++k) v = fmaf(uk[k], tv[r + k], v);
+                logit[r][0] = fmaf(q0.x, v, logit[r][0]); logit[r][1] = fmaf(q0.y, v, logit[r][1]); logit[r][2] = fmaf(q0.z, v, logit[r][2]);
+                logit[r][3] = fmaf(q0.w, v, logit[r][3]); logit[r][4] = fmaf(q1.x, v, logit[r][4]); logit[r][5] = fmaf(q1.y, v, logit[r][5]);
+                logit[r][6] = fmaf(q1.z, v, logit[r][6]); logit[r][7] = fmaf(q1.w, v, logit[r][7]); logit[r][8] = fmaf(q2.x, v, logit[r][8]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < LS_R; ++r) {
+        if (r0 + r >= H) break;
+        const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
+#pragma unroll
+        for (int j = 0; j < 9; ++j) store_mixed<T>(q.mask, o + j, p.mask_f32, sigmoidf_(logit[r][j]));
+    }
+}
+
 // ------------------------------------------------------------------------------ SE
 // Channel means from per-tile sums, by all 256 threads of a block and in a fixed order: K tiles are summed side by side
 // (thread = (tile residue, channel), coalesced), then the K partial sums of a channel are added in order.
@@ -1032,6 +1165,60 @@ int kad::lcsa_mask_from_prepared(const float* rowsum, int rows_are_means, const 
         kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means);
     });
     KAD_CHECK_LAUNCH("lcsa_mask_from_partials");
+    return KAD_OK;
+}
+
+// Shared memory of lcsa_fused_kernel for one branch; 0 if the branch does not qualify (W > 128: a block spans all columns).
+static size_t lcsa_fused_smem(int H, int W, int C) {
+    if (W > 128 || W < 1 || H < 1 || C < 1 || C > 256) return 0;
+    const int Cp = (C + 3) & ~3, groups = 128 / W, P = groups * LS_R + 12;
+    (void)H;
+    return sizeof(float) * ((size_t)24 * Cp + (size_t)Cp * P + (size_t)2 * W * Cp + (size_t)W * C);
+}
+
+extern "C" int kad_lcsa_masks3_supported(int H, int W, int c0, int c1, int c2) {
+    const int c[3] = {c0, c1, c2};
+    for (int i = 0; i < 3; ++i) {
+        const size_t s = lcsa_fused_smem(H >> i, W >> i, c[i]);
+        if (s == 0 || s > 160 * 1024) return 0;
+    }
+    return 1;
+}
+
+extern "C" int kad_lcsa_masks3_from_partials(const float* const* rowpart, const float* const* colpart, int n_col_tiles, int n_row_groups,
+                                             const float* const* w1, const float* const* b1, const float* const* bn_scale, const float* const* bn_shift,
+                                             const float* const* w2, const float* const* b2, const float* const* w3, const float* const* b3,
+                                             void* const* mask, int B, int H, int W, const int* c, int mask_f32, int dtype, void* stream) {
+    KAD_CHECK_ARG(rowpart && colpart && w1 && b1 && bn_scale && bn_shift && w2 && b2 && w3 && b3 && mask && c, "kad_lcsa_masks3_from_partials: null pointer");
+    KAD_CHECK_ARG(B > 0 && B <= 65535 && H >= 4 && W >= 4 && n_col_tiles > 0 && n_row_groups > 0, "kad_lcsa_masks3_from_partials: bad shape");
+    if (!kad_lcsa_masks3_supported(H, W, c[0], c[1], c[2]))
+        return fail(KAD_ERR_UNSUPPORTED, "kad_lcsa_masks3_from_partials: needs W <= 128 and the per-image operands in shared memory (W=%d, c=%d,%d,%d)", W, c[0], c[1], c[2]);
+    LcsaFusedParams p{};
+    p.nct = n_col_tiles; p.nrg = n_row_groups; p.mask_f32 = mask_f32;
+    size_t smem = 0;
+    int blocks = 0;
+    for (int i = 0; i < 3; ++i) {
+        KAD_CHECK_ARG(rowpart[i] && colpart[i] && w1[i] && b1[i] && bn_scale[i] && bn_shift[i] && w2[i] && b2[i] && w3[i] && b3[i] && mask[i],
+                      "kad_lcsa_masks3_from_partials: null pointer for branch %d", i);
+        LcsaBranch& q = p.br[i];
+        q.rowpart = rowpart[i]; q.colpart = colpart[i]; q.w1 = w1[i]; q.b1 = b1[i]; q.bn_m = bn_scale[i]; q.bn_a = bn_shift[i];
+        q.w2 = w2[i]; q.b2 = b2[i]; q.w3 = w3[i]; q.b3 = b3[i]; q.mask = mask[i];
+        q.H = H >> i; q.W = W >> i; q.C = c[i]; q.Cp = (c[i] + 3) & ~3; q.groups = 128 / q.W;
+        const int RB = q.groups * LS_R;
+        q.row_blocks = (q.H + RB - 1) / RB; q.first_block = blocks; blocks += q.row_blocks;
+        const size_t s = lcsa_fused_smem(q.H, q.W, q.C);
+        if (s > smem) smem = s;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    KAD_DISPATCH_DTYPE(dtype, {
+        auto kern = lcsa_fused_kernel<T>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "lcsa_fused smem attribute: %s", cudaGetErrorString(e));
+        }
+        kern<<<dim3(blocks, B), 128, smem, st>>>(p);
+    });
+    KAD_CHECK_LAUNCH("lcsa_fused_kernel");
     return KAD_OK;
 }
 

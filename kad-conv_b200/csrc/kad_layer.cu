@@ -72,6 +72,7 @@ struct LayerPlan {
     BranchWs ws[3];
     int path[3], tiles[3];
     bool pyramid, partials;      // one kernel for the three projections; LCSA sums taken from that kernel's partial sums
+    bool fused_lcsa;             // the three LCSAs can run as one launch from the partial sums
     bool tail_prep;              // LCSA first stage can be finished in the pyramid kernel's tail
     bool inline_mask;            // ... and the masks can be evaluated inside the deformable convolutions
     int nct, nrg;
@@ -96,6 +97,7 @@ LayerPlan plan_layer(int B, int H, int W, int dim, int dtype, int tc_mask) {
         o = L.ws[i].end;
     }
     L.bytes = o;
+    L.fused_lcsa = L.partials && kad_lcsa_masks3_supported(H, W, widths[0], widths[1], widths[2]) != 0;
     L.tail_prep = L.partials && kad_pyramid_lcsa_supported(dim, widths[0], widths[1], widths[2], dtype, H, W) != 0;
     L.inline_mask = L.tail_prep;
     for (int i = 0; i < 3; ++i)
@@ -114,12 +116,17 @@ extern "C" size_t kad_kadconv_workspace_bytes(int B, int H, int W, int dim, int 
 }
 
 // 1 = separate kernels, 2 = first stage in the pyramid tail + mask kernels, 3 = tail + masks inside the deformable convolutions
-// Default (scheme 0) = 1: measured on the detector forward (CUDA-graph replay, 64 / 8 / 1 images) the eleven-launch form is the
-// fastest (16.6 / 4.8 / 3.2 ms against 17.4 / 6.2 / 4.3 ms for 2 and 17.3 / 5.9 / 4.2 ms for 3): inside a graph the extra launches
-// cost little and run on three streams, whereas the tail of the pyramid kernel is one block per image on the critical path and the
-// in-kernel mask cannot share work between vertically adjacent pixels the way the column-strip mask kernel does.
-static int resolve_scheme(const LayerPlan& L, bool pyramid_ok, bool counters, int scheme) {
-    if (!counters || !pyramid_ok || !L.tail_prep || scheme <= 1) return 1;
+// 1 = preparation + mask kernel per branch on the branch streams, 2 = first stage in the pyramid tail + mask kernels, 3 = tail +
+// masks inside the deformable convolutions, 4 = one launch for the three LCSAs in front of the fork. Default (scheme 0) = 1: it is
+// the fastest in every regime measured on the detector forward (CUDA-graph replay, 64 / 8 / 1 images): 1: 15.6 / 4.5 / 3.0 ms,
+// 4: 16.0 / 4.9 / 3.4 ms; (earlier build) 1: 16.6 / 4.8 / 3.2, 2: 17.4 / 6.2 / 4.3, 3: 17.3 / 5.9 / 4.2 ms. Fewer launches lose because
+// the three branches of a layer are independent until the merge: with one short chain of kernels per branch on its own stream the
+// small branches hide behind the full-resolution one, whereas a common kernel in front of the fork (4), a one-block-per-image tail
+// (2) or more work inside the largest kernel (3) all lengthen the critical path.
+static int resolve_scheme(const LayerPlan& L, bool partials_ok, bool counters, int scheme) {
+    if (!partials_ok || scheme <= 1) return 1;
+    if (scheme == 4) return L.fused_lcsa ? 4 : 1;
+    if (!counters || !L.tail_prep) return 1;
     if (scheme == 3) return L.inline_mask ? 3 : 2;
     return 2;
 }
@@ -127,10 +134,11 @@ static int resolve_scheme(const LayerPlan& L, bool pyramid_ok, bool counters, in
 extern "C" int kad_kadconv_launch_count(int B, int H, int W, int dim, int dtype, int tc_branches, int with_counters, int scheme) {
     if (B <= 0 || H < 4 || W < 4 || dim < 3) return 0;
     const LayerPlan L = plan_layer(B, H, W, dim, dtype, tc_branches);
-    const int sc = resolve_scheme(L, L.pyramid, with_counters != 0, scheme);
+    const int sc = resolve_scheme(L, L.partials, with_counters != 0, scheme);
     int n = L.pyramid ? 1 : 3;
+    if (sc == 4) n += 1;
     for (int i = 0; i < 3; ++i) {
-        n += sc == 3 ? 0 : (sc == 2 ? 1 : (L.partials ? 2 : 4));       // LCSA
+        n += (sc == 3 || sc == 4) ? 0 : (sc == 2 ? 1 : (L.partials ? 2 : 4));       // LCSA
         n += L.path[i] == 3 ? 1 : 2;                                    // deformable convolution (+ offset convolution unless fused)
     }
     (void)dtype;
@@ -166,7 +174,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
     const bool partials = pyramid && L.partials;
     const int scheme = resolve_scheme(L, partials, a->counters != nullptr, a->scheme);
     const bool inline_mask = scheme == 3;
-    if (scheme >= 2) {
+    if (scheme == 2 || scheme == 3) {
         KadPyramidArgs q{};
         q.x = a->x; q.B = a->B; q.H = a->H; q.W = a->W; q.dim = a->dim; q.dtype = a->dtype; q.counters = a->counters;
         for (int i = 0; i < 3; ++i) {
@@ -190,6 +198,20 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
         if (rc) return rc;
     }
 
+    if (scheme == 4) {
+        // the three LCSAs as one launch in front of the fork
+        const float* rp[3]; const float* cp[3]; const float* w1[3]; const float* b1[3]; const float* bm[3]; const float* ba[3];
+        const float* w2[3]; const float* b2[3]; const float* w3[3]; const float* b3[3]; void* mk[3];
+        for (int i = 0; i < 3; ++i) {
+            const KadBranchParams& br = a->br[i];
+            rp[i] = (const float*)(ws + L.ws[i].rowpart); cp[i] = (const float*)(ws + L.ws[i].colpart);
+            w1[i] = br.lcsa_w1; b1[i] = br.lcsa_b1; bm[i] = br.lcsa_bn_scale; ba[i] = br.lcsa_bn_shift;
+            w2[i] = br.lcsa_w2; b2[i] = br.lcsa_b2; w3[i] = br.lcsa_w3; b3[i] = br.lcsa_b3; mk[i] = ws + L.ws[i].mask;
+        }
+        rc = kad_lcsa_masks3_from_partials(rp, cp, L.nct, L.nrg, w1, b1, bm, ba, w2, b2, w3, b3, mk, a->B, a->H, a->W, widths, 1, a->dtype, stream);
+        if (rc) return rc;
+    }
+
     // fork
     if ((e = cudaEventRecord(ss->fork, main_s)) != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: fork: %s", cudaGetErrorString(e));
     for (int i = 1; i < 3; ++i)
@@ -208,8 +230,8 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
             rc = kad_pool_project(a->x, br.w_proj, br.b_proj, ws + p.t, a->B, a->H, a->W, a->dim, c, 1 << i, KAD_ACT_NONE, a->dim, c, a->dtype, s);
             if (rc) break;
         }
-        if (inline_mask) {
-            // nothing to launch: the pyramid kernel has left the LCSA operands, the deformable convolution evaluates the mask
+        if (inline_mask || scheme == 4) {
+            // nothing to launch here: the mask is evaluated inside the deformable convolution, or was written in front of the fork
         } else if (scheme == 2) {
             const int Cp = (c + 3) & ~3;
             rc = lcsa_mask_from_prepared((const float*)(ws + p.rows), 1, (const float*)(ws + p.scratch), (const float*)(ws + p.scratch) + (size_t)a->B * w * Cp,

@@ -72,6 +72,8 @@ SIGNATURES = {
     'kad_pyramid_partial_dims': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     'kad_lcsa_mask_from_partials_supported': (c_int, [c_int, c_int, c_int]),
     'kad_lcsa_mask_from_partials': (c_int, [c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 8 + [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_lcsa_masks3_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    'kad_lcsa_masks3_from_partials': (c_int, [c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 9 + [c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
     'kad_stem_conv_supported': (c_int, [c_int, c_int, c_int]),
     'kad_stem_conv_u8': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
     'kad_dsc_mma_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),

@@ -21,7 +21,8 @@ from . import ops
 _LAYER_TYPES = {'KADConv', 'KADC4', 'KADC4_m'}
 _FAST_ATTR = '_kad_b200'
 # How kad_kadconv_forward produces the LCSA masks (KadLayerArgs.scheme): 0 = the library's choice, 1 = separate kernels,
-# 2 = first stage in the pyramid kernel's tail + one mask kernel per branch, 3 = masks inside the deformable convolutions.
+# 2 = first stage in the pyramid kernel's tail + one mask kernel per branch, 3 = masks inside the deformable convolutions,
+# 4 = one launch for the three branches.
 # All forms are bit-identical; tests and benchmarks switch this to compare them.
 LAYER_SCHEME = 0
 

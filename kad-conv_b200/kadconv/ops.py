@@ -659,3 +659,25 @@ def spp_pool3_(cat, C):
         raise ValueError('cat must have 4*C channels')
     _abi.check(_abi.load().kad_spp_pool3(_ptr(cat), B, H, W, C, dtype_code(cat), _stream()), 'kad_spp_pool3')
     return cat
+
+
+def lcsa_masks3_supported(H, W, cs):
+    return bool(_abi.load().kad_lcsa_masks3_supported(H, W, cs[0], cs[1], cs[2]))
+
+
+def lcsa_masks3_from_partials(parts, prms, dtype, H, W, mask_f32=True):
+    """The LCSA masks of the three branches in one launch. parts[i] = (rowpart [B,h_i,nct,c_i], colpart [B,nrg,w_i,c_i]) from
+    pyramid_project(..., want_partials=True); prms[i] as for lcsa_mask. Returns three masks [B,h_i,w_i,9]."""
+    B, _, nct, _ = parts[0][0].shape
+    nrg = parts[0][1].shape[1]
+    dev = parts[0][0].device
+    cs = [int(p[0].shape[3]) for p in parts]
+    masks = [torch.empty((B, H >> i, W >> i, 9), dtype=torch.float32 if mask_f32 else dtype, device=dev) for i in range(3)]
+    arr = lambda ts: (ctypes.c_void_p * 3)(*[t.data_ptr() for t in ts])
+    f = lambda key: arr([_f32(p[key], key) for p in prms])
+    c3 = (ctypes.c_int * 3)(*cs)
+    _abi.check(_abi.load().kad_lcsa_masks3_from_partials(
+        arr([_f32(p[0], 'rowpart') for p in parts]), arr([_f32(p[1], 'colpart') for p in parts]), nct, nrg,
+        f('w1'), f('b1'), f('bn_m'), f('bn_a'), f('w2'), f('b2'), f('w3'), f('b3'), arr(masks), B, H, W, c3, int(mask_f32), _DT[dtype], _stream()),
+        'kad_lcsa_masks3_from_partials')
+    return masks

@@ -150,10 +150,10 @@ def test_layer_call_matches_stepwise_kernels(dtype):
     b = fast.kadconv_forward_nhwc(layer, x)
     torch.cuda.synchronize()
     assert torch.equal(a, ref) and torch.equal(b, ref)
-    # the three ways the layer call can produce the LCSA masks (separate kernels; first stage finished in the pyramid kernel's
-    # tail; masks evaluated inside the deformable convolutions) give the same bits
+    # the ways the layer call can produce the LCSA masks (separate kernels; first stage finished in the pyramid kernel's tail; masks
+    # evaluated inside the deformable convolutions; one launch for the three branches) give the same bits
     try:
-        for scheme in (1, 2, 3):
+        for scheme in (1, 2, 3, 4):
             fast.LAYER_SCHEME = scheme
             assert torch.equal(fast.kadconv_forward_nhwc(layer, x), ref), scheme
             assert torch.equal(fast.kadconv_forward_nhwc(layer, x), ref), scheme

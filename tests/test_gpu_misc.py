@@ -435,3 +435,27 @@ def test_spp_pooling_chain_in_place(shape, dtype):
     out = ops.spp_pool3_(cat, C)
     assert torch.equal(out.cpu(), ref)
     assert not ops.spp_pool3_supported(100, 100, 144, dtype) and not ops.spp_pool3_supported(25, 25, 12, dtype)
+
+
+@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((3, 64, 50, 50), torch.float16), ((2, 48, 100, 100), torch.float16),
+                                         ((5, 48, 9, 30), torch.bfloat16), ((2, 64, 25, 25), torch.float16)])
+def test_three_lcsa_masks_in_one_launch(shape, dtype):
+    """kad_lcsa_masks3_from_partials (first stage recomputed per block in shared memory, column strips) gives the bits of the
+    per-branch preparation + mask kernels, on maps where those run as strips and where they run one pixel per thread."""
+    from kadconv import ops
+    B, dim, H, W = shape
+    cs = (dim - 2 * (dim // 3), dim // 3, dim // 3)
+    f = lambda a: a.cuda()
+    x = nhwc(round_to(_rand((B, dim, H, W), 410), dtype)).cuda().to(dtype)
+    ws = [f(_rand((c, dim), 411 + i, 1.0 / np.sqrt(dim))) for i, c in enumerate(cs)]
+    bs = [f(_rand((c,), 415 + i, 0.1)) for i, c in enumerate(cs)]
+    prms = [dict(w1=f(_rand((c, 11), 420 + i, 0.3)), b1=f(_rand((c,), 423 + i, 0.1)), bn_m=f(1.0 + _rand((c,), 426 + i, 0.1)), bn_a=f(_rand((c,), 429 + i, 0.1)),
+                 w2=f(_rand((c, 11), 432 + i, 0.3)), b2=f(_rand((c,), 435 + i, 0.1)), w3=f(_rand((9, c), 438 + i, 0.3)), b3=f(_rand((9,), 441 + i, 0.1)))
+            for i, c in enumerate(cs)]
+    ts, parts = ops.pyramid_project(x, ws, bs, want_partials=True)
+    assert ops.lcsa_masks3_supported(H, W, cs)
+    masks = ops.lcsa_masks3_from_partials(parts, prms, dtype, H, W)
+    for i in range(3):
+        ref = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], prms[i], dtype, mask_f32=True)
+        assert torch.equal(masks[i], ref), i
+    assert not ops.lcsa_masks3_supported(200, 200, (44, 42, 42))
