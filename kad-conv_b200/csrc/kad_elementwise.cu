@@ -194,13 +194,28 @@ lcsa_prep_partials_kernel(const float* __restrict__ rowpart, int nct, const floa
     }
 }
 
+// n floats staged in shared memory in the order they have in global memory (they go to g[o0 .. o0 + n)), written with 16-byte
+// stores. A thread that owns a pixel would store its nine masks 36 bytes apart from its neighbour's: nine store instructions per
+// warp that each touch 36 sectors partially. `stage` holds element i at stage[(o0 & 3) + i], so that the 16-byte groups of shared
+// and global memory coincide whatever the offset of the block's first element (g itself is 16-byte aligned).
+__device__ __forceinline__ void store_staged_f32(float* __restrict__ g, size_t o0, const float* __restrict__ stage, int n, int t, int nthreads) {
+    const int mis = (int)(o0 & 3), head = mis ? min(n, 4 - mis) : 0;
+    if (t < head) g[o0 + t] = stage[mis + t];
+    const int nb = (n - head) >> 2;
+    const float4* s4 = reinterpret_cast<const float4*>(stage + mis + head);
+    float4* g4 = reinterpret_cast<float4*>(g + o0 + head);
+    for (int k = t; k < nb; k += nthreads) g4[k] = s4[k];
+    const int done = head + 4 * nb;
+    if (t < n - done) g[o0 + done + t] = stage[mis + done + t];
+}
+
 // The mask for 128 CONSECUTIVE pixels of an image per block (so narrow feature maps do not leave most lanes idle): the
 // staged operands of lcsa_mask_kernel, once per image row the block touches.
 template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                       const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
-                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int mask_f32, int rows_are_means) {
+                      const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int mask_f32, int rows_are_means, int staged) {
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.y, t = threadIdx.x, HW = H * W;
     const int p0 = blockIdx.x * 128, p1 = min(HW, p0 + 128);
@@ -208,6 +223,7 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
     float* rm = sw3 + 12 * Cp;           // [nrows][Cp][12] row means of rows h-5..h+5 (0 outside the image), pad 0
     float* sw2 = rm + nrows * 12 * Cp;   // [nrows][Cp][12] 11x1 taps (0 for rows outside the image), slot 11 = bias b2
+    float* stage = sw2 + nrows * 12 * Cp;     // [3 + 128 * 9] the block's masks in global order (only with `staged`)
     const float invW = rows_are_means ? 1.f : 1.f / (float)W;      // `rowsum` holds row means already
     for (int e = t; e < 12 * Cp; e += 128) { const int c = e / 12, k = e - c * 12; sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f; }
     for (int e = t; e < nrows * 12 * Cp; e += 128) {
@@ -218,7 +234,8 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     }
     __syncthreads();
     const int p = p0 + t;
-    if (p >= HW) return;
+    const size_t o0 = ((size_t)b * HW + p0) * 9;
+    if (p < HW) {
     const int h = p / W, w = p - h * W, r = h - r_lo;
     float logit[9];
 #pragma unroll
@@ -252,9 +269,20 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
             logit[6] = fmaf(q1.z, v, logit[6]); logit[7] = fmaf(q1.w, v, logit[7]); logit[8] = fmaf(q2.x, v, logit[8]);
         }
     }
-    const size_t o = ((size_t)b * HW + p) * 9;
+    if (staged) {
+        float* so = stage + (int)(o0 & 3) + t * 9;
 #pragma unroll
-    for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[j]));
+        for (int j = 0; j < 9; ++j) so[j] = sigmoidf_(logit[j]);
+    } else {
+        const size_t o = o0 + (size_t)t * 9;
+#pragma unroll
+        for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[j]));
+    }
+    }
+    if (staged) {                        // uniform over the block
+        __syncthreads();
+        store_staged_f32(reinterpret_cast<float*>(mask), o0, stage, (p1 - p0) * 9, t, 128);
+    }
 }
 
 // The same mask for column strips: a thread owns LS_R vertically consecutive pixels of one column, so the ReLU'd
@@ -266,7 +294,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, const float* __restrict__ Sm,
                        const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ w3,
-                       const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int groups, int mask_f32, int rows_are_means) {
+                       const float* __restrict__ b3, void* __restrict__ mask, int H, int W, int C, int Cp, int groups, int mask_f32, int rows_are_means, int staged) {
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.y, t = threadIdx.x;
     const int RB = groups * LS_R, P = RB + 12;           // rows per block; row pitch of the staged means (rows h0-5 .. h0+RB+6)
@@ -274,6 +302,7 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
     float* sw3 = sm;                     // [Cp][12] 1x1 weights of the 9 outputs, pad 0
     float* sw2 = sw3 + 12 * Cp;          // [Cp][12] 11x1 taps, slot 11 = bias b2
     float* rm = sw2 + 12 * Cp;           // [Cp][P] row means (0 outside the image; those rows are masked below)
+    float* stage = rm + Cp * P;          // [3 + RB * W * 9] the block's masks in global order (only with `staged`)
     const float invW = rows_are_means ? 1.f : 1.f / (float)W;
     for (int e = t; e < 12 * Cp; e += 128) {
         const int c = e / 12, k = e - c * 12;
@@ -286,9 +315,9 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
     }
     __syncthreads();
     const int g = t / W, w = t - g * W;
-    if (g >= groups) return;
     const int r0 = h0 + g * LS_R;                        // first row of this thread's strip
-    if (r0 >= H) return;
+    const size_t o0 = ((size_t)b * H + h0) * W * 9;      // the block's first mask element
+    if (g < groups && r0 < H) {
     uint32_t valid = 0;                                  // bit j: row r0 - 5 + j lies inside the image
 #pragma unroll
     for (int j = 0; j < LS_R + 10; ++j) valid |= (uint32_t)(r0 - 5 + j >= 0 && r0 - 5 + j < H) << j;
@@ -332,9 +361,20 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
 #pragma unroll
     for (int r = 0; r < LS_R; ++r) {
         if (r0 + r >= H) break;
-        const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
+        if (staged) {
+            float* so = stage + (int)(o0 & 3) + ((g * LS_R + r) * W + w) * 9;
 #pragma unroll
-        for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[r][j]));
+            for (int j = 0; j < 9; ++j) so[j] = sigmoidf_(logit[r][j]);
+        } else {
+            const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
+#pragma unroll
+            for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[r][j]));
+        }
+    }
+    }
+    if (staged) {                        // uniform over the block
+        __syncthreads();
+        store_staged_f32(reinterpret_cast<float*>(mask), o0, stage, min(RB, H - h0) * W * 9, t, 128);
     }
 }
 
@@ -908,42 +948,76 @@ merge_col_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, in
     const unsigned char* xp = reinterpret_cast<const unsigned char*>(x + ((size_t)b * HW + (size_t)row0 * p.W + xw) * p.C + ch0);
     T* op = out + ((size_t)b * HW + (size_t)row0 * p.W + xw) * out_ld + ch0;
     const size_t xstep = 2 * (size_t)p.W * p.C, ostep = (size_t)p.W * out_ld;
-    for (int yh = row0; yh < row1; ++yh, xp += xstep, op += ostep) {
-        const uint2 xin = ldg8<ALIGN>(xp);
-        const float2 xa = unpack2<T>(xin.x), xb = unpack2<T>(xin.y);
-        float v0, v1, v2, v3;
-        if (same) {
-            const uint2 v = ldg8<ALIGN>(yb + 2 * ((size_t)yh * wi + xw) * ci);
-            const float2 va = unpack2<T>(v.x), vb = unpack2<T>(v.y);
-            v0 = va.x; v1 = va.y; v2 = vb.x; v3 = vb.y;
-        } else {
-            int y0, y1; float ly;
-            src_index(yh, sy, hi, y0, y1, ly);
-            const float hy = 1.f - ly;
-            const unsigned char* r0 = yb + 2 * (size_t)y0 * wi * ci;
-            const unsigned char* r1 = yb + 2 * (size_t)y1 * wi * ci;
-            const uint2 q00 = ldg8<ALIGN>(r0 + 2 * x0 * ci), q01 = ldg8<ALIGN>(r0 + 2 * x1 * ci);
-            const uint2 q10 = ldg8<ALIGN>(r1 + 2 * x0 * ci), q11 = ldg8<ALIGN>(r1 + 2 * x1 * ci);
-            const float2 a00 = unpack2<T>(q00.x), b00 = unpack2<T>(q00.y), a01 = unpack2<T>(q01.x), b01 = unpack2<T>(q01.y);
-            const float2 a10 = unpack2<T>(q10.x), b10 = unpack2<T>(q10.y), a11 = unpack2<T>(q11.x), b11 = unpack2<T>(q11.y);
-            v0 = hy * (hx * a00.x + lx * a01.x) + ly * (hx * a10.x + lx * a11.x);
-            v1 = hy * (hx * a00.y + lx * a01.y) + ly * (hx * a10.y + lx * a11.y);
-            v2 = hy * (hx * b00.x + lx * b01.x) + ly * (hx * b10.x + lx * b11.x);
-            v3 = hy * (hx * b00.y + lx * b01.y) + ly * (hx * b10.y + lx * b11.y);
-        }
-        const uint32_t lo = pack2f<T>(fmaf(v0, a0, xa.x), fmaf(v1, a1, xa.y)), hi2 = pack2f<T>(fmaf(v2, a2, xb.x), fmaf(v3, a3, xb.y));
+    // stores one row's group (the channels of an overlapping last group that the neighbour covers are left alone)
+    auto put = [&](T* o, uint32_t lo, uint32_t hi2) {
         if (skip == 0) {
-            if (ALIGN == 8) *reinterpret_cast<uint2*>(op) = make_uint2(lo, hi2);
-            else if (ALIGN == 4) { reinterpret_cast<uint32_t*>(op)[0] = lo; reinterpret_cast<uint32_t*>(op)[1] = hi2; }
-            else { uint16_t* o16 = reinterpret_cast<uint16_t*>(op); o16[0] = (uint16_t)lo; o16[1] = (uint16_t)(lo >> 16); o16[2] = (uint16_t)hi2; o16[3] = (uint16_t)(hi2 >> 16); }
+            if (ALIGN == 8) *reinterpret_cast<uint2*>(o) = make_uint2(lo, hi2);
+            else if (ALIGN == 4) { reinterpret_cast<uint32_t*>(o)[0] = lo; reinterpret_cast<uint32_t*>(o)[1] = hi2; }
+            else { uint16_t* o16 = reinterpret_cast<uint16_t*>(o); o16[0] = (uint16_t)lo; o16[1] = (uint16_t)(lo >> 16); o16[2] = (uint16_t)hi2; o16[3] = (uint16_t)(hi2 >> 16); }
         } else if (skip == 2 && ALIGN >= 4) {
-            reinterpret_cast<uint32_t*>(op)[1] = hi2;
+            reinterpret_cast<uint32_t*>(o)[1] = hi2;
         } else {
-            uint16_t* o16 = reinterpret_cast<uint16_t*>(op);
+            uint16_t* o16 = reinterpret_cast<uint16_t*>(o);
             if (skip <= 1) o16[1] = (uint16_t)(lo >> 16);
             if (skip <= 2) o16[2] = (uint16_t)hi2;
             o16[3] = (uint16_t)(hi2 >> 16);
         }
+    };
+    // two rows per trip, all loads of both rows issued before the first use (the loop is bound by load latency, not by bandwidth)
+    if (same) {
+        const unsigned char* yp = yb + 2 * ((size_t)row0 * wi + xw) * ci;
+        const size_t ystep = 2 * (size_t)wi * ci;
+        int yh = row0;
+        for (; yh + 1 < row1; yh += 2, xp += 2 * xstep, op += 2 * ostep, yp += 2 * ystep) {
+            const uint2 xi0 = ldg8<ALIGN>(xp), xi1 = ldg8<ALIGN>(xp + xstep), v0 = ldg8<ALIGN>(yp), v1 = ldg8<ALIGN>(yp + ystep);
+            {
+                const float2 xa = unpack2<T>(xi0.x), xb = unpack2<T>(xi0.y), va = unpack2<T>(v0.x), vb = unpack2<T>(v0.y);
+                put(op, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
+            }
+            {
+                const float2 xa = unpack2<T>(xi1.x), xb = unpack2<T>(xi1.y), va = unpack2<T>(v1.x), vb = unpack2<T>(v1.y);
+                put(op + ostep, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
+            }
+        }
+        if (yh < row1) {
+            const uint2 xi0 = ldg8<ALIGN>(xp), v0 = ldg8<ALIGN>(yp);
+            const float2 xa = unpack2<T>(xi0.x), xb = unpack2<T>(xi0.y), va = unpack2<T>(v0.x), vb = unpack2<T>(v0.y);
+            put(op, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
+        }
+        return;
+    }
+    const unsigned char* c0p = yb + 2 * x0 * ci;
+    const unsigned char* c1p = yb + 2 * x1 * ci;
+    const size_t rstep = 2 * (size_t)wi * ci;
+    // one row of a pooled branch: vertical source rows and weight, the four corner groups, the blend
+    auto blend_row = [&](uint2 xin, uint2 q00, uint2 q01, uint2 q10, uint2 q11, float ly, T* o) {
+        const float hy = 1.f - ly;
+        const float2 xa = unpack2<T>(xin.x), xb = unpack2<T>(xin.y);
+        const float2 a00 = unpack2<T>(q00.x), b00 = unpack2<T>(q00.y), a01 = unpack2<T>(q01.x), b01 = unpack2<T>(q01.y);
+        const float2 a10 = unpack2<T>(q10.x), b10 = unpack2<T>(q10.y), a11 = unpack2<T>(q11.x), b11 = unpack2<T>(q11.y);
+        const float v0 = hy * (hx * a00.x + lx * a01.x) + ly * (hx * a10.x + lx * a11.x);
+        const float v1 = hy * (hx * a00.y + lx * a01.y) + ly * (hx * a10.y + lx * a11.y);
+        const float v2 = hy * (hx * b00.x + lx * b01.x) + ly * (hx * b10.x + lx * b11.x);
+        const float v3 = hy * (hx * b00.y + lx * b01.y) + ly * (hx * b10.y + lx * b11.y);
+        put(o, pack2f<T>(fmaf(v0, a0, xa.x), fmaf(v1, a1, xa.y)), pack2f<T>(fmaf(v2, a2, xb.x), fmaf(v3, a3, xb.y)));
+    };
+    int yh = row0;
+    for (; yh + 1 < row1; yh += 2, xp += 2 * xstep, op += 2 * ostep) {
+        int ya0, ya1, yb0, yb1; float lya, lyb;
+        src_index(yh, sy, hi, ya0, ya1, lya);
+        src_index(yh + 1, sy, hi, yb0, yb1, lyb);
+        const uint2 xi0 = ldg8<ALIGN>(xp), xi1 = ldg8<ALIGN>(xp + xstep);
+        const uint2 p00 = ldg8<ALIGN>(c0p + ya0 * rstep), p01 = ldg8<ALIGN>(c1p + ya0 * rstep), p10 = ldg8<ALIGN>(c0p + ya1 * rstep), p11 = ldg8<ALIGN>(c1p + ya1 * rstep);
+        const uint2 r00 = ldg8<ALIGN>(c0p + yb0 * rstep), r01 = ldg8<ALIGN>(c1p + yb0 * rstep), r10 = ldg8<ALIGN>(c0p + yb1 * rstep), r11 = ldg8<ALIGN>(c1p + yb1 * rstep);
+        blend_row(xi0, p00, p01, p10, p11, lya, op);
+        blend_row(xi1, r00, r01, r10, r11, lyb, op + ostep);
+    }
+    if (yh < row1) {
+        int ya0, ya1; float lya;
+        src_index(yh, sy, hi, ya0, ya1, lya);
+        const uint2 xi0 = ldg8<ALIGN>(xp);
+        const uint2 p00 = ldg8<ALIGN>(c0p + ya0 * rstep), p01 = ldg8<ALIGN>(c1p + ya0 * rstep), p10 = ldg8<ALIGN>(c0p + ya1 * rstep), p11 = ldg8<ALIGN>(c1p + ya1 * rstep);
+        blend_row(xi0, p00, p01, p10, p11, lya, op);
     }
 }
 
@@ -1141,28 +1215,32 @@ int kad::lcsa_mask_from_prepared(const float* rowsum, int rows_are_means, const 
                                  const float* w2, const float* b2, const float* w3, const float* b3,
                                  void* mask, int B, int H, int W, int C, int mask_f32, int dtype, cudaStream_t st) {
     const int Cp = (C + 3) & ~3;
+    // float32 masks at a 16-byte aligned address leave through shared memory, as 16-byte stores in global order
+    const int staged = mask_f32 && (uintptr_t)mask % 16 == 0;
     // column strips when the map is wide enough in rows and blocks to fill the GPU twice over; else one pixel per thread
     if (W <= 128) {
         const int groups = 128 / W, RB = groups * LS_R;
         const int row_blocks = (H + RB - 1) / RB;
-        const size_t smem_strip = sizeof(float) * (size_t)Cp * (24 + RB + 12);
+        size_t smem_strip = sizeof(float) * (size_t)Cp * (24 + RB + 12);
+        const int staged_strip = staged && smem_strip + sizeof(float) * (size_t)(RB * W * 9 + 4) <= 48 * 1024;
+        if (staged_strip) smem_strip += sizeof(float) * (size_t)(RB * W * 9 + 4);
         if ((long long)row_blocks * B >= 296 && smem_strip <= 48 * 1024) {
             KAD_DISPATCH_DTYPE(dtype, {
-                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32, rows_are_means);
+                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32, rows_are_means, staged_strip);
             });
             KAD_CHECK_LAUNCH("lcsa_mask_from_partials (strips)");
             return KAD_OK;
         }
     }
     const int nrows = (127 / W + 2) < H ? (127 / W + 2) : H;
-    const size_t smem = sizeof(float) * (size_t)(2 * nrows + 1) * 12 * Cp;
+    const size_t smem = sizeof(float) * ((size_t)(2 * nrows + 1) * 12 * Cp + (staged ? 128 * 9 + 4 : 0));
     KAD_DISPATCH_DTYPE(dtype, {
         auto kern = lcsa_mask_flat_kernel<T>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "lcsa_mask smem attribute: %s", cudaGetErrorString(e));
         }
-        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means);
+        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means, staged);
     });
     KAD_CHECK_LAUNCH("lcsa_mask_from_partials");
     return KAD_OK;

@@ -142,19 +142,24 @@ pyramid_project_kernel(const PyramidParams p) {
 
     const int vpp = dim >> 3;                                 // 16-byte vectors per pixel
     const unsigned char* xb = reinterpret_cast<const unsigned char*>(p.x) + (size_t)b * p.H * p.W * dim * 2;
+    // asynchronous copy of row tile `rt` of this block into xt (nothing if the tile lies below the image)
+    auto stage_x = [&](int rt) {
+        const int r0 = (blockIdx.y * p.RT + rt) * 4;
+        const int rows = min(4, p.H - r0);
+        for (int r = 0; r < rows; ++r) {          // a tile row is one contiguous run of cols * dim * 2 bytes in x
+            const unsigned char* src = xb + ((size_t)(r0 + r) * p.W + c0) * dim * 2;
+            unsigned char* dst = xt + (size_t)r * TW * xp;
+            for (int v = tid; v < cols * vpp; v += MMA_THREADS) {
+                const int c = (int)__umulhi((unsigned)v, p.vpp_magic), k = v - c * vpp;
+                cp_async16(dst + (size_t)c * xp + 16 * k, src + 16 * (size_t)v);
+            }
+        }
+    };
+    stage_x(0);
     for (int rt = 0; rt < p.RT; ++rt) {
     const int r0 = (blockIdx.y * p.RT + rt) * 4;
     if (r0 >= p.H) break;
-    const int rows = min(4, p.H - r0);
-    // ---- stage x (asynchronous), weights and bias meanwhile ----------------------------------------------------------
-    for (int r = 0; r < rows; ++r) {          // a tile row is one contiguous run of cols * dim * 2 bytes in x
-        const unsigned char* src = xb + ((size_t)(r0 + r) * p.W + c0) * dim * 2;
-        unsigned char* dst = xt + (size_t)r * TW * xp;
-        for (int v = tid; v < cols * vpp; v += MMA_THREADS) {
-            const int c = (int)__umulhi((unsigned)v, p.vpp_magic), k = v - c * vpp;
-            cp_async16(dst + (size_t)c * xp + 16 * k, src + 16 * (size_t)v);
-        }
-    }
+    // ---- x is on its way (asynchronous); weights and bias meanwhile --------------------------------------------------
     if (rt == 0) {
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
@@ -222,6 +227,7 @@ pyramid_project_kernel(const PyramidParams p) {
         }
     }
     __syncthreads();
+    if (rt + 1 < p.RT) stage_x(rt + 1);       // xt and the pooled tiles are consumed: the next tile loads during the copy-out and the sums
 
     // ---- result tiles -> global, row segment by row segment (contiguous) ---------------------------------------------
 #pragma unroll
