@@ -174,6 +174,12 @@ int kad_bias_act_inplace(void* y, const float* bias, long long M, int C, int act
  * result of a convolution lands in its channel slice of a concatenation (the torch.cat of ELAN1.forward /
  * RepNCSPELAN4.forward, KAD-CNet/models/common.py) without a copy of its own. */
 int kad_bias_act_to(const void* y, const float* bias, void* out, long long M, int C, int out_cstride, int act, int dtype, void* stream);
+/* Copy of a channel slice between NHWC tensors of different widths: dst[m][dst_coff .. dst_coff + C) = src[m][src_coff .. src_coff + C)
+ * for m < M, rows src_cstride / dst_cstride elements apart. The `chunk(2, 1)` of ELAN1.forward (KAD-CNet/models/common.py) feeds a
+ * library 3x3 convolution, which wants a dense tensor, and the convolution's output goes back into the concatenation: both moves
+ * are this call (the widest vectors that the addresses allow) instead of a strided tensor copy. dtype: any KAD_* (2 or 4 bytes). */
+int kad_copy_channels(const void* src, int src_cstride, int src_coff, void* dst, int dst_cstride, int dst_coff,
+                      long long M, int C, int dtype, void* stream);
 /* nn.Upsample(scale_factor=2, mode='nearest') followed by Concat([upsampled, skip]) (the top-down path of the neck,
  * yaml: [-1, 1, nn.Upsample, [None, 2, 'nearest']], [[-1, k], 1, Concat, [1]]) in one pass:
  *   low [B,h,w,C1], skip [B,2h,2w,C2] -> out [B,2h,2w,C1+C2], all NHWC dtype. */

@@ -1748,6 +1748,51 @@ extern "C" int kad_bias_act_inplace(void* y, const float* bias, long long M, int
     return kad_bias_act_to(y, bias, y, M, C, C, act, dtype, stream);
 }
 
+// ---- channel-slice copy: dst[m][dst_coff .. +C) = src[m][src_coff .. +C) for rows of different lengths --------------------------
+namespace kad {
+namespace {
+template <typename V>
+__global__ void __launch_bounds__(256)
+copy_channels_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, size_t nvec, unsigned vpr, unsigned vpr_magic, int exact,
+                     size_t src_pitch, size_t dst_pitch) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= nvec) return;
+    // row = i / vpr: by multiplication with a rounded-up reciprocal when the index fits 32 bits, else by division
+    const size_t m = exact ? (size_t)__umulhi((unsigned)i, vpr_magic) : i / vpr;
+    const size_t v = i - m * vpr;
+    *reinterpret_cast<V*>(dst + m * dst_pitch + v * sizeof(V)) = *reinterpret_cast<const V*>(src + m * src_pitch + v * sizeof(V));
+}
+}  // namespace
+}  // namespace kad
+
+extern "C" int kad_copy_channels(const void* src, int src_cstride, int src_coff, void* dst, int dst_cstride, int dst_coff,
+                                 long long M, int C, int dtype, void* stream) {
+    KAD_CHECK_ARG(src && dst && M > 0 && C > 0, "kad_copy_channels: bad argument");
+    KAD_CHECK_ARG(src_coff >= 0 && dst_coff >= 0 && src_coff + C <= src_cstride && dst_coff + C <= dst_cstride,
+                  "kad_copy_channels: slice [%d, %d) / [%d, %d) outside rows of %d / %d channels", src_coff, src_coff + C, dst_coff, dst_coff + C, src_cstride, dst_cstride);
+    KAD_CHECK_ARG(dtype == KAD_F32 || dtype == KAD_F16 || dtype == KAD_BF16, "kad_copy_channels: bad dtype");
+    const size_t es = dtype == KAD_F32 ? 4 : 2;
+    const unsigned char* s = (const unsigned char*)src + (size_t)src_coff * es;
+    unsigned char* d = (unsigned char*)dst + (size_t)dst_coff * es;
+    const size_t row = (size_t)C * es, sp = (size_t)src_cstride * es, dp = (size_t)dst_cstride * es;
+    // widest vector that the row length, both row pitches and both first addresses allow
+    const uintptr_t al = (uintptr_t)s | (uintptr_t)d | row | sp | dp;
+    const int vb = !(al & 15) ? 16 : (!(al & 7) ? 8 : (!(al & 3) ? 4 : 2));
+    const size_t vpr = row / vb, nvec = (size_t)M * vpr;
+    KAD_CHECK_ARG((nvec + 255) / 256 <= 0x7fffffffull, "kad_copy_channels: too many elements");
+    // floor(i * ceil(2^32 / vpr) / 2^32) == i / vpr whenever i * vpr < 2^32 (the rounding error of the reciprocal is below vpr / 2^32)
+    const int exact = vpr > 1 && nvec <= 0xffffffffull / vpr;
+    const unsigned magic = vpr > 1 ? (unsigned)((0x100000000ull + vpr - 1) / vpr) : 0u;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((nvec + 255) / 256);
+    if (vb == 16) copy_channels_kernel<uint4><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else if (vb == 8) copy_channels_kernel<uint2><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else if (vb == 4) copy_channels_kernel<uint32_t><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else copy_channels_kernel<uint16_t><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    KAD_CHECK_LAUNCH("copy_channels_kernel");
+    return KAD_OK;
+}
+
 extern "C" int kad_upsample2x_concat(const void* low, const void* skip, void* out, int B, int h, int w, int C1, int C2, int dtype, void* stream) {
     KAD_CHECK_ARG(low && skip && out && B > 0 && h > 0 && w > 0 && C1 > 0 && C2 > 0, "kad_upsample2x_concat: bad argument");
     const size_t n = (size_t)B * 4 * h * w * (C1 + C2);

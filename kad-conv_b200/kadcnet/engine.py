@@ -92,7 +92,7 @@ class _ConvKxK:
             return ops.conv3x3_bias_act(x, self.w, self.b, act=self.act, stride=self.stride[0], in_coff=in_coff, cin=self.cin,
                                         out=out, out_coff=out_coff)
         if in_coff or x.shape[-1] != self.w.shape[1] * self.groups:
-            x = x[..., in_coff:in_coff + self.w.shape[1] * self.groups].contiguous()
+            x = ops.copy_channels(x, in_coff, self.w.shape[1] * self.groups)
         y = _nhwc(F.conv2d(_nchw_view(x), self.w, None, self.stride, self.padding, 1, self.groups))
         if out is None:
             return ops.bias_act_(y, self.b, self.act)
@@ -161,8 +161,9 @@ class FastDetector(torch.nn.Module):
                     cv2(cat, in_coff=half, out=cat, out_coff=widths[0])
                     cv3(cat, in_coff=widths[0], out=cat, out_coff=widths[0] + widths[1])
                 else:
-                    y2 = cv2(cat[..., half:widths[0]].contiguous())
-                    cat[..., widths[0]:widths[0] + widths[1]].copy_(y2)
+                    # the library convolution wants a dense input: one vectorised slice copy each way
+                    y2 = cv2(ops.copy_channels(cat, half, widths[0] - half))
+                    ops.copy_channels(y2, 0, widths[1], cat, widths[0])
                     cv3(y2, out=cat, out_coff=widths[0] + widths[1])
                 return cv4(cat)
             return elan

@@ -86,6 +86,7 @@ SIGNATURES = {
     'kad_avg_pool2x2s1': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_bias_act_inplace': (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]),
     'kad_bias_act_to': (c_int, [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p]),
+    'kad_copy_channels': (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p]),
     'kad_upsample2x_concat': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_image_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     'kad_lcsa_sums': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),

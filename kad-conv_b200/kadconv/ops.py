@@ -498,6 +498,22 @@ def bias_act_to(y, bias, out, out_coff=0, act=ACT_SILU):
     return out
 
 
+def copy_channels(src, src_coff, C, dst=None, dst_coff=0):
+    """dst[..., dst_coff:dst_coff+C] = src[..., src_coff:src_coff+C] for contiguous tensors with the same leading shape; with
+    dst=None a new dense [..., C] tensor is returned (what `src[..., a:b].contiguous()` gives, in one vectorised kernel)."""
+    src = _cuda(src, 'src')
+    if dst is None:
+        dst = torch.empty(src.shape[:-1] + (C,), dtype=src.dtype, device=src.device)
+    dst = _cuda(dst, 'dst')
+    if dst.shape[:-1] != src.shape[:-1] or dst.dtype != src.dtype:
+        raise ValueError('dst must have the leading shape and dtype of src')
+    if src_coff < 0 or dst_coff < 0 or src_coff + C > src.shape[-1] or dst_coff + C > dst.shape[-1]:
+        raise ValueError('channel slice outside the tensor')
+    _abi.check(_abi.load().kad_copy_channels(_ptr(src), src.shape[-1], src_coff, _ptr(dst), dst.shape[-1], dst_coff,
+                                             src.numel() // src.shape[-1], C, dtype_code(src), _stream()), 'kad_copy_channels')
+    return dst
+
+
 def upsample2x_concat(low, skip):
     """cat((nearest-2x-upsample(low), skip), channels): low [B,h,w,C1], skip [B,2h,2w,C2] -> [B,2h,2w,C1+C2], NHWC."""
     low = _cuda(low, 'low'); skip = _cuda(skip, 'skip')

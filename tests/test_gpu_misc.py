@@ -459,3 +459,21 @@ def test_three_lcsa_masks_in_one_launch(shape, dtype):
         ref = ops.lcsa_mask_from_partials(parts[i][0], parts[i][1], prms[i], dtype, mask_f32=True)
         assert torch.equal(masks[i], ref), i
     assert not ops.lcsa_masks3_supported(200, 200, (44, 42, 42))
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.float32])
+@pytest.mark.parametrize('case', [(32, 16, 16, 16, 48, 32), (30, 7, 5, 22, 40, 11), (24, 8, 12, 12, 12, 0), (9, 3, 3, 9, 10, 1)])
+def test_copy_channels_moves_exactly_the_slice(dtype, case):
+    """kad_copy_channels against tensor slicing, with every vector width (16, 8, 4, 2 bytes) and an untouched remainder."""
+    from kadconv import ops
+    cs, soff, C, _, cd, doff = case
+    g = torch.Generator().manual_seed(5)
+    src = torch.randn((3, 17, 13, cs), generator=g).to(dtype).cuda()
+    dst = torch.randn((3, 17, 13, cd), generator=g).to(dtype).cuda()
+    want = dst.clone(); want[..., doff:doff + C] = src[..., soff:soff + C]
+    got = ops.copy_channels(src, soff, C, dst, doff)
+    assert got is dst and torch.equal(dst, want)
+    dense = ops.copy_channels(src, soff, C)
+    assert dense.is_contiguous() and torch.equal(dense, src[..., soff:soff + C])
+    with pytest.raises(ValueError):
+        ops.copy_channels(src, cs - C + 1, C)
