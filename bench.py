@@ -40,7 +40,8 @@ C1 = dict(B=16, C=256, H=100, W=100)
 C1_FLOPS = 2.0 * C1['B'] * C1['H'] * C1['W'] * C1['C'] * 9 * C1['C']                    # 188.74 GFLOP
 C1_BYTES = 2.0 * (C1['B'] * C1['H'] * C1['W'] * (2 * C1['C'] + 27) + 9 * C1['C'] * C1['C'])  # 173.66 MB
 NCU_TRAFFIC = {'c1': 129.8e6, 'c4_dsc_mma': 38.5e6}   # c4_dsc_mma: reads only; the 15.4 MB written were still in L2 when the counters stopped   # DRAM bytes per launch from the committed ncu summary (profiles/), filled below
-NCU_ISSUE = {'c4_dsc_mma': 0.58}        # issue slots busy, from the committed ncu summary of that kernel
+NCU_ISSUE = {'c4_dsc_mma': 0.48}        # issue slots busy, from the committed ncu summary of that kernel
+NCU_LSU_PIPE = {'c4_dsc_mma': 0.71}     # L1 / shared-memory data pipe (LSU wavefronts) busy, same summary
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
 
 
@@ -540,10 +541,11 @@ def run_c4(args, rank, world, local):
                      'kernel': 'dsc_mma_kernel (offset convolution + deformable convolution of a KAD-Conv branch), the largest '
                                'share of the forward; timed alone on its largest detector shape', 'shape': dom['shape'],
                      'us_per_launch': dom['us'], 'algorithmic_bytes': dom['bytes'],
-                     'limiter': 'instruction issue', 'issue_slot_frac': NCU_ISSUE['c4_dsc_mma'],
-                     'note': 'HBM is not what limits this kernel (12-channel maps: 84 bytes per pixel against about 4000 warp instructions per 32 pixels '
-                             'of gather geometry): `frac` relates it to the HBM roofline as the contract asks, `issue_slot_frac` is the fraction '
-                             'of issue slots it keeps busy in the committed ncu summary (profiles/dsc_mma_kernel_c4.md)'},
+                     'limiter': 'shared-memory data pipe', 'lsu_pipe_frac': NCU_LSU_PIPE['c4_dsc_mma'], 'issue_slot_frac': NCU_ISSUE['c4_dsc_mma'],
+                     'note': 'HBM is not what limits this kernel (12-channel maps: 84 bytes per pixel against about 2570 warp instructions and about '
+                             '1100 shared-memory wavefronts per 32 pixels of bilinear gather): `frac` relates it to the HBM roofline as the contract '
+                             'asks; `lsu_pipe_frac` and `issue_slot_frac` are how busy the L1 / shared-memory data pipe and the issue slots are in '
+                             'the committed ncu summary (profiles/dsc_mma_kernel_c4.md)'},
         'roofline_forward_graph': {'bound': 'hbm', 'achieved': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                                    'frac': ips_fwd * C4_MIN_BYTES_PER_IMAGE / 1e9 / pk['hbm_gbs'],
                                    'kernel': 'whole forward graph (minimum activation traffic 0.35 GB/image, fp16)',
