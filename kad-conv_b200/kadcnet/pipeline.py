@@ -21,25 +21,34 @@ class DetectionPipeline:
     with to_host=False the padded device tensors (dets [mb,max_det,6], counts [mb]) of a double buffer instead: consume them
     before the batch after the next one is submitted.
 
-    Three streams: the copy stream uploads batch i+1 while batch i is in the forward graph on the main stream, and the
+    Streams: the copy stream uploads batch i+1 while batch i is in the forward graph on the main stream, and the
     post-processing stream runs the batched NMS (one CTA per image: it leaves most of the GPU idle) and the device-to-host copy
     of batch i while batch i+1 is already in the forward graph. The prediction tensor is copied out of the graph's output buffer
     (40 MB per 64 images, a few microseconds) so that the next replay cannot overwrite what NMS still reads.
     """
 
-    def __init__(self, fast_model, batch_shape, conf_thres=0.25, iou_thres=0.45, max_det=300, device=None):
+    def __init__(self, fast_model, batch_shape, conf_thres=0.25, iou_thres=0.45, max_det=300, device=None, splits=1):
+        """splits > 1: the forward of a batch runs as `splits` CUDA graphs over equal parts of it, replayed side by side on
+        their own streams (the layers on the small feature maps of the detector do not fill the GPU; two half-batches
+        interleave better than one batch). The results are the same bit for bit."""
         self.device = torch.device(device) if device is not None else fast_model.device
         if self.device.type != 'cuda':
             raise RuntimeError('DetectionPipeline needs a CUDA device (there is no CPU path)')
         self.conf, self.iou, self.max_det = conf_thres, iou_thres, max_det
         self.shape = tuple(batch_shape)
         mb = self.shape[0]
+        if splits < 1 or mb % splits:
+            raise ValueError(f'splits = {splits} does not divide the batch of {mb}')
+        self.splits, self.part = splits, mb // splits
         with torch.cuda.device(self.device):
             self.stage = [torch.empty(self.shape, dtype=torch.uint8, device=self.device) for _ in range(2)]
-            self.graph = StaticGraph(lambda u8: fast_model(u8)[0], self.stage[0])
+            self.graphs = [StaticGraph(lambda u8: fast_model(u8)[0], self.stage[0][k * self.part:(k + 1) * self.part]) for k in range(splits)]
+            self.graph = self.graphs[0]
+            self.fwd_streams = [torch.cuda.Stream(self.device) for _ in range(splits)] if splits > 1 else []
             self.copy_stream = torch.cuda.Stream(self.device)
             self.post_stream = torch.cuda.Stream(self.device)
-            self.pred = [torch.empty_like(self.graph.output) for _ in range(2)]
+            out = self.graph.output
+            self.pred = [torch.empty((mb,) + tuple(out.shape[1:]), dtype=out.dtype, device=self.device) for _ in range(2)]
             self.dets = [torch.zeros((mb, max_det, 6), dtype=torch.float32, device=self.device) for _ in range(2)]
             self.counts = [torch.zeros((mb,), dtype=torch.int32, device=self.device) for _ in range(2)]
             self.status_host = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -86,11 +95,24 @@ class DetectionPipeline:
             if following is not None:
                 self._upload(following, slot ^ 1)                      # overlaps the forward below
             main.wait_event(self.h2d_done[slot])
-            self.graph.input.copy_(self.stage[slot], non_blocking=True)
-            self.stage_free[slot].record(main)
-            self.graph.graph.replay()
-            main.wait_event(self.result_ready[slot])                   # post-processing of batch i-2 no longer reads this slot
-            self.pred[slot].copy_(self.graph.output, non_blocking=True)
+            if self.splits == 1:
+                self.graph.input.copy_(self.stage[slot], non_blocking=True)
+                self.stage_free[slot].record(main)
+                self.graph.graph.replay()
+                main.wait_event(self.result_ready[slot])               # post-processing of batch i-2 no longer reads this slot
+                self.pred[slot].copy_(self.graph.output, non_blocking=True)
+            else:
+                main.wait_event(self.result_ready[slot])
+                for k, (g, st) in enumerate(zip(self.graphs, self.fwd_streams)):
+                    part = slice(k * self.part, (k + 1) * self.part)
+                    st.wait_stream(main)
+                    with torch.cuda.stream(st):
+                        g.input.copy_(self.stage[slot][part], non_blocking=True)
+                        g.graph.replay()
+                        self.pred[slot][part].copy_(g.output, non_blocking=True)
+                for st in self.fwd_streams:
+                    main.wait_stream(st)
+                self.stage_free[slot].record(main)
             self.fwd_done[slot].record(main)
             with torch.cuda.stream(post):                              # overlaps the forward of the next batch
                 post.wait_event(self.fwd_done[slot])

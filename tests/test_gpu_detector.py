@@ -308,3 +308,24 @@ def test_streaming_pipeline_matches_direct_calls(golden_dir):
     assert list(pipe.run([])) == []
     again = list(pipe.run(batches[:1]))
     assert all(torch.equal(a, b) for a, b in zip(again[0], got[0]))
+
+
+def test_streaming_pipeline_with_two_graphs_side_by_side(golden_dir):
+    """splits=2: the halves of every batch go through two CUDA graphs replayed on two streams at once; the detections equal
+    those of the direct call on each half (same kernels on the same half-batch shape), batch by batch."""
+    import kadcnet
+    from kadcnet.postprocess import non_max_suppression_device
+    g, sd = _sd(golden_dir)
+    fast = kadcnet.load_model(None, 'optimized', 'cuda:0', state_dict=sd, dtype=torch.float16)
+    batches = [seeding.seeded_input((4, 3, 160, 192), seed=40 + i, kind='image').pin_memory() for i in range(4)]
+    pipe = kadcnet.DetectionPipeline(fast, (4, 3, 160, 192), 0.25, 0.65, 300, splits=2)
+    got = list(pipe.run(batches))
+    assert len(got) == 4
+    for b, dets in zip(batches, got):
+        y = torch.cat([fast(b[:2].cuda())[0], fast(b[2:].cuda())[0]], 0)
+        ref = non_max_suppression_device(y, 0.25, 0.65, max_det=300)
+        assert len(dets) == 4
+        for d, r in zip(dets, ref):
+            assert torch.equal(d, r.cpu())
+    with pytest.raises(ValueError):
+        kadcnet.DetectionPipeline(fast, (3, 3, 160, 192), splits=2)
