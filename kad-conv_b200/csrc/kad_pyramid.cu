@@ -78,8 +78,8 @@ __device__ void lcsa_prepare_image(const float* rowpart, int nct, const float* c
 
 // Weight fragments of a 1x1 convolution w[Cout][Cin] (see stage_weights of the deformable kernel for the slot layout).
 template <typename T>
-__device__ __forceinline__ void stage_weights_1x1(uint2* dst, const float* __restrict__ w, int Cin, int Cout, int KC, int NT, int tid) {
-    for (int e = tid; e < KC * NT * 32; e += MMA_THREADS) {
+__device__ __forceinline__ void stage_weights_1x1(uint2* dst, const float* __restrict__ w, int Cin, int Cout, int KC, int NT, int tid, int nthreads = MMA_THREADS) {
+    for (int e = tid; e < KC * NT * 32; e += nthreads) {
         const int lane = e & 31, f = e >> 5, nt = f % NT, kc = f / NT;
         const int n = nt * 8 + (lane >> 2), t = lane & 3, ch = kc * 16 + 4 * t;
         const int first = lane_first_channel(kc, t, Cin);
@@ -321,6 +321,164 @@ pyramid_project_kernel(const PyramidParams p) {
     }
 }
 
+// ---- the same three projections by warps that own column segments ------------------------------------------------------------------
+// A block covers PC_COLS columns of x and RG rows of one image; a warp owns one 16-pixel segment of ONE branch (8 + 4 + 2 segments
+// for 128 columns) and walks down the rows of the group. Its A fragments come straight from global memory (a quarter-warp reads the
+// 32 contiguous bytes of a pixel's 16-channel chunk: every sector is used in full; for a pooled branch the lane averages the 2x2 or
+// 4x4 pixels in the order and with the rounding of the staged kernel above), the results leave from the accumulators, and the
+// by-products need no second pass: column sums accumulate in the registers that hold the accumulator layout (same lane = same
+// column in every row), row sums are a butterfly over the eight pixel lanes plus one small reduction over the segments at the end
+// of the block. No shared-memory tile of x, no barrier between rows; x is read once from HBM and, for the pooled branches, again
+// from L2 / L1. Outputs are bit-identical to the staged kernel's (same contraction order); the partial sums differ in summation order.
+constexpr int PC_COLS = 128;
+
+struct ColsPlan { int nct, RT, nrg, S[3], warps; size_t smem; };
+
+template <typename T, int P>
+__device__ __forceinline__ uint2 pooled8(const unsigned char* p, size_t rowbytes, int pixbytes) {
+    if (P == 1) return ldg8<8>(p);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < P; ++r) {
+        uint2 v[P];
+#pragma unroll
+        for (int c = 0; c < P; ++c) v[c] = ldg8<8>(p + r * rowbytes + c * pixbytes);
+#pragma unroll
+        for (int c = 0; c < P; ++c) {
+            const float2 a = up2<T>(v[c].x), b = up2<T>(v[c].y);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        }
+    }
+    const float inv = 1.f / (float)(P * P);
+    return make_uint2(pack2<T>(acc[0] * inv, acc[1] * inv), pack2<T>(acc[2] * inv, acc[3] * inv));
+}
+
+// one warp's rows of branch I (pooling factor P = 2^I)
+template <typename T, int NT, int P>
+__device__ __forceinline__ void cols_branch(const PyramidParams& p, const uint2* __restrict__ Bi, const float* __restrict__ bias_i, float* __restrict__ rowseg_i,
+                                            int i, int s, int nseg, int RG, int nct, int nrg, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.z, rg = blockIdx.y, ct = blockIdx.x;
+    const int hi = p.H >> i, wi = p.W >> i, ci = p.c[i], KC = p.KC, dim = p.dim;
+    const int tile_lo = (ct * PC_COLS) >> i, tile_hi = min(wi, ((ct + 1) * PC_COLS) >> i);
+    const int col0 = tile_lo + 16 * s;
+    if (col0 >= tile_hi) return;                                     // this tile has fewer segments than the widest one
+    const bool ok_lo = col0 + g < tile_hi, ok_hi = col0 + g + 8 < tile_hi;
+    const int cl = min(col0 + g, tile_hi - 1), ch = min(col0 + g + 8, tile_hi - 1);      // lanes past the end re-read the last pixel, never stored
+    const int rgi = RG >> i, r_begin = rg * rgi, r_end = min(hi, r_begin + rgi);
+    const int pix = dim * 2;
+    const size_t rowbytes = (size_t)p.W * pix;
+    const bool sums = p.rowpart[0] != nullptr, pairs = !(ci & 1);
+    T* tb = reinterpret_cast<T*>(p.t[i]);
+    float colsum[NT][4], bz[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) colsum[nt][j] = 0.f;
+        const int co = nt * 8 + 2 * t;
+        bz[nt][0] = co < ci ? bias_i[co] : 0.f; bz[nt][1] = co + 1 < ci ? bias_i[co + 1] : 0.f;
+    }
+    constexpr int KC_UNROLL = P == 1 ? 2 : 1;
+    for (int r = r_begin; r < r_end; ++r) {
+        const unsigned char* base = reinterpret_cast<const unsigned char*>(p.x) + ((size_t)b * p.H + (size_t)P * r) * rowbytes;
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+#pragma unroll KC_UNROLL
+        for (int kc = 0; kc < KC; ++kc) {
+            const int coff = 2 * lane_first_channel(kc, t, dim);
+            const uint2 lo = pooled8<T, P>(base + (size_t)(P * cl) * pix + coff, rowbytes, pix);
+            const uint2 hv = pooled8<T, P>(base + (size_t)(P * ch) * pix + coff, rowbytes, pix);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816<T>(acc[nt], lo.x, hv.x, lo.y, hv.y, Bi[(kc * NT + nt) * 32 + lane]);
+        }
+        T* trow = tb + ((size_t)b * hi + r) * wi * ci;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int co = nt * 8 + 2 * t;
+            const bool c0ok = co < ci, c1ok = co + 1 < ci;
+            const float b0 = bz[nt][0], b1 = bz[nt][1];
+            const uint32_t ulo = pack2<T>(acc[nt][0] + b0, acc[nt][1] + b1), uhi = pack2<T>(acc[nt][2] + b0, acc[nt][3] + b1);
+            if (c0ok) {
+                if (pairs) {
+                    if (ok_lo) *reinterpret_cast<uint32_t*>(trow + (size_t)cl * ci + co) = ulo;
+                    if (ok_hi) *reinterpret_cast<uint32_t*>(trow + (size_t)ch * ci + co) = uhi;
+                } else {
+                    uint16_t* o = reinterpret_cast<uint16_t*>(trow);
+                    if (ok_lo) { o[(size_t)cl * ci + co] = (uint16_t)ulo; if (c1ok) o[(size_t)cl * ci + co + 1] = (uint16_t)(ulo >> 16); }
+                    if (ok_hi) { o[(size_t)ch * ci + co] = (uint16_t)uhi; if (c1ok) o[(size_t)ch * ci + co + 1] = (uint16_t)(uhi >> 16); }
+                }
+            }
+            if (sums) {                                              // of the values as stored (rounded to T)
+                const float2 flo = up2<T>(ulo), fhi = up2<T>(uhi);
+                const float l0 = (ok_lo && c0ok) ? flo.x : 0.f, l1 = (ok_lo && c1ok) ? flo.y : 0.f;
+                const float h0 = (ok_hi && c0ok) ? fhi.x : 0.f, h1 = (ok_hi && c1ok) ? fhi.y : 0.f;
+                colsum[nt][0] += l0; colsum[nt][1] += l1; colsum[nt][2] += h0; colsum[nt][3] += h1;
+                float rs0 = l0 + h0, rs1 = l1 + h1;
+#pragma unroll
+                for (int m = 4; m < 32; m <<= 1) { rs0 += __shfl_xor_sync(0xffffffffu, rs0, m); rs1 += __shfl_xor_sync(0xffffffffu, rs1, m); }
+                if (g == 0) {
+                    float* rsq = rowseg_i + ((size_t)(r - r_begin) * nseg + s) * (NT * 8) + co;
+                    rsq[0] = rs0; rsq[1] = rs1;
+                }
+            }
+        }
+    }
+    if (sums) {
+        float* cp = p.colpart[i] + ((size_t)b * nrg + rg) * wi * ci;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int co = nt * 8 + 2 * t;
+            if (co < ci) {
+                if (ok_lo) { cp[(size_t)cl * ci + co] = colsum[nt][0]; if (co + 1 < ci) cp[(size_t)cl * ci + co + 1] = colsum[nt][1]; }
+                if (ok_hi) { cp[(size_t)ch * ci + co] = colsum[nt][2]; if (co + 1 < ci) cp[(size_t)ch * ci + co + 1] = colsum[nt][3]; }
+            }
+        }
+    }
+}
+
+template <typename T, int NT>
+__global__ void __launch_bounds__(448)
+pyramid_cols_kernel(const PyramidParams p, int S0, int S1, int S2, int RG, int nct, int nrg) {
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+    const int KC = p.KC;
+    uint2* Bs = reinterpret_cast<uint2*>(sm);                                  // [3][KC][NT][32]
+    float* bias = reinterpret_cast<float*>(sm + (size_t)3 * KC * NT * 32 * 8);  // [3][NT*8]
+    float* rowseg0 = bias + 3 * NT * 8;                                        // branch i: [RG >> i][S_i][NT*8]
+    float* rowseg1 = rowseg0 + (size_t)RG * S0 * NT * 8;
+    float* rowseg2 = rowseg1 + (size_t)(RG >> 1) * S1 * NT * 8;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        stage_weights_1x1<T>(Bs + i * KC * NT * 32, p.w[i], p.dim, p.c[i], KC, NT, tid, nthreads);
+        for (int e = tid; e < NT * 8; e += nthreads) bias[i * NT * 8 + e] = (e < p.c[i] && p.b[i]) ? p.b[i][e] : 0.f;
+    }
+    __syncthreads();
+    if (warp < S0) cols_branch<T, NT, 1>(p, Bs, bias, rowseg0, 0, warp, S0, RG, nct, nrg, lane);
+    else if (warp < S0 + S1) cols_branch<T, NT, 2>(p, Bs + KC * NT * 32, bias + NT * 8, rowseg1, 1, warp - S0, S1, RG, nct, nrg, lane);
+    else cols_branch<T, NT, 4>(p, Bs + 2 * KC * NT * 32, bias + 2 * NT * 8, rowseg2, 2, warp - S0 - S1, S2, RG, nct, nrg, lane);
+    if (p.rowpart[0] == nullptr) return;
+    __syncthreads();
+    // row sums over the segments this block's tile really has, in segment order
+    const int b = blockIdx.z, rg = blockIdx.y, ct = blockIdx.x;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int hi = p.H >> i, wi = p.W >> i, ci = p.c[i];
+        const int tile_lo = (ct * PC_COLS) >> i, tile_hi = min(wi, ((ct + 1) * PC_COLS) >> i);
+        const int have = max(0, (tile_hi - tile_lo + 15) >> 4), S = i == 0 ? S0 : (i == 1 ? S1 : S2);
+        const int rgi = RG >> i, r_begin = rg * rgi, rows = max(0, min(hi, r_begin + rgi) - r_begin);
+        const float* rs = i == 0 ? rowseg0 : (i == 1 ? rowseg1 : rowseg2);
+        for (int e = tid; e < rows * ci; e += nthreads) {
+            const int rl = e / ci, c = e - rl * ci;
+            float a = 0.f;
+            for (int q = 0; q < have; ++q) a += rs[((size_t)rl * S + q) * (NT * 8) + c];
+            p.rowpart[i][(((size_t)b * hi + r_begin + rl) * nct + ct) * ci + c] = a;
+        }
+    }
+}
+
 inline int pyr_nt(int c) {
     const int n = (c + 7) / 8;
     return n <= 2 ? 2 : n <= 3 ? 3 : n <= 4 ? 4 : n <= 6 ? 6 : 8;
@@ -381,11 +539,37 @@ static int pyramid_row_tiles_per_block(int B, int H, int n_col_tiles) {
     return rt < 1 ? 1 : (rt > 8 ? 8 : (int)rt);
 }
 
+// Partition and shared memory of pyramid_cols_kernel; false if the shape does not qualify (the staged kernel takes it then).
+static bool pyramid_cols_plan(int B, int H, int W, int dim, const int c[3], kad::ColsPlan* q) {
+    using namespace kad;
+    const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
+    const int KC = (dim + 15) / 16;
+    const int Wt = W < PC_COLS ? W : PC_COLS;
+    ColsPlan r{};
+    r.nct = (W + PC_COLS - 1) / PC_COLS;
+    r.S[0] = (Wt + 15) / 16; r.S[1] = ((Wt >> 1) + 15) / 16; r.S[2] = ((Wt >> 2) + 15) / 16;
+    if (r.S[1] < 1 || r.S[2] < 1) return false;
+    r.warps = r.S[0] + r.S[1] + r.S[2];
+    r.RT = pyramid_row_tiles_per_block(B, H, r.nct);
+    r.nrg = ((H + 3) / 4 + r.RT - 1) / r.RT;
+    const int RG = 4 * r.RT;
+    r.smem = (size_t)3 * KC * nt * 32 * 8 + (size_t)3 * nt * 8 * 4 +
+             ((size_t)RG * r.S[0] + (size_t)(RG >> 1) * r.S[1] + (size_t)(RG >> 2) * r.S[2]) * nt * 8 * 4;
+    if (r.smem > 100 * 1024 || r.nrg > 65535) return false;
+    if (q) *q = r;
+    return true;
+}
+
 extern "C" int kad_pyramid_partial_dims(int B, int H, int W, int dim, int c0, int c1, int c2, int dtype, int* n_col_tiles, int* n_row_groups) {
     KAD_CHECK_ARG(n_col_tiles && n_row_groups, "kad_pyramid_partial_dims: null pointer");
     if (!kad_pyramid_project_supported(dim, c0, c1, c2, dtype, H, W))
         return fail(KAD_ERR_UNSUPPORTED, "kad_pyramid_partial_dims: shape not supported by kad_pyramid_project");
     const int c[3] = {c0, c1, c2};
+    ColsPlan q{};
+    if (pyramid_cols_plan(B, H, W, dim, c, &q)) {          // the kernel kad_pyramid_project runs for this shape
+        *n_col_tiles = q.nct; *n_row_groups = q.nrg;
+        return KAD_OK;
+    }
     PyramidParams p{};
     pyramid_plan(W, dim, c, &p);
     *n_col_tiles = (W + p.TW - 1) / p.TW;
@@ -400,6 +584,25 @@ int launch_pyramid(PyramidParams& p, int dtype, cudaStream_t st) {
     const int* c = p.c;
     const size_t smem = pyramid_plan(p.W, p.dim, c, &p);
     const int nt = pyr_nt(c[0] > c[1] ? (c[0] > c[2] ? c[0] : c[2]) : (c[1] > c[2] ? c[1] : c[2]));
+    ColsPlan q{};
+    if (!p.counters && pyramid_cols_plan(p.B, p.H, p.W, p.dim, c, &q)) {      // (the tail variant stays with the staged kernel)
+        dim3 grid(q.nct, q.nrg, p.B);
+#define KAD_PYC(TT, N)                                                                                                \
+    {                                                                                                                 \
+        auto kern = pyramid_cols_kernel<TT, N>;                                                                       \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q.smem);         \
+        if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "pyramid smem attribute: %s", cudaGetErrorString(e));         \
+        kern<<<grid, 32 * q.warps, q.smem, st>>>(p, q.S[0], q.S[1], q.S[2], 4 * q.RT, q.nct, q.nrg);                  \
+    }
+#define KAD_PYC_NT(TT)                                                                                                \
+    switch (nt) { case 2: KAD_PYC(TT, 2) break; case 3: KAD_PYC(TT, 3) break; case 4: KAD_PYC(TT, 4) break;          \
+                  case 6: KAD_PYC(TT, 6) break; default: KAD_PYC(TT, 8) break; }
+        if (dtype == KAD_F16) { KAD_PYC_NT(__half) } else { KAD_PYC_NT(__nv_bfloat16) }
+#undef KAD_PYC_NT
+#undef KAD_PYC
+        KAD_CHECK_LAUNCH("pyramid_cols_kernel");
+        return KAD_OK;
+    }
     const int nct = (p.W + p.TW - 1) / p.TW;
     p.RT = pyramid_row_tiles_per_block(p.B, p.H, nct);
     dim3 grid(nct, ((p.H + 3) / 4 + p.RT - 1) / p.RT, p.B);
@@ -450,7 +653,12 @@ extern "C" int kad_pyramid_project(const void* x, const float* const* w, const f
 extern "C" int kad_pyramid_lcsa_supported(int dim, int c0, int c1, int c2, int dtype, int H, int W) {
     if (!kad_pyramid_project_supported(dim, c0, c1, c2, dtype, H, W)) return 0;
     const int c[3] = {c0, c1, c2};
-    const size_t smem = pyramid_plan(W, dim, c, nullptr);
+    PyramidParams pp{};
+    const size_t smem = pyramid_plan(W, dim, c, &pp);
+    // the partial sums are laid out for the kernel kad_pyramid_project runs; the tail variant runs the staged kernel, so the
+    // two partitions have to be the same one (the row groups follow from the column tiles)
+    ColsPlan q{};
+    if (pyramid_cols_plan(1, H, W, dim, c, &q) && q.nct != (W + pp.TW - 1) / pp.TW) return 0;
     size_t need = (size_t)W * c0 * 4;                        // the widest column-sum table (branch 0)
     if ((size_t)(W >> 1) * c1 * 4 > need) need = (size_t)(W >> 1) * c1 * 4;
     if ((size_t)(W >> 2) * c2 * 4 > need) need = (size_t)(W >> 2) * c2 * 4;

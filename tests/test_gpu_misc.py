@@ -376,7 +376,7 @@ def test_lcsa_mask_from_pyramid_partial_sums(shape, dtype):
         assert (m1 - m0).abs().max().item() <= 2e-5
 
 
-@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((3, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
+@pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((3, 64, 50, 50), torch.float16), ((2, 128, 14, 28), torch.bfloat16),
                                          ((5, 48, 9, 30), torch.float16)])
 def test_inline_lcsa_mask_equals_mask_tensor(shape, dtype):
     """The five-launch form of a KAD-Conv branch (LCSA first stage finished in the pyramid kernel's tail by the last block of each
@@ -395,6 +395,8 @@ def test_inline_lcsa_mask_equals_mask_tensor(shape, dtype):
                  w2=f(_rand((c, 11), 232 + i, 0.3)), b2=f(_rand((c,), 235 + i, 0.1)), w3=f(_rand((9, c), 238 + i, 0.3)), b3=f(_rand((9,), 241 + i, 0.1)))
             for i, c in enumerate(cs)]
     assert ops.pyramid_lcsa_supported(dim, cs, dtype, H, W)
+    # (declined where the staged kernel behind the tail variant would tile the columns differently from kad_pyramid_project)
+    assert not ops.pyramid_lcsa_supported(128, (44, 42, 42), torch.bfloat16, 12, 70)
     ts0, parts = ops.pyramid_project(x, ws, bs, want_partials=True)
     for rep in range(2):
         ts1, lops = ops.pyramid_project_lcsa(x, ws, bs, prms)
