@@ -379,49 +379,69 @@ __device__ __forceinline__ void cols_branch(const PyramidParams& p, const uint2*
         bz[nt][0] = co < ci ? bias_i[co] : 0.f; bz[nt][1] = co + 1 < ci ? bias_i[co + 1] : 0.f;
     }
     constexpr int KC_UNROLL = P == 1 ? 2 : 1;
-    for (int r = r_begin; r < r_end; ++r) {
-        const unsigned char* base = reinterpret_cast<const unsigned char*>(p.x) + ((size_t)b * p.H + (size_t)P * r) * rowbytes;
-        float acc[NT][4];
+    // rows per trip. Two rows at once double the loads a warp has in flight, but the 28 registers they cost take a block off
+    // every SM at the detector's widths, and the forward measured 2 % slower: one row.
+    constexpr int RPT = 1;
+    for (int r = r_begin; r < r_end; r += RPT) {
+        const unsigned char* base[RPT];
+        float acc[RPT][NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int q = 0; q < RPT; ++q) {
+            const int rr = min(r + q, r_end - 1);                    // a row past the end repeats the last one, never stored
+            base[q] = reinterpret_cast<const unsigned char*>(p.x) + ((size_t)b * p.H + (size_t)P * rr) * rowbytes;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[q][nt][j] = 0.f;
+        }
 #pragma unroll KC_UNROLL
         for (int kc = 0; kc < KC; ++kc) {
             const int coff = 2 * lane_first_channel(kc, t, dim);
-            const uint2 lo = pooled8<T, P>(base + (size_t)(P * cl) * pix + coff, rowbytes, pix);
-            const uint2 hv = pooled8<T, P>(base + (size_t)(P * ch) * pix + coff, rowbytes, pix);
+            uint2 lo[RPT], hv[RPT];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma16816<T>(acc[nt], lo.x, hv.x, lo.y, hv.y, Bi[(kc * NT + nt) * 32 + lane]);
-        }
-        T* trow = tb + ((size_t)b * hi + r) * wi * ci;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int co = nt * 8 + 2 * t;
-            const bool c0ok = co < ci, c1ok = co + 1 < ci;
-            const float b0 = bz[nt][0], b1 = bz[nt][1];
-            const uint32_t ulo = pack2<T>(acc[nt][0] + b0, acc[nt][1] + b1), uhi = pack2<T>(acc[nt][2] + b0, acc[nt][3] + b1);
-            if (c0ok) {
-                if (pairs) {
-                    if (ok_lo) *reinterpret_cast<uint32_t*>(trow + (size_t)cl * ci + co) = ulo;
-                    if (ok_hi) *reinterpret_cast<uint32_t*>(trow + (size_t)ch * ci + co) = uhi;
-                } else {
-                    uint16_t* o = reinterpret_cast<uint16_t*>(trow);
-                    if (ok_lo) { o[(size_t)cl * ci + co] = (uint16_t)ulo; if (c1ok) o[(size_t)cl * ci + co + 1] = (uint16_t)(ulo >> 16); }
-                    if (ok_hi) { o[(size_t)ch * ci + co] = (uint16_t)uhi; if (c1ok) o[(size_t)ch * ci + co + 1] = (uint16_t)(uhi >> 16); }
-                }
+            for (int q = 0; q < RPT; ++q) {
+                lo[q] = pooled8<T, P>(base[q] + (size_t)(P * cl) * pix + coff, rowbytes, pix);
+                hv[q] = pooled8<T, P>(base[q] + (size_t)(P * ch) * pix + coff, rowbytes, pix);
             }
-            if (sums) {                                              // of the values as stored (rounded to T)
-                const float2 flo = up2<T>(ulo), fhi = up2<T>(uhi);
-                const float l0 = (ok_lo && c0ok) ? flo.x : 0.f, l1 = (ok_lo && c1ok) ? flo.y : 0.f;
-                const float h0 = (ok_hi && c0ok) ? fhi.x : 0.f, h1 = (ok_hi && c1ok) ? fhi.y : 0.f;
-                colsum[nt][0] += l0; colsum[nt][1] += l1; colsum[nt][2] += h0; colsum[nt][3] += h1;
-                float rs0 = l0 + h0, rs1 = l1 + h1;
 #pragma unroll
-                for (int m = 4; m < 32; m <<= 1) { rs0 += __shfl_xor_sync(0xffffffffu, rs0, m); rs1 += __shfl_xor_sync(0xffffffffu, rs1, m); }
-                if (g == 0) {
-                    float* rsq = rowseg_i + ((size_t)(r - r_begin) * nseg + s) * (NT * 8) + co;
-                    rsq[0] = rs0; rsq[1] = rs1;
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint2 bf = Bi[(kc * NT + nt) * 32 + lane];
+#pragma unroll
+                for (int q = 0; q < RPT; ++q) mma16816<T>(acc[q][nt], lo[q].x, hv[q].x, lo[q].y, hv[q].y, bf);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < RPT; ++q) {
+            if (r + q >= r_end) break;
+            T* trow = tb + ((size_t)b * hi + r + q) * wi * ci;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int co = nt * 8 + 2 * t;
+                const bool c0ok = co < ci, c1ok = co + 1 < ci;
+                const float b0 = bz[nt][0], b1 = bz[nt][1];
+                const uint32_t ulo = pack2<T>(acc[q][nt][0] + b0, acc[q][nt][1] + b1), uhi = pack2<T>(acc[q][nt][2] + b0, acc[q][nt][3] + b1);
+                if (c0ok) {
+                    if (pairs) {
+                        if (ok_lo) *reinterpret_cast<uint32_t*>(trow + (size_t)cl * ci + co) = ulo;
+                        if (ok_hi) *reinterpret_cast<uint32_t*>(trow + (size_t)ch * ci + co) = uhi;
+                    } else {
+                        uint16_t* o = reinterpret_cast<uint16_t*>(trow);
+                        if (ok_lo) { o[(size_t)cl * ci + co] = (uint16_t)ulo; if (c1ok) o[(size_t)cl * ci + co + 1] = (uint16_t)(ulo >> 16); }
+                        if (ok_hi) { o[(size_t)ch * ci + co] = (uint16_t)uhi; if (c1ok) o[(size_t)ch * ci + co + 1] = (uint16_t)(uhi >> 16); }
+                    }
+                }
+                if (sums) {                                          // of the values as stored (rounded to T)
+                    const float2 flo = up2<T>(ulo), fhi = up2<T>(uhi);
+                    const float l0 = (ok_lo && c0ok) ? flo.x : 0.f, l1 = (ok_lo && c1ok) ? flo.y : 0.f;
+                    const float h0 = (ok_hi && c0ok) ? fhi.x : 0.f, h1 = (ok_hi && c1ok) ? fhi.y : 0.f;
+                    colsum[nt][0] += l0; colsum[nt][1] += l1; colsum[nt][2] += h0; colsum[nt][3] += h1;
+                    float rs0 = l0 + h0, rs1 = l1 + h1;
+#pragma unroll
+                    for (int m = 4; m < 32; m <<= 1) { rs0 += __shfl_xor_sync(0xffffffffu, rs0, m); rs1 += __shfl_xor_sync(0xffffffffu, rs1, m); }
+                    if (g == 0) {
+                        float* rsq = rowseg_i + ((size_t)(r + q - r_begin) * nseg + s) * (NT * 8) + co;
+                        rsq[0] = rs0; rsq[1] = rs1;
+                    }
                 }
             }
         }
