@@ -84,10 +84,15 @@ __device__ __forceinline__ void stage_weights_1x1(uint2* dst, const float* __res
         const int n = nt * 8 + (lane >> 2), t = lane & 3, ch = kc * 16 + 4 * t;
         const int first = lane_first_channel(kc, t, Cin);
         float v[4];
+        if (n < Cout && first == ch && !(Cin & 3) && !(reinterpret_cast<uintptr_t>(w) & 15)) {      // the lane's four channels exist: one 16-byte load
+            const float4 q = __ldg(reinterpret_cast<const float4*>(w + (size_t)n * Cin + ch));
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int c = first + j;
-            v[j] = (n < Cout && c >= ch && c < Cin) ? w[(size_t)n * Cin + c] : 0.f;
+            for (int j = 0; j < 4; ++j) {
+                const int c = first + j;
+                v[j] = (n < Cout && c >= ch && c < Cin) ? w[(size_t)n * Cin + c] : 0.f;
+            }
         }
         dst[e] = make_uint2(pack2<T>(v[0], v[1]), pack2<T>(v[2], v[3]));
     }
@@ -378,7 +383,7 @@ __device__ __forceinline__ void cols_branch(const PyramidParams& p, const uint2*
         const int co = nt * 8 + 2 * t;
         bz[nt][0] = co < ci ? bias_i[co] : 0.f; bz[nt][1] = co + 1 < ci ? bias_i[co + 1] : 0.f;
     }
-    constexpr int KC_UNROLL = P == 1 ? 2 : 1;
+    constexpr int KC_UNROLL = P == 1 ? 2 : 1;       // 16-channel chunks whose loads are in flight together (4 / 8 / 32 loads per lane; deeper measured no faster)
     // rows per trip. Two rows at once double the loads a warp has in flight, but the 28 registers they cost take a block off
     // every SM at the detector's widths, and the forward measured 2 % slower: one row.
     constexpr int RPT = 1;
@@ -571,6 +576,11 @@ static bool pyramid_cols_plan(int B, int H, int W, int dim, const int c[3], kad:
     if (r.S[1] < 1 || r.S[2] < 1) return false;
     r.warps = r.S[0] + r.S[1] + r.S[2];
     r.RT = pyramid_row_tiles_per_block(B, H, r.nct);
+    if (nt >= 6) {              // wide outputs: one block per SM (registers), 37 KB of weight fragments to stage per block: about three rounds of blocks
+        const long long tiles = (long long)B * ((H + 3) / 4) * r.nct;
+        long long rt = (tiles + 443) / 444;
+        r.RT = rt < 1 ? 1 : (rt > 8 ? 8 : (int)rt);
+    }
     r.nrg = ((H + 3) / 4 + r.RT - 1) / r.RT;
     const int RG = 4 * r.RT;
     r.smem = (size_t)3 * KC * nt * 32 * 8 + (size_t)3 * nt * 8 * 4 +
