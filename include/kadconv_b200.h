@@ -138,7 +138,9 @@ int kad_pyramid_project(const void* x, const float* const* w, const float* const
  * which kad_dsc_forward (path 3, lcsa_* fields) consumes; the same values kad_lcsa_mask_from_partials derives in a kernel of
  * its own. lcsa_w1[i] [c_i][11], lcsa_b1[i] [c_i]: the 1x11 depthwise convolution; lcsa_bn_scale / lcsa_bn_shift [c_i]: folded BatchNorm.
  * counters: device int[B], zero before the first call; every call leaves them zero again (calls that share them must not overlap).
- * kad_pyramid_lcsa_supported: kad_pyramid_project_supported and the widest column-sum table (W * c0 floats) fits the block's shared memory. */
+ * kad_pyramid_lcsa_supported: kad_pyramid_project_supported, the widest column-sum table (W * c0 floats) fits the block's shared memory,
+ * and this variant's kernel partitions the partial sums as kad_pyramid_partial_dims says (true for maps up to 128 columns whose
+ * 4-row tile of x fits shared memory in one piece; wider or deeper inputs get 0 and take kad_pyramid_project + kad_lcsa_mask_from_partials). */
 typedef struct KadPyramidArgs {
     const void* x; const float* w[3]; const float* bias[3]; void* t[3];
     int B, H, W, dim, c[3], dtype;
