@@ -19,6 +19,27 @@ int fail(int code, const char* fmt, ...);
 #define KAD_CHECK_LAUNCH(what) do { cudaError_t e_ = cudaGetLastError(); \
     if (e_ != cudaSuccess) return kad::fail(KAD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e_)); } while (0)
 
+// ---- programmatic dependent launch ----------------------------------------------------------------------
+// launch_pdl: the grid may be scheduled while the kernel before it in the stream is still draining (once every block of that
+// kernel has called grid_dependents_go() or has ended), so its launch latency and whatever it does before grid_dependency_wait()
+// (staging weights, setting up barriers) overlap that kernel's tail. A kernel launched this way MUST call grid_dependency_wait()
+// before it reads or writes anything another kernel touches: the wait returns when the kernels before it have completed and
+// their writes are visible. Both instructions do nothing in a kernel launched the ordinary way, and the pair is recorded as a
+// programmatic edge when the launch is captured into a CUDA graph.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_go() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- storage types -----------------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f(T v);
 template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }

@@ -304,6 +304,31 @@ dsc_mma_kernel(const MmaParams p) {
     float* my_offs = offs + warp * 32 * OFF_PITCH;
     const float relu_floor = p.act == KAD_ACT_RELU ? 0.f : -INFINITY;
 
+    // ---- parameters first: weight fragments, epilogue vectors, the block of zeros. Nothing here was written by another kernel, so
+    // with a programmatic launch this part runs while the kernel before this one is still draining ----------------------------------
+    if (MODE == 0) stage_weights_rows<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
+    else stage_weights<T>(Bs, p.Wt, Cin, Cout, p.KT, p.TPC, KS, NT, tid);
+    if (FUSED) {
+        stage_weights_rows<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
+        if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
+    }
+    if (INLINE) {
+        for (int e = tid; e < 12 * p.Cp; e += MMA_THREADS) {
+            const int c = e / 12, k = e - c * 12;
+            sw3[e] = (k < 9 && c < Cin) ? p.l_w3[k * Cin + c] : 0.f;
+            sw2[e] = c < Cin ? (k < 11 ? p.l_w2[c * 11 + k] : p.l_b2[c]) : 0.f;
+        }
+    }
+    for (int e = tid; e < COP; e += MMA_THREADS) {
+        const bool on = e < Cout;
+        ep[e] = (on && p.scale) ? p.scale[e] : 1.f;
+        ep[COP + e] = (on && p.shift) ? p.shift[e] : 0.f;
+        ep[2 * COP + e] = (on && p.post) ? p.post[e] : 1.f;
+    }
+    if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(smem_mma + zoff)[tid] = 0u;
+    grid_dependency_wait();              // x, offsets, mask and the LCSA vectors come from the kernels before
+    grid_dependents_go();
+
     bool first = true;
     for (int gi = blockIdx.x; gi < total; gi += gridDim.x) {
         const int b = gi / gpi, grp = gi - b * gpi, base = grp * MMA_THREADS;
@@ -340,27 +365,7 @@ dsc_mma_kernel(const MmaParams p) {
         // shared-memory address of image element e: sel0 + 2*e
         const int sel0 = static_cast<int>(wdata) - static_cast<int>(static_cast<ptrdiff_t>(a16) - static_cast<ptrdiff_t>(reinterpret_cast<uintptr_t>(gimg)));
         if (first) {
-            if (MODE == 0) stage_weights_rows<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
-            else stage_weights<T>(Bs, p.Wt, Cin, Cout, p.KT, p.TPC, KS, NT, tid);
-            if (FUSED) {
-                stage_weights_rows<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
-                if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
-            }
-            if (INLINE) {
-                for (int e = tid; e < 12 * p.Cp; e += MMA_THREADS) {
-                    const int c = e / 12, k = e - c * 12;
-                    sw3[e] = (k < 9 && c < Cin) ? p.l_w3[k * Cin + c] : 0.f;
-                    sw2[e] = c < Cin ? (k < 11 ? p.l_w2[c * 11 + k] : p.l_b2[c]) : 0.f;
-                }
-                if (p.stage_cols) for (int e = tid; e < W * p.Cp; e += MMA_THREADS) Sms[e] = p.l_Sm[e];
-            }
-            for (int e = tid; e < COP; e += MMA_THREADS) {
-                const bool on = e < Cout;
-                ep[e] = (on && p.scale) ? p.scale[e] : 1.f;
-                ep[COP + e] = (on && p.shift) ? p.shift[e] : 0.f;
-                ep[2 * COP + e] = (on && p.post) ? p.post[e] : 1.f;
-            }
-            if (tid < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(smem_mma + zoff)[tid] = 0u;
+            if (INLINE && p.stage_cols) for (int e = tid; e < W * p.Cp; e += MMA_THREADS) Sms[e] = p.l_Sm[e];
             first = false;
         }
         // lane l describes pixel wbase + l; its modulation mask is fetched while the copy is in flight
@@ -651,7 +656,7 @@ int launch_mma_align(const MmaParams& p, dim3 grid, size_t smem, cudaStream_t st
         auto kern = dsc_mma_kernel<T, NT, MODE, A, GT>;                                                              \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "dsc_mma smem attribute: %s", cudaGetErrorString(e));         \
-        kern<<<grid, MMA_THREADS, smem, st>>>(p);                                                                     \
+        launch_pdl(kern, grid, MMA_THREADS, smem, st, p);                                                            \
     }
     if (p.align == 16) KAD_MMA_LAUNCH(16) else if (p.align == 8) KAD_MMA_LAUNCH(8) else if (p.align == 4) KAD_MMA_LAUNCH(4) else KAD_MMA_LAUNCH(2)
 #undef KAD_MMA_LAUNCH

@@ -151,6 +151,8 @@ lcsa_prep_partials_kernel(const float* __restrict__ rowpart, int nct, const floa
                           int H, int W, int C, int Cp) {
     // A [B][W][Cp], Sm [W][Cp] (channels innermost, padded to a multiple of 4: the mask kernel reads them as float4)
     extern __shared__ float colsum_s[];          // [PREP_COLS + 10][C], column w0 - 5 first
+    grid_dependency_wait();                      // everything here reads the partial sums of the kernel before
+    grid_dependents_go();
     const int b = blockIdx.y, t = threadIdx.x;
     const int w0 = blockIdx.x * PREP_COLS, nw = min(PREP_COLS, W - w0);
     const int lo = max(0, w0 - 5), hi = min(W, w0 + nw + 5);      // columns [lo, hi) are summed
@@ -226,6 +228,8 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     float* stage = sw2 + nrows * 12 * Cp;     // [3 + 128 * 9] the block's masks in global order (only with `staged`)
     const float invW = rows_are_means ? 1.f : 1.f / (float)W;      // `rowsum` holds row means already
     for (int e = t; e < 12 * Cp; e += 128) { const int c = e / 12, k = e - c * 12; sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f; }
+    grid_dependency_wait();              // the weights above are parameters; rowsum, A and Sm come from the kernel before
+    grid_dependents_go();
     for (int e = t; e < nrows * 12 * Cp; e += 128) {
         const int r = e / (12 * Cp), rem = e - r * 12 * Cp, c = rem / 12, k = rem - c * 12, hh = r_lo + r + k - 5;
         const bool in = k < 11 && hh >= 0 && hh < H && c < C;
@@ -309,6 +313,8 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
         sw3[e] = (k < 9 && c < C) ? w3[k * C + c] : 0.f;
         sw2[e] = c < C ? (k < 11 ? w2[c * 11 + k] : b2[c]) : 0.f;
     }
+    grid_dependency_wait();              // the weights above are parameters; rowsum, A and Sm come from the kernel before
+    grid_dependents_go();
     for (int e = t; e < Cp * P; e += 128) {
         const int j = e / Cp, c = e - j * Cp, hh = h0 - 5 + j;       // consecutive threads read consecutive channels
         rm[c * P + j] = (hh >= 0 && hh < H && c < C) ? rowsum[((size_t)b * H + hh) * C + c] * invW : 0.f;
@@ -542,6 +548,8 @@ se_excite_kernel(const float* __restrict__ gap_partial, int tiles, float inv_cou
     float* hid = sm + C;                 // [Hd]
     float* part = hid + Hd;              // [max(256, C)]
     int b = blockIdx.x, t = threadIdx.x;
+    grid_dependency_wait();              // the channel sums come from the kernel before
+    grid_dependents_go();
     se_partial_sums(gap_partial + (size_t)b * tiles * C, tiles, C, part, t);
     __syncthreads();
     for (int c = t; c < C; c += 256) mean[c] = se_mean_of(part, tiles, C, c, inv_count);
@@ -924,6 +932,8 @@ template <typename T, int ALIGN>
 __global__ void __launch_bounds__(256)
 merge_col_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, int G, int PL, int R, int out_ld) {
     const int tid = threadIdx.x;
+    grid_dependency_wait();              // branch tensors and attention values come from the kernels before
+    grid_dependents_go();
     if (tid >= G * PL) return;
     const int g = tid % G, pl = tid / G, b = blockIdx.z;
     const int xw = blockIdx.x * PL + pl;
@@ -1204,8 +1214,8 @@ extern "C" int kad_lcsa_mask_from_partials(const float* rowpart, int n_col_tiles
     KAD_CHECK_ARG((uintptr_t)scratch % 16 == 0, "kad_lcsa_mask_from_partials: scratch must be 16-byte aligned");
     float* A = scratch;
     float* Sm = scratch + (size_t)B * W * Cp;
-    lcsa_prep_partials_kernel<<<dim3((W + PREP_COLS - 1) / PREP_COLS, B), 256, sizeof(float) * (size_t)(PREP_COLS + 10) * C, st>>>(
-        rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C, Cp);
+    launch_pdl(lcsa_prep_partials_kernel, dim3((W + PREP_COLS - 1) / PREP_COLS, B), 256, sizeof(float) * (size_t)(PREP_COLS + 10) * C, st,
+               rowpart, n_col_tiles, colpart, n_row_groups, w1, b1, bn_scale, bn_shift, A, Sm, rowsum, H, W, C, Cp);
     return kad::lcsa_mask_from_prepared(rowsum, 0, A, Sm, w2, b2, w3, b3, mask, B, H, W, C, mask_f32, dtype, st);
 }
 
@@ -1226,7 +1236,7 @@ int kad::lcsa_mask_from_prepared(const float* rowsum, int rows_are_means, const 
         if (staged_strip) smem_strip += sizeof(float) * (size_t)(RB * W * 9 + 4);
         if ((long long)row_blocks * B >= 296 && smem_strip <= 48 * 1024) {
             KAD_DISPATCH_DTYPE(dtype, {
-                lcsa_mask_strip_kernel<T><<<dim3(row_blocks, B), 128, smem_strip, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32, rows_are_means, staged_strip);
+                launch_pdl(lcsa_mask_strip_kernel<T>, dim3(row_blocks, B), 128, smem_strip, st, rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, groups, mask_f32, rows_are_means, staged_strip);
             });
             KAD_CHECK_LAUNCH("lcsa_mask_from_partials (strips)");
             return KAD_OK;
@@ -1240,7 +1250,7 @@ int kad::lcsa_mask_from_prepared(const float* rowsum, int rows_are_means, const 
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "lcsa_mask smem attribute: %s", cudaGetErrorString(e));
         }
-        kern<<<dim3((H * W + 127) / 128, B), 128, smem, st>>>(rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means, staged);
+        launch_pdl(kern, dim3((H * W + 127) / 128, B), 128, smem, st, rowsum, A, Sm, w2, b2, w3, b3, mask, H, W, C, Cp, mask_f32, rows_are_means, staged);
     });
     KAD_CHECK_LAUNCH("lcsa_mask_from_partials");
     return KAD_OK;
@@ -1307,7 +1317,7 @@ extern "C" int kad_se_excite(const float* gap_partial, int tiles, float inv_coun
     KAD_CHECK_ARG(B > 0 && C > 0 && Hd > 0 && tiles > 0, "kad_se_excite: bad shape");
     size_t smem = sizeof(float) * (size_t)(C + Hd + (C > 256 ? C : 256));
     KAD_CHECK_ARG(smem <= 48 * 1024, "kad_se_excite: C + hidden = %d too large", C + Hd);
-    se_excite_kernel<<<B, 256, smem, (cudaStream_t)stream>>>(gap_partial, tiles, inv_count, w1, b1, w2, b2, att, C, Hd);
+    launch_pdl(se_excite_kernel, B, 256, smem, (cudaStream_t)stream, gap_partial, tiles, inv_count, w1, b1, w2, b2, att, C, Hd);
     KAD_CHECK_LAUNCH("se_excite_kernel");
     return KAD_OK;
 }
@@ -1402,7 +1412,7 @@ extern "C" int kad_merge_upsample_residual(const KadMergeArgs* a, void* stream) 
         if (R > a->H) R = a->H;
         dim3 grid(xstrips, (a->H + R - 1) / R, a->B);
         KAD_CHECK_ARG(grid.y <= 65535, "kad_merge_upsample_residual: image too tall");
-#define KAD_MERGE_COL(TT, AL) merge_col_kernel<TT, AL><<<grid, 256, 0, st>>>((const TT*)a->x, (TT*)a->out, p, C4, PL, R, out_ld)
+#define KAD_MERGE_COL(TT, AL) launch_pdl(merge_col_kernel<TT, AL>, grid, 256, 0, st, (const TT*)a->x, (TT*)a->out, p, C4, PL, R, out_ld)
         if (a->dtype == KAD_F16) { if (align == 8) KAD_MERGE_COL(__half, 8); else if (align == 4) KAD_MERGE_COL(__half, 4); else KAD_MERGE_COL(__half, 2); }
         else { if (align == 8) KAD_MERGE_COL(__nv_bfloat16, 8); else if (align == 4) KAD_MERGE_COL(__nv_bfloat16, 4); else KAD_MERGE_COL(__nv_bfloat16, 2); }
 #undef KAD_MERGE_COL

@@ -480,6 +480,8 @@ pyramid_cols_kernel(const PyramidParams p, int S0, int S1, int S2, int RG, int n
         stage_weights_1x1<T>(Bs + i * KC * NT * 32, p.w[i], p.dim, p.c[i], KC, NT, tid, nthreads);
         for (int e = tid; e < NT * 8; e += nthreads) bias[i * NT * 8 + e] = (e < p.c[i] && p.b[i]) ? p.b[i][e] : 0.f;
     }
+    grid_dependency_wait();              // weights and bias are parameters; x comes from the kernel before
+    grid_dependents_go();
     __syncthreads();
     if (warp < S0) cols_branch<T, NT, 1>(p, Bs, bias, rowseg0, 0, warp, S0, RG, nct, nrg, lane);
     else if (warp < S0 + S1) cols_branch<T, NT, 2>(p, Bs + KC * NT * 32, bias + NT * 8, rowseg1, 1, warp - S0, S1, RG, nct, nrg, lane);
@@ -622,7 +624,7 @@ int launch_pyramid(PyramidParams& p, int dtype, cudaStream_t st) {
         auto kern = pyramid_cols_kernel<TT, N>;                                                                       \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q.smem);         \
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "pyramid smem attribute: %s", cudaGetErrorString(e));         \
-        kern<<<grid, 32 * q.warps, q.smem, st>>>(p, q.S[0], q.S[1], q.S[2], 4 * q.RT, q.nct, q.nrg);                  \
+        launch_pdl(kern, grid, 32 * q.warps, q.smem, st, p, q.S[0], q.S[1], q.S[2], 4 * q.RT, q.nct, q.nrg);          \
     }
 #define KAD_PYC_NT(TT)                                                                                                \
     switch (nt) { case 2: KAD_PYC(TT, 2) break; case 3: KAD_PYC(TT, 3) break; case 4: KAD_PYC(TT, 4) break;          \
