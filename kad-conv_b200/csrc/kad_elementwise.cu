@@ -1605,6 +1605,7 @@ namespace kad { namespace {
 // 2x2 average pool with stride 1 (AConv's pre-pool, KAD-CNet/models/common.py:65): y[b,y,x,:] = mean of the 2x2 block at (y,x).
 template <typename T>
 __global__ void avg_pool2x2s1_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int C8, size_t n) {
+    grid_dependency_wait(); grid_dependents_go();      // launched programmatically: nothing is read before the kernels in front are done
     const int Ho = H - 1, Wo = W - 1;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const int c = (int)(e % C8);
@@ -1642,6 +1643,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bias_act_vec8_kernel(const uint4* __restrict__ y, uint4* __restrict__ out, const float* __restrict__ bias, unsigned C8, unsigned out_ld8,
                      unsigned long long n, int act) {
+    grid_dependency_wait(); grid_dependents_go();      // launched programmatically: nothing is read before the kernels in front are done
     const unsigned long long stride = (unsigned long long)gridDim.x * 256;
     for (unsigned long long e0 = (unsigned long long)blockIdx.x * 256 + threadIdx.x; e0 < n; e0 += 2 * stride) {
         const unsigned long long e1 = e0 + stride;
@@ -1670,6 +1672,7 @@ bias_act_vec8_kernel(const uint4* __restrict__ y, uint4* __restrict__ out, const
 }
 template <typename T>
 __global__ void bias_act_kernel(const T* __restrict__ y, T* __restrict__ out, const float* __restrict__ bias, int C, int out_ld, size_t n, int act) {
+    grid_dependency_wait(); grid_dependents_go();      // launched programmatically: nothing is read before the kernels in front are done
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const size_t m = e / C; const int c = (int)(e - m * C);
         const float a = to_f<T>(y[e]) + (bias ? bias[c] : 0.f);
@@ -1682,6 +1685,7 @@ __global__ void bias_act_kernel(const T* __restrict__ y, T* __restrict__ out, co
 __global__ void __launch_bounds__(256)
 upsample2x_concat_vec8_kernel(const uint4* __restrict__ low, const uint4* __restrict__ skip, uint4* __restrict__ out,
                               int h, int w, unsigned G1, unsigned G2, unsigned long long n) {
+    grid_dependency_wait(); grid_dependents_go();      // launched programmatically: nothing is read before the kernels in front are done
     const unsigned G = G1 + G2;
     const int W = 2 * w;
     for (unsigned long long e = (unsigned long long)blockIdx.x * 256 + threadIdx.x; e < n; e += (unsigned long long)gridDim.x * 256) {
@@ -1726,8 +1730,8 @@ extern "C" int kad_avg_pool2x2s1(const void* x, void* y, int B, int H, int W, in
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype != KAD_F32 && C % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
         const size_t nv = n / 8;
-        if (dtype == KAD_F16) avg_pool2x2s1_vec8_kernel<__half><<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, H, W, C / 8, nv);
-        else avg_pool2x2s1_vec8_kernel<__nv_bfloat16><<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, H, W, C / 8, nv);
+        if (dtype == KAD_F16) launch_pdl(avg_pool2x2s1_vec8_kernel<__half>, grid_for(nv, 256), 256, 0, st, (const uint4*)x, (uint4*)y, H, W, C / 8, nv);
+        else launch_pdl(avg_pool2x2s1_vec8_kernel<__nv_bfloat16>, grid_for(nv, 256), 256, 0, st, (const uint4*)x, (uint4*)y, H, W, C / 8, nv);
     } else {
         KAD_DISPATCH_DTYPE(dtype, { avg_pool2x2s1_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)x, (T*)y, H, W, C, n); });
     }
@@ -1745,10 +1749,10 @@ extern "C" int kad_bias_act_to(const void* y, const float* bias, void* out, long
         const size_t nv = n / 8;
         size_t blocks = (nv + 511) / 512;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        if (dtype == KAD_F16) bias_act_vec8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
-        else bias_act_vec8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
+        if (dtype == KAD_F16) launch_pdl(bias_act_vec8_kernel<__half>, (unsigned)blocks, 256, 0, st, (const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
+        else launch_pdl(bias_act_vec8_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, st, (const uint4*)y, (uint4*)out, bias, C / 8, out_ld / 8, nv, act);
     } else {
-        KAD_DISPATCH_DTYPE(dtype, { bias_act_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)y, (T*)out, bias, C, out_ld, n, act); });
+        KAD_DISPATCH_DTYPE(dtype, { launch_pdl(bias_act_kernel<T>, grid_for(n, 256), 256, 0, st, (const T*)y, (T*)out, bias, C, out_ld, n, act); });
     }
     KAD_CHECK_LAUNCH("bias_act_kernel");
     return KAD_OK;
@@ -1765,6 +1769,7 @@ template <typename V>
 __global__ void __launch_bounds__(256)
 copy_channels_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, size_t nvec, unsigned vpr, unsigned vpr_magic, int exact,
                      size_t src_pitch, size_t dst_pitch) {
+    grid_dependency_wait(); grid_dependents_go();      // launched programmatically: nothing is read before the kernels in front are done
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= nvec) return;
     // row = i / vpr: by multiplication with a rounded-up reciprocal when the index fits 32 bits, else by division
@@ -1795,10 +1800,10 @@ extern "C" int kad_copy_channels(const void* src, int src_cstride, int src_coff,
     const unsigned magic = vpr > 1 ? (unsigned)((0x100000000ull + vpr - 1) / vpr) : 0u;
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((nvec + 255) / 256);
-    if (vb == 16) copy_channels_kernel<uint4><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
-    else if (vb == 8) copy_channels_kernel<uint2><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
-    else if (vb == 4) copy_channels_kernel<uint32_t><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
-    else copy_channels_kernel<uint16_t><<<blocks, 256, 0, st>>>(s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    if (vb == 16) launch_pdl(copy_channels_kernel<uint4>, blocks, 256, 0, st, s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else if (vb == 8) launch_pdl(copy_channels_kernel<uint2>, blocks, 256, 0, st, s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else if (vb == 4) launch_pdl(copy_channels_kernel<uint32_t>, blocks, 256, 0, st, s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
+    else launch_pdl(copy_channels_kernel<uint16_t>, blocks, 256, 0, st, s, d, nvec, (unsigned)vpr, magic, exact, sp, dp);
     KAD_CHECK_LAUNCH("copy_channels_kernel");
     return KAD_OK;
 }
@@ -1809,7 +1814,7 @@ extern "C" int kad_upsample2x_concat(const void* low, const void* skip, void* ou
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype != KAD_F32 && C1 % 8 == 0 && C2 % 8 == 0 && (uintptr_t)low % 16 == 0 && (uintptr_t)skip % 16 == 0 && (uintptr_t)out % 16 == 0) {
         const size_t nv = n / 8;
-        upsample2x_concat_vec8_kernel<<<grid_for(nv, 256), 256, 0, st>>>((const uint4*)low, (const uint4*)skip, (uint4*)out, h, w, C1 / 8, C2 / 8, nv);
+        launch_pdl(upsample2x_concat_vec8_kernel, grid_for(nv, 256), 256, 0, st, (const uint4*)low, (const uint4*)skip, (uint4*)out, h, w, C1 / 8, C2 / 8, nv);
     } else {
         KAD_DISPATCH_DTYPE(dtype, { upsample2x_concat_kernel<T><<<grid_for(n, 256), 256, 0, st>>>((const T*)low, (const T*)skip, (T*)out, h, w, C1, C2, n); });
     }

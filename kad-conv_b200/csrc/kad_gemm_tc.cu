@@ -74,6 +74,9 @@ gemm1x1_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+    // barriers, tensor memory and the bias are set up: with a programmatic launch that happened while the kernel before drained
+    grid_dependency_wait();
+    grid_dependents_go();
 
     if (warp < G_EPI_WARPS) {
         const int quad = warp & 3, half = warp >> 2;       // TMEM lane quadrant; which half of the column chunks
@@ -268,12 +271,12 @@ extern "C" int kad_gemm1x1_bias_act(const void* x, const void* w, const float* b
         auto kern = gemm1x1_tc_kernel<__half>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "gemm1x1 smem attribute: %s", cudaGetErrorString(e));
-        kern<<<grid, G_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_b, p);
+        launch_pdl(kern, grid, G_THREADS, smem, (cudaStream_t)stream, map_a, map_b, p);
     } else {
         auto kern = gemm1x1_tc_kernel<__nv_bfloat16>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "gemm1x1 smem attribute: %s", cudaGetErrorString(e));
-        kern<<<grid, G_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_b, p);
+        launch_pdl(kern, grid, G_THREADS, smem, (cudaStream_t)stream, map_a, map_b, p);
     }
     KAD_CHECK_LAUNCH("gemm1x1_tc_kernel");
     return KAD_OK;
