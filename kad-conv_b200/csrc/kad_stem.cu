@@ -7,7 +7,7 @@
 // 1/255 is applied to the fp32 accumulator; SiLU uses the hardware exponential and reciprocal. A block owns 8 x 32 output pixels;
 // its (17 x 65 x Cin)-byte input patch goes through shared memory, and each warp's 32 output pixels leave as one
 // contiguous run of 16-byte vectors.
-#include "kad_common.cuh"
+#include "kad_mma.cuh"
 
 namespace kad {
 namespace {
@@ -15,7 +15,7 @@ namespace {
 constexpr int STEM_THREADS = 256;
 constexpr int ST_ROWS = 8, ST_COLS = 32;                  // output pixels per block
 constexpr int ST_IN_ROWS = 2 * ST_ROWS + 1, ST_IN_COLS = 2 * ST_COLS + 1;
-constexpr int ST_PITCH = 68;                              // bytes per staged input row
+constexpr int ST_PITCH = 72;                              // bytes per staged input row (18 words: the row may start 3 bytes into the first)
 constexpr int ST_MAX_CIN = 4, ST_MAX_NT = 8;
 
 template <typename T> __device__ __forceinline__ uint32_t st_pack2(float a, float b);
@@ -36,28 +36,50 @@ __device__ __forceinline__ float fast_silu(float v) { return silu_fast(v); }
 
 // K index of the contraction: k = ci*9 + ky*3 + kx (the flattening of an [Cout][Cin][3][3] weight). Lane t of a 16-chunk
 // owns k = chunk*16 + {2t, 2t+1, 2t+8, 2t+9} (the operand layout of mma.sync, no permutation needed here).
-template <typename T, int NT, int KC>
-__global__ void __launch_bounds__(STEM_THREADS)
+template <typename T, int NT, int KC, bool WORDS>
+__global__ void __launch_bounds__(STEM_THREADS, NT <= 5 ? 4 : 2)
 stem_conv_kernel(const unsigned char* __restrict__ img, const float* __restrict__ w, const float* __restrict__ bias, T* __restrict__ y,
-                 int Cin, int H, int W, int OH, int OW, int Cout, float scale, int act) {
-    __shared__ __align__(16) unsigned char patch[ST_MAX_CIN * ST_IN_ROWS * ST_PITCH];
+                 int Cin, int H, int W, int OH, int OW, int Cout, float scale, int act, int tiles_per_block) {
+    // WORDS (W % 4 == 0, image 4-byte aligned): the patch is staged as aligned 4-byte words by asynchronous copies, the patch of
+    // the next row tile while the current one is computed; a row of the patch then starts 3 bytes into its first word.
+    __shared__ __align__(16) unsigned char patches[2][ST_MAX_CIN * ST_IN_ROWS * ST_PITCH];
     __shared__ uint2 Bs[KC * NT * 32];
     __shared__ float bs[NT * 8];
     __shared__ int koff[KC * 16];                          // byte offset of k inside the patch, relative to the pixel's corner; -1: padding
     __shared__ __align__(16) unsigned char tiles[STEM_THREADS / 32][32 * NT * 8 * 2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int b = blockIdx.z, oy0 = blockIdx.y * ST_ROWS, ox0 = blockIdx.x * ST_COLS;
-    const int iy0 = 2 * oy0 - 1, ix0 = 2 * ox0 - 1;
+    const int b = blockIdx.z, ox0 = blockIdx.x * ST_COLS;
+    const int ix0 = 2 * ox0 - 1;
     const int K = Cin * 9;
+    constexpr int SHIFT = WORDS ? 3 : 0;                    // patch column of input column ix0
+    const int ty0 = blockIdx.y * tiles_per_block, nty = (OH + ST_ROWS - 1) / ST_ROWS;
+    const int ntiles = min(tiles_per_block, nty - ty0);
 
-    // input patch (zero outside the image)
     const unsigned char* ib = img + (size_t)b * Cin * H * W;
-    for (int e = tid; e < Cin * ST_IN_ROWS * ST_PITCH; e += STEM_THREADS) {
-        const int c = e % ST_PITCH, r = (e / ST_PITCH) % ST_IN_ROWS, ci = e / (ST_PITCH * ST_IN_ROWS);
-        const int yy = iy0 + r, xx = ix0 + c;
-        patch[e] = (c < ST_IN_COLS && yy >= 0 && yy < H && xx >= 0 && xx < W) ? ib[((size_t)ci * H + yy) * W + xx] : (unsigned char)0;
-    }
+    // input patch of row tile ty (zero outside the image)
+    auto stage_patch = [&](int ty, unsigned char* patch) {
+        const int iy0 = 2 * ty * ST_ROWS - 1;
+        if (WORDS) {
+            constexpr int WPR = ST_PITCH / 4;
+            const int xa0 = ix0 - 3;                            // a multiple of 4
+            for (int e = tid; e < Cin * ST_IN_ROWS * WPR; e += STEM_THREADS) {
+                const int wd = e % WPR, r = (e / WPR) % ST_IN_ROWS, ci = e / (WPR * ST_IN_ROWS);
+                const int yy = iy0 + r, xx = xa0 + 4 * wd;
+                unsigned char* dst = patch + (ci * ST_IN_ROWS + r) * ST_PITCH + 4 * wd;
+                if (yy >= 0 && yy < H && xx >= 0 && xx < W) cp_async4(dst, ib + ((size_t)ci * H + yy) * W + xx);
+                else *reinterpret_cast<uint32_t*>(dst) = 0u;
+            }
+        } else {
+            for (int e = tid; e < Cin * ST_IN_ROWS * ST_PITCH; e += STEM_THREADS) {
+                const int c = e % ST_PITCH, r = (e / ST_PITCH) % ST_IN_ROWS, ci = e / (ST_PITCH * ST_IN_ROWS);
+                const int yy = iy0 + r, xx = ix0 + c;
+                patch[e] = (c < ST_IN_COLS && yy >= 0 && yy < H && xx >= 0 && xx < W) ? ib[((size_t)ci * H + yy) * W + xx] : (unsigned char)0;
+            }
+        }
+    };
+    if (ntiles > 0) stage_patch(ty0, patches[0]);
+    cp_async_commit();
     for (int e = tid; e < KC * NT * 32; e += STEM_THREADS) {
         const int l = e & 31, nt = (e >> 5) % NT, kc = (e >> 5) / NT;
         const int n = nt * 8 + (l >> 2), k0 = kc * 16 + 2 * (l & 3);
@@ -72,8 +94,15 @@ stem_conv_kernel(const unsigned char* __restrict__ img, const float* __restrict_
     for (int e = tid; e < NT * 8; e += STEM_THREADS) bs[e] = (e < Cout && bias) ? bias[e] : 0.f;
     for (int k = tid; k < KC * 16; k += STEM_THREADS) {
         const int ci = k / 9, r = (k % 9) / 3, c = k % 3;
-        koff[k] = k < K ? (ci * ST_IN_ROWS + r) * ST_PITCH + c : -1;
+        koff[k] = k < K ? (ci * ST_IN_ROWS + r) * ST_PITCH + c + SHIFT : -1;
     }
+
+    for (int kt = 0; kt < ntiles; ++kt) {
+    const unsigned char* patch = patches[kt & 1];
+    const int oy0 = (ty0 + kt) * ST_ROWS;
+    if (kt + 1 < ntiles) stage_patch(ty0 + kt + 1, patches[(kt + 1) & 1]);      // in flight while this tile is computed
+    cp_async_commit();
+    cp_async_wait_but_one();                                                    // this tile's patch has landed
     __syncthreads();
 
     // this warp: output row oy0 + warp, 32 pixels = two 16-row tiles; lane rows g and g+8
@@ -138,6 +167,8 @@ stem_conv_kernel(const unsigned char* __restrict__ img, const float* __restrict_
             for (int i = lane; i < (nb >> 4); i += 32) dst[i] = src[i];
         }
     }
+    __syncthreads();                     // every warp is done with this patch (the tile after the next lands in it) and with its output tile
+    }   // row tiles
 }
 
 }  // namespace
@@ -159,16 +190,24 @@ extern "C" int kad_stem_conv_u8(const void* img_u8, const float* w_oihw, const f
     KAD_CHECK_ARG((uintptr_t)y % 16 == 0, "kad_stem_conv_u8: y must be 16-byte aligned");
     KAD_CHECK_ARG(act == KAD_ACT_NONE || act == KAD_ACT_SILU || act == KAD_ACT_RELU, "kad_stem_conv_u8: unknown activation %d", act);
     const int OH = (H - 1) / 2 + 1, OW = (W - 1) / 2 + 1;
-    dim3 grid((OW + ST_COLS - 1) / ST_COLS, (OH + ST_ROWS - 1) / ST_ROWS, B);
+    // row tiles per block: the weights are staged once per block and the next patch loads during a tile, so a block takes several
+    // tiles as long as a few thousand blocks remain
+    const int nty = (OH + ST_ROWS - 1) / ST_ROWS, ntx = (OW + ST_COLS - 1) / ST_COLS;
+    int tpb = (int)(((long long)nty * ntx * B) / 4096);
+    tpb = tpb < 1 ? 1 : (tpb > 8 ? 8 : tpb);
+    dim3 grid(ntx, (nty + tpb - 1) / tpb, B);
     KAD_CHECK_ARG(grid.y <= 65535, "kad_stem_conv_u8: image too tall");
+    const bool words = W % 4 == 0 && (uintptr_t)img_u8 % 4 == 0 && ((size_t)H * W) % 4 == 0;
     const int nt = (Cout + 7) / 8, kc = (Cin * 9 + 15) / 16;
     cudaStream_t st = (cudaStream_t)stream;
-#define KAD_STEM(TT, N, KCC) stem_conv_kernel<TT, N, KCC><<<grid, STEM_THREADS, 0, st>>>((const unsigned char*)img_u8, w_oihw, bias, (TT*)y, Cin, H, W, OH, OW, Cout, scale, act)
+#define KAD_STEM(TT, N, KCC)                                                                                                                          \
+    { if (words) stem_conv_kernel<TT, N, KCC, true><<<grid, STEM_THREADS, 0, st>>>((const unsigned char*)img_u8, w_oihw, bias, (TT*)y, Cin, H, W, OH, OW, Cout, scale, act, tpb); \
+      else stem_conv_kernel<TT, N, KCC, false><<<grid, STEM_THREADS, 0, st>>>((const unsigned char*)img_u8, w_oihw, bias, (TT*)y, Cin, H, W, OH, OW, Cout, scale, act, tpb); }
 #define KAD_STEM_NT(TT, KCC)                                                                                      \
     switch (nt) {                                                                                                 \
-        case 1: KAD_STEM(TT, 1, KCC); break; case 2: KAD_STEM(TT, 2, KCC); break; case 3: KAD_STEM(TT, 3, KCC); break; \
-        case 4: KAD_STEM(TT, 4, KCC); break; case 5: KAD_STEM(TT, 5, KCC); break; case 6: KAD_STEM(TT, 6, KCC); break; \
-        case 7: KAD_STEM(TT, 7, KCC); break; default: KAD_STEM(TT, 8, KCC); break;                               \
+        case 1: KAD_STEM(TT, 1, KCC) break; case 2: KAD_STEM(TT, 2, KCC) break; case 3: KAD_STEM(TT, 3, KCC) break; \
+        case 4: KAD_STEM(TT, 4, KCC) break; case 5: KAD_STEM(TT, 5, KCC) break; case 6: KAD_STEM(TT, 6, KCC) break; \
+        case 7: KAD_STEM(TT, 7, KCC) break; default: KAD_STEM(TT, 8, KCC) break;                               \
     }
 #define KAD_STEM_KC(TT)                                                                                           \
     switch (kc) { case 1: KAD_STEM_NT(TT, 1) break; case 2: KAD_STEM_NT(TT, 2) break; default: KAD_STEM_NT(TT, 3) break; }

@@ -283,10 +283,11 @@ def test_detector_glue_kernels():
 
 
 @pytest.mark.parametrize('shape,dtype', [((2, 3, 50, 70, 40), torch.float16), ((1, 3, 33, 47, 32), torch.bfloat16), ((2, 1, 16, 16, 8), torch.float16),
-                                         ((1, 4, 21, 130, 64), torch.float16)])
+                                         ((1, 4, 21, 130, 64), torch.float16), ((70, 3, 150, 136, 40), torch.float16), ((3, 3, 37, 68, 16), torch.bfloat16)])
 def test_stem_conv_on_uint8_images(shape, dtype):
     """uint8 planes -> /255 -> 3x3 stride-2 convolution + bias + SiLU -> NHWC, against torch in float32 (odd sizes, image
-    borders, widths that do not fill the 32-pixel tiles)."""
+    borders, widths that do not fill the 32-pixel tiles; widths that are multiples of four take the word-staged path, and the
+    batch of 70 gives every block several row tiles, the last of them partial)."""
     from kadconv import ops
     B, Cin, H, W, Cout = shape
     g = np.random.default_rng(sum(shape))
