@@ -10,6 +10,11 @@
  *   - the caller owns every buffer (inputs, outputs, scratch); nothing is allocated, nothing
  *     synchronises, every kernel is launched on `stream` (a cudaStream_t passed as void*) and the
  *     calls can be captured in a CUDA graph;
+ *   - most kernels are launched with programmatic stream serialization: they read their PARAMETERS (weights,
+ *     bias, scale / shift vectors) first, then wait for everything in front of them in the stream, then touch
+ *     activations. Activations may come from any earlier work in the stream; parameters must not be written by
+ *     the kernel that IMMEDIATELY precedes the call in the same stream (anything in between, or one
+ *     synchronisation after the weights were prepared, is enough);
  *   - return value 0 on success, a negative KAD_ERR_* otherwise; kad_last_error_string() gives the
  *     reason for the calling thread. No call throws or exits.
  *

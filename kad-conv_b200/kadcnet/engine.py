@@ -127,6 +127,7 @@ class FastDetector(torch.nn.Module):
         self.stride = model.stride
         self._fused_up = set()
         self.plan = [self._compile(m) for m in model.model]
+        ops.parameters_fence(device)         # converted weights and biases: see kadconv.ops.parameters_fence
         # raw uint8 images: the first layer (3x3, stride 2) runs as one kernel that also normalises and changes layout
         self.stem = None
         first = model.model[0]

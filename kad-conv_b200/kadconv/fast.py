@@ -88,6 +88,7 @@ def _prepare(layer, device):
         st = {'device': device, 'fingerprint': fp,
               'branches': [_BranchParams(layer.convs[i], layer.fc[i], layer.weight[i], device) for i in range(layer.n)]}
         object.__setattr__(layer, _FAST_ATTR, st)
+        ops.parameters_fence(device)         # the kernels read these before they wait for the work in front of them
     return st
 
 
@@ -123,6 +124,7 @@ def _layer_args(layer, st, dtype, H, W):
             if all(ops.lcsa_mask_from_partials_supported(H >> i, W >> i, br.c) for i, br in enumerate(st['branches'])):
                 launches -= 6      # row/column sums come out of the pyramid kernel
         st[key] = (a, tc_mask, keep, launches)
+        ops.parameters_fence(st['device'])   # packed deformable-convolution weights may have just been produced
         a.counters = ops.layer_counters(st['device']).data_ptr()
     return st[key]
 

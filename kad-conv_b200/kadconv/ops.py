@@ -498,6 +498,19 @@ def bias_act_to(y, bias, out, out_coff=0, act=ACT_SILU):
     return out
 
 
+def parameters_fence(device):
+    """One ordinary, tiny piece of work on the current stream. Most kernels of this package are launched with programmatic stream
+    serialization and read their PARAMETERS (weights, bias, folded BatchNorm vectors) before they wait for the kernel in front of
+    them; parameters that the stream has only just produced (folding, packing, a dtype conversion) must therefore not come from the
+    kernel IMMEDIATELY before such a launch. Whatever runs between the two (this call) restores the ordinary stream order for them.
+    Called wherever this package derives parameters; a caller of the C ABI that computes weights on the stream right before a call
+    does the same, or synchronises once."""
+    _FENCE.setdefault(str(device), torch.zeros(1, dtype=torch.int32, device=device)).zero_()
+
+
+_FENCE = {}
+
+
 def copy_channels(src, src_coff, C, dst=None, dst_coff=0):
     """dst[..., dst_coff:dst_coff+C] = src[..., src_coff:src_coff+C] for contiguous tensors with the same leading shape; with
     dst=None a new dense [..., C] tensor is returned (what `src[..., a:b].contiguous()` gives, in one vectorised kernel)."""
