@@ -62,6 +62,9 @@ __device__ __forceinline__ void store_mixed(void* p, size_t i, int f32, float v)
 }
 
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+// The LCSA modulation mask (nine per pixel): hardware exponential and reciprocal, about 2 ulp of float32 on a value in (0, 1), i.e.
+// below 1e-6 absolute. Every kernel that produces a mask uses this one, so the forms stay bit-identical among themselves.
+__device__ __forceinline__ float sigmoid_mask(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 // SiLU for the 16-bit epilogues: v / (1 + 2^(-v * log2 e)) with the hardware exponential and reciprocal (two
 // special-function instructions, about 2 ulp of float32: far below the rounding of the 16-bit store that follows).
 // Building with -DKAD_SILU_TANH selects v * (0.5 * tanh.approx(v / 2) + 0.5) instead: one special-function

@@ -267,7 +267,7 @@ __device__ __forceinline__ void lcsa_mask_pixel(float (&mk)[9], const float* A, 
         }
     }
 #pragma unroll
-    for (int j = 0; j < 9; ++j) mk[j] = sigmoidf_(logit[j]);
+    for (int j = 0; j < 9; ++j) mk[j] = sigmoid_mask(logit[j]);
 }
 
 template <typename T, int NT, int MODE, int ALIGN, int GT>       // MODE 0 plain, 1 deform, 2 fused, 3 fused + inline LCSA mask; GT: channel groups per tap when known at compile time

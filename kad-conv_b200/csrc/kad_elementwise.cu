@@ -136,7 +136,7 @@ lcsa_mask_kernel(const float* __restrict__ rowsum, const float* __restrict__ A, 
     }
     size_t o = (((size_t)b * H + h) * W + w) * 9;
 #pragma unroll
-    for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[j]));
+    for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoid_mask(logit[j]));
 }
 
 // ---- LCSA from the partial sums the pyramid kernel leaves behind --------------------------------------------------------
@@ -276,11 +276,11 @@ lcsa_mask_flat_kernel(const float* __restrict__ rowsum, const float* __restrict_
     if (staged) {
         float* so = stage + (int)(o0 & 3) + t * 9;
 #pragma unroll
-        for (int j = 0; j < 9; ++j) so[j] = sigmoidf_(logit[j]);
+        for (int j = 0; j < 9; ++j) so[j] = sigmoid_mask(logit[j]);
     } else {
         const size_t o = o0 + (size_t)t * 9;
 #pragma unroll
-        for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[j]));
+        for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoid_mask(logit[j]));
     }
     }
     if (staged) {                        // uniform over the block
@@ -370,11 +370,11 @@ lcsa_mask_strip_kernel(const float* __restrict__ rowsum, const float* __restrict
         if (staged) {
             float* so = stage + (int)(o0 & 3) + ((g * LS_R + r) * W + w) * 9;
 #pragma unroll
-            for (int j = 0; j < 9; ++j) so[j] = sigmoidf_(logit[r][j]);
+            for (int j = 0; j < 9; ++j) so[j] = sigmoid_mask(logit[r][j]);
         } else {
             const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
 #pragma unroll
-            for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoidf_(logit[r][j]));
+            for (int j = 0; j < 9; ++j) store_mixed<T>(mask, o + j, mask_f32, sigmoid_mask(logit[r][j]));
         }
     }
     }
@@ -513,7 +513,7 @@ lcsa_fused_kernel(const LcsaFusedParams p) {
         if (r0 + r >= H) break;
         const size_t o = ((size_t)b * H * W + (size_t)(r0 + r) * W + w) * 9;
 #pragma unroll
-        for (int j = 0; j < 9; ++j) store_mixed<T>(q.mask, o + j, p.mask_f32, sigmoidf_(logit[r][j]));
+        for (int j = 0; j < 9; ++j) store_mixed<T>(q.mask, o + j, p.mask_f32, sigmoid_mask(logit[r][j]));
     }
 }
 
