@@ -62,7 +62,7 @@ class ClockSampler:
          'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.t_begin = index, None, [], 0.0
 
     def start(self):
         try:
@@ -74,16 +74,26 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def begin(self):
+        """The timed region starts now: only samples taken from here on count. (The sampler itself is started before the warm-up,
+        so that nvidia-smi's start-up, which attaches to every GPU of the box, is over by then.)"""
+        deadline = time.time() + 5.0
+        while self.proc is not None and not self.lines and time.time() < deadline:      # its first line means the start-up is over
+            time.sleep(0.01)
+        self.t_begin = time.time()
 
     def stop(self):
         if self.proc is None:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        t_end = time.time()
         time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        for ln in self.lines:
+        inside = [ln for ts, ln in self.lines if self.t_begin - 0.05 <= ts <= t_end + 0.12]
+        for ln in (inside or [ln for _, ln in self.lines[-3:]]):
             f = [v.strip() for v in ln.split(',')]
             if len(f) < 7:
                 continue
@@ -214,11 +224,12 @@ def run_c1(args, rank, world, local):
         s = sets[i & 1]
         return ops.dsc_forward(s['x'], wp, s['off'], s['msk'], path=ops.PATH_TC, cout=C1['C'])
 
+    sampler = ClockSampler(local); sampler.start()
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize(); ops.check_status(device)
-    sampler = ClockSampler(local); sampler.start()
     barrier(world); torch.cuda.synchronize()
+    sampler.begin()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -445,12 +456,13 @@ def run_c4(args, rank, world, local):
     dev_batches = [dev[i:i + mb] for i in range(0, n_local, mb)]
     host_batches = [host[i:i + mb] for i in range(0, n_local, mb)]
     dets = []
+    sampler = ClockSampler(local); sampler.start()
     for _ in range(max(args.warmup, 3)):
         dets = [d for batch in pipe.run(dev_batches) for d in batch]
     torch.cuda.synchronize(); ops.check_status(device)
     n_det = sum(t.shape[0] for t in dets)
-    sampler = ClockSampler(local); sampler.start()
     barrier(world); torch.cuda.synchronize()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in pipe.run(dev_batches * args.steps, to_host=False):
@@ -725,12 +737,13 @@ def run_c2(args, rank, world, local):
         att = ops.se_excite(ops.se_squeeze(z), (H // 2) * (W // 2), *se)
         return ops.se_rescale(z, att)
 
+    sampler = ClockSampler(local); sampler.start()
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize(); ops.check_status(device)
     k0 = _abi.KERNELS_LAUNCHED[0]
-    sampler = ClockSampler(local); sampler.start()
     barrier(world); torch.cuda.synchronize()
+    sampler.begin()
     stream = torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
