@@ -973,33 +973,14 @@ merge_col_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, in
             o16[3] = (uint16_t)(hi2 >> 16);
         }
     };
-    // two rows per trip, all loads of both rows issued before the first use (the loop is bound by load latency, not by bandwidth)
-    if (same) {
-        const unsigned char* yp = yb + 2 * ((size_t)row0 * wi + xw) * ci;
-        const size_t ystep = 2 * (size_t)wi * ci;
-        int yh = row0;
-        for (; yh + 1 < row1; yh += 2, xp += 2 * xstep, op += 2 * ostep, yp += 2 * ystep) {
-            const uint2 xi0 = ldg8<ALIGN>(xp), xi1 = ldg8<ALIGN>(xp + xstep), v0 = ldg8<ALIGN>(yp), v1 = ldg8<ALIGN>(yp + ystep);
-            {
-                const float2 xa = unpack2<T>(xi0.x), xb = unpack2<T>(xi0.y), va = unpack2<T>(v0.x), vb = unpack2<T>(v0.y);
-                put(op, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
-            }
-            {
-                const float2 xa = unpack2<T>(xi1.x), xb = unpack2<T>(xi1.y), va = unpack2<T>(v1.x), vb = unpack2<T>(v1.y);
-                put(op + ostep, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
-            }
-        }
-        if (yh < row1) {
-            const uint2 xi0 = ldg8<ALIGN>(xp), v0 = ldg8<ALIGN>(yp);
-            const float2 xa = unpack2<T>(xi0.x), xb = unpack2<T>(xi0.y), va = unpack2<T>(v0.x), vb = unpack2<T>(v0.y);
-            put(op, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
-        }
-        return;
-    }
+    // Two rows per trip, all loads of both rows issued before the first use (the loop is bound by load latency, not by bandwidth).
+    // A warp holds groups of the full-resolution branch and of the pooled ones side by side: ONE loop for both kinds, so that the
+    // loads of either kind are in flight together (two loops would run one after the other with half the lanes masked).
+    const unsigned char* yp = yb + 2 * ((size_t)row0 * wi + xw) * ci;          // full-resolution branch: this pixel in row row0
+    const size_t ystep = 2 * (size_t)wi * ci;
     const unsigned char* c0p = yb + 2 * x0 * ci;
     const unsigned char* c1p = yb + 2 * x1 * ci;
-    const size_t rstep = 2 * (size_t)wi * ci;
-    // one row of a pooled branch: vertical source rows and weight, the four corner groups, the blend
+    // one row of a pooled branch: the four corner groups, the blend
     auto blend_row = [&](uint2 xin, uint2 q00, uint2 q01, uint2 q10, uint2 q11, float ly, T* o) {
         const float hy = 1.f - ly;
         const float2 xa = unpack2<T>(xin.x), xb = unpack2<T>(xin.y);
@@ -1011,23 +992,37 @@ merge_col_kernel(const T* __restrict__ x, T* __restrict__ out, MergeParams p, in
         const float v3 = hy * (hx * b00.y + lx * b01.y) + ly * (hx * b10.y + lx * b11.y);
         put(o, pack2f<T>(fmaf(v0, a0, xa.x), fmaf(v1, a1, xa.y)), pack2f<T>(fmaf(v2, a2, xb.x), fmaf(v3, a3, xb.y)));
     };
+    auto same_row = [&](uint2 xin, uint2 v, T* o) {
+        const float2 xa = unpack2<T>(xin.x), xb = unpack2<T>(xin.y), va = unpack2<T>(v.x), vb = unpack2<T>(v.y);
+        put(o, pack2f<T>(fmaf(va.x, a0, xa.x), fmaf(va.y, a1, xa.y)), pack2f<T>(fmaf(vb.x, a2, xb.x), fmaf(vb.y, a3, xb.y)));
+    };
     int yh = row0;
-    for (; yh + 1 < row1; yh += 2, xp += 2 * xstep, op += 2 * ostep) {
-        int ya0, ya1, yb0, yb1; float lya, lyb;
-        src_index(yh, sy, hi, ya0, ya1, lya);
-        src_index(yh + 1, sy, hi, yb0, yb1, lyb);
+    for (; yh + 1 < row1; yh += 2, xp += 2 * xstep, op += 2 * ostep, yp += 2 * ystep) {
         const uint2 xi0 = ldg8<ALIGN>(xp), xi1 = ldg8<ALIGN>(xp + xstep);
-        const uint2 p00 = ldg8<ALIGN>(c0p + ya0 * rstep), p01 = ldg8<ALIGN>(c1p + ya0 * rstep), p10 = ldg8<ALIGN>(c0p + ya1 * rstep), p11 = ldg8<ALIGN>(c1p + ya1 * rstep);
-        const uint2 r00 = ldg8<ALIGN>(c0p + yb0 * rstep), r01 = ldg8<ALIGN>(c1p + yb0 * rstep), r10 = ldg8<ALIGN>(c0p + yb1 * rstep), r11 = ldg8<ALIGN>(c1p + yb1 * rstep);
-        blend_row(xi0, p00, p01, p10, p11, lya, op);
-        blend_row(xi1, r00, r01, r10, r11, lyb, op + ostep);
+        uint2 p00, p01, p10, p11, r00, r01, r10, r11;
+        float lya = 0.f, lyb = 0.f;
+        if (same) {
+            p00 = ldg8<ALIGN>(yp); r00 = ldg8<ALIGN>(yp + ystep);
+            p01 = p10 = p11 = r01 = r10 = r11 = make_uint2(0u, 0u);
+        } else {
+            int ya0, ya1, yb0, yb1;
+            src_index(yh, sy, hi, ya0, ya1, lya);
+            src_index(yh + 1, sy, hi, yb0, yb1, lyb);
+            p00 = ldg8<ALIGN>(c0p + ya0 * ystep); p01 = ldg8<ALIGN>(c1p + ya0 * ystep); p10 = ldg8<ALIGN>(c0p + ya1 * ystep); p11 = ldg8<ALIGN>(c1p + ya1 * ystep);
+            r00 = ldg8<ALIGN>(c0p + yb0 * ystep); r01 = ldg8<ALIGN>(c1p + yb0 * ystep); r10 = ldg8<ALIGN>(c0p + yb1 * ystep); r11 = ldg8<ALIGN>(c1p + yb1 * ystep);
+        }
+        if (same) { same_row(xi0, p00, op); same_row(xi1, r00, op + ostep); }
+        else { blend_row(xi0, p00, p01, p10, p11, lya, op); blend_row(xi1, r00, r01, r10, r11, lyb, op + ostep); }
     }
     if (yh < row1) {
-        int ya0, ya1; float lya;
-        src_index(yh, sy, hi, ya0, ya1, lya);
         const uint2 xi0 = ldg8<ALIGN>(xp);
-        const uint2 p00 = ldg8<ALIGN>(c0p + ya0 * rstep), p01 = ldg8<ALIGN>(c1p + ya0 * rstep), p10 = ldg8<ALIGN>(c0p + ya1 * rstep), p11 = ldg8<ALIGN>(c1p + ya1 * rstep);
-        blend_row(xi0, p00, p01, p10, p11, lya, op);
+        if (same) same_row(xi0, ldg8<ALIGN>(yp), op);
+        else {
+            int ya0, ya1; float lya;
+            src_index(yh, sy, hi, ya0, ya1, lya);
+            const uint2 p00 = ldg8<ALIGN>(c0p + ya0 * ystep), p01 = ldg8<ALIGN>(c1p + ya0 * ystep), p10 = ldg8<ALIGN>(c0p + ya1 * ystep), p11 = ldg8<ALIGN>(c1p + ya1 * ystep);
+            blend_row(xi0, p00, p01, p10, p11, lya, op);
+        }
     }
 }
 
