@@ -677,14 +677,15 @@ GEMM1X1_SHAPES = [(72, 64, 200), (128, 72, 200), (144, 128, 100), (64, 32, 100),
 
 def run_gemm1x1(args, local):
     """The detector's 1x1 GEMM + bias + SiLU shapes (fp16, batch = --mini-batch) on gemm1x1_tc_kernel: microseconds and achieved
-    GB/s of the algorithmic bytes 2*M*(K+N) + 2*K*N against the measured HBM peak. --profile: the (256, 144, 100) shape only."""
+    GB/s of the algorithmic bytes 2*M*(K+N) + 2*K*N against the measured HBM peak. --profile: the (256, 144, 100) shape only, or the one given by --gemm-shape."""
     from kadconv import ops
     device = torch.device('cuda', local); torch.cuda.set_device(device)
     B, dt = args.mini_batch, torch.float16
     peak = peaks(); src = peak['_source']
     rows, tot, tot_floor = [], 0.0, 0.0
     g = torch.Generator(device='cpu').manual_seed(0)
-    for K, N, H in ([(256, 144, 100)] if args.profile else GEMM1X1_SHAPES):
+    one = tuple(int(v) for v in args.gemm_shape.split(',')) if args.gemm_shape else (256, 144, 100)
+    for K, N, H in ([one] if (args.profile or args.gemm_shape) else GEMM1X1_SHAPES):
         x = torch.randn((B, H, H, K), generator=g).to(device, dt)
         w = (torch.randn((N, K), generator=g) / K ** 0.5).to(device, dt)
         b = torch.randn((N,), generator=g).to(device)
@@ -865,6 +866,7 @@ def main():
     ap.add_argument('--conv3x3', default='library', choices=['library', 'tcgen05'],
                     help="c4: 3x3 convolutions through the library (default, faster at this model's widths) or this package's tcgen05 kernel")
     ap.add_argument('--profile', action='store_true', help='short run for ncu: no e2e leg, no CPU baseline')
+    ap.add_argument('--gemm-shape', default=None, help="gemm1x1: one shape 'Cin,Cout,map' instead of the detector's 19")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: anything libraries print while they initialise (NCCL's version banner) goes to stderr
     sys.stdout.flush()
