@@ -173,3 +173,24 @@ def test_layer_call_matches_stepwise_kernels(dtype):
     assert torch.equal(out, ref)
     assert torch.equal(out2, fast.kadconv_forward_nhwc_stepwise(layer, ref))
     ops.check_status(x.device)
+
+
+@pytest.mark.parametrize('dtype,dim', [(torch.float16, 32), (torch.bfloat16, 48)])
+def test_first_call_equals_later_calls(dtype, dim):
+    """The kernels of the layer are launched programmatically and read their parameters before they wait for the work in front of
+    them. The very first call of a layer derives those parameters (folding, packing, conversions) on the same stream just before
+    it launches: its result must be the one every later call gives, bit for bit, also when parameters change in between."""
+    import kadconv
+    for trial in range(3):
+        layer, _ = _layer(dim, 50 + trial, dtype)
+        layer = layer.cuda().to(dtype)
+        kadconv.enable_fast_inference(layer)
+        x = round_to(seeding.seeded_input((4, dim, 36, 44), seed=60 + trial), dtype).cuda().to(dtype)
+        with torch.no_grad():
+            first = layer(x).clone()
+            again = layer(x).clone()
+            assert torch.equal(first, again)
+            for p in layer.parameters():                    # new parameters: the cached copies are rebuilt inside the next call
+                p.mul_(1.01)
+            changed = layer(x).clone()
+            assert torch.equal(changed, layer(x)) and not torch.equal(changed, first)
