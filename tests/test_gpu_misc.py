@@ -329,7 +329,8 @@ def test_bias_act_into_a_channel_slice(dtype, C, act):
 
 
 @pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((1, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
-                                         ((1, 24, 9, 7), torch.float16), ((1, 72, 21, 33), torch.bfloat16)])
+                                         ((1, 24, 9, 7), torch.float16), ((1, 72, 21, 33), torch.bfloat16), ((2, 16, 13, 203), torch.float16),
+                                         ((1, 40, 6, 131), torch.bfloat16)])
 def test_pyramid_projection(shape, dtype):
     """One kernel for the three pooled 1x1 projections of a KAD-Conv layer: odd sizes (floor-mode pooling drops the
     last rows / columns), widths with partial 16-channel chunks, several column tiles."""
@@ -353,7 +354,7 @@ def test_pyramid_projection(shape, dtype):
 
 
 @pytest.mark.parametrize('shape,dtype', [((2, 32, 26, 19), torch.float16), ((1, 64, 50, 50), torch.float16), ((2, 128, 12, 70), torch.bfloat16),
-                                         ((3, 64, 7, 5), torch.float16)])
+                                         ((3, 64, 7, 5), torch.float16), ((2, 16, 13, 203), torch.float16), ((1, 40, 22, 131), torch.bfloat16)])
 def test_lcsa_mask_from_pyramid_partial_sums(shape, dtype):
     """The row / column sums the pyramid kernel emits as by-products give the same LCSA mask as summing the branch
     tensors in a second pass (kad_lcsa_sums + kad_lcsa_mask), also on maps narrower than a block."""
