@@ -13,6 +13,9 @@ constexpr int NMS_THREADS = 1024;
 constexpr int NMS_MAX_ANCHORS = 16384;   // sort buffer in shared memory: 16384 x 8 bytes
 constexpr int NMS_CHUNK = 64;
 constexpr int NMS_MAX_DET = 1024;
+constexpr int NMS_TOP = 4096;            // candidates that are sorted first (the kept boxes nearly always come from these)
+constexpr int NMS_TOP_TARGET = 3072;     // how many a chosen threshold should let through
+constexpr int NMS_BINS = 4096;           // histogram of 12 key bits
 
 __device__ __forceinline__ bool iou_exceeds(const float4& a, const float4& b, float thr) {
     const float left = fmaxf(a.x, b.x), right = fminf(a.z, b.z), top = fmaxf(a.y, b.y), bottom = fminf(a.w, b.w);
@@ -36,7 +39,9 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
     unsigned long long* cmask = reinterpret_cast<unsigned long long*>(cmeta + NMS_CHUNK);   // [64] intra-chunk suppression
     unsigned int* csupp = reinterpret_cast<unsigned int*>(cmask + NMS_CHUNK);            // [64] suppressed by a kept box
     unsigned char* scls = reinterpret_cast<unsigned char*>(csupp + NMS_CHUNK);          // [npow2] best class of every anchor
-    __shared__ int s_ncand, s_nkept;
+    unsigned long long* top = reinterpret_cast<unsigned long long*>(scls + npow2);       // [NMS_TOP] the largest keys (npow2 is a multiple of 64)
+    int* hist = reinterpret_cast<int*>(top + NMS_TOP);                                   // [NMS_BINS]
+    __shared__ int s_ncand, s_nkept, s_cnt, s_tb, s_above;
 
     const int b = blockIdx.x, tid = threadIdx.x;
     const T* pb = pred + (size_t)b * (4 + nc) * A;
@@ -67,73 +72,146 @@ nms_kernel(const T* __restrict__ pred, int nc, int A, int npow2, float conf_thre
     __syncthreads();
     const int ncand = s_ncand;
 
-    // 2. bitonic sort, descending
-    for (int k = 2; k <= npow2; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int i = tid; i < npow2; i += NMS_THREADS) {
-                const int ixj = i ^ j;
-                if (ixj > i) {
-                    const unsigned long long x = keys[i], y = keys[ixj];
-                    const bool desc = (i & k) == 0;
-                    if (desc ? (x < y) : (x > y)) { keys[i] = y; keys[ixj] = x; }
+    // 2. sort, descending. The kept boxes come from the top of the order, so the NMS_TOP largest keys are selected first (all
+    // candidates, if there are no more than that; else those above a threshold on the 24 leading key bits, found with two
+    // 12-bit histograms), sorted and processed; only if they run out before max_det boxes are kept, the whole array is sorted
+    // and the NMS starts over. Either way the boxes are visited in exactly the order of the full sort.
+    auto sort_desc = [&](unsigned long long* buf, int n2) {
+        for (int k = 2; k <= n2; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int i = tid; i < n2; i += NMS_THREADS) {
+                    const int ixj = i ^ j;
+                    if (ixj > i) {
+                        const unsigned long long x = buf[i], y = buf[ixj];
+                        const bool desc = (i & k) == 0;
+                        if (desc ? (x < y) : (x > y)) { buf[i] = y; buf[ixj] = x; }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+    };
+    // 3. greedy NMS over chunks of 64 candidates in score order
+    float* out = dets + (size_t)b * max_det * 6;
+    auto run_nms = [&](const unsigned long long* buf, int count) {
+        for (int c0 = 0; c0 < count; c0 += NMS_CHUNK) {
+            if (s_nkept >= max_det) break;
+            const int nch = min(NMS_CHUNK, count - c0);
+            if (tid < NMS_CHUNK) {
+                cmask[tid] = 0ull;
+                csupp[tid] = tid < nch ? 0u : 1u;
+                if (tid < nch) {
+                    const unsigned long long key = buf[c0 + tid];
+                    const int a = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+                    // box corners are formed in the storage type, as the reference does before it widens to float32
+                    const float cx = to_f<T>(pb[a]), cy = to_f<T>(pb[(size_t)A + a]);
+                    const float hw = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)2 * A + a]) * 0.5f)), hh = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)3 * A + a]) * 0.5f));
+                    float4 r;
+                    r.x = to_f<T>(from_f<T>(cx - hw)); r.y = to_f<T>(from_f<T>(cy - hh));
+                    r.z = to_f<T>(from_f<T>(cx + hw)); r.w = to_f<T>(from_f<T>(cy + hh));
+                    // score and class come from the sort key and the per-anchor table of step 1: no second pass over the class scores
+                    const unsigned int u = (unsigned int)(key >> 32);
+                    const float best = __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+                    const int cls = scls[a];
+                    const float sh = (float)cls * max_wh;
+                    craw[tid] = r;
+                    cbox[tid] = make_float4(r.x + sh, r.y + sh, r.z + sh, r.w + sh);
+                    cmeta[tid] = make_float2(best, (float)cls);
                 }
             }
             __syncthreads();
+            const int nk = s_nkept;
+            for (int p = tid; p < nk * NMS_CHUNK; p += NMS_THREADS) {
+                const int k = p / NMS_CHUNK, c = p % NMS_CHUNK;
+                if (c < nch && iou_exceeds(kept[k], cbox[c], iou_thres)) atomicOr(&csupp[c], 1u);
+            }
+            for (int p = tid; p < NMS_CHUNK * NMS_CHUNK; p += NMS_THREADS) {
+                const int i = p / NMS_CHUNK, j = p % NMS_CHUNK;
+                if (j > i && j < nch && iou_exceeds(cbox[i], cbox[j], iou_thres)) atomicOr(&cmask[i], 1ull << j);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long dead = 0ull;
+                int n = nk;
+                for (int c = 0; c < nch && n < max_det; ++c) {
+                    if (csupp[c] || ((dead >> c) & 1ull)) continue;
+                    kept[n] = cbox[c];
+                    float* o = out + (size_t)n * 6;
+                    o[0] = craw[c].x; o[1] = craw[c].y; o[2] = craw[c].z; o[3] = craw[c].w; o[4] = cmeta[c].x; o[5] = cmeta[c].y;
+                    dead |= cmask[c];
+                    ++n;
+                }
+                s_nkept = n;
+            }
+            __syncthreads();
         }
-    }
-
-    // 3. greedy NMS over chunks of 64 candidates in score order
-    float* out = dets + (size_t)b * max_det * 6;
-    for (int c0 = 0; c0 < ncand; c0 += NMS_CHUNK) {
-        if (s_nkept >= max_det) break;
-        const int nch = min(NMS_CHUNK, ncand - c0);
-        if (tid < NMS_CHUNK) {
-            cmask[tid] = 0ull;
-            csupp[tid] = tid < nch ? 0u : 1u;
-            if (tid < nch) {
-                const unsigned long long key = keys[c0 + tid];
-                const int a = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
-                // box corners are formed in the storage type, as the reference does before it widens to float32
-                const float cx = to_f<T>(pb[a]), cy = to_f<T>(pb[(size_t)A + a]);
-                const float hw = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)2 * A + a]) * 0.5f)), hh = to_f<T>(from_f<T>(to_f<T>(pb[(size_t)3 * A + a]) * 0.5f));
-                float4 r;
-                r.x = to_f<T>(from_f<T>(cx - hw)); r.y = to_f<T>(from_f<T>(cy - hh));
-                r.z = to_f<T>(from_f<T>(cx + hw)); r.w = to_f<T>(from_f<T>(cy + hh));
-                // score and class come from the sort key and the per-anchor table of step 1: no second pass over the class scores
-                const unsigned int u = (unsigned int)(key >> 32);
-                const float best = __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
-                const int cls = scls[a];
-                const float sh = (float)cls * max_wh;
-                craw[tid] = r;
-                cbox[tid] = make_float4(r.x + sh, r.y + sh, r.z + sh, r.w + sh);
-                cmeta[tid] = make_float2(best, (float)cls);
+    };
+    // the largest bin t with count(bin >= t) >= target, and how many keys lie in the bins above it (warp 0; 128 bins per lane)
+    auto find_bin = [&](int target) {
+        if (tid < 32) {
+            int seg = 0;
+            for (int i = 0; i < NMS_BINS / 32; ++i) seg += hist[tid * (NMS_BINS / 32) + i];
+            int suf = seg;                                   // sum over this lane's segment and all higher ones
+            for (int d = 1; d < 32; d <<= 1) { const int o = __shfl_down_sync(0xffffffffu, suf, d); if (tid + d < 32) suf += o; }
+            const unsigned int reach = __ballot_sync(0xffffffffu, suf >= target);
+            const int L = reach ? 31 - __clz(reach) : 0;     // the highest lane whose suffix reaches the target
+            if (tid == L) {
+                int cum = suf - seg, tb = L * (NMS_BINS / 32);
+                for (int bin = (L + 1) * (NMS_BINS / 32) - 1; bin >= L * (NMS_BINS / 32); --bin) {
+                    if (cum + hist[bin] >= target) { tb = bin; break; }
+                    cum += hist[bin];
+                }
+                s_tb = tb; s_above = cum;
             }
         }
         __syncthreads();
-        const int nk = s_nkept;
-        for (int p = tid; p < nk * NMS_CHUNK; p += NMS_THREADS) {
-            const int k = p / NMS_CHUNK, c = p % NMS_CHUNK;
-            if (c < nch && iou_exceeds(kept[k], cbox[c], iou_thres)) atomicOr(&csupp[c], 1u);
-        }
-        for (int p = tid; p < NMS_CHUNK * NMS_CHUNK; p += NMS_THREADS) {
-            const int i = p / NMS_CHUNK, j = p % NMS_CHUNK;
-            if (j > i && j < nch && iou_exceeds(cbox[i], cbox[j], iou_thres)) atomicOr(&cmask[i], 1ull << j);
-        }
-        __syncthreads();
-        if (tid == 0) {
-            unsigned long long dead = 0ull;
-            int n = nk;
-            for (int c = 0; c < nch && n < max_det; ++c) {
-                if (csupp[c] || ((dead >> c) & 1ull)) continue;
-                kept[n] = cbox[c];
-                float* o = out + (size_t)n * 6;
-                o[0] = craw[c].x; o[1] = craw[c].y; o[2] = craw[c].z; o[3] = craw[c].w; o[4] = cmeta[c].x; o[5] = cmeta[c].y;
-                dead |= cmask[c];
-                ++n;
+    };
+    bool done = ncand == 0;
+    if (!done) {
+        // Selection threshold: keys with (key >> sel_shift) >= sel_prefix are taken. It is refined 12 key bits at a time (score bits
+        // first, then, among equal scores, the anchor order) until what it lets through fits NMS_TOP: one or two rounds when the
+        // scores are spread, more when thousands of anchors share a score.
+        unsigned long long sel_prefix = 0ull;
+        int sel_shift = 64, above_total = 0, group = ncand;  // keys above the crossing group; size of the crossing group
+        for (int shift = 52; above_total + group > NMS_TOP && shift >= 4; shift -= 12) {
+            for (int i = tid; i < NMS_BINS; i += NMS_THREADS) hist[i] = 0;
+            __syncthreads();
+            for (int a = tid; a < npow2; a += NMS_THREADS) {
+                const unsigned long long k = keys[a];
+                if (k && (sel_shift == 64 || (k >> sel_shift) == sel_prefix)) atomicAdd(&hist[(unsigned int)(k >> shift) & 0xFFFu], 1);
             }
-            s_nkept = n;
+            __syncthreads();
+            find_bin(NMS_TOP_TARGET - above_total);
+            above_total += s_above;
+            group = hist[s_tb];
+            sel_prefix = (sel_prefix << 12) | (unsigned long long)s_tb;
+            sel_shift = shift;
+            __syncthreads();
+        }
+        if (tid == 0) s_cnt = 0;
+        __syncthreads();
+        for (int a = tid; a < npow2; a += NMS_THREADS) {
+            const unsigned long long k = keys[a];
+            if (k && (sel_shift == 64 || (k >> sel_shift) >= sel_prefix)) { const int pos = atomicAdd(&s_cnt, 1); if (pos < NMS_TOP) top[pos] = k; }
         }
         __syncthreads();
+        const int M = s_cnt;
+        if (M <= NMS_TOP) {
+            int n2 = 64;
+            while (n2 < M) n2 <<= 1;
+            for (int i = M + tid; i < n2; i += NMS_THREADS) top[i] = 0ull;
+            __syncthreads();
+            sort_desc(top, n2);
+            run_nms(top, M);
+            done = s_nkept >= max_det || M == ncand;
+        }
+        if (!done) {                                         // rare: the selection ran out first (or held too many equal prefixes)
+            __syncthreads();
+            if (tid == 0) s_nkept = 0;
+            __syncthreads();
+            sort_desc(keys, npow2);
+            run_nms(keys, ncand);
+        }
     }
     if (tid == 0) counts[b] = s_nkept;
 }
@@ -197,7 +275,7 @@ extern "C" int kad_nms_batched(const void* pred, int B, int nc, int A, float con
     int npow2 = 64;
     while (npow2 < A) npow2 <<= 1;
     KAD_CHECK_ARG(nc <= 256, "kad_nms_batched: at most 256 classes (the per-anchor class table holds bytes)");
-    size_t smem = (size_t)npow2 * 8 + (size_t)max_det * 16 + NMS_CHUNK * (16 + 16 + 8 + 8 + 4) + (size_t)npow2 + 64;
+    size_t smem = (size_t)npow2 * 8 + (size_t)max_det * 16 + NMS_CHUNK * (16 + 16 + 8 + 8 + 4) + (size_t)npow2 + (size_t)NMS_TOP * 8 + (size_t)NMS_BINS * 4 + 64;
     KAD_DISPATCH_DTYPE(dtype, {
         auto kern = nms_kernel<T>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
