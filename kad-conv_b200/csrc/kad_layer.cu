@@ -23,8 +23,12 @@ int side_streams(int dev, SideStreams** out) {
     std::lock_guard<std::mutex> lock(g_side_mutex);
     SideStreams& ss = g_side[dev];
     if (!ss.ready) {
+        // the pooled branches run on streams of the LOWEST priority: the full-resolution branch on the caller's stream is the
+        // longest chain of a layer, and its blocks should get an SM first when both have blocks waiting
+        int prio_lo = 0, prio_hi = 0;
+        cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);        // numerically lowest = highest priority
         for (int i = 0; i < 2; ++i) {
-            cudaError_t e = cudaStreamCreateWithFlags(&ss.s[i], cudaStreamNonBlocking);
+            cudaError_t e = cudaStreamCreateWithPriority(&ss.s[i], cudaStreamNonBlocking, prio_lo);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: side stream: %s", cudaGetErrorString(e));
             e = cudaEventCreateWithFlags(&ss.join[i], cudaEventDisableTiming);
             if (e != cudaSuccess) return fail(KAD_ERR_CUDA, "kad_kadconv_forward: event: %s", cudaGetErrorString(e));
