@@ -91,6 +91,10 @@ typedef struct KadDscArgs {
        kad_dsc_mma_inline_mask_supported() says whether the operands fit shared memory for this shape. */
     const float* lcsa_rowmean; const float* lcsa_A; const float* lcsa_Sm;
     const float* lcsa_w2; const float* lcsa_b2; const float* lcsa_w3; const float* lcsa_b3;
+    /* path 3 with offset_weight and a mask tensor, optional: the weight fragments of both convolutions as kad_dsc_mma_pack_frags
+       wrote them (kad_dsc_mma_frag_bytes bytes, 16-byte aligned). Every block then copies them instead of deriving them from
+       `weight` and `offset_weight`, which must still be passed (they are what the fragments were packed from). */
+    const void* mma_frags;
 } KadDscArgs;
 int kad_dsc_forward(const KadDscArgs* args, void* stream);
 int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path);
@@ -101,6 +105,8 @@ int kad_dsc_tc_supported(int Cin, int Cout, int dtype);
  * Path 3 writes its channel sums per group of 256 pixels: kad_dsc_gap_tiles(..., 3) = ceil(H*W / 256). */
 int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
 int kad_dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W);
+size_t kad_dsc_mma_frag_bytes(int Cin, int Cout, int dtype);
+int kad_dsc_mma_pack_frags(const float* weight_simt, const float* offset_weight_simt, void* dst, int Cin, int Cout, int dtype, void* stream);
 /* Packs W[Cout][Cin][3][3] (float32, the layout of DSC.weight) into the tensor path's K-major
  * operand: dst is dtype [9*Cin/64 (rounded up)][Cout][64]; K index = (ci/32)*288 + tap*32 + ci%32. */
 int kad_dsc_pack_weight_tc(const float* w_oihw, void* dst, int Cin, int Cout, int dtype, void* stream);
@@ -299,6 +305,7 @@ typedef struct KadBranchParams {
     const float* lcsa_w2; const float* lcsa_b2; const float* lcsa_w3; const float* lcsa_b3;
     const float* w_off; const float* b_off;                         /* [9][c][18], [18] */
     const float* w_dsc_simt; const void* w_dsc_tc;
+    const void* w_dsc_mma;                                          /* kad_dsc_mma_pack_frags of w_dsc_simt + w_off in dtype, or NULL */
     const float* ep_scale; const float* ep_shift; const float* ep_post;
     const float* fc_w1; const float* fc_b1; const float* fc_w2; const float* fc_b2;   /* [hidden][c], [hidden], [c][hidden], [c] */
     int c, hidden;

@@ -29,6 +29,8 @@ int dsc_mma_tiles(int H, int W);
 bool dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W);
 bool dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W);
 int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st);
+size_t dsc_mma_frag_bytes(int Cin, int Cout);
+int dsc_mma_pack_frags(const float* w_simt, const float* w_off_simt, void* dst, int Cin, int Cout, int dtype, cudaStream_t st);
 
 }  // namespace kad
 
@@ -46,6 +48,18 @@ extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {
 
 extern "C" int kad_dsc_mma_supported(int Cin, int Cout, int dtype, int H, int W) { return dsc_mma_supported(Cin, Cout, dtype, H, W) ? 1 : 0; }
 extern "C" int kad_dsc_mma_inline_mask_supported(int Cin, int Cout, int dtype, int H, int W) { return dsc_mma_inline_mask_supported(Cin, Cout, dtype, H, W) ? 1 : 0; }
+
+extern "C" size_t kad_dsc_mma_frag_bytes(int Cin, int Cout, int dtype) {
+    if (!(dtype == KAD_F16 || dtype == KAD_BF16) || Cin < 4 || Cin > 64 || Cout < 1 || Cout > 64) return 0;
+    return dsc_mma_frag_bytes(Cin, Cout);
+}
+
+extern "C" int kad_dsc_mma_pack_frags(const float* weight_simt, const float* offset_weight_simt, void* dst, int Cin, int Cout, int dtype, void* stream) {
+    KAD_CHECK_ARG(weight_simt && offset_weight_simt && dst, "kad_dsc_mma_pack_frags: null pointer");
+    KAD_CHECK_ARG(kad_dsc_mma_frag_bytes(Cin, Cout, dtype) != 0, "kad_dsc_mma_pack_frags: needs f16/bf16, 4 <= Cin <= 64, Cout <= 64 (Cin=%d Cout=%d dtype=%d)", Cin, Cout, dtype);
+    KAD_CHECK_ARG((uintptr_t)dst % 16 == 0, "kad_dsc_mma_pack_frags: dst must be 16-byte aligned");
+    return dsc_mma_pack_frags(weight_simt, offset_weight_simt, dst, Cin, Cout, dtype, (cudaStream_t)stream);
+}
 
 extern "C" int kad_dsc_forward(const KadDscArgs* a, void* stream) {
     KAD_CHECK_ARG(a != nullptr, "kad_dsc_forward: null args");

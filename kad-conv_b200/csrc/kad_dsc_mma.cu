@@ -55,6 +55,7 @@ struct MmaParams {
     const float* l_rowmean; const float* l_A; const float* l_Sm; const float* l_w2; const float* l_b2; const float* l_w3; const float* l_b3;
     int Cp, rm_rows;                    // rm_rows: image rows a group of 256 pixels can span, + 10 for the 11x1 window
     int stage_cols;                     // 1: the image's A rows and Sm are staged in shared memory (they fit); 0: read through L2
+    const uint4* frags; int frag_vecs;  // fused mode, optional: the weight fragments of both convolutions as kad_dsc_mma_pack_frags wrote them, in 16-byte units
 };
 
 constexpr int ZERO_BYTES = 160;         // block of zeros in shared memory that out-of-image corners point at
@@ -306,12 +307,17 @@ dsc_mma_kernel(const MmaParams p) {
 
     // ---- parameters first: weight fragments, epilogue vectors, the block of zeros. Nothing here was written by another kernel, so
     // with a programmatic launch this part runs while the kernel before this one is still draining ----------------------------------
-    if (MODE == 0) stage_weights_rows<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
-    else stage_weights<T>(Bs, p.Wt, Cin, Cout, p.KT, p.TPC, KS, NT, tid);
-    if (FUSED) {
-        stage_weights_rows<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
-        if (tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
+    if (MODE == 2 && p.frags) {
+        // fragments packed once by kad_dsc_mma_pack_frags: a straight copy (both convolutions lie one after the other, as here);
+        // the copy is waited for together with the first group's image rows
+        uint4* dst = reinterpret_cast<uint4*>(Bs);
+        for (int i = tid; i < p.frag_vecs; i += MMA_THREADS) cp_async16(dst + i, p.frags + i);
+    } else {
+        if (MODE == 0) stage_weights_rows<T>(Bs, p.Wt, Cin, Cout, KC, NT, tid);
+        else stage_weights<T>(Bs, p.Wt, Cin, Cout, p.KT, p.TPC, KS, NT, tid);
+        if (FUSED) stage_weights_rows<T>(Bo, p.Woff, Cin, 18, KC, NT_OFF, tid);
     }
+    if (FUSED && tid < 24) boffs[tid] = (tid < 18 && p.boff) ? p.boff[tid] : 0.f;
     if (INLINE) {
         for (int e = tid; e < 12 * p.Cp; e += MMA_THREADS) {
             const int c = e / 12, k = e - c * 12;
@@ -604,6 +610,15 @@ inline int pick_nt(int Cout) {
     return n <= 2 ? 2 : n <= 3 ? 3 : n <= 4 ? 4 : n <= 6 ? 6 : 8;
 }
 
+// The weight fragments of the fused mode (deformable convolution, then offset convolution) written to global memory once, in the
+// order the kernel keeps them in shared memory, so that every block of every launch copies them instead of deriving them.
+template <typename T>
+__global__ void __launch_bounds__(MMA_THREADS)
+pack_frags_kernel(uint2* __restrict__ dst, const float* __restrict__ Wt, const float* __restrict__ Woff, int Cin, int Cout, int KT, int TPC, int KS, int NT, int KC) {
+    stage_weights<T>(dst, Wt, Cin, Cout, KT, TPC, KS, NT, threadIdx.x);
+    stage_weights_rows<T>(dst + (9 / TPC) * KS * NT * 32, Woff, Cin, 18, KC, NT_OFF, threadIdx.x);
+}
+
 // K structure of the A tile for Cin channels: groups of four channels per tap, taps per chunk (a kernel row of three taps while
 // its K stays <= 80, i.e. up to 24 channels, else single taps), 16-wide k-steps per chunk, row pitch (an odd number of 16-byte units, so that the eight
 // rows of an ldmatrix phase hit different banks) and the per-warp scratch (A tile or output tile, whichever is larger).
@@ -706,6 +721,21 @@ int sm_count() {
 
 }  // namespace
 
+// bytes of the fragment image of the fused mode: (9 / TPC) * KS * NT deformable + 9 * KC * NT_OFF offset fragments of 32 lanes x 8 bytes
+size_t dsc_mma_frag_bytes(int Cin, int Cout) {
+    const KPlan k = k_plan(Cin, Cout);
+    return ((size_t)(9 / k.TPC) * k.KS * pick_nt(Cout) + (size_t)9 * ((Cin + 15) / 16) * NT_OFF) * 32 * 8;
+}
+
+int dsc_mma_pack_frags(const float* w_simt, const float* w_off_simt, void* dst, int Cin, int Cout, int dtype, cudaStream_t st) {
+    const KPlan k = k_plan(Cin, Cout);
+    const int nt = pick_nt(Cout), KC = (Cin + 15) / 16;
+    if (dtype == KAD_F16) pack_frags_kernel<__half><<<1, MMA_THREADS, 0, st>>>((uint2*)dst, w_simt, w_off_simt, Cin, Cout, k.KT, k.TPC, k.KS, nt, KC);
+    else pack_frags_kernel<__nv_bfloat16><<<1, MMA_THREADS, 0, st>>>((uint2*)dst, w_simt, w_off_simt, Cin, Cout, k.KT, k.TPC, k.KS, nt, KC);
+    KAD_CHECK_LAUNCH("pack_frags_kernel");
+    return KAD_OK;
+}
+
 // channel sums are written per group of 256 pixels
 int dsc_mma_tiles(int H, int W) { return (H * W + MMA_THREADS - 1) / MMA_THREADS; }
 
@@ -747,6 +777,11 @@ int launch_dsc_mma(const KadDscArgs& a, cudaStream_t st) {
     p.l_rowmean = a.lcsa_rowmean; p.l_A = a.lcsa_A; p.l_Sm = a.lcsa_Sm; p.l_w2 = a.lcsa_w2; p.l_b2 = a.lcsa_b2; p.l_w3 = a.lcsa_w3; p.l_b3 = a.lcsa_b3;
     p.Cp = (a.Cin + 3) & ~3; p.rm_rows = lcsa_rm_rows(a.H, a.W); p.stage_cols = (inline_mask && lcsa_stage_cols(a.Cin, a.W)) ? 1 : 0;
     const int nt = pick_nt(a.Cout);
+    if (mode == 2 && a.mma_frags) {
+        KAD_CHECK_ARG((uintptr_t)a.mma_frags % 16 == 0, "kad_dsc_forward: mma_frags must be 16-byte aligned");
+        p.frags = reinterpret_cast<const uint4*>(a.mma_frags);
+        p.frag_vecs = (int)(dsc_mma_frag_bytes(a.Cin, a.Cout) / 16);
+    }
     size_t smem = fixed_smem(a.Cin, a.Cout, nt, mode) + (inline_mask ? lcsa_smem(a.Cin, a.H, a.W, p.stage_cols != 0) : 0);
     // rows of margin for the learned offsets: as many as fit, at most 2 (none for the plain convolution); the narrow
     // variants (128 registers) keep two blocks per SM when the halo alone allows it

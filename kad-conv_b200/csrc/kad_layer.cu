@@ -275,6 +275,7 @@ extern "C" int kad_kadconv_forward(const KadLayerArgs* a, void* stream) {
             q.mask = ws + p.mask; q.mask_f32 = 1;
         }
         q.weight = path == 1 ? br.w_dsc_tc : (const void*)br.w_dsc_simt;
+        if (path == 3 && !inline_mask) q.mma_frags = br.w_dsc_mma;
         q.scale = br.ep_scale; q.shift = br.ep_shift; q.post = br.ep_post; q.y = ws + p.y; q.gap_partial = (float*)(ws + p.gap);
         q.B = a->B; q.H = h; q.W = w; q.Cin = c; q.Cout = c; q.dtype = a->dtype; q.act = KAD_ACT_RELU; q.path = path; q.status = a->status;
         rc = kad_dsc_forward(&q, s);

@@ -23,7 +23,8 @@ class KadDscArgs(Structure):
                 ('path', c_int), ('status', c_void_p),
                 ('offset_weight', c_void_p), ('offset_bias', c_void_p),
                 ('lcsa_rowmean', c_void_p), ('lcsa_A', c_void_p), ('lcsa_Sm', c_void_p),
-                ('lcsa_w2', c_void_p), ('lcsa_b2', c_void_p), ('lcsa_w3', c_void_p), ('lcsa_b3', c_void_p)]
+                ('lcsa_w2', c_void_p), ('lcsa_b2', c_void_p), ('lcsa_w3', c_void_p), ('lcsa_b3', c_void_p),
+                ('mma_frags', c_void_p)]
 
 
 class KadPyramidArgs(Structure):
@@ -44,7 +45,7 @@ class KadMergeArgs(Structure):
 
 class KadBranchParams(Structure):
     _fields_ = [(n, c_void_p) for n in ('w_proj', 'b_proj', 'lcsa_w1', 'lcsa_b1', 'lcsa_bn_scale', 'lcsa_bn_shift', 'lcsa_w2', 'lcsa_b2',
-                                        'lcsa_w3', 'lcsa_b3', 'w_off', 'b_off', 'w_dsc_simt', 'w_dsc_tc', 'ep_scale', 'ep_shift', 'ep_post',
+                                        'lcsa_w3', 'lcsa_b3', 'w_off', 'b_off', 'w_dsc_simt', 'w_dsc_tc', 'w_dsc_mma', 'ep_scale', 'ep_shift', 'ep_post',
                                         'fc_w1', 'fc_b1', 'fc_w2', 'fc_b2')] + [('c', c_int), ('hidden', c_int)]
 
 
@@ -68,6 +69,8 @@ SIGNATURES = {
     'kad_pyramid_lcsa_supported': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     'kad_pyramid_project_lcsa': (c_int, [POINTER(KadPyramidArgs), c_void_p]),
     'kad_dsc_mma_inline_mask_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    'kad_dsc_mma_frag_bytes': (c_size_t, [c_int, c_int, c_int]),
+    'kad_dsc_mma_pack_frags': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     'kad_kadconv_launch_count': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     'kad_pyramid_partial_dims': (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     'kad_lcsa_mask_from_partials_supported': (c_int, [c_int, c_int, c_int]),

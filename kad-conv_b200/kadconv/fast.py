@@ -54,6 +54,7 @@ class _BranchParams:
         self.dsc_weight_raw = f(dsc.weight)
         self.w_dsc_simt = ops.pack_dsc_weight_simt(self.dsc_weight_raw)
         self.w_dsc_tc = {}
+        self.w_dsc_mma = {}
         m, a = _bn_fold(bn)
         self.ep_scale = f(m)
         self.ep_shift = f(a + dsc.bias.detach().float() * m)     # conv bias passes through the BN affine
@@ -68,6 +69,8 @@ class _BranchParams:
                 self.w_dsc_tc[dtype] = ops.pack_dsc_weight_tc(self.dsc_weight_raw, dtype)
             return ops.PATH_TC, self.w_dsc_tc[dtype]
         if ops.dsc_mma_supported(self.c, self.c, dtype, h, w):
+            if dtype not in self.w_dsc_mma:      # fragments of both convolutions, packed once: the kernel's blocks copy them
+                self.w_dsc_mma[dtype] = ops.pack_dsc_mma_frags(self.w_dsc_simt, self.w_off, dtype)
             return ops.PATH_MMA, self.w_dsc_simt
         return ops.PATH_SIMT, self.w_dsc_simt
 
@@ -112,6 +115,8 @@ def _layer_args(layer, st, dtype, H, W):
                 setattr(p, name, t.data_ptr())
             if path == ops.PATH_TC:
                 p.w_dsc_tc = w.data_ptr(); keep.append(w); tc_mask |= 1 << i
+            if path == ops.PATH_MMA:
+                p.w_dsc_mma = br.w_dsc_mma[dtype].data_ptr()
             p.c, p.hidden = br.c, br.fc_w1.shape[0]
         a.dtype = ops._DT[dtype]
         # per branch: project, 2 LCSA sums, 2 LCSA mask, offset conv (unless fused), DSC, SE (unless inside the merge); + merge

@@ -153,7 +153,7 @@ def status_snapshot(device):
 
 
 def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=None, act=ACT_NONE,
-                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None, offset_weight=None, offset_bias=None, lcsa_inline=None):
+                path=PATH_SIMT, y_f32=False, want_gap=False, cout=None, offset_weight=None, offset_bias=None, lcsa_inline=None, mma_frags=None):
     """Deformable 3x3 convolution with fused epilogue on NHWC tensors.
 
     x [B,H,W,Cin]; offset [B,H,W,18] (float32 or x.dtype) or None; mask [B,H,W,9] or None;
@@ -201,6 +201,12 @@ def dsc_forward(x, weight, offset=None, mask=None, scale=None, shift=None, post=
             if _f32(offset_bias, 'offset_bias').numel() != 18:
                 raise ValueError('offset_bias must have 18 elements')
             a.offset_bias = offset_bias.data_ptr()
+    if mma_frags is not None:        # pack_dsc_mma_frags(weight, offset_weight, ...): every block copies the fragments instead of deriving them
+        if offset_weight is None or lcsa_inline is not None:
+            raise ValueError('mma_frags goes with offset_weight and a mask tensor (PATH_MMA)')
+        if mma_frags.dtype != torch.uint8 or mma_frags.numel() != _abi.load().kad_dsc_mma_frag_bytes(Cin, Cout, dtype_code(x)):
+            raise ValueError('mma_frags must be the uint8 tensor pack_dsc_mma_frags made for these channel counts and this dtype')
+        a.mma_frags = _cuda(mma_frags, 'mma_frags').data_ptr()
     if lcsa_inline is not None:
         if offset_weight is None:
             raise ValueError('lcsa_inline goes with offset_weight (PATH_MMA)')
@@ -509,6 +515,21 @@ def parameters_fence(device):
 
 
 _FENCE = {}
+
+
+def pack_dsc_mma_frags(weight_simt, offset_weight_simt, dtype):
+    """Weight fragments of the warp-MMA deformable convolution with fused offsets (both convolutions), packed once for `dtype`:
+    pass the result as dsc_forward(..., mma_frags=...) together with the two weights it was made from."""
+    w = _f32(weight_simt, 'weight_simt'); wo = _f32(offset_weight_simt, 'offset_weight_simt')
+    cin, cout = w.shape[1], w.shape[2]
+    if tuple(wo.shape) != (9, cin, 18):
+        raise ValueError('offset_weight_simt must be float32 [9,Cin,18]')
+    n = _abi.load().kad_dsc_mma_frag_bytes(cin, cout, _DT[dtype])
+    if n == 0:
+        raise ValueError('no warp-MMA path for these channel counts / this dtype')
+    out = torch.empty(n, dtype=torch.uint8, device=w.device)
+    _abi.check(_abi.load().kad_dsc_mma_pack_frags(_ptr(w), _ptr(wo), _ptr(out), cin, cout, _DT[dtype], _stream()), 'kad_dsc_mma_pack_frags')
+    return out
 
 
 def copy_channels(src, src_coff, C, dst=None, dst_coff=0):

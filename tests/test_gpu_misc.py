@@ -481,3 +481,26 @@ def test_copy_channels_moves_exactly_the_slice(dtype, case):
     assert dense.is_contiguous() and torch.equal(dense, src[..., soff:soff + C])
     with pytest.raises(ValueError):
         ops.copy_channels(src, cs - C + 1, C)
+
+
+@pytest.mark.parametrize('dtype,cin,cout,shape', [(torch.float16, 12, 12, (3, 30, 41)), (torch.bfloat16, 21, 21, (2, 9, 7)), (torch.float16, 16, 16, (2, 50, 50)),
+                                                   (torch.float16, 44, 44, (1, 20, 24))])
+def test_packed_mma_fragments_equal_in_kernel_staging(dtype, cin, cout, shape):
+    """kad_dsc_mma_pack_frags writes, once, the weight fragments every block of the warp-MMA kernel would derive from the two
+    float32 weights; a launch that copies them gives the same bits as one that derives them."""
+    from kadconv import ops
+    B, H, W = shape
+    f = lambda a: a.cuda()
+    x = nhwc(round_to(_rand((B, cin, H, W), 400), dtype)).cuda().to(dtype)
+    wd = ops.pack_dsc_weight_simt(f(_rand((cout, cin, 3, 3), 401, 1.0 / np.sqrt(9 * cin))))
+    wo = ops.pack_dsc_weight_simt(f(_rand((18, cin, 3, 3), 402, 0.6 / np.sqrt(9 * cin))))
+    bo = f(_rand((18,), 403, 0.2))
+    mask = torch.sigmoid(f(_rand((B, H, W, 9), 404)))
+    assert ops.dsc_mma_supported(cin, cout, dtype, H, W)
+    frags = ops.pack_dsc_mma_frags(wd, wo, dtype)
+    y0, g0 = ops.dsc_forward(x, wd, None, mask, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo)
+    y1, g1 = ops.dsc_forward(x, wd, None, mask, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo, mma_frags=frags)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y0) and torch.equal(g1, g0)
+    with pytest.raises(ValueError):
+        ops.dsc_forward(x, wd, None, mask, path=ops.PATH_MMA, offset_weight=wo, offset_bias=bo, mma_frags=frags[:-16])
