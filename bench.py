@@ -331,13 +331,14 @@ def c4_dominant_kernel(device, mb, stream, n=20, variant='tensor'):
         sets.append((x, extra))
     w = ops.pack_dsc_weight_simt((torch.rand((c, c, 3, 3), device=device, generator=g) * 2 - 1) / (3 * c ** 0.5))
     wo = ops.pack_dsc_weight_simt((torch.rand((18, c, 3, 3), device=device, generator=g) * 2 - 1) / (3 * c ** 0.5))
+    frags = ops.pack_dsc_mma_frags(w, wo, torch.float16)      # as the layer call passes them: packed once, copied by every block
     bo = torch.zeros(18, device=device)
 
     def launch(i):
         x, extra = sets[i & 1]
         if variant == 'inline':
             return ops.dsc_forward(x, w, None, None, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo, lcsa_inline=extra)
-        return ops.dsc_forward(x, w, None, extra, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo)
+        return ops.dsc_forward(x, w, None, extra, act=ops.ACT_RELU, path=ops.PATH_MMA, want_gap=True, offset_weight=wo, offset_bias=bo, mma_frags=frags)
 
     for i in range(3):
         launch(i)
