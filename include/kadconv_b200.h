@@ -38,6 +38,10 @@ enum { KAD_ACT_NONE = 0, KAD_ACT_SILU = 1, KAD_ACT_RELU = 2 };
 
 /* Library version (major*10000 + minor*100 + patch). */
 int kad_version(void);
+/* sizeof of an argument struct of this header as the library was compiled: 0 KadDscArgs, 1 KadPyramidArgs, 2 KadMergeArgs,
+ * 3 KadBranchParams, 4 KadLayerArgs (-1 otherwise). A binding in another language checks its own declarations against it: the
+ * library reads every field, so a struct declared too short is read past its end. */
+int kad_struct_size(int which);
 /* Reason for the last non-zero return on this thread (empty string if none). */
 const char* kad_last_error_string(void);
 

@@ -38,6 +38,17 @@ using namespace kad;
 
 extern "C" int kad_version(void) { return 100; }
 
+extern "C" int kad_struct_size(int which) {
+    switch (which) {
+        case 0: return (int)sizeof(KadDscArgs);
+        case 1: return (int)sizeof(KadPyramidArgs);
+        case 2: return (int)sizeof(KadMergeArgs);
+        case 3: return (int)sizeof(KadBranchParams);
+        case 4: return (int)sizeof(KadLayerArgs);
+        default: return -1;
+    }
+}
+
 extern "C" const char* kad_last_error_string(void) { return last_error().c_str(); }
 
 extern "C" int kad_dsc_gap_tiles(int H, int W, int Cin, int Cout, int path) {

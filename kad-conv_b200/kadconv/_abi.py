@@ -58,6 +58,7 @@ class KadLayerArgs(Structure):
 # name -> (restype, argtypes); every symbol declared in include/kadconv_b200.h
 SIGNATURES = {
     'kad_version': (c_int, []),
+    'kad_struct_size': (c_int, [c_int]),
     'kad_last_error_string': (c_char_p, []),
     'kad_nchw_to_nhwc': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'kad_nhwc_to_nchw': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -42,3 +42,13 @@ def test_argument_errors_do_not_need_a_gpu():
     assert lib.kad_dsc_packed_weight_bytes(256, 256, _abi.KAD_F16) == 36 * 256 * 64 * 2
     assert lib.kad_gemm1x1_tc_supported(128, 256, _abi.KAD_BF16) == 1
     assert lib.kad_gemm1x1_tc_supported(130, 256, _abi.KAD_BF16) == 0
+
+
+def test_ctypes_structs_have_the_size_the_library_was_compiled_with():
+    """The library reads every field of an argument struct: a declaration that is too short (a field added to the header and
+    not to the binding) would be read past its end. kad_struct_size gives sizeof as compiled."""
+    from kadconv import _abi
+    lib = _abi.load()
+    for which, cls in enumerate((_abi.KadDscArgs, _abi.KadPyramidArgs, _abi.KadMergeArgs, _abi.KadBranchParams, _abi.KadLayerArgs)):
+        assert lib.kad_struct_size(which) == ctypes.sizeof(cls), cls.__name__
+    assert lib.kad_struct_size(99) == -1
